@@ -1,0 +1,982 @@
+// libcoli_cuda_b200: the reference engine's GPU backend interface
+// (c/backend_cuda.h) implemented for B200 (sm_100a), plus the additive fused
+// MoE-layer entry points. See include/coli_cuda_b200.h for the contract of
+// every exported function and the reference declaration it replaces.
+//
+// There is no CPU fallback anywhere in this file: a call either runs on the
+// GPU or returns 0 with its outputs untouched.
+#include "../../include/coli_cuda_b200.h"
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+#include "common.cuh"
+#include "gemv_stream.cuh"
+#include "kernels_misc.cuh"
+#include "router.cuh"
+
+// ---------------------------------------------------------------------------
+// Context
+// ---------------------------------------------------------------------------
+struct Buf {
+    void *p = nullptr;
+    size_t cap = 0;
+};
+
+struct DeviceCtx {
+    int device = -1;
+    int sms = 0;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr, ev_done = nullptr;
+    size_t tensor_count = 0, tensor_bytes = 0, physical_bytes = 0;
+    // workspaces (grow-only)
+    Buf stage_w, stage_s;                     // upload staging
+    Buf x, y, bq, bs, pg, pu, hq, hs, pd, segs1, segs2, ctl, gbuf, ubuf, misc;
+    Buf pipe[27];
+    float *host_x = nullptr, *host_y = nullptr;
+    size_t host_x_cap = 0, host_y_cap = 0;
+    int group_pending = 0;
+    int *status = nullptr;                    // device int: sticky kernel status
+    float last_ms = 0.f;
+    int last_launches = 0;
+    int have_timing = 0;
+    uint64_t g_calls = 0, g_experts = 0, g_rows = 0;
+    double g_h2d = 0, g_kern = 0, g_d2h = 0;
+};
+
+static DeviceCtx g_ctx[COLI_CUDA_MAX_DEVICES];
+static int g_nctx = 0;
+static std::mutex g_mu;
+static int g_timing = 0;
+static long g_gpu_calls = 0;
+static thread_local int g_cur_dev = -1;
+
+static int cuda_ok(cudaError_t e, const char *what) {
+    if (e == cudaSuccess) return 1;
+    std::fprintf(stderr, "[CUDA] %s: %s\n", what, cudaGetErrorString(e));
+    (void)cudaGetLastError();   // consume: a failed call must not poison the next launch check
+    return 0;
+}
+static DeviceCtx *find_ctx(int device) {
+    for (int i = 0; i < g_nctx; i++) if (g_ctx[i].device == device) return &g_ctx[i];
+    return nullptr;
+}
+static int select_ctx(DeviceCtx *c) {
+    if (!c) return 0;
+    if (g_cur_dev == c->device) return 1;
+    if (!cuda_ok(cudaSetDevice(c->device), "select device")) return 0;
+    g_cur_dev = c->device;
+    return 1;
+}
+// Grow-only device buffer. Growing waits for the stream first: queued work may
+// still read the old allocation.
+static int reserve(DeviceCtx *c, Buf *b, size_t bytes) {
+    if (bytes <= b->cap) return 1;
+    if (b->p) { cudaStreamSynchronize(c->stream); cudaFree(b->p); b->p = nullptr; b->cap = 0; }
+    size_t want = bytes + bytes / 4;
+    if (!cuda_ok(cudaMalloc(&b->p, want), "workspace allocation")) {
+        if (!cuda_ok(cudaMalloc(&b->p, bytes), "workspace allocation")) { b->p = nullptr; return 0; }
+        want = bytes;
+    }
+    b->cap = want;
+    return 1;
+}
+static int reserve_pinned(float **p, size_t *cap, size_t bytes) {
+    if (bytes <= *cap) return 1;
+    if (*p) cudaFreeHost(*p);
+    *p = nullptr; *cap = 0;
+    if (!cuda_ok(cudaMallocHost((void **)p, bytes), "pinned allocation")) return 0;
+    *cap = bytes;
+    return 1;
+}
+// Test hook of the reference (c/backend_cuda.cu:1340-1348): COLI_GPU_FAIL_AFTER=N
+// makes every compute entry point report failure after N successful calls.
+static int fault_injected() {
+    const char *fa = std::getenv("COLI_GPU_FAIL_AFTER");
+    return fa && g_gpu_calls++ >= std::atol(fa);
+}
+
+static size_t row_bytes(int fmt, int I) {
+    switch (fmt) {
+    case 0: return (size_t)I * 4;
+    case 1: return (size_t)I;
+    case 2: case 4: case 7: return ((size_t)I + 1) / 2;
+    case 3: return ((size_t)I + 3) / 4;
+    }
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Lifecycle
+// ---------------------------------------------------------------------------
+static void fill_exp2_table(uint64_t *tab) { coli_expf_fill_table(tab); }
+
+template <typename K>
+static void set_smem(K kern, int bytes) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+}
+
+// launch geometry of the streaming GEMV per column-set count
+template <int NC> struct GemvCfg { static constexpr int WARPS = NC <= 2 ? 16 : 8; static constexpr int NST = NC <= 2 ? 4 : 6; };
+
+template <int MODE, int NC>
+static void setup_one() {
+    constexpr int W = GemvCfg<NC>::WARPS, N = GemvCfg<NC>::NST;
+    set_smem(k_gemv_stream<MODE, NC, W, N>, W * N * (chunk_bytes_of(MODE) + 8));
+}
+template <int MODE>
+static void setup_mode() { setup_one<MODE, 1>(); setup_one<MODE, 2>(); setup_one<MODE, 4>(); setup_one<MODE, 8>(); }
+
+extern "C" void coli_cuda_shutdown(void);
+
+extern "C" int coli_cuda_init(const int *devices, int count) {
+    if (!devices || count < 1 || count > COLI_CUDA_MAX_DEVICES) return 0;
+    if (g_nctx) coli_cuda_shutdown();
+    int ndev = 0;
+    if (!cuda_ok(cudaGetDeviceCount(&ndev), "device count") || ndev < 1) return 0;
+    for (int i = 0; i < count; i++) {
+        if (devices[i] < 0 || devices[i] >= ndev) return 0;
+        for (int j = 0; j < i; j++) if (devices[j] == devices[i]) return 0;
+    }
+    uint64_t tab[32];
+    fill_exp2_table(tab);
+    for (int i = 0; i < count; i++) {
+        DeviceCtx *c = &g_ctx[i];
+        *c = DeviceCtx();
+        c->device = devices[i];
+        if (!cuda_ok(cudaSetDevice(c->device), "init device")) { g_nctx = i; coli_cuda_shutdown(); return 0; }
+        g_cur_dev = c->device;
+        cudaDeviceProp prop{};
+        if (!cuda_ok(cudaGetDeviceProperties(&prop, c->device), "device properties")) { g_nctx = i; coli_cuda_shutdown(); return 0; }
+        if (prop.major < 10) {
+            std::fprintf(stderr, "[CUDA] device %d is sm_%d%d: this backend is built for sm_100a only\n",
+                         c->device, prop.major, prop.minor);
+            g_nctx = i; coli_cuda_shutdown(); return 0;
+        }
+        c->sms = prop.multiProcessorCount;
+        if (!cuda_ok(cudaStreamCreate(&c->stream), "stream") ||
+            !cuda_ok(cudaEventCreate(&c->ev0), "event") || !cuda_ok(cudaEventCreate(&c->ev1), "event") ||
+            !cuda_ok(cudaEventCreateWithFlags(&c->ev_done, cudaEventDisableTiming), "event") ||
+            !cuda_ok(cudaMalloc((void **)&c->status, sizeof(int)), "status") ||
+            !cuda_ok(cudaMemset(c->status, 0, sizeof(int)), "status") ||
+            !cuda_ok(cudaMemcpyToSymbol(c_exp2_tab, tab, sizeof(tab)), "exp table")) {
+            g_nctx = i + 1; coli_cuda_shutdown(); return 0;
+        }
+        setup_mode<SC_ROW>(); setup_mode<SC_H16>(); setup_mode<SC_F32>(); setup_mode<SC_MX>();
+        if (!cuda_ok(cudaGetLastError(), "kernel attributes")) { g_nctx = i + 1; coli_cuda_shutdown(); return 0; }
+    }
+    g_nctx = count;
+    return 1;
+}
+
+static void free_buf(Buf *b) { if (b->p) cudaFree(b->p); b->p = nullptr; b->cap = 0; }
+
+extern "C" void coli_cuda_shutdown(void) {
+    for (int i = 0; i < g_nctx; i++) {
+        DeviceCtx *c = &g_ctx[i];
+        if (c->device < 0) continue;
+        if (cudaSetDevice(c->device) != cudaSuccess) { (void)cudaGetLastError(); continue; }
+        cudaDeviceSynchronize();
+        Buf *bufs[] = {&c->stage_w, &c->stage_s, &c->x, &c->y, &c->bq, &c->bs, &c->pg, &c->pu, &c->hq,
+                       &c->hs, &c->pd, &c->segs1, &c->segs2, &c->ctl, &c->gbuf, &c->ubuf, &c->misc};
+        for (Buf *b : bufs) free_buf(b);
+        for (int s = 0; s < 27; s++) free_buf(&c->pipe[s]);
+        if (c->host_x) cudaFreeHost(c->host_x);
+        if (c->host_y) cudaFreeHost(c->host_y);
+        if (c->status) cudaFree(c->status);
+        if (c->ev0) cudaEventDestroy(c->ev0);
+        if (c->ev1) cudaEventDestroy(c->ev1);
+        if (c->ev_done) cudaEventDestroy(c->ev_done);
+        if (c->stream) cudaStreamDestroy(c->stream);
+        (void)cudaGetLastError();
+        *c = DeviceCtx();
+    }
+    g_nctx = 0;
+    g_cur_dev = -1;
+    g_gpu_calls = 0;
+}
+
+extern "C" int coli_cuda_device_count(void) { return g_nctx; }
+extern "C" int coli_cuda_device_at(int index) { return index >= 0 && index < g_nctx ? g_ctx[index].device : -1; }
+extern "C" int coli_cuda_mem_info(int device, size_t *free_bytes, size_t *total_bytes) {
+    DeviceCtx *c = find_ctx(device);
+    if (!free_bytes || !total_bytes || !select_ctx(c)) return 0;
+    return cuda_ok(cudaMemGetInfo(free_bytes, total_bytes), "memory info");
+}
+extern "C" int coli_cuda_device_integrated(int device) {
+    cudaDeviceProp prop{};
+    if (!cuda_ok(cudaGetDeviceProperties(&prop, device), "device properties")) return 0;
+    return prop.integrated ? 1 : 0;
+}
+extern "C" void coli_cuda_stats(int device, size_t *tensor_count, size_t *tensor_bytes) {
+    size_t n = 0, b = 0;
+    for (int i = 0; i < g_nctx; i++)
+        if (device < 0 || g_ctx[i].device == device) { n += g_ctx[i].tensor_count; b += g_ctx[i].tensor_bytes; }
+    if (tensor_count) *tensor_count = n;
+    if (tensor_bytes) *tensor_bytes = b;
+}
+extern "C" size_t coli_cuda_physical_bytes(int device) {
+    size_t b = 0;
+    for (int i = 0; i < g_nctx; i++) if (device < 0 || g_ctx[i].device == device) b += g_ctx[i].physical_bytes;
+    return b;
+}
+extern "C" void coli_cuda_group_stats(uint64_t *calls, uint64_t *experts, uint64_t *rows,
+                                      double *h2d_ms, double *kernel_ms, double *d2h_ms) {
+    std::lock_guard<std::mutex> lock(g_mu);
+    uint64_t a = 0, b = 0, r = 0; double h = 0, k = 0, d = 0;
+    for (int i = 0; i < g_nctx; i++) {
+        a += g_ctx[i].g_calls; b += g_ctx[i].g_experts; r += g_ctx[i].g_rows;
+        h += g_ctx[i].g_h2d; k += g_ctx[i].g_kern; d += g_ctx[i].g_d2h;
+    }
+    if (calls) *calls = a; if (experts) *experts = b; if (rows) *rows = r;
+    if (h2d_ms) *h2d_ms = h; if (kernel_ms) *kernel_ms = k; if (d2h_ms) *d2h_ms = d;
+}
+extern "C" void coli_cuda_group_stats_device(int device, uint64_t *calls, uint64_t *experts,
+                                             uint64_t *rows, double *h2d_ms, double *kernel_ms,
+                                             double *d2h_ms) {
+    std::lock_guard<std::mutex> lock(g_mu);
+    DeviceCtx *c = find_ctx(device);
+    if (calls) *calls = c ? c->g_calls : 0; if (experts) *experts = c ? c->g_experts : 0;
+    if (rows) *rows = c ? c->g_rows : 0; if (h2d_ms) *h2d_ms = c ? c->g_h2d : 0;
+    if (kernel_ms) *kernel_ms = c ? c->g_kern : 0; if (d2h_ms) *d2h_ms = c ? c->g_d2h : 0;
+}
+extern "C" int coli_cuda_e8_set_grid(const void *) { return 0; }
+extern "C" int coli_cuda_fp8_set_lut(const float *) { return 0; }
+extern "C" void coli_cuda_set_timing(int enabled) { g_timing = enabled ? 1 : 0; }
+extern "C" int coli_cuda_last_timing(int device, float *kernel_ms, int *launches) {
+    DeviceCtx *c = find_ctx(device);
+    if (!c || !c->have_timing) return 0;
+    if (kernel_ms) *kernel_ms = c->last_ms;
+    if (launches) *launches = c->last_launches;
+    return 1;
+}
+extern "C" void *coli_cuda_stream(int device) {
+    DeviceCtx *c = find_ctx(device);
+    return c ? (void *)c->stream : nullptr;
+}
+extern "C" int coli_cuda_kernel_status(int device) {
+    DeviceCtx *c = find_ctx(device);
+    if (!select_ctx(c)) return -1;
+    int v = 0;
+    if (!cuda_ok(cudaMemcpy(&v, c->status, sizeof(int), cudaMemcpyDeviceToHost), "status read")) return -1;
+    return v;
+}
+
+// ---------------------------------------------------------------------------
+// Tensors
+// ---------------------------------------------------------------------------
+static int scales_fit_half(const float *s, size_t n) {
+    for (size_t i = 0; i < n; i++) {
+        float v = s[i];
+        if (__half2float(__float2half(v)) != v) return 0;
+    }
+    return 1;
+}
+
+static void tensor_release(ColiCudaTensor *t) {
+    if (t->raw_w) cudaFree(t->raw_w);
+    if (t->raw_s) cudaFree(t->raw_s);
+    if (t->pk) cudaFree(t->pk);
+    if (t->rowscale) cudaFree(t->rowscale);
+    t->raw_w = t->raw_s = nullptr; t->pk = nullptr; t->rowscale = nullptr;
+}
+
+// Copies weights/scales to the device in the tensor's storage class. `t` has
+// fmt/I/O/gs/ng set; allocations are made when `allocate` is set (upload) and
+// reused otherwise (update).
+static int tensor_fill(DeviceCtx *c, ColiCudaTensor *t, const void *weights, const void *scales,
+                       int allocate) {
+    const size_t wbytes = row_bytes(t->fmt, t->I) * (size_t)t->O;
+    const size_t scount = t->fmt == 0 ? 0 : (size_t)t->O * (size_t)t->ng;
+    const size_t sbytes = t->fmt == 7 ? scount : scount * sizeof(float);
+    if (!t->packed) {
+        if (allocate) {
+            if (!cuda_ok(cudaMalloc(&t->raw_w, wbytes), "tensor allocation")) return 0;
+            if (sbytes && !cuda_ok(cudaMalloc(&t->raw_s, sbytes), "scale allocation")) return 0;
+            t->physical_bytes = wbytes + sbytes;
+        }
+        if (!cuda_ok(cudaMemcpyAsync(t->raw_w, weights, wbytes, cudaMemcpyHostToDevice, c->stream), "tensor upload")) return 0;
+        if (sbytes && !cuda_ok(cudaMemcpyAsync(t->raw_s, scales, sbytes, cudaMemcpyHostToDevice, c->stream), "scale upload")) return 0;
+        return cuda_ok(cudaStreamSynchronize(c->stream), "tensor upload sync");
+    }
+    int mode = t->mode;
+    if (allocate) {
+        mode = t->fmt == 2 ? SC_ROW : t->fmt == 7 ? SC_MX
+             : scales_fit_half(static_cast<const float *>(scales), scount) ? SC_H16 : SC_F32;
+        t->mode = mode;
+    } else if (t->fmt == 4 && mode == SC_H16 &&
+               !scales_fit_half(static_cast<const float *>(scales), scount)) {
+        return 0;   // the refreshed scales no longer fit the storage chosen at upload
+    }
+    const int ch = chunk_bytes_of(mode);
+    const size_t nblk = (size_t)(t->O / TILE_ROWS) * (t->I / BLOCK_K);
+    const size_t pkbytes = nblk * ch;
+    if (!reserve(c, &c->stage_w, wbytes) || (sbytes && !reserve(c, &c->stage_s, sbytes))) return 0;
+    if (allocate) {
+        if (!cuda_ok(cudaMalloc((void **)&t->pk, pkbytes), "tensor allocation")) return 0;
+        t->physical_bytes = pkbytes;
+        if (mode == SC_ROW) {
+            if (!cuda_ok(cudaMalloc((void **)&t->rowscale, (size_t)t->O * sizeof(float)), "scale allocation")) return 0;
+            t->physical_bytes += (size_t)t->O * sizeof(float);
+        }
+    }
+    if (!cuda_ok(cudaMemcpyAsync(c->stage_w.p, weights, wbytes, cudaMemcpyHostToDevice, c->stream), "tensor upload")) return 0;
+    if (mode == SC_ROW) {
+        if (!cuda_ok(cudaMemcpyAsync(t->rowscale, scales, (size_t)t->O * sizeof(float), cudaMemcpyHostToDevice, c->stream), "scale upload")) return 0;
+    } else if (!cuda_ok(cudaMemcpyAsync(c->stage_s.p, scales, sbytes, cudaMemcpyHostToDevice, c->stream), "scale upload")) return 0;
+    size_t words = nblk * 512;
+    k_repack_codes<<<(unsigned)((words + 255) / 256), 256, 0, c->stream>>>(
+        t->pk, static_cast<const uint8_t *>(c->stage_w.p), t->O, t->I, ch, t->fmt == 7);
+    if (mode != SC_ROW) {
+        size_t n = nblk * 128;
+        k_repack_scales<<<(unsigned)((n + 255) / 256), 256, 0, c->stream>>>(
+            t->pk, c->stage_s.p, t->O, t->I, ch, mode, t->gs > 0 ? t->gs : t->I, t->ng);
+    }
+    if (!cuda_ok(cudaGetLastError(), "repack launch")) return 0;
+    return cuda_ok(cudaStreamSynchronize(c->stream), "tensor upload sync");
+}
+
+static thread_local int g_upload_gs = 0;
+
+extern "C" int coli_cuda_tensor_upload(ColiCudaTensor **tensor, const void *weights,
+                                       const float *scales, int fmt, int I, int O, int device) {
+    if (!tensor) return 0;
+    const int want_gs = (fmt == 4 && g_upload_gs > 0) ? g_upload_gs : 0;
+    if (*tensor) {
+        ColiCudaTensor *t = *tensor;
+        return t->fmt == fmt && t->I == I && t->O == O && t->device == device && t->gs == want_gs;
+    }
+    DeviceCtx *c = find_ctx(device);
+    if (!weights || I < 1 || O < 1 || !select_ctx(c)) return 0;
+    if (!(fmt == 0 || fmt == 1 || fmt == 2 || fmt == 3 || fmt == 4 || fmt == 7)) return 0;
+    if (fmt && !scales) return 0;
+    ColiCudaTensor *t = static_cast<ColiCudaTensor *>(std::calloc(1, sizeof(*t)));
+    if (!t) return 0;
+    t->fmt = fmt; t->I = I; t->O = O; t->device = device; t->gs = want_gs;
+    t->ng = fmt == 7 ? (I + 31) / 32 : (want_gs ? (I + want_gs - 1) / want_gs : 1);
+    const size_t wbytes = row_bytes(fmt, I) * (size_t)O;
+    t->logical_bytes = wbytes + (fmt == 0 ? 0 : fmt == 7 ? (size_t)O * t->ng : (size_t)O * t->ng * sizeof(float));
+    t->packed = (fmt == 2 || fmt == 7 || (fmt == 4 && (want_gs == 32 || want_gs == 64 || want_gs == 128))) &&
+                I % BLOCK_K == 0 && O % TILE_ROWS == 0;
+    if (!tensor_fill(c, t, weights, scales, 1)) {
+        tensor_release(t);
+        std::free(t);
+        return 0;
+    }
+    c->tensor_count++;
+    c->tensor_bytes += t->logical_bytes;
+    c->physical_bytes += t->physical_bytes;
+    *tensor = t;
+    return 1;
+}
+extern "C" int coli_cuda_tensor_upload_g(ColiCudaTensor **tensor, const void *weights,
+                                         const float *scales, int fmt, int I, int O, int device,
+                                         int gs) {
+    g_upload_gs = gs > 0 ? gs : 0;
+    int r = coli_cuda_tensor_upload(tensor, weights, scales, fmt, I, O, device);
+    g_upload_gs = 0;
+    return r;
+}
+extern "C" void coli_cuda_tensor_free(ColiCudaTensor *t) {
+    if (!t) return;
+    DeviceCtx *c = find_ctx(t->device);
+    if (c) {
+        select_ctx(c);
+        cudaStreamSynchronize(c->stream);
+        if (c->tensor_count) c->tensor_count--;
+        if (c->tensor_bytes >= t->logical_bytes) c->tensor_bytes -= t->logical_bytes;
+        if (c->physical_bytes >= t->physical_bytes) c->physical_bytes -= t->physical_bytes;
+        tensor_release(t);
+        (void)cudaGetLastError();
+    }
+    std::free(t);
+}
+extern "C" size_t coli_cuda_tensor_bytes(const ColiCudaTensor *t) { return t ? t->logical_bytes : 0; }
+extern "C" int coli_cuda_tensor_device(const ColiCudaTensor *t) { return t ? t->device : -1; }
+extern "C" int coli_cuda_tensor_update(ColiCudaTensor *t, const void *weights, const float *scales) {
+    if (!t || !weights || (t->fmt && !scales)) return 0;
+    DeviceCtx *c = find_ctx(t->device);
+    if (!select_ctx(c)) return 0;
+    cudaStreamSynchronize(c->stream);
+    return tensor_fill(c, t, weights, scales, 0);
+}
+
+// ---------------------------------------------------------------------------
+// Streaming GEMV launch helpers
+// ---------------------------------------------------------------------------
+typedef void (*GemvKernel)(const GemvSeg *, const GemvCtl *, const __half *, const float *, int *);
+
+template <int MODE, int NC>
+static void launch_one(DeviceCtx *c, const GemvSeg *segs, const GemvCtl *ctl, const __half *bq,
+                       const float *bs) {
+    constexpr int W = GemvCfg<NC>::WARPS, N = GemvCfg<NC>::NST;
+    size_t smem = (size_t)W * N * (chunk_bytes_of(MODE) + 8);
+    k_gemv_stream<MODE, NC, W, N><<<c->sms, W * 32, smem, c->stream>>>(segs, ctl, bq, bs, c->status);
+}
+template <int MODE>
+static void launch_mode(DeviceCtx *c, int nc, const GemvSeg *segs, const GemvCtl *ctl,
+                        const __half *bq, const float *bs) {
+    switch (nc) {
+    case 1: launch_one<MODE, 1>(c, segs, ctl, bq, bs); break;
+    case 2: launch_one<MODE, 2>(c, segs, ctl, bq, bs); break;
+    case 4: launch_one<MODE, 4>(c, segs, ctl, bq, bs); break;
+    default: launch_one<MODE, 8>(c, segs, ctl, bq, bs); break;
+    }
+}
+static void launch_gemv(DeviceCtx *c, int mode, int nc, const GemvSeg *segs, const GemvCtl *ctl,
+                        const __half *bq, const float *bs) {
+    switch (mode) {
+    case SC_ROW: launch_mode<SC_ROW>(c, nc, segs, ctl, bq, bs); break;
+    case SC_H16: launch_mode<SC_H16>(c, nc, segs, ctl, bq, bs); break;
+    case SC_F32: launch_mode<SC_F32>(c, nc, segs, ctl, bq, bs); break;
+    default: launch_mode<SC_MX>(c, nc, segs, ctl, bq, bs); break;
+    }
+    c->last_launches++;
+}
+
+// column sets (4 rows each) per pass for a given largest row count
+static int pick_nc(int max_rows) { return max_rows <= 4 ? 1 : max_rows <= 8 ? 2 : max_rows <= 16 ? 4 : 8; }
+
+// Split of the contraction: enough tasks that every SM gets a few dozen, at
+// least two blocks per task so that the copy pipeline stays primed, and a
+// divisor of the block count.
+static int pick_nkpart(int nkb, long base_tasks, int sms) {
+    long want = ((long)sms * 24 + base_tasks - 1) / (base_tasks > 0 ? base_tasks : 1);
+    int cap = nkb >= 2 ? nkb / 2 : 1;
+    if (want > cap) want = cap;
+    if (want < 1) want = 1;
+    int k = (int)want;
+    while (k < nkb && nkb % k) k++;
+    if (k > cap) { k = cap; while (k > 1 && nkb % k) k--; }
+    return k;
+}
+
+static void timing_begin(DeviceCtx *c) {
+    c->last_launches = 0;
+    c->have_timing = 0;
+    if (g_timing) cudaEventRecord(c->ev0, c->stream);
+}
+static void timing_end(DeviceCtx *c) {
+    if (g_timing) cudaEventRecord(c->ev1, c->stream);
+}
+static void timing_collect(DeviceCtx *c) {   // after a stream synchronize
+    if (g_timing && cudaEventElapsedTime(&c->last_ms, c->ev0, c->ev1) == cudaSuccess) c->have_timing = 1;
+    else (void)cudaGetLastError();
+}
+
+struct HostSegs {
+    std::vector<GemvSeg> v[4];   // by scale mode
+    int ntask[4] = {0, 0, 0, 0};
+};
+
+static void add_seg(HostSegs *hs, const ColiCudaTensor *t, float *out, const int *rowid, int nrows,
+                    int pos0, int nkpart) {
+    GemvSeg s;
+    std::memset(&s, 0, sizeof(s));
+    s.w = t->pk; s.rowscale = t->rowscale; s.out = out;
+    for (int r = 0; r < nrows; r++) s.rowid[r] = rowid[r];
+    s.nrows = nrows; s.pos0 = pos0;
+    s.O = t->O; s.ntiles = t->O / TILE_ROWS; s.nkb = t->I / BLOCK_K;
+    s.nkpart = nkpart; s.kb_per_part = s.nkb / nkpart;
+    s.task0 = hs->ntask[t->mode];
+    hs->ntask[t->mode] += s.ntiles * nkpart;
+    hs->v[t->mode].push_back(s);
+}
+
+// Uploads the host-built segment lists and launches one GEMV per scale mode present.
+static int run_host_segs(DeviceCtx *c, HostSegs *hs, Buf *segbuf, int ctl_slot, int nc, int npos,
+                         const __half *bq, const float *bs) {
+    size_t total = 0;
+    for (int m = 0; m < 4; m++) total += hs->v[m].size();
+    size_t seg_bytes = total * sizeof(GemvSeg);
+    size_t need = seg_bytes + 4 * sizeof(GemvCtl);
+    if (!reserve(c, segbuf, need)) return 0;
+    // Pageable staging: cudaMemcpyAsync from pageable memory returns once the
+    // source has been captured, so the vector can die with this call even
+    // though the stream has not run yet.
+    std::vector<uint8_t> stage(need);
+    uint8_t *hp = stage.data();
+    (void)ctl_slot;
+    uint8_t *dp = static_cast<uint8_t *>(segbuf->p);
+    size_t off = 0;
+    GemvCtl ctl[4];
+    size_t seg_off[4];
+    for (int m = 0; m < 4; m++) {
+        seg_off[m] = off;
+        size_t b = hs->v[m].size() * sizeof(GemvSeg);
+        if (b) std::memcpy(hp + off, hs->v[m].data(), b);
+        off += b;
+        ctl[m].nseg = (int)hs->v[m].size(); ctl[m].ntask = hs->ntask[m]; ctl[m].npos = npos; ctl[m].pad = 0;
+    }
+    std::memcpy(hp + seg_bytes, ctl, sizeof(ctl));
+    if (!cuda_ok(cudaMemcpyAsync(dp, hp, need, cudaMemcpyHostToDevice, c->stream), "segment upload")) return 0;
+    for (int m = 0; m < 4; m++) {
+        if (hs->v[m].empty()) continue;
+        launch_gemv(c, m, nc, reinterpret_cast<const GemvSeg *>(dp + seg_off[m]),
+                    reinterpret_cast<const GemvCtl *>(dp + seg_bytes) + m, bq, bs);
+    }
+    return cuda_ok(cudaGetLastError(), "gemv launch");
+}
+
+// y_dev[S,O] = x_dev[S,I] @ W^T for a packed tensor, all on c->stream.
+static int linear_packed(DeviceCtx *c, const ColiCudaTensor *t, float *y_dev, const float *x_dev, int S) {
+    const int nkb = t->I / BLOCK_K;
+    const int nc = pick_nc(S), rpp = 4 * nc;
+    const int npass = (S + rpp - 1) / rpp;
+    const int nkpart = pick_nkpart(nkb, (long)npass * (t->O / TILE_ROWS), c->sms);
+    if (!reserve(c, &c->bq, (size_t)S * t->I * 2 * sizeof(__half)) ||
+        !reserve(c, &c->bs, (size_t)S * nkb * sizeof(float)) ||
+        !reserve(c, &c->pd, (size_t)nkpart * S * t->O * sizeof(float))) return 0;
+    int nw = S * nkb;
+    k_prep_rows<<<(nw * 32 + 255) / 256, 256, 0, c->stream>>>((__half *)c->bq.p, (float *)c->bs.p, x_dev, nullptr, S, t->I);
+    c->last_launches++;
+    HostSegs hs;
+    int rowid[SEG_MAX_ROWS];
+    for (int p = 0; p < npass; p++) {
+        int r0 = p * rpp, nr = S - r0 < rpp ? S - r0 : rpp;
+        for (int r = 0; r < nr; r++) rowid[r] = r0 + r;
+        add_seg(&hs, t, (float *)c->pd.p, rowid, nr, r0, nkpart);
+    }
+    if (!run_host_segs(c, &hs, &c->segs2, 1, nc, S, (const __half *)c->bq.p, (const float *)c->bs.p)) return 0;
+    size_t n4 = (size_t)S * t->O / 4;
+    k_reduce_parts<<<(unsigned)((n4 + 255) / 256), 256, 0, c->stream>>>(y_dev, (const float *)c->pd.p, S, t->O, nkpart);
+    c->last_launches++;
+    return cuda_ok(cudaGetLastError(), "linear launch");
+}
+
+static int linear_raw(DeviceCtx *c, const ColiCudaTensor *t, float *y_dev, const float *x_dev, int S) {
+    dim3 grid((unsigned)((t->O + 7) / 8), (unsigned)((S + 7) / 8));
+    k_generic_matmul<<<grid, 256, 0, c->stream>>>(y_dev, x_dev, t->raw_w, t->raw_s, t->fmt, S, t->I, t->O,
+                                                  t->gs > 0 ? t->gs : t->I, t->ng);
+    c->last_launches++;
+    return cuda_ok(cudaGetLastError(), "matmul launch");
+}
+static int linear_any(DeviceCtx *c, const ColiCudaTensor *t, float *y_dev, const float *x_dev, int S) {
+    return t->packed ? linear_packed(c, t, y_dev, x_dev, S) : linear_raw(c, t, y_dev, x_dev, S);
+}
+
+static int check_status(DeviceCtx *c) {
+    int v = 0;
+    if (!cuda_ok(cudaMemcpyAsync(&v, c->status, sizeof(int), cudaMemcpyDeviceToHost, c->stream), "status read")) return 0;
+    if (!cuda_ok(cudaStreamSynchronize(c->stream), "synchronize")) return 0;
+    if (v) {
+        std::fprintf(stderr, "[CUDA] kernel wait guard expired (status %d)\n", v);
+        return 0;
+    }
+    return 1;
+}
+
+extern "C" int coli_cuda_matmul(ColiCudaTensor **tensor, float *y, const float *x, const void *weights,
+                                const float *scales, int fmt, int S, int I, int O, int device, int gs) {
+    if (fault_injected()) return 0;
+    if (fmt == 4 && gs <= 0) return 0;
+    if (S < 1 || !tensor || !x || !y) return 0;
+    if (gs > 0) { if (!coli_cuda_tensor_upload_g(tensor, weights, scales, fmt, I, O, device, gs)) return 0; }
+    else if (!coli_cuda_tensor_upload(tensor, weights, scales, fmt, I, O, device)) return 0;
+    ColiCudaTensor *t = *tensor;
+    DeviceCtx *c = find_ctx(t->device);
+    if (!select_ctx(c)) return 0;
+    size_t xb = (size_t)S * I * sizeof(float), yb = (size_t)S * O * sizeof(float);
+    if (!reserve(c, &c->x, xb) || !reserve(c, &c->y, yb)) return 0;
+    if (!cuda_ok(cudaMemcpyAsync(c->x.p, x, xb, cudaMemcpyHostToDevice, c->stream), "input upload")) return 0;
+    timing_begin(c);
+    if (!linear_any(c, t, (float *)c->y.p, (const float *)c->x.p, S)) return 0;
+    timing_end(c);
+    if (!check_status(c)) return 0;
+    timing_collect(c);
+    return cuda_ok(cudaMemcpy(y, c->y.p, yb, cudaMemcpyDeviceToHost), "output download");
+}
+
+extern "C" int coli_cuda_matmul_mxfp4(float *y, const float *x, const unsigned char *q4,
+                                      const unsigned char *e8s, int S, int I, int O) {
+    if (S < 1 || I < 1 || O < 1 || !y || !x || !q4 || !e8s || g_nctx < 1) return 0;
+    ColiCudaTensor *t = nullptr;
+    int dev = g_ctx[0].device;
+    // a stateless call: the temporary tensor is freed again before returning
+    int ok = coli_cuda_matmul(&t, y, x, q4, reinterpret_cast<const float *>(e8s), 7, S, I, O, dev, 0);
+    if (t) coli_cuda_tensor_free(t);
+    return ok;
+}
+
+extern "C" int coli_cuda_pipe_gemm(ColiCudaTensor *t, float *y_dev, const float *x_dev, int S) {
+    if (fault_injected()) return 0;
+    if (!t || S < 1 || !y_dev || !x_dev) return 0;
+    DeviceCtx *c = find_ctx(t->device);
+    if (!select_ctx(c)) return 0;
+    return linear_any(c, t, y_dev, x_dev, S);
+}
+
+// ---------------------------------------------------------------------------
+// Expert FFN over a packed group (device buffers), all on c->stream:
+//   x_dev [total, D] rows in call order -> y_dev [total, D]
+// ---------------------------------------------------------------------------
+static int group_shape_ok(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
+                          ColiCudaTensor *const *downs, const int *rows, int count, int *device,
+                          int *D, int *I, int *total, int *max_rows, int *all_packed, int *any_packed) {
+    if (!gates || !ups || !downs || count < 1 || !gates[0]) return 0;
+    *device = gates[0]->device; *D = gates[0]->I; *I = gates[0]->O;
+    *total = 0; *max_rows = 0; *all_packed = 1; *any_packed = 0;
+    for (int cidx = 0; cidx < count; cidx++) {
+        ColiCudaTensor *g = gates[cidx], *u = ups[cidx], *d = downs[cidx];
+        int r = rows ? rows[cidx] : 1;
+        if (!g || !u || !d || r < 1 || g->device != *device || u->device != *device || d->device != *device ||
+            g->I != *D || u->I != *D || g->O != *I || u->O != *I || d->I != *I || d->O != *D) return 0;
+        if ((g->fmt == 4 && g->gs <= 0) || (u->fmt == 4 && u->gs <= 0) || (d->fmt == 4 && d->gs <= 0)) return 0;
+        int p = g->packed && u->packed && d->packed;
+        *all_packed &= p;
+        *any_packed |= g->packed | u->packed | d->packed;
+        *total += r;
+        if (r > *max_rows) *max_rows = r;
+    }
+    return 1;
+}
+
+static int group_device(DeviceCtx *c, ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
+                        ColiCudaTensor *const *downs, const int *rows, int count, int D, int I,
+                        int total, int max_rows, int all_packed, float *y_dev, const float *x_dev,
+                        const int *bcast_src /* optional: every row reads x row 0 */) {
+    if (all_packed) {
+        const int nc = pick_nc(max_rows), rpp = 4 * nc;
+        long npass = 0;
+        for (int e = 0; e < count; e++) npass += ((rows ? rows[e] : 1) + rpp - 1) / rpp;
+        const int nkb1 = D / BLOCK_K, nkb2 = I / BLOCK_K;
+        const int nkp1 = pick_nkpart(nkb1, 2 * npass * (I / TILE_ROWS), c->sms);
+        const int nkp2 = pick_nkpart(nkb2, npass * (D / TILE_ROWS), c->sms);
+        const int nxrows = bcast_src ? 1 : total;
+        if (!reserve(c, &c->bq, (size_t)nxrows * D * 2 * sizeof(__half)) ||
+            !reserve(c, &c->bs, (size_t)nxrows * nkb1 * sizeof(float)) ||
+            !reserve(c, &c->pg, (size_t)nkp1 * total * I * sizeof(float)) ||
+            !reserve(c, &c->pu, (size_t)nkp1 * total * I * sizeof(float)) ||
+            !reserve(c, &c->hq, (size_t)total * I * 2 * sizeof(__half)) ||
+            !reserve(c, &c->hs, (size_t)total * nkb2 * sizeof(float)) ||
+            !reserve(c, &c->pd, (size_t)nkp2 * total * D * sizeof(float))) return 0;
+        int nw = nxrows * nkb1;
+        k_prep_rows<<<(nw * 32 + 255) / 256, 256, 0, c->stream>>>((__half *)c->bq.p, (float *)c->bs.p, x_dev, nullptr, nxrows, D);
+        c->last_launches++;
+        HostSegs h1, h2;
+        int rowid[SEG_MAX_ROWS], posid[SEG_MAX_ROWS], off = 0;
+        for (int e = 0; e < count; e++) {
+            int re = rows ? rows[e] : 1;
+            for (int r0 = 0; r0 < re; r0 += rpp) {
+                int nr = re - r0 < rpp ? re - r0 : rpp;
+                for (int r = 0; r < nr; r++) { rowid[r] = bcast_src ? 0 : off + r0 + r; posid[r] = off + r0 + r; }
+                add_seg(&h1, gates[e], (float *)c->pg.p, rowid, nr, off + r0, nkp1);
+                add_seg(&h1, ups[e], (float *)c->pu.p, rowid, nr, off + r0, nkp1);
+                add_seg(&h2, downs[e], (float *)c->pd.p, posid, nr, off + r0, nkp2);
+            }
+            off += re;
+        }
+        if (!run_host_segs(c, &h1, &c->segs1, 0, nc, total, (const __half *)c->bq.p, (const float *)c->bs.p)) return 0;
+        int nw2 = total * nkb2;
+        k_swiglu_prep<<<(nw2 * 32 + 255) / 256, 256, 0, c->stream>>>(
+            (__half *)c->hq.p, (float *)c->hs.p, (const float *)c->pg.p, (const float *)c->pu.p, nullptr,
+            total, I, nkp1, nullptr);
+        c->last_launches++;
+        if (!run_host_segs(c, &h2, &c->segs2, 1, nc, total, (const __half *)c->hq.p, (const float *)c->hs.p)) return 0;
+        size_t n4 = (size_t)total * D / 4;
+        k_reduce_parts<<<(unsigned)((n4 + 255) / 256), 256, 0, c->stream>>>(y_dev, (const float *)c->pd.p, total, D, nkp2);
+        c->last_launches++;
+        return cuda_ok(cudaGetLastError(), "expert group launch");
+    }
+    // raw tensors: three generic matmuls and the SwiGLU per expert
+    if (!reserve(c, &c->gbuf, (size_t)max_rows * I * sizeof(float)) ||
+        !reserve(c, &c->ubuf, (size_t)max_rows * I * sizeof(float))) return 0;
+    int off = 0;
+    for (int e = 0; e < count; e++) {
+        int re = rows ? rows[e] : 1;
+        if (gates[e]->packed || ups[e]->packed || downs[e]->packed) return 0;
+        const float *xe = bcast_src ? x_dev : x_dev + (size_t)off * D;
+        int rs = bcast_src ? 1 : re;
+        if (!linear_raw(c, gates[e], (float *)c->gbuf.p, xe, rs) ||
+            !linear_raw(c, ups[e], (float *)c->ubuf.p, xe, rs)) return 0;
+        size_t n = (size_t)rs * I;
+        k_silu_mul<<<(unsigned)((n + 255) / 256), 256, 0, c->stream>>>((float *)c->gbuf.p, (const float *)c->ubuf.p, n);
+        c->last_launches++;
+        if (!linear_raw(c, downs[e], y_dev + (size_t)off * D, (const float *)c->gbuf.p, rs)) return 0;
+        off += re;
+    }
+    return cuda_ok(cudaGetLastError(), "expert group launch");
+}
+
+static void count_group(DeviceCtx *c, int count, int total) {
+    std::lock_guard<std::mutex> lock(g_mu);
+    c->g_calls++; c->g_experts += (uint64_t)count; c->g_rows += (uint64_t)total;
+}
+
+static int group_host(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
+                      ColiCudaTensor *const *downs, const int *rows, int count, float *y,
+                      const float *x, int async_issue) {
+    if (!gates || !ups || !downs || !rows || !x || count < 1 || count > 64) return 0;
+    if (!async_issue && !y) return 0;
+    int device, D, I, total, max_rows, all_packed, any_packed;
+    if (!group_shape_ok(gates, ups, downs, rows, count, &device, &D, &I, &total, &max_rows, &all_packed, &any_packed)) return 0;
+    if (!all_packed && any_packed) return 0;   // a group mixing packed and raw tensors is not handled
+    if (async_issue && total > 8) return 0;
+    DeviceCtx *c = find_ctx(device);
+    if (!c || (async_issue && c->group_pending) || !select_ctx(c)) return 0;
+    size_t xb = (size_t)total * D * sizeof(float);
+    if (!reserve(c, &c->x, xb) || !reserve(c, &c->y, xb) ||
+        !reserve_pinned(&c->host_x, &c->host_x_cap, xb) || !reserve_pinned(&c->host_y, &c->host_y_cap, xb)) return 0;
+    const char *pe = std::getenv("COLI_CUDA_PROFILE");
+    int profile = pe && std::atoi(pe);
+    cudaEvent_t ev[4] = {};
+    if (profile) for (int i = 0; i < 4; i++) if (!cuda_ok(cudaEventCreate(&ev[i]), "profile event")) {
+        for (int j = 0; j < i; j++) cudaEventDestroy(ev[j]);
+        profile = 0; break;
+    }
+    if (profile) cudaEventRecord(ev[0], c->stream);
+    std::memcpy(c->host_x, x, xb);
+    if (!cuda_ok(cudaMemcpyAsync(c->x.p, c->host_x, xb, cudaMemcpyHostToDevice, c->stream), "expert group input upload")) return 0;
+    if (profile) cudaEventRecord(ev[1], c->stream);
+    timing_begin(c);
+    if (!group_device(c, gates, ups, downs, rows, count, D, I, total, max_rows, all_packed,
+                      (float *)c->y.p, (const float *)c->x.p, nullptr)) return 0;
+    timing_end(c);
+    if (profile) cudaEventRecord(ev[2], c->stream);
+    if (!cuda_ok(cudaMemcpyAsync(c->host_y, c->y.p, xb, cudaMemcpyDeviceToHost, c->stream), "expert group output download")) return 0;
+    if (profile) cudaEventRecord(ev[3], c->stream);
+    if (async_issue) {
+        c->group_pending = 1;
+        count_group(c, count, total);
+        if (profile) for (int i = 0; i < 4; i++) cudaEventDestroy(ev[i]);
+        return 1;
+    }
+    if (!check_status(c)) return 0;
+    timing_collect(c);
+    std::memcpy(y, c->host_y, xb);
+    if (profile) {
+        float a = 0, b = 0, d = 0;
+        cudaEventElapsedTime(&a, ev[0], ev[1]); cudaEventElapsedTime(&b, ev[1], ev[2]); cudaEventElapsedTime(&d, ev[2], ev[3]);
+        { std::lock_guard<std::mutex> lock(g_mu); c->g_h2d += a; c->g_kern += b; c->g_d2h += d; }
+        for (int i = 0; i < 4; i++) cudaEventDestroy(ev[i]);
+    }
+    count_group(c, count, total);
+    return 1;
+}
+
+extern "C" int coli_cuda_expert_group(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
+                                      ColiCudaTensor *const *downs, const int *rows, int count,
+                                      float *y, const float *x) {
+    if (fault_injected()) return 0;
+    return group_host(gates, ups, downs, rows, count, y, x, 0);
+}
+extern "C" int coli_cuda_expert_group_issue(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
+                                            ColiCudaTensor *const *downs, const int *rows, int count,
+                                            const float *x) {
+    return group_host(gates, ups, downs, rows, count, nullptr, x, 1);
+}
+extern "C" const float *coli_cuda_expert_group_take(int device) {
+    DeviceCtx *c = find_ctx(device);
+    if (!c || !c->group_pending) return nullptr;
+    c->group_pending = 0;
+    if (!select_ctx(c)) return nullptr;
+    if (!check_status(c)) return nullptr;
+    timing_collect(c);
+    return c->host_y;
+}
+extern "C" int coli_cuda_expert_mlp(ColiCudaTensor *gate, ColiCudaTensor *up, ColiCudaTensor *down,
+                                    float *y, const float *x, int S) {
+    if (fault_injected()) return 0;
+    if (!gate || !up || !down || !x || !y || S < 1) return 0;
+    ColiCudaTensor *g[1] = {gate}, *u[1] = {up}, *d[1] = {down};
+    int rows[1] = {S};
+    int device, D, I, total, max_rows, all_packed, any_packed;
+    if (!group_shape_ok(g, u, d, rows, 1, &device, &D, &I, &total, &max_rows, &all_packed, &any_packed)) return 0;
+    if (!all_packed && any_packed) return 0;
+    DeviceCtx *c = find_ctx(device);
+    if (!select_ctx(c)) return 0;
+    size_t xb = (size_t)S * D * sizeof(float);
+    if (!reserve(c, &c->x, xb) || !reserve(c, &c->y, xb)) return 0;
+    if (!cuda_ok(cudaMemcpyAsync(c->x.p, x, xb, cudaMemcpyHostToDevice, c->stream), "expert input upload")) return 0;
+    timing_begin(c);
+    if (!group_device(c, g, u, d, rows, 1, D, I, total, max_rows, all_packed, (float *)c->y.p, (const float *)c->x.p, nullptr)) return 0;
+    timing_end(c);
+    if (!check_status(c)) return 0;
+    timing_collect(c);
+    return cuda_ok(cudaMemcpy(y, c->y.p, xb, cudaMemcpyDeviceToHost), "expert output download");
+}
+// The reference's W4A16 tensor-core shared-expert call (c/backend_cuda.cu:1457-1484)
+// is the same function with per-row int4 tensors required.
+extern "C" int coli_cuda_shared_mlp_w4a16(ColiCudaTensor *gate, ColiCudaTensor *up, ColiCudaTensor *down,
+                                          float *y, const float *x, int S) {
+    if (!gate || !up || !down || gate->fmt != 2 || up->fmt != 2 || down->fmt != 2) return 0;
+    return coli_cuda_expert_mlp(gate, up, down, y, x, S);
+}
+
+// ---------------------------------------------------------------------------
+// Attention / RoPE entry points: outside this backend's path ("not offloaded").
+// ---------------------------------------------------------------------------
+extern "C" int coli_cuda_attention_absorb(ColiCudaTensor *, float *, const float *, const float *, const float *, int, int, int, int, int, int, float) { return 0; }
+extern "C" int coli_cuda_attention_absorb_batch(ColiCudaTensor *, float *, const float *, const float *, const float *, int, int, int, int, int, int, int, float) { return 0; }
+extern "C" int coli_cuda_attention_project_batch(ColiCudaTensor *, ColiCudaTensor *, float *, const float *, const float *, const float *, int, int, int, int, int, int, int, float) { return 0; }
+extern "C" int coli_cuda_attention_project_ragged(ColiCudaTensor *, ColiCudaTensor *, float *, const float *, const void *const *, const float *const *, const float *const *, const int *, int, int, int, int, int, int, int, float) { return 0; }
+extern "C" int coli_cuda_attention_project_batch_dev(ColiCudaTensor *, ColiCudaTensor *, float *, const float *, const float *, const float *, int, int, int, int, int, int, int, float) { return 0; }
+extern "C" int coli_cuda_attention_absorb_batch_dev(ColiCudaTensor *, float *, const float *, const float *, const float *, int, int, int, int, int, int, int, float) { return 0; }
+extern "C" int coli_cuda_attention_absorb_kvdev(ColiCudaTensor *, float *, const float *, const float *, const float *, int, int, int, int, int, int, float) { return 0; }
+extern "C" int coli_cuda_attention_project_batch_dev_out(ColiCudaTensor *, ColiCudaTensor *, float *, const float *, const float *, const float *, int, int, int, int, int, int, int, float) { return 0; }
+extern "C" int coli_cuda_pipe_rope(int, float *, const int *, int, int, int, int, int, float) { return 0; }
+extern "C" int coli_cuda_pipe_rope_base(int, float *, int, int, int, int, int, int, float) { return 0; }
+
+// ---------------------------------------------------------------------------
+// Resident-pipeline primitives
+// ---------------------------------------------------------------------------
+extern "C" float *coli_cuda_pipe_scratch(int device, int slot, size_t bytes) {
+    DeviceCtx *c = find_ctx(device);
+    if (slot < 0 || slot >= 27 || !select_ctx(c)) return nullptr;
+    if (!reserve(c, &c->pipe[slot], bytes)) return nullptr;
+    return (float *)c->pipe[slot].p;
+}
+extern "C" void *coli_cuda_pipe_alloc(int device, size_t bytes) {
+    DeviceCtx *c = find_ctx(device);
+    if (!select_ctx(c)) return nullptr;
+    void *p = nullptr;
+    if (!cuda_ok(cudaMalloc(&p, bytes), "pipe alloc")) return nullptr;
+    return p;
+}
+extern "C" void coli_cuda_pipe_free(int device, void *p) {
+    DeviceCtx *c = find_ctx(device);
+    if (!p || !select_ctx(c)) return;
+    cudaFree(p);
+}
+extern "C" int coli_cuda_pipe_upload(int device, void *dst, const void *src, size_t bytes) {
+    DeviceCtx *c = find_ctx(device);
+    if (!select_ctx(c)) return 0;
+    return cuda_ok(cudaMemcpy(dst, src, bytes, cudaMemcpyHostToDevice), "pipe upload");
+}
+extern "C" int coli_cuda_pipe_download(int device, const void *src, void *dst, size_t bytes) {
+    DeviceCtx *c = find_ctx(device);
+    if (!select_ctx(c)) return 0;
+    if (!cuda_ok(cudaStreamSynchronize(c->stream), "pipe download sync")) return 0;
+    return cuda_ok(cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToHost), "pipe download");
+}
+extern "C" int coli_cuda_pipe_rmsnorm_s(int device, float *y_dev, const float *x_dev, const float *w_dev,
+                                        int S, int D, float eps, int xstride, int ystride) {
+    if (fault_injected()) return 0;
+    DeviceCtx *c = find_ctx(device);
+    if (S < 1 || D < 1 || xstride < D || ystride < D || !select_ctx(c)) return 0;
+    k_rmsnorm<<<S, 256, 0, c->stream>>>(y_dev, x_dev, w_dev, D, eps, xstride, ystride);
+    return cuda_ok(cudaGetLastError(), "pipe rmsnorm");
+}
+extern "C" int coli_cuda_pipe_rmsnorm(int device, float *y_dev, const float *x_dev, const float *w_dev,
+                                      int S, int D, float eps) {
+    return coli_cuda_pipe_rmsnorm_s(device, y_dev, x_dev, w_dev, S, D, eps, D, D);
+}
+extern "C" int coli_cuda_pipe_silu_mul(int device, float *gate_dev, const float *up_dev, size_t n) {
+    if (fault_injected()) return 0;
+    DeviceCtx *c = find_ctx(device);
+    if (!n || !select_ctx(c)) return 0;
+    k_silu_mul<<<(unsigned)((n + 255) / 256), 256, 0, c->stream>>>(gate_dev, up_dev, n);
+    return cuda_ok(cudaGetLastError(), "pipe silu mul");
+}
+extern "C" int coli_cuda_pipe_add(int device, float *x_dev, const float *t_dev, size_t n) {
+    if (fault_injected()) return 0;
+    DeviceCtx *c = find_ctx(device);
+    if (!n || !select_ctx(c)) return 0;
+    k_add<<<(unsigned)((n + 255) / 256), 256, 0, c->stream>>>(x_dev, t_dev, n);
+    return cuda_ok(cudaGetLastError(), "pipe add");
+}
+extern "C" int coli_cuda_pipe_rows_add(int device, float *x_dev, const float *partial_dev,
+                                       const int *rows_dev, int nrows, int D) {
+    if (fault_injected()) return 0;
+    DeviceCtx *c = find_ctx(device);
+    if (nrows < 1 || D < 1 || !select_ctx(c)) return 0;
+    k_rows_add<<<nrows, 256, 0, c->stream>>>(x_dev, partial_dev, rows_dev, D);
+    return cuda_ok(cudaGetLastError(), "pipe rows add");
+}
+extern "C" int coli_cuda_pipe_copy2d(int device, float *dst, int dpitch, const float *src, int spitch,
+                                     int width, int height) {
+    DeviceCtx *c = find_ctx(device);
+    if (!select_ctx(c)) return 0;
+    return cuda_ok(cudaMemcpy2DAsync(dst, (size_t)dpitch * 4, src, (size_t)spitch * 4, (size_t)width * 4,
+                                     height, cudaMemcpyDeviceToDevice, c->stream), "pipe copy2d");
+}
+extern "C" int coli_cuda_pipe_peer_copy(int dst_dev, float *dst, int src_dev, const float *src, size_t bytes) {
+    if (!dst || !src) return 0;
+    DeviceCtx *cd = find_ctx(dst_dev), *cs = find_ctx(src_dev);
+    if (!cd || !cs) return 0;
+    if (!select_ctx(cs) || !cuda_ok(cudaStreamSynchronize(cs->stream), "peer copy sync")) return 0;
+    if (dst_dev == src_dev)
+        return cuda_ok(cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToDevice), "pipe intra copy");
+    if (!select_ctx(cd) || !cuda_ok(cudaStreamSynchronize(cd->stream), "peer copy sync")) return 0;
+    return cuda_ok(cudaMemcpyPeer(dst, dst_dev, src, src_dev, bytes), "pipe peer copy");
+}
+extern "C" int coli_cuda_pipe_sync(int device) {
+    DeviceCtx *c = find_ctx(device);
+    if (!select_ctx(c)) return 0;
+    return cuda_ok(cudaDeviceSynchronize(), "pipe sync");
+}
+
+extern "C" int coli_cuda_pipe_router(int device, const float *x_dev, const void *rw_dev, const void *rb_dev,
+                                     int D, int E, int Ksel, float topp, int norm_topk, float routed_scale,
+                                     int *idx_host, float *w_host, int *keff_host) {
+    DeviceCtx *c = find_ctx(device);
+    if (!x_dev || !rw_dev || !rb_dev || D < 1 || E < 1 || E > ROUTE_MAX_E || Ksel < 1 || Ksel > ROUTE_MAX_K ||
+        Ksel > E || !idx_host || !w_host || !keff_host || !select_ctx(c)) return 0;
+    size_t need = (size_t)E * 4 + (size_t)Ksel * 8 + 16;
+    if (!reserve(c, &c->misc, need)) return 0;
+    float *logits = (float *)c->misc.p;
+    int *idx = (int *)(logits + E);
+    float *w = (float *)(idx + Ksel);
+    int *keff = (int *)(w + Ksel);
+    RouteRule rule{D, 0, E, Ksel, 1, norm_topk, routed_scale, topp};
+    k_router_logits<<<(E + 127) / 128, 128, 0, c->stream>>>(logits, x_dev, (const float *)rw_dev, 1, D, E);
+    size_t sm = (size_t)(2 * E + 2 * ROUTE_MAX_K) * sizeof(float);
+    k_route_topk<<<1, 32, sm, c->stream>>>(logits, (const float *)rb_dev, rule, 1, idx, w, keff);
+    if (!cuda_ok(cudaGetLastError(), "pipe router launch")) return 0;
+    std::vector<char> buf((size_t)Ksel * 8 + 4);
+    if (!cuda_ok(cudaMemcpyAsync(buf.data(), idx, buf.size(), cudaMemcpyDeviceToHost, c->stream), "pipe router readback") ||
+        !cuda_ok(cudaStreamSynchronize(c->stream), "pipe router sync")) return 0;
+    std::memcpy(idx_host, buf.data(), (size_t)Ksel * 4);
+    std::memcpy(w_host, buf.data() + (size_t)Ksel * 4, (size_t)Ksel * 4);
+    std::memcpy(keff_host, buf.data() + (size_t)Ksel * 8, 4);
+    return 1;
+}
+
+extern "C" int coli_cuda_expert_group_resident_issue(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
+                                                     ColiCudaTensor *const *downs, const float *weights,
+                                                     int count, int home_device, const float *x_src_dev,
+                                                     float *partial_slot_dev) {
+    if (!gates || !ups || !downs || !weights || count < 1 || count > 64 || !x_src_dev || !partial_slot_dev) return 0;
+    int device, D, I, total, max_rows, all_packed, any_packed;
+    if (!group_shape_ok(gates, ups, downs, nullptr, count, &device, &D, &I, &total, &max_rows, &all_packed, &any_packed)) return 0;
+    if (!all_packed && any_packed) return 0;
+    DeviceCtx *c = find_ctx(device), *home = find_ctx(home_device);
+    if (!home || !select_ctx(c)) return 0;
+    // fixed capacities (64 experts) so that a re-issue never reallocates under queued work
+    if (!reserve(c, &c->x, (size_t)64 * D * sizeof(float)) || !reserve(c, &c->y, (size_t)64 * D * sizeof(float)) ||
+        !reserve(c, &c->misc, (size_t)(D + 64) * sizeof(float) + 4096)) return 0;
+    float *partial_local = (float *)c->misc.p, *w_dev = partial_local + D;
+    if (!cuda_ok(cudaMemcpyAsync(w_dev, weights, (size_t)count * sizeof(float), cudaMemcpyHostToDevice, c->stream), "resident group weights")) return 0;
+    cudaError_t e = device == home_device
+        ? cudaMemcpyAsync(c->x.p, x_src_dev, (size_t)D * sizeof(float), cudaMemcpyDeviceToDevice, c->stream)
+        : cudaMemcpyPeerAsync(c->x.p, device, x_src_dev, home_device, (size_t)D * sizeof(float), c->stream);
+    if (!cuda_ok(e, "resident group x copy")) return 0;
+    int one = 1;
+    if (!group_device(c, gates, ups, downs, nullptr, count, D, I, total, 1, all_packed, (float *)c->y.p,
+                      (const float *)c->x.p, &one)) return 0;
+    k_weighted_sum_rows<<<48, 256, 0, c->stream>>>(partial_local, (const float *)c->y.p, w_dev, count, D);
+    e = device == home_device
+        ? cudaMemcpyAsync(partial_slot_dev, partial_local, (size_t)D * sizeof(float), cudaMemcpyDeviceToDevice, c->stream)
+        : cudaMemcpyPeerAsync(partial_slot_dev, home_device, partial_local, device, (size_t)D * sizeof(float), c->stream);
+    if (!cuda_ok(e, "resident partial copy")) return 0;
+    if (!cuda_ok(cudaEventRecord(c->ev_done, c->stream), "resident event record")) return 0;
+    return cuda_ok(cudaGetLastError(), "resident group launch");
+}
+extern "C" int coli_cuda_expert_group_resident_take(int home_device, const int *devices, int n_issued,
+                                                    float *slots_dev, float *acc_dev, int D) {
+    if (n_issued < 1 || !devices || !slots_dev || !acc_dev || D < 1) return 0;
+    DeviceCtx *home = find_ctx(home_device);
+    if (!select_ctx(home)) return 0;
+    for (int i = 0; i < n_issued; i++) {
+        DeviceCtx *src = find_ctx(devices[i]);
+        if (!src) return 0;
+        if (!cuda_ok(cudaStreamWaitEvent(home->stream, src->ev_done, 0), "resident take wait")) return 0;
+    }
+    k_sum_slots<<<48, 256, 0, home->stream>>>(acc_dev, slots_dev, n_issued, D);
+    return cuda_ok(cudaGetLastError(), "resident take reduce");
+}
+
+#include "moe_layer.cuh"

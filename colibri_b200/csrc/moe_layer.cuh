@@ -1,0 +1,262 @@
+// Additive entry points: a whole MoE layer (route -> union -> gather -> expert
+// FFN -> weighted combine + shared expert) on the device. Included at the end
+// of backend.cu.
+#pragma once
+
+struct ColiCudaMoeLayer {
+    int device;
+    RouteRule rule;
+    int max_rows, has_shared, mode_gu, mode_d;
+    float *router_w, *router_bias;           // device copies (or NULL)
+    void *table_mem;                         // device block behind `tab`
+    LayerTables tab;
+    // per-call buffers (device, grow-only)
+    Buf x, out, logits, idx, w, keff, pos_of, uniq, scal, xq, xs, pg, pu, hq, hs, pd, seg1, seg2, ctl;
+    float *host_io;                          // pinned staging
+    size_t host_io_cap;
+};
+
+static int layer_mode_of(const ColiCudaTensor *t) { return t && t->packed ? t->mode : -1; }
+
+extern "C" int coli_cuda_moe_layer_create(ColiCudaMoeLayer **layer, const ColiCudaMoeDesc *d, int max_rows) {
+    if (!layer || !d || max_rows < 1 || d->E < 1 || d->K < 1 || d->K > d->E || d->E > ROUTE_MAX_E ||
+        d->K > ROUTE_MAX_K || !d->gates || !d->ups || !d->downs || !d->gates[0]) return 0;
+    if (d->D % BLOCK_K || d->I % BLOCK_K) return 0;
+    const int device = d->gates[0]->device;
+    DeviceCtx *c = find_ctx(device);
+    if (!select_ctx(c)) return 0;
+    const int mgu = layer_mode_of(d->gates[0]), md = layer_mode_of(d->downs[0]);
+    if (mgu < 0 || md < 0) return 0;
+    for (int e = 0; e < d->E; e++) {
+        const ColiCudaTensor *g = d->gates[e], *u = d->ups[e], *dn = d->downs[e];
+        if (!g || !u || !dn || g->device != device || u->device != device || dn->device != device ||
+            g->I != d->D || g->O != d->I || u->I != d->D || u->O != d->I || dn->I != d->I || dn->O != d->D ||
+            layer_mode_of(g) != mgu || layer_mode_of(u) != mgu || layer_mode_of(dn) != md) return 0;
+    }
+    const int has_shared = d->shared_gate || d->shared_up || d->shared_down;
+    if (has_shared) {
+        const ColiCudaTensor *g = d->shared_gate, *u = d->shared_up, *dn = d->shared_down;
+        if (!g || !u || !dn || g->device != device || u->device != device || dn->device != device ||
+            g->I != d->D || g->O != d->I || u->I != d->D || u->O != d->I || dn->I != d->I || dn->O != d->D ||
+            layer_mode_of(g) != mgu || layer_mode_of(u) != mgu || layer_mode_of(dn) != md) return 0;
+    }
+    ColiCudaMoeLayer *L = new ColiCudaMoeLayer();
+    std::memset(L, 0, sizeof(*L));   // plain data (Buf is two scalars)
+    L->device = device;
+    L->rule = RouteRule{d->D, d->I, d->E, d->K, d->gating, d->norm_topk, d->routed_scale, d->topp};
+    L->max_rows = max_rows; L->has_shared = has_shared; L->mode_gu = mgu; L->mode_d = md;
+    const int E = d->E;
+    // device tables: 3 arrays of code pointers + 3 arrays of row-scale pointers
+    std::vector<const void *> host(6 * (size_t)E);
+    for (int e = 0; e < E; e++) {
+        host[0 * E + e] = d->gates[e]->pk; host[1 * E + e] = d->ups[e]->pk; host[2 * E + e] = d->downs[e]->pk;
+        host[3 * E + e] = d->gates[e]->rowscale; host[4 * E + e] = d->ups[e]->rowscale; host[5 * E + e] = d->downs[e]->rowscale;
+    }
+    int ok = cuda_ok(cudaMalloc(&L->table_mem, host.size() * sizeof(void *)), "layer tables") &&
+             cuda_ok(cudaMemcpy(L->table_mem, host.data(), host.size() * sizeof(void *), cudaMemcpyHostToDevice), "layer tables");
+    if (ok && d->router_w) {
+        ok = cuda_ok(cudaMalloc((void **)&L->router_w, (size_t)E * d->D * sizeof(float)), "router weights") &&
+             cuda_ok(cudaMemcpy(L->router_w, d->router_w, (size_t)E * d->D * sizeof(float), cudaMemcpyHostToDevice), "router weights");
+    }
+    if (ok && d->router_bias) {
+        ok = cuda_ok(cudaMalloc((void **)&L->router_bias, (size_t)E * sizeof(float)), "router bias") &&
+             cuda_ok(cudaMemcpy(L->router_bias, d->router_bias, (size_t)E * sizeof(float), cudaMemcpyHostToDevice), "router bias");
+    }
+    if (!ok) { coli_cuda_moe_layer_free(L); return 0; }
+    const void *const *tp = static_cast<const void *const *>(L->table_mem);
+    L->tab.gate_pk = reinterpret_cast<const uint8_t *const *>(tp);
+    L->tab.up_pk = reinterpret_cast<const uint8_t *const *>(tp + E);
+    L->tab.down_pk = reinterpret_cast<const uint8_t *const *>(tp + 2 * E);
+    L->tab.gate_rs = mgu == SC_ROW ? reinterpret_cast<const float *const *>(tp + 3 * E) : nullptr;
+    L->tab.up_rs = mgu == SC_ROW ? reinterpret_cast<const float *const *>(tp + 4 * E) : nullptr;
+    L->tab.down_rs = md == SC_ROW ? reinterpret_cast<const float *const *>(tp + 5 * E) : nullptr;
+    if (has_shared) {
+        L->tab.sh_gate_pk = d->shared_gate->pk; L->tab.sh_up_pk = d->shared_up->pk; L->tab.sh_down_pk = d->shared_down->pk;
+        L->tab.sh_gate_rs = d->shared_gate->rowscale; L->tab.sh_up_rs = d->shared_up->rowscale; L->tab.sh_down_rs = d->shared_down->rowscale;
+    }
+    *layer = L;
+    return 1;
+}
+
+extern "C" void coli_cuda_moe_layer_free(ColiCudaMoeLayer *L) {
+    if (!L) return;
+    DeviceCtx *c = find_ctx(L->device);
+    if (c && select_ctx(c)) {
+        cudaStreamSynchronize(c->stream);
+        Buf *bufs[] = {&L->x, &L->out, &L->logits, &L->idx, &L->w, &L->keff, &L->pos_of, &L->uniq, &L->scal,
+                       &L->xq, &L->xs, &L->pg, &L->pu, &L->hq, &L->hs, &L->pd, &L->seg1, &L->seg2, &L->ctl};
+        for (Buf *b : bufs) free_buf(b);
+        if (L->router_w) cudaFree(L->router_w);
+        if (L->router_bias) cudaFree(L->router_bias);
+        if (L->table_mem) cudaFree(L->table_mem);
+        if (L->host_io) cudaFreeHost(L->host_io);
+        (void)cudaGetLastError();
+    }
+    delete L;
+}
+
+struct LayerPlan {
+    int nc, rpp, nkp1, nkp2, seg_cap, npos_cap;
+};
+
+static LayerPlan layer_plan(const ColiCudaMoeLayer *L, const DeviceCtx *c, int M) {
+    LayerPlan p;
+    const RouteRule &r = L->rule;
+    long mk = (long)M * r.K;
+    long expect_rows = (2 * mk + r.E - 1) / r.E;          // twice the uniform-routing mean
+    if (expect_rows > M) expect_rows = M;
+    if (expect_rows < 1) expect_rows = 1;
+    p.nc = pick_nc((int)expect_rows);
+    p.rpp = 4 * p.nc;
+    long experts = mk < r.E ? mk : r.E;
+    long passes = experts + (L->has_shared ? (M + p.rpp - 1) / p.rpp : 0);
+    p.nkp1 = pick_nkpart(r.D / BLOCK_K, 2 * passes * (r.I / TILE_ROWS), c->sms);
+    p.nkp2 = pick_nkpart(r.I / BLOCK_K, passes * (r.D / TILE_ROWS), c->sms);
+    p.seg_cap = (int)(experts + mk / p.rpp + (M + p.rpp - 1) / p.rpp + 2);
+    p.npos_cap = (int)(mk + (L->has_shared ? M : 0));
+    return p;
+}
+
+// Everything on c->stream with device buffers. idx/w/keff must be device
+// buffers of the layer or the caller ([M,K], [M,K], [M]).
+static int layer_run(ColiCudaMoeLayer *L, DeviceCtx *c, float *out_dev, const float *x_dev,
+                     const float *logits_dev, int M, int *idx_dev, float *w_dev, int *keff_dev,
+                     int route_only, int *uniq_dev, int *nu_dev) {
+    const RouteRule &r = L->rule;
+    const LayerPlan p = layer_plan(L, c, M);
+    const int nkb1 = r.D / BLOCK_K, nkb2 = r.I / BLOCK_K;
+    if (!reserve(c, &L->logits, (size_t)M * r.E * sizeof(float)) ||
+        !reserve(c, &L->pos_of, (size_t)M * r.K * sizeof(int)) ||
+        !reserve(c, &L->uniq, (size_t)r.E * sizeof(int)) || !reserve(c, &L->scal, 64) ||
+        !reserve(c, &L->seg1, (size_t)2 * p.seg_cap * sizeof(GemvSeg)) ||
+        !reserve(c, &L->seg2, (size_t)p.seg_cap * sizeof(GemvSeg)) ||
+        !reserve(c, &L->ctl, 2 * sizeof(GemvCtl))) return 0;
+    if (!route_only &&
+        (!reserve(c, &L->xq, (size_t)M * r.D * 2 * sizeof(__half)) ||
+         !reserve(c, &L->xs, (size_t)M * nkb1 * sizeof(float)) ||
+         !reserve(c, &L->pg, (size_t)p.nkp1 * p.npos_cap * r.I * sizeof(float)) ||
+         !reserve(c, &L->pu, (size_t)p.nkp1 * p.npos_cap * r.I * sizeof(float)) ||
+         !reserve(c, &L->hq, (size_t)p.npos_cap * r.I * 2 * sizeof(__half)) ||
+         !reserve(c, &L->hs, (size_t)p.npos_cap * nkb2 * sizeof(float)) ||
+         !reserve(c, &L->pd, (size_t)p.nkp2 * p.npos_cap * r.D * sizeof(float)))) return 0;
+    const float *lg = logits_dev;
+    if (!lg) {
+        if (!L->router_w) return 0;
+        int n = M * r.E;
+        k_router_logits<<<(n + 63) / 64, 64, 0, c->stream>>>((float *)L->logits.p, x_dev, L->router_w, M, r.D, r.E);
+        c->last_launches++;
+        lg = (const float *)L->logits.p;
+    }
+    {
+        const int warps = 4;
+        size_t sm = (size_t)warps * (2 * r.E + 2 * ROUTE_MAX_K) * sizeof(float);
+        k_route_topk<<<(M + warps - 1) / warps, warps * 32, sm, c->stream>>>(lg, L->router_bias, r, M, idx_dev, w_dev, keff_dev);
+        c->last_launches++;
+    }
+    int *scal = (int *)L->scal.p;   // [0]=nu [1]=npos [2]=shared_pos0
+    BuildOut bo;
+    bo.seg1 = (GemvSeg *)L->seg1.p; bo.seg2 = (GemvSeg *)L->seg2.p;
+    bo.ctl1 = (GemvCtl *)L->ctl.p; bo.ctl2 = bo.ctl1 + 1;
+    bo.pos_of = (int *)L->pos_of.p; bo.uniq = uniq_dev ? uniq_dev : (int *)L->uniq.p;
+    bo.nu = nu_dev ? nu_dev : scal; bo.npos = scal + 1; bo.shared_pos0 = scal + 2;
+    bo.partG = (float *)L->pg.p; bo.partU = (float *)L->pu.p; bo.partD = (float *)L->pd.p;
+    k_route_build<<<1, 1024, (size_t)5 * r.E * sizeof(int), c->stream>>>(idx_dev, keff_dev, M, r, L->tab, bo, p.rpp,
+                                                                      p.nkp1, p.nkp2, p.seg_cap);
+    c->last_launches++;
+    if (route_only) return cuda_ok(cudaGetLastError(), "route launch");
+    int nw = M * nkb1;
+    k_prep_rows<<<(nw * 32 + 255) / 256, 256, 0, c->stream>>>((__half *)L->xq.p, (float *)L->xs.p, x_dev, nullptr, M, r.D);
+    c->last_launches++;
+    launch_gemv(c, L->mode_gu, p.nc, bo.seg1, bo.ctl1, (const __half *)L->xq.p, (const float *)L->xs.p);
+    long nw2 = (long)p.npos_cap * nkb2;
+    k_swiglu_prep<<<(unsigned)((nw2 * 32 + 255) / 256), 256, 0, c->stream>>>(
+        (__half *)L->hq.p, (float *)L->hs.p, (const float *)L->pg.p, (const float *)L->pu.p, scal + 1,
+        p.npos_cap, r.I, p.nkp1, nullptr);
+    c->last_launches++;
+    launch_gemv(c, L->mode_d, p.nc, bo.seg2, bo.ctl2, (const __half *)L->hq.p, (const float *)L->hs.p);
+    size_t n4 = (size_t)M * r.D / 4;
+    k_combine<<<(unsigned)((n4 + 255) / 256), 256, 0, c->stream>>>(
+        out_dev, (const float *)L->pd.p, (const int *)L->pos_of.p, w_dev, keff_dev, scal + 1, M, r.K, r.D,
+        p.nkp2, L->has_shared ? scal + 2 : nullptr);
+    c->last_launches++;
+    return cuda_ok(cudaGetLastError(), "layer launch");
+}
+
+static int layer_route_bufs(ColiCudaMoeLayer *L, DeviceCtx *c, int M) {
+    return reserve(c, &L->idx, (size_t)M * L->rule.K * sizeof(int)) &&
+           reserve(c, &L->w, (size_t)M * L->rule.K * sizeof(float)) &&
+           reserve(c, &L->keff, (size_t)M * sizeof(int));
+}
+
+extern "C" int coli_cuda_moe_layer_dev(ColiCudaMoeLayer *L, float *out_dev, const float *x_dev,
+                                       const float *logits_dev, int M, int *idx_dev, float *w_dev,
+                                       int *keff_dev) {
+    if (fault_injected()) return 0;
+    if (!L || !out_dev || !x_dev || M < 1 || M > L->max_rows) return 0;
+    DeviceCtx *c = find_ctx(L->device);
+    if (!select_ctx(c) || !layer_route_bufs(L, c, M)) return 0;
+    timing_begin(c);
+    int ok = layer_run(L, c, out_dev, x_dev, logits_dev, M, idx_dev ? idx_dev : (int *)L->idx.p,
+                       w_dev ? w_dev : (float *)L->w.p, keff_dev ? keff_dev : (int *)L->keff.p, 0, nullptr, nullptr);
+    timing_end(c);
+    if (ok && g_timing) { ok = check_status(c); timing_collect(c); }
+    return ok;
+}
+
+extern "C" int coli_cuda_moe_route_dev(ColiCudaMoeLayer *L, const float *x_dev, const float *logits_dev,
+                                       int M, int *idx_dev, float *w_dev, int *keff_dev, int *uniq_dev,
+                                       int *nu_dev) {
+    if (!L || M < 1 || M > L->max_rows || (!x_dev && !logits_dev)) return 0;
+    DeviceCtx *c = find_ctx(L->device);
+    if (!select_ctx(c) || !layer_route_bufs(L, c, M)) return 0;
+    return layer_run(L, c, nullptr, x_dev, logits_dev, M, idx_dev ? idx_dev : (int *)L->idx.p,
+                     w_dev ? w_dev : (float *)L->w.p, keff_dev ? keff_dev : (int *)L->keff.p, 1, uniq_dev, nu_dev);
+}
+
+extern "C" int coli_cuda_moe_layer(ColiCudaMoeLayer *L, float *out, const float *x, const float *logits,
+                                   int M, int *idx_out, float *w_out, int *keff_out) {
+    if (fault_injected()) return 0;
+    if (!L || !out || !x || M < 1 || M > L->max_rows) return 0;
+    DeviceCtx *c = find_ctx(L->device);
+    if (!select_ctx(c) || !layer_route_bufs(L, c, M)) return 0;
+    const RouteRule &r = L->rule;
+    const size_t xb = (size_t)M * r.D * sizeof(float), lb = logits ? (size_t)M * r.E * sizeof(float) : 0;
+    const size_t rb = (size_t)M * r.K * 8 + (size_t)M * 4;
+    if (!reserve(c, &L->x, xb + lb) || !reserve(c, &L->out, xb)) return 0;
+    // pinned staging: [x | logits | out | idx | w | keff]
+    size_t need = xb + lb + xb + rb;
+    if (need > L->host_io_cap) {
+        if (L->host_io) { cudaStreamSynchronize(c->stream); cudaFreeHost(L->host_io); L->host_io = nullptr; L->host_io_cap = 0; }
+        if (!cuda_ok(cudaMallocHost((void **)&L->host_io, need), "pinned allocation")) return 0;
+        L->host_io_cap = need;
+    }
+    uint8_t *hp = reinterpret_cast<uint8_t *>(L->host_io);
+    std::memcpy(hp, x, xb);
+    if (lb) std::memcpy(hp + xb, logits, lb);
+    if (!cuda_ok(cudaMemcpyAsync(L->x.p, hp, xb + lb, cudaMemcpyHostToDevice, c->stream), "layer input upload")) return 0;
+    const float *x_dev = (const float *)L->x.p;
+    const float *lg_dev = lb ? reinterpret_cast<const float *>(static_cast<uint8_t *>(L->x.p) + xb) : nullptr;
+    timing_begin(c);
+    if (!layer_run(L, c, (float *)L->out.p, x_dev, lg_dev, M, (int *)L->idx.p, (float *)L->w.p, (int *)L->keff.p,
+                   0, nullptr, nullptr)) return 0;
+    timing_end(c);
+    uint8_t *ho = hp + xb + lb;
+    if (!cuda_ok(cudaMemcpyAsync(ho, L->out.p, xb, cudaMemcpyDeviceToHost, c->stream), "layer output download")) return 0;
+    const int want_route = idx_out || w_out || keff_out;
+    if (want_route) {
+        size_t kb = (size_t)M * r.K * 4;
+        cudaMemcpyAsync(ho + xb, L->idx.p, kb, cudaMemcpyDeviceToHost, c->stream);
+        cudaMemcpyAsync(ho + xb + kb, L->w.p, kb, cudaMemcpyDeviceToHost, c->stream);
+        cudaMemcpyAsync(ho + xb + 2 * kb, L->keff.p, (size_t)M * 4, cudaMemcpyDeviceToHost, c->stream);
+    }
+    if (!check_status(c)) return 0;
+    timing_collect(c);
+    std::memcpy(out, ho, xb);
+    if (want_route) {
+        size_t kb = (size_t)M * r.K * 4;
+        if (idx_out) std::memcpy(idx_out, ho + xb, kb);
+        if (w_out) std::memcpy(w_out, ho + xb + kb, kb);
+        if (keff_out) std::memcpy(keff_out, ho + xb + 2 * kb, (size_t)M * 4);
+    }
+    return 1;
+}

@@ -1,0 +1,237 @@
+/* C ABI of the B200-native MoE expert-FFN backend (libcoli_cuda_b200.so).
+ *
+ * Part 1 is the reference engine's GPU backend interface, symbol for symbol:
+ * every function below has the name, parameter list, return convention and
+ * ownership rules of the declaration it replaces in the reference's
+ * c/backend_cuda.h (line numbers given per group), so an engine that links
+ * c/backend_cuda.o can link this library instead without source changes.
+ * Return convention (c/backend_cuda.h:70-80): 1 = done, 0 = refused or failed
+ * with every output untouched (the engine then runs its CPU path); pointer
+ * returns use NULL for failure. Host buffers are borrowed for the duration of
+ * a call only.
+ *
+ * Part 2 declares the additive entry points of this backend (no counterpart in
+ * the reference header): device-resident layer handles that run routing,
+ * union building, gather, the expert FFN and the weighted combine without
+ * leaving the GPU. Their shapes follow the reference's Metal backend, which
+ * already exposes such fused calls (c/backend_metal.h:71-112,132-169).
+ */
+#ifndef COLI_CUDA_B200_H
+#define COLI_CUDA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define COLI_CUDA_MAX_DEVICES 16 /* c/backend_cuda.h:22 */
+
+/* Opaque resident tensor (c/backend_cuda.h:25). */
+typedef struct ColiCudaTensor ColiCudaTensor;
+
+/* ===================== Part 1: the reference ABI ========================= */
+
+/* Lifecycle and queries — c/backend_cuda.h:28-40. Devices are CUDA ordinals. */
+int coli_cuda_init(const int *devices, int count);
+void coli_cuda_shutdown(void);
+int coli_cuda_device_count(void);
+int coli_cuda_device_at(int index);
+int coli_cuda_mem_info(int device, size_t *free_bytes, size_t *total_bytes);
+int coli_cuda_device_integrated(int device);
+/* Logical container bytes (weights + scales as the caller supplied them), never
+ * the repacked device footprint; device < 0 aggregates. */
+void coli_cuda_stats(int device, size_t *tensor_count, size_t *tensor_bytes);
+void coli_cuda_group_stats(uint64_t *calls, uint64_t *experts, uint64_t *rows,
+                           double *h2d_ms, double *kernel_ms, double *d2h_ms);
+void coli_cuda_group_stats_device(int device, uint64_t *calls, uint64_t *experts, uint64_t *rows,
+                                  double *h2d_ms, double *kernel_ms, double *d2h_ms);
+
+/* Decode tables for formats outside this backend's scope — c/backend_cuda.h:45-50.
+ * fmt=6 (E8 lattice) and fmt=8 (FP8 block) tensors are refused, so both return 0. */
+int coli_cuda_e8_set_grid(const void *grid);
+int coli_cuda_fp8_set_lut(const float *lut);
+
+/* Resident tensors — c/backend_cuda.h:53-59,142-149.
+ * fmt: 0=f32, 1=int8 per-row scale, 2=int4 per-row, 3=int2 per-row, 4=int4 with
+ * one f32 scale per `gs` columns (scales[o*ceil(I/gs)+g]), 7=MXFP4 (e2m1
+ * nibbles, `scales` points at [O, ceil(I/32)] ue8m0 BYTES). With *tensor
+ * already set the call only checks that (fmt,I,O,device,gs) match and works
+ * with NULL host pointers. */
+int coli_cuda_tensor_upload_g(ColiCudaTensor **tensor, const void *weights, const float *scales,
+                              int fmt, int I, int O, int device, int gs);
+int coli_cuda_tensor_upload(ColiCudaTensor **tensor, const void *weights, const float *scales,
+                            int fmt, int I, int O, int device);
+void coli_cuda_tensor_free(ColiCudaTensor *tensor);
+size_t coli_cuda_tensor_bytes(const ColiCudaTensor *tensor);
+int coli_cuda_tensor_device(const ColiCudaTensor *tensor);
+int coli_cuda_tensor_update(ColiCudaTensor *tensor, const void *weights, const float *scales);
+
+/* y[S,O] = x[S,I] @ W[O,I]^T with host x,y — c/backend_cuda.h:69-91. */
+int coli_cuda_matmul_mxfp4(float *y, const float *x, const unsigned char *q4,
+                           const unsigned char *e8s, int S, int I, int O);
+int coli_cuda_matmul(ColiCudaTensor **tensor, float *y, const float *x, const void *weights,
+                     const float *scales, int fmt, int S, int I, int O, int device, int gs);
+
+/* One expert, y = down(silu(gate x) * up x), host x,y [S,D] — c/backend_cuda.h:93-104. */
+int coli_cuda_expert_mlp(ColiCudaTensor *gate, ColiCudaTensor *up, ColiCudaTensor *down,
+                         float *y, const float *x, int S);
+int coli_cuda_shared_mlp_w4a16(ColiCudaTensor *gate, ColiCudaTensor *up, ColiCudaTensor *down,
+                               float *y, const float *x, int S);
+
+/* Packed group of same-shaped experts: x and y hold sum(rows) consecutive [D]
+ * rows in call order, count <= 64 — c/backend_cuda.h:105-121. issue/take is the
+ * asynchronous split: sum(rows) <= 8, one outstanding issue per device, take
+ * returns pinned rows valid until the next issue on that device. The two forms
+ * return bit-identical rows. */
+int coli_cuda_expert_group_issue(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
+                                 ColiCudaTensor *const *downs, const int *rows, int count,
+                                 const float *x);
+const float *coli_cuda_expert_group_take(int device);
+int coli_cuda_expert_group(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
+                           ColiCudaTensor *const *downs, const int *rows, int count, float *y,
+                           const float *x);
+
+/* MLA attention entry points — c/backend_cuda.h:123-140,186-203. Attention is
+ * outside this backend's path: each returns 0 ("not offloaded"), which is the
+ * interface's own refusal and leaves the engine on its CPU attention. */
+int coli_cuda_attention_absorb(ColiCudaTensor *kv_b, float *ctx, const float *q,
+                               const float *latent, const float *rope, int H, int Q, int R, int V,
+                               int K, int T, float attention_scale);
+int coli_cuda_attention_absorb_batch(ColiCudaTensor *kv_b, float *ctx, const float *q,
+                                     const float *latent, const float *rope, int S, int H, int Q,
+                                     int R, int V, int K, int T, float attention_scale);
+int coli_cuda_attention_project_batch(ColiCudaTensor *kv_b, ColiCudaTensor *o_proj, float *out,
+                                      const float *q, const float *latent, const float *rope,
+                                      int S, int H, int Q, int R, int V, int K, int T,
+                                      float attention_scale);
+int coli_cuda_attention_project_ragged(ColiCudaTensor *kv_b, ColiCudaTensor *o_proj, float *out,
+                                       const float *q, const void *const *keys,
+                                       const float *const *latent, const float *const *rope,
+                                       const int *lengths, int S, int H, int Q, int R, int V,
+                                       int K, int max_t, float attention_scale);
+int coli_cuda_attention_project_batch_dev(ColiCudaTensor *kv_b, ColiCudaTensor *o_proj, float *out,
+                                          const float *q_dev, const float *latent_dev,
+                                          const float *rope_dev, int S, int H, int Q, int R, int V,
+                                          int K, int T, float scale);
+int coli_cuda_attention_absorb_batch_dev(ColiCudaTensor *kv_b_shard, float *ctx_dev,
+                                         const float *q_dev, const float *latent_dev,
+                                         const float *rope_dev, int S, int H, int Q, int R, int V,
+                                         int K, int T, float scale);
+int coli_cuda_attention_absorb_kvdev(ColiCudaTensor *kv_b, float *ctx, const float *q,
+                                     const float *latent_dev, const float *rope_dev, int H, int Q,
+                                     int R, int V, int K, int T, float scale);
+int coli_cuda_attention_project_batch_dev_out(ColiCudaTensor *kv_b, ColiCudaTensor *o_proj,
+                                              float *out_dev, const float *q_dev,
+                                              const float *latent_dev, const float *rope_dev,
+                                              int S, int H, int Q, int R, int V, int K, int T,
+                                              float scale);
+
+/* Resident-pipeline primitives on device pointers — c/backend_cuda.h:151-204. */
+float *coli_cuda_pipe_scratch(int device, int slot, size_t bytes);
+void *coli_cuda_pipe_alloc(int device, size_t bytes);
+void coli_cuda_pipe_free(int device, void *p);
+int coli_cuda_pipe_upload(int device, void *dst, const void *src, size_t bytes);
+int coli_cuda_pipe_download(int device, const void *src, void *dst, size_t bytes);
+int coli_cuda_pipe_rmsnorm(int device, float *y_dev, const float *x_dev, const float *w_dev,
+                           int S, int D, float eps);
+int coli_cuda_pipe_rmsnorm_s(int device, float *y_dev, const float *x_dev, const float *w_dev,
+                             int S, int D, float eps, int xstride, int ystride);
+/* RoPE belongs to the attention path: both return 0. */
+int coli_cuda_pipe_rope(int device, float *v_dev, const int *pos_dev, int rows, int stride,
+                        int offset, int R, int heads, float theta);
+int coli_cuda_pipe_rope_base(int device, float *v_dev, int pos_base, int rows, int stride,
+                             int offset, int R, int heads, float theta);
+int coli_cuda_pipe_silu_mul(int device, float *gate_dev, const float *up_dev, size_t n);
+int coli_cuda_pipe_add(int device, float *x_dev, const float *t_dev, size_t n);
+int coli_cuda_pipe_rows_add(int device, float *x_dev, const float *partial_dev,
+                            const int *rows_dev, int nrows, int D);
+int coli_cuda_pipe_gemm(ColiCudaTensor *t, float *y_dev, const float *x_dev, int S);
+int coli_cuda_pipe_copy2d(int device, float *dst, int dpitch, const float *src, int spitch,
+                          int width, int height);
+int coli_cuda_pipe_peer_copy(int dst_dev, float *dst, int src_dev, const float *src, size_t bytes);
+int coli_cuda_pipe_sync(int device);
+/* One decode row routed on the device: sigmoid scores, bias-augmented top-K by
+ * strict '>' (lowest index wins), optional top-p, norm, scale; E<=4096, Ksel<=64. */
+int coli_cuda_pipe_router(int device, const float *x_dev, const void *rw_dev, const void *rb_dev,
+                          int D, int E, int Ksel, float topp, int norm_topk, float routed_scale,
+                          int *idx_host, float *w_host, int *keff_host);
+/* S=1 resident expert group: x row pulled from the home device, outputs
+ * weighted and reduced on the device in call order, partial pushed to a slot on
+ * the home device; take sums the slots in issue order. */
+int coli_cuda_expert_group_resident_issue(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
+                                          ColiCudaTensor *const *downs, const float *weights,
+                                          int count, int home_device, const float *x_src_dev,
+                                          float *partial_slot_dev);
+int coli_cuda_expert_group_resident_take(int home_device, const int *devices, int n_issued,
+                                         float *slots_dev, float *acc_dev, int D);
+
+/* ===================== Part 2: additive entry points ===================== */
+
+/* No counterpart in the reference header. A layer handle binds already
+ * uploaded expert tensors (E triples, plus an optional shared expert) and the
+ * routing rule, so that one call runs the whole MoE layer on the device. */
+typedef struct ColiCudaMoeLayer ColiCudaMoeLayer;
+
+typedef struct {
+    int D, I, E, K;
+    int gating;          /* 0: softmax over E then top-K (c/olmoe.c:666-681);
+                            1: sigmoid(+bias) top-K (c/colibri.c:3982-4123) */
+    int norm_topk;       /* divide the K weights by their sum (+1e-20 in mode 1) */
+    float routed_scale;  /* mode 1 only */
+    float topp;          /* mode 1 only; 0 disables */
+    const float *router_w;    /* host [E,D] f32 or NULL (then logits are passed per call) */
+    const float *router_bias; /* host [E] f32 or NULL */
+    ColiCudaTensor *const *gates, *const *ups, *const *downs; /* [E] each, one device */
+    ColiCudaTensor *shared_gate, *shared_up, *shared_down;    /* all NULL: no shared expert */
+} ColiCudaMoeDesc;
+
+/* Creates / destroys a layer handle. The tensors stay owned by the caller and
+ * must outlive the handle. max_rows bounds M of later calls. */
+int coli_cuda_moe_layer_create(ColiCudaMoeLayer **layer, const ColiCudaMoeDesc *desc, int max_rows);
+void coli_cuda_moe_layer_free(ColiCudaMoeLayer *layer);
+
+/* One MoE layer for M rows with HOST buffers: x [M,D] in, out [M,D] out,
+ * logits [M,E] or NULL (then the layer's router weights are used); optional
+ * host outputs idx [M,K], w [M,K], keff [M]. Accumulation order per row is the
+ * row's selection order kk=0..keff-1, shared expert last. */
+int coli_cuda_moe_layer(ColiCudaMoeLayer *layer, float *out, const float *x, const float *logits,
+                        int M, int *idx_out, float *w_out, int *keff_out);
+
+/* Same with DEVICE buffers on the layer's device; returns after enqueueing on
+ * the backend's stream for that device (coli_cuda_pipe_sync waits). */
+int coli_cuda_moe_layer_dev(ColiCudaMoeLayer *layer, float *out_dev, const float *x_dev,
+                            const float *logits_dev, int M, int *idx_dev, float *w_dev,
+                            int *keff_dev);
+
+/* Routing + union only (device buffers): idx/w/keff as above, uniq [E] receives
+ * the distinct experts in first-appearance order, *nu_dev their number. */
+int coli_cuda_moe_route_dev(ColiCudaMoeLayer *layer, const float *x_dev, const float *logits_dev,
+                            int M, int *idx_dev, float *w_dev, int *keff_dev, int *uniq_dev,
+                            int *nu_dev);
+
+/* Physical device bytes held by resident tensors after repacking (the logical
+ * figure is coli_cuda_stats). */
+size_t coli_cuda_physical_bytes(int device);
+
+/* Timing of the most recent layer/group call on a device, measured with CUDA
+ * events on the backend's stream: kernel-only milliseconds and the number of
+ * kernel launches it made. Returns 0 if nothing was recorded. */
+int coli_cuda_last_timing(int device, float *kernel_ms, int *launches);
+/* Enables (1) or disables (0) that per-call event timing; off by default. */
+void coli_cuda_set_timing(int enabled);
+
+/* The backend's stream for a device as a cudaStream_t cast to void* (so that
+ * callers can order their own work or time with events), or NULL. */
+void *coli_cuda_stream(int device);
+
+/* Sticky error state of the device-side wait guards: 0 = none. Every bounded
+ * wait in the kernels (mbarrier polls) records a code here instead of spinning
+ * forever; the call that observed it returns 0. */
+int coli_cuda_kernel_status(int device);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* COLI_CUDA_B200_H */

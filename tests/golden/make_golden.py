@@ -1,0 +1,67 @@
+"""Generates tests/golden/ref_vectors.npz from the reference's own CPU kernels.
+
+Run in a container that has the reference checkout (so that oracle/_ref builds):
+    python tests/golden/make_golden.py
+It feeds seeded inputs through oracle/_ref/libcoli_ref_cpu.so (the reference's
+c/quant.h compiled unchanged) and stores inputs and outputs. The CPU tests then
+hold the restated oracle to these vectors on machines without the reference.
+"""
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+
+from colibri_b200.quant import quantize  # noqa: E402
+from oracle.oracle import RefCpu, build  # noqa: E402
+
+CASES = [  # name, fmt, gs, S, I, O  (shapes of c/tests/test_i4_grouped.c and test_mxfp4_cuda.cu)
+    ("g64_multiple", 4, 64, 2, 512, 8), ("g64_partial_200", 4, 64, 2, 200, 4),
+    ("g64_odd_201", 4, 64, 2, 201, 4), ("g16_odd_33", 4, 16, 1, 33, 2),
+    ("g128_gt_I", 4, 128, 1, 64, 4), ("g32_batch8", 4, 32, 8, 320, 6),
+    ("row_int4", 2, 0, 3, 130, 5), ("row_int8", 1, 0, 2, 96, 7), ("f32", 0, 0, 2, 64, 5),
+    ("mx_64", 7, 0, 1, 64, 32), ("mx_batch", 7, 0, 4, 128, 64), ("mx_wide", 7, 0, 1, 2048, 16),
+    ("mx_96", 7, 0, 1, 96, 8),
+]
+
+
+def main():
+    build()
+    ref = RefCpu()
+    out = {}
+    for i, (name, fmt, gs, S, I, O) in enumerate(CASES):
+        rng = np.random.default_rng(1000 + i)
+        w = (rng.standard_normal((O, I)) * 0.05).astype(np.float32)
+        if fmt == 7:
+            t = quantize(w, 7)
+            t.s = (110 + rng.integers(0, 30, size=t.s.shape)).astype(np.uint8)
+        else:
+            t = quantize(w, fmt, gs)
+        x = ((rng.integers(0, 2001, size=(S, I)) - 1000) / 1000.0).astype(np.float32)
+        y = ref.matmul(x, t)
+        out[name + ".w"] = t.w
+        if t.s is not None:
+            out[name + ".s"] = t.s
+        out[name + ".x"] = x
+        out[name + ".y"] = y
+        out[name + ".meta"] = np.array([fmt, gs, S, I, O], np.int32)
+    # fused expert: gate/up/down through the reference kernels + its SwiGLU expression
+    rng = np.random.default_rng(77)
+    D, I = 256, 128
+    g = quantize((rng.standard_normal((I, D)) * 0.02).astype(np.float32), 4, 32)
+    u = quantize((rng.standard_normal((I, D)) * 0.02).astype(np.float32), 4, 32)
+    d = quantize((rng.standard_normal((D, I)) * 0.02).astype(np.float32), 4, 32)
+    x = rng.standard_normal((3, D)).astype(np.float32)
+    for nm, t in (("g", g), ("u", u), ("d", d)):
+        out["mlp." + nm + ".w"] = t.w
+        out["mlp." + nm + ".s"] = t.s
+    out["mlp.x"] = x
+    out["mlp.y"] = ref.expert_mlp(x, g, u, d)
+    np.savez_compressed(os.path.join(os.path.dirname(os.path.abspath(__file__)), "ref_vectors.npz"), **out)
+    print("wrote", len(out), "arrays")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,136 @@
+"""Conformance with the reference's API-level CUDA test
+(c/tests/test_backend_cuda.cu), restated call for call through the C ABI:
+known answers per format, cached tensors with released host pointers, graceful
+upload failures, the fault-injection hook, tensor_update, the identity expert,
+sync == async for a packed int4 group, group statistics and exact accounting.
+Attention and fmt=6 steps of that test are outside this backend's path."""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+X = np.array([1, -2, 3, -4, 2, 1, -1, 0.5], np.float32)
+
+
+def close(a, b):
+    return np.all(np.abs(np.asarray(a, np.float64).ravel() - np.asarray(b, np.float64).ravel()) <= 1e-4)
+
+
+def test_reference_conformance_sequence(be):
+    assert be.device_count() == 1
+    assert be.stats_tuple(-1) == (0, 0)
+    d0 = 0
+    q8 = np.array([1, 2, 3, 4, -1, 2, -3, 4], np.int8)
+    s8 = np.array([0.5, 2.0], np.float32)
+    want8 = [-5.0, -60.0, 1.5, 10.0]
+    t8 = be.upload(q8, s8, 1, 4, 2, d0)
+    assert t8
+    h = C.c_void_p(t8)
+    assert be.tensor_upload(C.byref(h), q8.ctypes.data, s8.ctypes.data, 1, 5, 2, d0) == 0   # shape mismatch
+    box = [t8]
+    ok, got = be.run_matmul(box, X.reshape(2, 4), q8, s8, 1, 4, 2, d0)
+    assert ok and close(got, want8)
+    for _ in range(64):   # cached tensor stays callable with NULL host pointers
+        ok, got = be.run_matmul(box, X.reshape(2, 4), None, None, 1, 4, 2, d0)
+        assert ok and close(got, want8)
+    # upload from a temporary buffer that is scribbled afterwards
+    tmpw, tmps = q8.copy(), s8.copy()
+    tt = be.upload(tmpw, tmps, 1, 4, 2, d0)
+    tmpw[:] = 99
+    del tmpw, tmps
+    ok, got = be.run_matmul([tt], X.reshape(2, 4), None, None, 1, 4, 2, d0)
+    assert ok and close(got, want8)
+    be.tensor_free(tt)
+    # graceful failures leave accounting untouched and do not poison the next launch
+    c0 = be.stats_tuple(-1)
+    assert be.upload(q8, s8, 1, 4, 2, 9999) is None
+    assert be.upload(q8, s8, 99, 4, 2, d0) is None
+    assert be.upload(q8, None, 1, 4, 2, d0) is None
+    assert be.upload(None, s8, 1, 4, 2, d0) is None
+    assert be.upload(q8, s8, 1, 1 << 20, 1 << 24, d0) is None          # ~16 TB
+    assert be.stats_tuple(-1) == c0
+    w7 = np.zeros((4, 32), np.uint8)
+    s7 = np.full((4, 2), 127, np.uint8)
+    t7 = be.upload(w7, s7, 7, 64, 4, d0)
+    assert t7
+    be.tensor_free(t7)
+    ok, got = be.run_matmul(box, X.reshape(2, 4), None, None, 1, 4, 2, d0)
+    assert ok and close(got, want8)
+    # fault injection hook
+    os.environ["COLI_GPU_FAIL_AFTER"] = "0"
+    try:
+        ok, _ = be.run_matmul(box, X.reshape(2, 4), None, None, 1, 4, 2, d0)
+        assert ok == 0
+    finally:
+        del os.environ["COLI_GPU_FAIL_AFTER"]
+    ok, got = be.run_matmul(box, X.reshape(2, 4), None, None, 1, 4, 2, d0)
+    assert ok and close(got, want8)
+    q8b = np.array([-1, -2, -3, -4, 1, -2, 3, -4], np.int8)
+    s8b = np.array([1.0, 0.5], np.float32)
+    assert be.tensor_update(t8, q8b.ctypes.data, s8b.ctypes.data)
+    ok, got = be.run_matmul(box, X.reshape(2, 4), q8b, s8b, 1, 4, 2, d0)
+    assert ok and close(got, [10.0, 15.0, -3.0, -2.5])
+
+    q4 = np.array([0x70, 0xf8, 0xa9, 0xcb], np.uint8)
+    s4 = np.array([1.0, 0.25], np.float32)
+    b4 = [None]
+    ok, got = be.run_matmul(b4, X[:4].reshape(1, 4), q4, s4, 2, 4, 2, d0)
+    assert ok and close(got, [-34.0, -2.5])
+    q2 = np.array([0xe4, 0x1b], np.uint8)
+    s2 = np.array([0.5, 2.0], np.float32)
+    b2 = [None]
+    ok, got = be.run_matmul(b2, X[:4].reshape(1, 4), q2, s2, 3, 4, 2, d0)
+    assert ok and close(got, [-2.0, 12.0])
+    wf = np.array([1, 0, -1, 2, 0.5, 0.5, 0.5, 0.5], np.float32)
+    bf = [None]
+    ok, got = be.run_matmul(bf, X[:4].reshape(1, 4), wf, None, 0, 4, 2, d0)
+    assert ok and close(got, [-10.0, -1.0])
+    # fmt=4 without a group size is refused (c/backend_cuda.cu:1359)
+    ok, _ = be.run_matmul([None], X[:4].reshape(1, 4), q4, s4, 4, 4, 2, d0, 0)
+    assert ok == 0
+
+    eg = np.array([1, 0, 0, 0, 0, 1, 0, 0], np.float32)
+    ed = np.array([1, 0, 0, 1, 1, 1, 1, -1], np.float32)
+    tg, tu, td = be.upload(eg, None, 0, 4, 2, d0), be.upload(eg, None, 0, 4, 2, d0), be.upload(ed, None, 0, 2, 4, d0)
+    want = []
+    for s in range(2):
+        a, b = float(X[s * 4]), float(X[s * 4 + 1])
+        a = (a / (1 + np.exp(-a))) * a
+        b = (b / (1 + np.exp(-b))) * b
+        want += [a, b, a + b, a - b]
+    ok, y = be.run_expert_mlp(tg, tu, td, X.reshape(2, 4), 4)
+    assert ok and close(y, want)
+    ok, y = be.run_expert_group([tg, tg], [tu, tu], [td, td], [1, 1], X.reshape(2, 4), 4)
+    assert ok and close(y, want)
+    # attention is not offloaded: the interface's refusal
+    assert be.attention_absorb(None, None, None, None, None, 1, 2, 2, 2, 4, 3, C.c_float(1.0)) == 0
+
+    # packed s4: sync vs issue/take, bitwise
+    w4 = np.zeros(32 * 16, np.uint8)
+    for i in range(w4.size):
+        lo, hi = ((i % 15) - 7) & 15, (((i * 3) % 15) - 7) & 15
+        w4[i] = lo | (hi << 4)
+    ws4 = (0.01 + (np.arange(32) % 5) * 0.002).astype(np.float32)
+    gx4 = (np.sin((np.arange(64) + 1) * 0.17) * 2).astype(np.float32)
+    g4, u4, dd4 = (be.upload(w4, ws4, 2, 32, 32, d0) for _ in range(3))
+    ok, sync = be.run_expert_group([g4, g4], [u4, u4], [dd4, dd4], [1, 1], gx4.reshape(2, 32), 32)
+    assert ok
+    ok, asy = be.run_expert_group_async([g4, g4], [u4, u4], [dd4, dd4], [1, 1], gx4.reshape(2, 32), 32)
+    assert ok and np.array_equal(sync.view(np.uint32), asy.view(np.uint32))
+    ok, again = be.run_expert_group([g4, g4], [u4, u4], [dd4, dd4], [1, 1], gx4.reshape(2, 32), 32)
+    assert ok and np.array_equal(sync.view(np.uint32), again.view(np.uint32))
+    for t in (g4, u4, dd4):
+        be.tensor_free(t)
+    calls, experts, rows = be.group_stats_tuple()[:3]
+    assert (calls, experts, rows) == (4, 8, 8)
+
+    assert be.stats_tuple(-1) == (7, 166)   # 16+12+10+32+32+32+32
+    assert be.stats_tuple(d0) == (7, 166)
+    assert be.tensor_device(t8) == d0 and be.tensor_device(None) == -1 and be.tensor_bytes(None) == 0
+    for t in (t8, b4[0], b2[0], bf[0], tg, tu, td):
+        be.tensor_free(t)
+    assert be.stats_tuple(-1) == (0, 0)
+    assert be.physical_bytes(-1) == 0

@@ -1,0 +1,50 @@
+"""Shared helpers of the parity tests."""
+import numpy as np
+
+from oracle.oracle import HostLayer
+
+
+def host_layer(cfg, L, routed_scale=1.0, topp=0.0, order=1, with_router=False):
+    return HostLayer(cfg["D"], cfg["I"], cfg["E"], cfg["K"], L.gate, L.up, L.down, cfg["gating"],
+                     cfg["norm_topk"], routed_scale, topp, order,
+                     L.router_w if with_router else None, L.router_bias, L.shared)
+
+
+def ref_style_close(got, want, rel=1e-3, floor=1e-3):
+    """|got-want| <= rel*(|want|+floor): the criterion of the reference's own
+    grouped-int4 CUDA test (c/tests/test_grouped_g4_cuda.cu:101)."""
+    got = np.asarray(got, np.float64)
+    want = np.asarray(want, np.float64)
+    return np.abs(got - want) <= rel * (np.abs(want) + floor)
+
+
+def max_rel_err(got, want):
+    """max |got-want| / max(|want|, 1e-3*rms(want)): relative error with a floor
+    that keeps cancellation-to-zero outputs from dominating."""
+    got = np.asarray(got, np.float64)
+    want = np.asarray(want, np.float64)
+    rms = float(np.sqrt(np.mean(want * want))) if want.size else 0.0
+    den = np.maximum(np.abs(want), 1e-3 * rms + 1e-30)
+    return float(np.max(np.abs(got - want) / den)) if want.size else 0.0
+
+
+def upload_qt(be, t, device=0):
+    h = be.upload(t.w, t.s, t.fmt, t.I, t.O, device, t.gs)
+    assert h, f"upload refused fmt={t.fmt} I={t.I} O={t.O} gs={t.gs}"
+    return h
+
+
+def upload_layer(be, L, device=0):
+    g = [upload_qt(be, t, device) for t in L.gate]
+    u = [upload_qt(be, t, device) for t in L.up]
+    d = [upload_qt(be, t, device) for t in L.down]
+    sh = None
+    if L.shared is not None:
+        sh = tuple(upload_qt(be, t, device) for t in L.shared)
+    return g, u, d, sh
+
+
+def free_layer(be, handles):
+    g, u, d, sh = handles
+    for h in list(g) + list(u) + list(d) + (list(sh) if sh else []):
+        be.tensor_free(h)

@@ -1,0 +1,431 @@
+#!/usr/bin/env python
+"""Benchmark of the MoE expert-FFN hot path.
+
+Workload `c2_decode` (default): the isolated MoE layer op at OLMoE shapes
+(hidden 2048, 64 experts, top-8 softmax routing, SwiGLU intermediate 1024, int4
+group-32 experts with fp16-valued scales) for M decode rows (default 1), run
+through L=16 distinct layers per step, as one decoded token passes the 16 MoE
+layers of OLMoE-1B-7B. A step touches L x (distinct experts) x 3.54 MB, well
+above the 126 MB L2, so no explicit L2 flush is needed.
+
+Metric: achieved HBM GB/s of the expert FFN = algorithmic bytes of a step
+(weights + scales of every distinct routed expert read once, plus activations
+in and out) / step time.
+
+  value     device-resident: inputs already in HBM, coli_cuda_moe_layer_dev,
+            CUDA events on the backend's stream.
+  e2e       the same steps through coli_cuda_moe_layer with HOST buffers: every
+            layer call copies its input rows and router logits to the device
+            and its output rows back.
+  roofline  for the dominant kernel (the streaming dequant GEMV): algorithmic
+            weight bytes of its launches / their summed event-bracketed time,
+            against the measured copy bandwidth in MEASURED_PEAKS.json.
+  cpu_baseline  the reference's own CPU kernels (oracle/_ref, c/quant.h compiled
+            unchanged) on a bounded sample of the same steps, rank 0 only.
+
+`--impl reference` times that CPU implementation alone with the same metric.
+Multi-GPU (`--gpus N` under torchrun): the path has no exchange step at this
+configuration, so every rank decodes its own rows through its own replica
+(weak scaling); value = all ranks' bytes / max-over-ranks time.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from colibri_b200 import workloads as W  # noqa: E402
+from colibri_b200.quant import QTensor  # noqa: E402
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            d = json.load(open(p))
+            return float(d["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+# ---------------------------------------------------------------------------
+# synthetic weights, generated on the GPU with torch (fast) in the reference
+# converter's rules (colibri_b200.quant restates the same rules in numpy; the
+# two are compared in tests/test_gpu_bench_inputs.py)
+# ---------------------------------------------------------------------------
+def gen_int4_g32_torch(torch, E, O, I, seed, device):
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    w = torch.randn((E, O, I), generator=g, device=device, dtype=torch.float32) * 0.02
+    wr = w.view(E, O, I // 32, 32)
+    amax = wr.abs().amax(dim=3, keepdim=True)
+    s = torch.clamp(amax / 7.0, min=1e-8)
+    s = s.to(torch.float16).to(torch.float32).clamp(min=6e-8)
+    q = torch.clamp(torch.round(wr / s), -8, 7).to(torch.int32) + 8
+    q = q.view(E, O, I)
+    packed = (q[:, :, 0::2] | (q[:, :, 1::2] << 4)).to(torch.uint8)
+    return packed.cpu().numpy(), s.view(E, O * (I // 32)).cpu().numpy()
+
+
+def gen_layer_host(torch, cfg, seed, device):
+    """-> lists of QTensor (gate, up, down) for one layer."""
+    D, I, E = cfg["D"], cfg["I"], cfg["E"]
+    out = []
+    for k, (O, K) in enumerate(((I, D), (I, D), (D, I))):
+        pk, sc = gen_int4_g32_torch(torch, E, O, K, seed * 10 + k, device)
+        out.append([QTensor(pk[e], sc[e], 4, K, O, 32) for e in range(E)])
+    return out
+
+
+def expert_bytes_device(cfg):
+    """Algorithmic bytes of one expert as stored on the device: nibbles + fp16
+    scales for int4 g32 (4.5 bits per weight)."""
+    D, I = cfg["D"], cfg["I"]
+    per_w = 3 * D * I
+    return per_w // 2 + (per_w // 32) * 2
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled during the timed region."""
+
+    def __init__(self, index):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            f = [c.strip() for c in r.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0])); mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(sm)) if sm else None,
+                "sm_max_mhz": float(max(mx)) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def route_counts(oracle, logits, K, E):
+    idx, _, _ = oracle.route_softmax(logits, K, False)
+    return int(len(np.unique(idx)))
+
+
+# ---------------------------------------------------------------------------
+# CPU arm (reference kernels)
+# ---------------------------------------------------------------------------
+def cpu_step(ref, oracle, cfg, layers_host, xs, logits, layer_ids):
+    """One pass over `layer_ids` with the reference's CPU kernels in the engine's
+    per-expert order (c/colibri.c:4731-4786); returns the bytes it touched."""
+    K, E, D = cfg["K"], cfg["E"], cfg["D"]
+    nbytes = 0
+    eb = expert_bytes_device(cfg)
+    for li in layer_ids:
+        gate, up, down = layers_host[li]
+        x, lg = xs[li], logits[li]
+        idx, val, _ = oracle.route_softmax(lg, K, False)
+        uniq = oracle.union(idx, np.full(x.shape[0], K, np.int32), E)
+        out = np.zeros_like(x)
+        for e in uniq:
+            rows, col = np.nonzero(idx == e)
+            y = ref.expert_mlp(x[rows], gate[e], up[e], down[e])
+            out[rows] += val[rows, col][:, None] * y
+        nbytes += len(uniq) * eb + 2 * x.nbytes
+    return nbytes
+
+
+def run_reference_arm(args):
+    from oracle.oracle import Oracle, RefCpu
+    cfg = W.CONFIGS["c2"]
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    oracle = Oracle()
+    kind = "reference" if RefCpu.available() else "port"
+    ref = RefCpu() if RefCpu.available() else None
+    if ref is None:
+        class Port:   # the restated oracle as the CPU implementation
+            def expert_mlp(self, x, g, u, d): return oracle.expert_mlp(x, g, u, d)
+            def threads(self): return oracle.threads()
+        ref = Port()
+    L = args.layers
+    # bounded sample: only the experts a step routes to are generated (numpy, CPU)
+    M = args.M
+    xs = [W.activations(M, cfg["D"], 100 + li) for li in range(L)]
+    lgs = [W.router_logits(M, cfg["E"], 200 + li) for li in range(L)]
+    layers_host = []
+    for li in range(L):
+        idx, _, _ = oracle.route_softmax(lgs[li], cfg["K"], False)
+        need = set(np.unique(idx).tolist())
+        gate, up, down = {}, {}, {}
+        for e in need:
+            g, u, d = W.expert_weights(cfg["D"], cfg["I"], 4, 32, 9000 + li * 64 + e)
+            gate[e], up[e], down[e] = g, u, d
+        layers_host.append((gate, up, down))
+    ids = list(range(L))
+    for _ in range(args.warmup):
+        cpu_step(ref, oracle, cfg, layers_host, xs, lgs, ids)
+    t0 = time.perf_counter()
+    nbytes = 0
+    for _ in range(args.steps):
+        nbytes += cpu_step(ref, oracle, cfg, layers_host, xs, lgs, ids)
+    dt = time.perf_counter() - t0
+    gbs = nbytes / dt / 1e9
+    line = {
+        "metric": "moe_expert_ffn_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "impl": "reference",
+        "config": {"workload": f"c2_decode: OLMoE-shape MoE layer op, int4 g32, M={M}, {L} layers per step"},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": ref.threads(), "kind": kind,
+                         "sample": f"{args.steps} steps x {L} layers, routed experts only"},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------
+def run_gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+    from colibri_b200.backend import Backend, MoeLayer
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    cfg = W.CONFIGS["c2"]
+    D, I, E, K = cfg["D"], cfg["I"], cfg["E"], cfg["K"]
+    L, M = args.layers, args.M
+
+    be = Backend()
+    if be.init_devices((local,)) != 1:
+        raise RuntimeError("coli_cuda_init failed: the CUDA backend is required (no CPU fallback)")
+    layers, handles, host_keep = [], [], []
+    for li in range(L):
+        gate, up, down = gen_layer_host(torch, cfg, 1000 * (rank + 1) + li, dev)
+        hg = [be.upload(t.w, t.s, 4, t.I, t.O, local, 32) for t in gate]
+        hu = [be.upload(t.w, t.s, 4, t.I, t.O, local, 32) for t in up]
+        hd = [be.upload(t.w, t.s, 4, t.I, t.O, local, 32) for t in down]
+        if not all(hg + hu + hd):
+            raise RuntimeError("tensor upload failed")
+        handles.append((hg, hu, hd))
+        layers.append(MoeLayer(be, D, I, E, K, hg, hu, hd, 0, 0, max_rows=max(M, 8)))
+        if rank == 0 and li < args.cpu_layers:
+            host_keep.append((gate, up, down))
+        del gate, up, down
+    torch.cuda.synchronize()
+
+    xs = [W.activations(M, D, 100 + li + 1000 * rank) for li in range(L)]
+    lgs = [W.router_logits(M, E, 200 + li + 1000 * rank) for li in range(L)]
+    from oracle.oracle import Oracle   # routing counts for the byte accounting only
+    orc = Oracle()
+    nus = [route_counts(orc, lgs[li], K, E) for li in range(L)]
+    eb = expert_bytes_device(cfg)
+    act_bytes = 2 * M * D * 4
+    step_bytes = sum(nu * eb + act_bytes for nu in nus)
+    weight_bytes_step = sum(nu * eb for nu in nus)
+
+    stream = torch.cuda.ExternalStream(be.stream(local), device=dev)
+    x_dev = [torch.from_numpy(x).to(dev) for x in xs]
+    lg_dev = [torch.from_numpy(l).to(dev) for l in lgs]
+    out_dev = [torch.empty((M, D), device=dev, dtype=torch.float32) for _ in range(L)]
+    torch.cuda.synchronize()
+
+    def step_dev():
+        for li in range(L):
+            ok = be.moe_layer_dev(layers[li].handle, out_dev[li].data_ptr(), x_dev[li].data_ptr(),
+                                  lg_dev[li].data_ptr(), M, None, None, None)
+            if not ok:
+                raise RuntimeError("coli_cuda_moe_layer_dev failed")
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident value ----------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        step_dev()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        step_dev()
+    e1.record(stream)
+    barrier()
+    ms = e0.elapsed_time(e1)
+    launches = 0
+    lt_ms, lt_n = C.c_float(), C.c_int()
+    be.set_timing(1)
+    step_dev()
+    torch.cuda.synchronize()
+    be.set_timing(0)
+    be.last_timing(local, C.byref(lt_ms), C.byref(lt_n))
+    launches = lt_n.value * L * args.steps
+    if be.kernel_status(local) != 0:
+        raise RuntimeError("a kernel wait guard expired")
+
+    # ---- dominant kernel, event-bracketed -----------------------------------
+    be.set_kernel_events(1)
+    for _ in range(args.steps):
+        step_dev()
+    k_ms, k_n = C.c_float(), C.c_int()
+    be.kernel_events(local, C.byref(k_ms), C.byref(k_n))
+    be.set_kernel_events(0)
+    if rank == 0:
+        clocks = sampler.stop()
+
+    # ---- e2e through the host-buffer call -------------------------------------
+    def step_host():
+        for li in range(L):
+            layers[li](xs[li], lgs[li], want_route=False)
+    for _ in range(max(args.warmup, 3)):
+        step_host()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step_host()
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+
+    tmax = torch.tensor([ms, e2e_s * 1e3], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        tot = torch.tensor([float(step_bytes)], device=dev, dtype=torch.float64)
+        dist.all_reduce(tot, op=dist.ReduceOp.SUM)
+        all_bytes = float(tot.item())
+    else:
+        all_bytes = float(step_bytes)
+    ms_all, e2e_ms_all = float(tmax[0].item()), float(tmax[1].item())
+
+    if rank == 0:
+        peak, which = measured_peaks()
+        value = all_bytes * args.steps / (ms_all * 1e-3) / 1e9
+        e2e = all_bytes * args.steps / (e2e_ms_all * 1e-3) / 1e9
+        ach = (weight_bytes_step * args.steps) / (k_ms.value * 1e-3) / 1e9 if k_ms.value > 0 else None
+        # CPU baseline on a bounded sample (first cpu_layers layers of the step)
+        cpu = None
+        try:
+            from oracle.oracle import RefCpu
+            ref = RefCpu() if RefCpu.available() else None
+            kind = "reference" if ref else "port"
+            if ref is None:
+                class Port:
+                    def expert_mlp(self, x, g, u, d): return orc.expert_mlp(x, g, u, d)
+                    def threads(self): return orc.threads()
+                ref = Port()
+            ids = list(range(len(host_keep)))
+            cpu_step(ref, orc, cfg, host_keep, xs, lgs, ids)
+            t0 = time.perf_counter()
+            nb, reps = 0, 0
+            while time.perf_counter() - t0 < args.cpu_seconds:
+                nb += cpu_step(ref, orc, cfg, host_keep, xs, lgs, ids)
+                reps += 1
+            dt = time.perf_counter() - t0
+            cpu = {"value": nb / dt / 1e9, "unit": "GB/s", "cores": ref.threads(), "kind": kind,
+                   "sample": f"{reps} passes over the first {len(ids)} of {L} layers, {dt:.1f} s"}
+        except Exception as ex:   # the baseline is reported, never required
+            cpu = {"value": None, "unit": "GB/s", "cores": 0, "kind": "port", "sample": f"failed: {ex}"}
+        line = {
+            "metric": "moe_expert_ffn_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_all / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": f"c2_decode: OLMoE-shape MoE layer op (D={D}, I={I}, E={E}, top-{K} softmax), "
+                                   f"int4 g32 fp16-valued scales, M={M} rows, {L} distinct layers per step",
+                       "l2": f"{L} distinct layers, {weight_bytes_step / 1e6:.0f} MB of weights touched per step "
+                             f"(> 126 MB L2); no flush needed",
+                       "bytes_per_step": step_bytes, "distinct_experts_per_layer": nus,
+                       "vs_8tbs_nominal": value / world / 8000.0},
+            "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": L * (M * D * 4 + M * E * 4),
+                    "d2h_bytes_per_step": L * M * D * 4, "ms_per_step": e2e_ms_all / args.steps},
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s",
+                         "frac": (ach / peak) if ach else None, "traffic": None,
+                         "kernel": "k_gemv_stream", "launches": k_n.value,
+                         "avg_launch_us": (k_ms.value / k_n.value * 1e3) if k_n.value else None,
+                         "peak_source": which},
+            "cpu_baseline": cpu,
+        }
+        print(json.dumps(line), flush=True)
+    for lay in layers:
+        lay.free()
+    for hg, hu, hd in handles:
+        for t in hg + hu + hd:
+            be.tensor_free(t)
+    be.shutdown()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--M", type=int, default=1, help="rows per layer call")
+    ap.add_argument("--layers", type=int, default=16)
+    ap.add_argument("--cpu-layers", type=int, default=4, help="layers kept on the host for the CPU baseline sample")
+    ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -43,6 +43,8 @@ struct DeviceCtx {
     float last_ms = 0.f;
     int last_launches = 0;
     int have_timing = 0;
+    std::vector<cudaEvent_t> *kev = nullptr;   // per-launch event pairs of the streaming GEMV
+    int kev_used = 0;
     uint64_t g_calls = 0, g_experts = 0, g_rows = 0;
     double g_h2d = 0, g_kern = 0, g_d2h = 0;
 };
@@ -190,6 +192,7 @@ extern "C" void coli_cuda_shutdown(void) {
         if (c->ev0) cudaEventDestroy(c->ev0);
         if (c->ev1) cudaEventDestroy(c->ev1);
         if (c->ev_done) cudaEventDestroy(c->ev_done);
+        if (c->kev) { for (cudaEvent_t e : *c->kev) cudaEventDestroy(e); delete c->kev; c->kev = nullptr; }
         if (c->stream) cudaStreamDestroy(c->stream);
         (void)cudaGetLastError();
         *c = DeviceCtx();
@@ -426,15 +429,51 @@ static void launch_mode(DeviceCtx *c, int nc, const GemvSeg *segs, const GemvCtl
     default: launch_one<MODE, 8>(c, segs, ctl, bq, bs); break;
     }
 }
+static int g_kernel_events = 0;   // 1: bracket every streaming-GEMV launch with an event pair
+#define KEV_MAX_PAIRS 8192
 static void launch_gemv(DeviceCtx *c, int mode, int nc, const GemvSeg *segs, const GemvCtl *ctl,
                         const __half *bq, const float *bs) {
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    if (g_kernel_events && c->kev_used < KEV_MAX_PAIRS) {
+        if (!c->kev) c->kev = new std::vector<cudaEvent_t>();
+        while ((int)c->kev->size() < 2 * (c->kev_used + 1)) {
+            cudaEvent_t e;
+            if (cudaEventCreate(&e) != cudaSuccess) { (void)cudaGetLastError(); break; }
+            c->kev->push_back(e);
+        }
+        if ((int)c->kev->size() >= 2 * (c->kev_used + 1)) {
+            e0 = (*c->kev)[2 * c->kev_used]; e1 = (*c->kev)[2 * c->kev_used + 1];
+            c->kev_used++;
+        }
+    }
+    if (e0) cudaEventRecord(e0, c->stream);
     switch (mode) {
     case SC_ROW: launch_mode<SC_ROW>(c, nc, segs, ctl, bq, bs); break;
     case SC_H16: launch_mode<SC_H16>(c, nc, segs, ctl, bq, bs); break;
     case SC_F32: launch_mode<SC_F32>(c, nc, segs, ctl, bq, bs); break;
     default: launch_mode<SC_MX>(c, nc, segs, ctl, bq, bs); break;
     }
+    if (e1) cudaEventRecord(e1, c->stream);
     c->last_launches++;
+}
+extern "C" void coli_cuda_set_kernel_events(int enabled) {
+    g_kernel_events = enabled ? 1 : 0;
+    for (int i = 0; i < g_nctx; i++) g_ctx[i].kev_used = 0;
+}
+extern "C" int coli_cuda_kernel_events(int device, float *total_ms, int *launches) {
+    DeviceCtx *c = find_ctx(device);
+    if (!select_ctx(c)) return 0;
+    if (!cuda_ok(cudaStreamSynchronize(c->stream), "synchronize")) return 0;
+    float tot = 0.f;
+    for (int i = 0; i < c->kev_used; i++) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, (*c->kev)[2 * i], (*c->kev)[2 * i + 1]) == cudaSuccess) tot += ms;
+        else (void)cudaGetLastError();
+    }
+    if (total_ms) *total_ms = tot;
+    if (launches) *launches = c->kev_used;
+    c->kev_used = 0;
+    return 1;
 }
 
 // column sets (4 rows each) per pass for a given largest row count

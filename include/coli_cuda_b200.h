@@ -222,6 +222,13 @@ int coli_cuda_last_timing(int device, float *kernel_ms, int *launches);
 /* Enables (1) or disables (0) that per-call event timing; off by default. */
 void coli_cuda_set_timing(int enabled);
 
+/* Per-kernel timing of the dominant kernel: while enabled, every launch of the
+ * streaming GEMV is bracketed by a CUDA event pair on the backend's stream.
+ * coli_cuda_kernel_events synchronises, returns the summed duration and the
+ * number of launches since the last query, and clears the list. */
+void coli_cuda_set_kernel_events(int enabled);
+int coli_cuda_kernel_events(int device, float *total_ms, int *launches);
+
 /* The backend's stream for a device as a cudaStream_t cast to void* (so that
  * callers can order their own work or time with events), or NULL. */
 void *coli_cuda_stream(int device);

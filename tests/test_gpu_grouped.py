@@ -37,7 +37,10 @@ def run_case(be, oracle, experts, rows, D, seed, check_async=True):
     off = 0
     for e, r in zip(experts, rows):
         want = oracle.expert_mlp(x[off:off + r], *e)
-        good = ref_style_close(y[off:off + r], want)
+        # int4: the reference test's own criterion. MXFP4 with random exponents spans
+        # many orders of magnitude, so its absolute floor scales with the row's range.
+        floor = 1e-3 if e[0].fmt != 7 else 1e-3 * float(np.abs(want).max())
+        good = ref_style_close(y[off:off + r], want, 1e-3, floor)
         assert good.all(), (np.abs(y[off:off + r] - want).max(), np.abs(want).max())
         off += r
     if check_async and total <= 8:

@@ -17,6 +17,7 @@
 #include "gemv_stream.cuh"
 #include "kernels_misc.cuh"
 #include "router.cuh"
+#include "moe_decode.cuh"
 
 // ---------------------------------------------------------------------------
 // Context
@@ -40,6 +41,8 @@ struct DeviceCtx {
     size_t host_x_cap = 0, host_y_cap = 0;
     int group_pending = 0;
     int *status = nullptr;                    // device int: sticky kernel status
+    unsigned long long *gridbar = nullptr;    // arrival counter of the fused decode kernel's grid barrier
+    unsigned long long epoch = 0;             // launches of that kernel since the counter was zeroed
     float last_ms = 0.f;
     int last_launches = 0;
     int have_timing = 0;
@@ -134,6 +137,11 @@ static void setup_mode() { setup_one<MODE, 1>(); setup_one<MODE, 2>(); setup_one
 
 extern "C" void coli_cuda_shutdown(void);
 
+static int decode_smem_bytes(int mode) {
+    return DEC_WARPS * DEC_NST * (chunk_bytes_of(mode) + 8) + (int)((sizeof(DecShared) + 15) & ~15) +
+           DEC_MAX_M * 2 * DEC_MAX_E * (int)sizeof(float);
+}
+
 extern "C" int coli_cuda_init(const int *devices, int count) {
     if (!devices || count < 1 || count > COLI_CUDA_MAX_DEVICES) return 0;
     if (g_nctx) coli_cuda_shutdown();
@@ -164,10 +172,14 @@ extern "C" int coli_cuda_init(const int *devices, int count) {
             !cuda_ok(cudaEventCreateWithFlags(&c->ev_done, cudaEventDisableTiming), "event") ||
             !cuda_ok(cudaMalloc((void **)&c->status, sizeof(int)), "status") ||
             !cuda_ok(cudaMemset(c->status, 0, sizeof(int)), "status") ||
+            !cuda_ok(cudaMalloc((void **)&c->gridbar, sizeof(unsigned long long)), "grid barrier") ||
+            !cuda_ok(cudaMemset(c->gridbar, 0, sizeof(unsigned long long)), "grid barrier") ||
             !cuda_ok(cudaMemcpyToSymbol(c_exp2_tab, tab, sizeof(tab)), "exp table")) {
             g_nctx = i + 1; coli_cuda_shutdown(); return 0;
         }
         setup_mode<SC_ROW>(); setup_mode<SC_H16>(); setup_mode<SC_F32>(); setup_mode<SC_MX>();
+        set_smem(k_moe_decode<SC_ROW>, decode_smem_bytes(SC_ROW)); set_smem(k_moe_decode<SC_H16>, decode_smem_bytes(SC_H16));
+        set_smem(k_moe_decode<SC_F32>, decode_smem_bytes(SC_F32)); set_smem(k_moe_decode<SC_MX>, decode_smem_bytes(SC_MX));
         if (!cuda_ok(cudaGetLastError(), "kernel attributes")) { g_nctx = i + 1; coli_cuda_shutdown(); return 0; }
     }
     g_nctx = count;
@@ -189,6 +201,7 @@ extern "C" void coli_cuda_shutdown(void) {
         if (c->host_x) cudaFreeHost(c->host_x);
         if (c->host_y) cudaFreeHost(c->host_y);
         if (c->status) cudaFree(c->status);
+        if (c->gridbar) cudaFree(c->gridbar);
         if (c->ev0) cudaEventDestroy(c->ev0);
         if (c->ev1) cudaEventDestroy(c->ev1);
         if (c->ev_done) cudaEventDestroy(c->ev_done);
@@ -431,21 +444,22 @@ static void launch_mode(DeviceCtx *c, int nc, const GemvSeg *segs, const GemvCtl
 }
 static int g_kernel_events = 0;   // 1: bracket every streaming-GEMV launch with an event pair
 #define KEV_MAX_PAIRS 8192
+static void kernel_event_pair(DeviceCtx *c, cudaEvent_t *e0, cudaEvent_t *e1) {
+    *e0 = *e1 = nullptr;
+    if (!g_kernel_events || c->kev_used >= KEV_MAX_PAIRS) return;
+    if (!c->kev) c->kev = new std::vector<cudaEvent_t>();
+    while ((int)c->kev->size() < 2 * (c->kev_used + 1)) {
+        cudaEvent_t e;
+        if (cudaEventCreate(&e) != cudaSuccess) { (void)cudaGetLastError(); return; }
+        c->kev->push_back(e);
+    }
+    *e0 = (*c->kev)[2 * c->kev_used]; *e1 = (*c->kev)[2 * c->kev_used + 1];
+    c->kev_used++;
+}
 static void launch_gemv(DeviceCtx *c, int mode, int nc, const GemvSeg *segs, const GemvCtl *ctl,
                         const __half *bq, const float *bs) {
     cudaEvent_t e0 = nullptr, e1 = nullptr;
-    if (g_kernel_events && c->kev_used < KEV_MAX_PAIRS) {
-        if (!c->kev) c->kev = new std::vector<cudaEvent_t>();
-        while ((int)c->kev->size() < 2 * (c->kev_used + 1)) {
-            cudaEvent_t e;
-            if (cudaEventCreate(&e) != cudaSuccess) { (void)cudaGetLastError(); break; }
-            c->kev->push_back(e);
-        }
-        if ((int)c->kev->size() >= 2 * (c->kev_used + 1)) {
-            e0 = (*c->kev)[2 * c->kev_used]; e1 = (*c->kev)[2 * c->kev_used + 1];
-            c->kev_used++;
-        }
-    }
+    kernel_event_pair(c, &e0, &e1);
     if (e0) cudaEventRecord(e0, c->stream);
     switch (mode) {
     case SC_ROW: launch_mode<SC_ROW>(c, nc, segs, ctl, bq, bs); break;
@@ -483,7 +497,7 @@ static int pick_nc(int max_rows) { return max_rows <= 4 ? 1 : max_rows <= 8 ? 2 
 // least two blocks per task so that the copy pipeline stays primed, and a
 // divisor of the block count.
 static int pick_nkpart(int nkb, long base_tasks, int sms) {
-    long want = ((long)sms * 24 + base_tasks - 1) / (base_tasks > 0 ? base_tasks : 1);
+    long want = ((long)sms * 13 + base_tasks - 1) / (base_tasks > 0 ? base_tasks : 1);
     int cap = nkb >= 2 ? nkb / 2 : 1;
     if (want > cap) want = cap;
     if (want < 1) want = 1;
@@ -509,6 +523,7 @@ static void timing_collect(DeviceCtx *c) {   // after a stream synchronize
 struct HostSegs {
     std::vector<GemvSeg> v[4];   // by scale mode
     int ntask[4] = {0, 0, 0, 0};
+    int uniform[4] = {0, 0, 0, 0};   // tasks per segment when all segments of a mode agree, else -1
 };
 
 static void add_seg(HostSegs *hs, const ColiCudaTensor *t, float *out, const int *rowid, int nrows,
@@ -521,7 +536,10 @@ static void add_seg(HostSegs *hs, const ColiCudaTensor *t, float *out, const int
     s.O = t->O; s.ntiles = t->O / TILE_ROWS; s.nkb = t->I / BLOCK_K;
     s.nkpart = nkpart; s.kb_per_part = s.nkb / nkpart;
     s.task0 = hs->ntask[t->mode];
-    hs->ntask[t->mode] += s.ntiles * nkpart;
+    const int nt = s.ntiles * nkpart;
+    if (hs->uniform[t->mode] == 0) hs->uniform[t->mode] = nt;
+    else if (hs->uniform[t->mode] != nt) hs->uniform[t->mode] = -1;
+    hs->ntask[t->mode] += nt;
     hs->v[t->mode].push_back(s);
 }
 
@@ -548,7 +566,8 @@ static int run_host_segs(DeviceCtx *c, HostSegs *hs, Buf *segbuf, int ctl_slot, 
         size_t b = hs->v[m].size() * sizeof(GemvSeg);
         if (b) std::memcpy(hp + off, hs->v[m].data(), b);
         off += b;
-        ctl[m].nseg = (int)hs->v[m].size(); ctl[m].ntask = hs->ntask[m]; ctl[m].npos = npos; ctl[m].pad = 0;
+        ctl[m].nseg = (int)hs->v[m].size(); ctl[m].ntask = hs->ntask[m]; ctl[m].npos = npos;
+        ctl[m].tasks_per_seg = hs->uniform[m] > 0 ? hs->uniform[m] : 0;
     }
     std::memcpy(hp + seg_bytes, ctl, sizeof(ctl));
     if (!cuda_ok(cudaMemcpyAsync(dp, hp, need, cudaMemcpyHostToDevice, c->stream), "segment upload")) return 0;
@@ -603,6 +622,9 @@ static int check_status(DeviceCtx *c) {
     if (!cuda_ok(cudaStreamSynchronize(c->stream), "synchronize")) return 0;
     if (v) {
         std::fprintf(stderr, "[CUDA] kernel wait guard expired (status %d)\n", v);
+        // the grid barrier's arrival count is no longer a multiple of the grid: start over
+        cudaMemsetAsync(c->gridbar, 0, sizeof(unsigned long long), c->stream);
+        c->epoch = 0;
         return 0;
     }
     return 1;

@@ -83,7 +83,8 @@ struct GemvSeg {
 
 // Control block of one GEMV launch (device memory).
 struct GemvCtl {
-    int nseg, ntask, npos, pad;
+    int nseg, ntask, npos;
+    int tasks_per_seg;   // > 0 when every segment has this many tasks (then seg = task / tasks_per_seg)
 };
 
 #define KSTAT_MBAR_TIMEOUT 1

@@ -139,9 +139,9 @@ __device__ __forceinline__ int find_seg(const GemvSeg *segs, int nseg, int task)
 }
 
 template <int CH>
-__device__ __forceinline__ void task_setup(TaskPos &p, const GemvSeg *segs, int nseg, int &seg_i,
+__device__ __forceinline__ void task_setup(TaskPos &p, const GemvSeg *segs, int nseg, int tps, int &seg_i,
                                            int &tile, int &kpart) {
-    seg_i = find_seg(segs, nseg, p.task);
+    seg_i = tps > 0 ? p.task / tps : find_seg(segs, nseg, p.task);
     const GemvSeg &s = segs[seg_i];
     int local = p.task - s.task0;
     kpart = local / s.ntiles;
@@ -168,7 +168,7 @@ k_gemv_stream(const GemvSeg *__restrict__ segs, const GemvCtl *__restrict__ ctl,
     }
     __syncwarp();
 
-    const int nseg = ctl->nseg, ntask = ctl->ntask, npos = ctl->npos;
+    const int nseg = ctl->nseg, ntask = ctl->ntask, npos = ctl->npos, tps = ctl->tasks_per_seg;
     const int P = gridDim.x * WARPS;
     const int p0 = blockIdx.x * WARPS + warp;
 
@@ -176,7 +176,7 @@ k_gemv_stream(const GemvSeg *__restrict__ segs, const GemvCtl *__restrict__ ctl,
     TaskPos prod;
     prod.task = p0;
     int dummy_a, dummy_b, dummy_c;
-    if (prod.task < ntask) task_setup<CH>(prod, segs, nseg, dummy_a, dummy_b, dummy_c);
+    if (prod.task < ntask) task_setup<CH>(prod, segs, nseg, tps, dummy_a, dummy_b, dummy_c);
     int issued = 0;
     auto issue_one = [&]() {
         if (prod.task >= ntask) return;
@@ -190,7 +190,7 @@ k_gemv_stream(const GemvSeg *__restrict__ segs, const GemvCtl *__restrict__ ctl,
         prod.ptr += CH;
         if (prod.kb == prod.kb_end) {
             prod.task += P;
-            if (prod.task < ntask) task_setup<CH>(prod, segs, nseg, dummy_a, dummy_b, dummy_c);
+            if (prod.task < ntask) task_setup<CH>(prod, segs, nseg, tps, dummy_a, dummy_b, dummy_c);
         }
     };
     for (int s = 0; s < NST; s++) issue_one();
@@ -202,7 +202,7 @@ k_gemv_stream(const GemvSeg *__restrict__ segs, const GemvCtl *__restrict__ ctl,
     bool failed = false;
     while (cons.task < ntask) {
         int seg_i, tile, kpart;
-        task_setup<CH>(cons, segs, nseg, seg_i, tile, kpart);
+        task_setup<CH>(cons, segs, nseg, tps, seg_i, tile, kpart);
         const GemvSeg &sg = segs[seg_i];
         const int nrows = sg.nrows, nkb = sg.nkb;
         // B operand: lane (g,t) supplies column g of each 8-column set: row

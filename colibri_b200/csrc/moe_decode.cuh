@@ -1,0 +1,540 @@
+// One MoE layer for a decode-sized batch (M <= 8 rows) as ONE persistent
+// cooperative kernel: route -> union -> activation prep -> gate/up GEMV ->
+// SwiGLU -> down GEMV -> weighted combine (+ shared expert).
+//
+// Why one kernel: at decode sizes a layer moves only tens of MB (28 MB for the
+// OLMoE shape at M=1, about 4 us of HBM time), so the drain/fill of every
+// kernel boundary costs as much as the work itself. Here the phases are
+// separated by grid-wide barriers instead, and the weight stream never stops:
+// before a CTA waits at a barrier its warps have already issued the bulk copies
+// of their first blocks of the NEXT phase (weights do not depend on the
+// activations), so HBM stays busy while the barrier and the small distributed
+// steps (activation split, SwiGLU, combine) run.
+//
+// Routing is computed redundantly by every CTA (top-8 of a few hundred scores
+// is a microsecond of work and saves a barrier plus a round trip through
+// global memory); its tables live in shared memory. CTA 0 writes idx/w/keff.
+//
+// The GEMV inner loop is the one of gemv_stream.cuh with one 8-column set
+// (4 rows per pass; an expert with more rows takes two passes).
+//
+// Grid barrier: an arrival counter in global memory that only grows; launch
+// number `epoch` waits for (epoch*NBAR + k + 1) * gridDim.x arrivals at its k-th
+// barrier. Every spin is bounded (about a second); on expiry the CTA records
+// KSTAT_GRID_TIMEOUT, drains its copies and returns. The kernel is launched
+// cooperatively so that all CTAs are co-resident.
+#pragma once
+#include "common.cuh"
+#include "gemv_stream.cuh"
+#include "kernels_misc.cuh"
+#include "router.cuh"
+
+#define KSTAT_GRID_TIMEOUT 2
+#define DEC_MAX_M 8
+#define DEC_MAX_E 256
+#define DEC_MAX_PASS 80          // <= 64 distinct experts + second passes + shared passes
+#define DEC_NBAR 4
+#define DEC_WARPS 16
+#define DEC_NST 4
+
+struct DecPass {
+    int e;            // expert id, or -1 for the shared expert
+    int rowid[4];     // token rows
+    int nrows, pos0;
+};
+
+struct DecodeArgs {
+    RouteRule rule;
+    LayerTables tab;
+    const float *x, *logits, *router_bias;
+    float *out;
+    int *idx_out; float *w_out; int *keff_out;
+    __half *xq; float *xs;            // [M][nkb1][256], [M][nkb1]
+    float *partG, *partU;             // [nkp1][npos][I]
+    __half *hq; float *hs;            // [npos][nkb2][256], [npos][nkb2]
+    float *partD;                     // [nkp2][npos][D]
+    unsigned long long *bar;
+    unsigned long long epoch;
+    int *status;
+    int M, nkp1, nkp2;
+};
+
+struct DecShared {
+    int idx[DEC_MAX_M * ROUTE_MAX_K];
+    float w[DEC_MAX_M * ROUTE_MAX_K];
+    int keff[DEC_MAX_M];
+    int pos_of[DEC_MAX_M * ROUTE_MAX_K];
+    int first[DEC_MAX_E], cnt[DEC_MAX_E], base[DEC_MAX_E], passbase[DEC_MAX_E];
+    int uniq[DEC_MAX_E];
+    DecPass pass[DEC_MAX_PASS];
+    int nu, npass, npos, shared_pos0, failed;
+};
+
+__device__ __forceinline__ uint4 ldg128(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+// All threads of the CTA call this. Returns false on timeout.
+__device__ __forceinline__ bool grid_barrier(unsigned long long *counter, unsigned long long target,
+                                             int *s_failed) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        atomicAdd(counter, 1ULL);
+        long long t0 = clock64();
+        for (;;) {
+            unsigned long long v;
+            asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(counter) : "memory");
+            if (v >= target) break;
+            if (clock64() - t0 > 2000000000LL) { *s_failed = 1; break; }
+        }
+        __threadfence();
+    }
+    __syncthreads();
+    return *s_failed == 0;
+}
+
+// One row of routing by one warp: the body of k_route_topk with shared-memory outputs.
+__device__ __forceinline__ void route_row_warp(const float *z, const float *bias, const RouteRule &rule,
+                                               float *score, float *choice, int *idx, float *wk,
+                                               int *keff, int lane) {
+    const int E = rule.E, K = rule.K;
+    if (rule.gating == 0) {
+        float m = -1e30f;
+        for (int e = lane; e < E; e += 32) { float v = z[e]; if (v > m) m = v; }
+#pragma unroll
+        for (int off = 16; off; off >>= 1) { float o = __shfl_xor_sync(0xffffffffu, m, off); if (o > m) m = o; }
+        for (int e = lane; e < E; e += 32) score[e] = expf_host_exact(__fsub_rn(z[e], m));
+        __syncwarp();
+        float tot = 0.f;
+        if (lane == 0) for (int e = 0; e < E; e++) tot = __fadd_rn(tot, score[e]);
+        tot = __shfl_sync(0xffffffffu, tot, 0);
+        for (int e = lane; e < E; e += 32) { float p = __fdiv_rn(score[e], tot); score[e] = p; choice[e] = p; }
+    } else {
+        for (int e = lane; e < E; e += 32) {
+            float sg = __fdiv_rn(1.f, __fadd_rn(1.f, expf_host_exact(-z[e])));
+            score[e] = sg;
+            choice[e] = bias ? __fadd_rn(sg, bias[e]) : sg;
+        }
+    }
+    __syncwarp();
+    for (int kk = 0; kk < K; kk++) {
+        int best = -1;
+        float bv = -1e30f;
+        for (int e = lane; e < E; e += 32) { float c = choice[e]; if (c > bv) { bv = c; best = e; } }
+#pragma unroll
+        for (int off = 16; off; off >>= 1) {
+            float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+            int ob = __shfl_xor_sync(0xffffffffu, best, off);
+            bool take = ob >= 0 && (best < 0 || ov > bv || (ov == bv && ob < best));
+            if (take) { bv = ov; best = ob; }
+        }
+        if (best < 0) best = kk < E ? kk : 0;
+        if (lane == 0) { idx[kk] = best; wk[kk] = score[best]; choice[best] = __uint_as_float(0x7fc00000u); }
+        __syncwarp();
+    }
+    if (lane == 0) {
+        int Ke = K;
+        if (rule.gating == 1 && rule.topp > 0.f && rule.topp < 1.f) {
+            for (int a = 1; a < K; a++) {
+                int ii = idx[a]; float ww = wk[a]; int b = a - 1;
+                while (b >= 0 && wk[b] < ww) { wk[b + 1] = wk[b]; idx[b + 1] = idx[b]; b--; }
+                wk[b + 1] = ww; idx[b + 1] = ii;
+            }
+            float tot = 1e-20f;
+            for (int kk = 0; kk < K; kk++) tot = __fadd_rn(tot, wk[kk]);
+            float cum = 0.f;
+            for (int kk = 0; kk < K; kk++) {
+                cum = __fadd_rn(cum, wk[kk]);
+                if (cum >= __fmul_rn(rule.topp, tot)) { Ke = kk + 1; break; }
+            }
+        }
+        if (rule.norm_topk) {
+            float sm = 0.f;
+            for (int kk = 0; kk < Ke; kk++) sm = __fadd_rn(sm, wk[kk]);
+            if (rule.gating == 1) sm = __fadd_rn(sm, 1e-20f);
+            for (int kk = 0; kk < Ke; kk++) wk[kk] = __fdiv_rn(wk[kk], sm);
+        }
+        if (rule.gating == 1) for (int kk = 0; kk < Ke; kk++) wk[kk] = __fmul_rn(wk[kk], rule.routed_scale);
+        *keff = Ke;
+    }
+    __syncwarp();
+}
+
+// Description of one GEMV phase of the fused kernel.
+struct DecPhase {
+    int which;        // 1: gate/up (segments alternate gate, up), 2: down
+    int ntask, tps, ntiles, nkb, nkpart, kb_per_part, O, npos;
+    const __half *bq;
+    const float *bscale;
+};
+
+struct DecIter {
+    int task, kb, kb_end;
+    const uint8_t *ptr;
+};
+
+template <int CH>
+__device__ __forceinline__ void dec_task_setup(DecIter &p, const DecPhase &ph, const DecodeArgs &a,
+                                               const DecShared *sh, int &seg_i, int &tile, int &kpart) {
+    seg_i = p.task / ph.tps;
+    int local = p.task - seg_i * ph.tps;
+    kpart = local / ph.ntiles;
+    tile = local - kpart * ph.ntiles;
+    const DecPass &ps = sh->pass[ph.which == 1 ? (seg_i >> 1) : seg_i];
+    const uint8_t *w;
+    if (ph.which == 1) {
+        if (ps.e >= 0) w = (seg_i & 1) ? a.tab.up_pk[ps.e] : a.tab.gate_pk[ps.e];
+        else w = (seg_i & 1) ? a.tab.sh_up_pk : a.tab.sh_gate_pk;
+    } else {
+        w = ps.e >= 0 ? a.tab.down_pk[ps.e] : a.tab.sh_down_pk;
+    }
+    p.kb = kpart * ph.kb_per_part;
+    p.kb_end = p.kb + ph.kb_per_part;
+    p.ptr = w + ((size_t)tile * ph.nkb + p.kb) * CH;
+}
+
+// Ring state of one warp across the phases of the kernel.
+struct WarpRing {
+    uint32_t ring, bars;
+    int issued, consumed;
+};
+
+template <int CH>
+__device__ __forceinline__ void dec_issue_one(WarpRing &wr, DecIter &prod, const DecPhase &ph,
+                                              const DecodeArgs &a, const DecShared *sh, int P, int lane) {
+    if (prod.task >= ph.ntask) return;
+    if (wr.issued - wr.consumed >= DEC_NST) return;
+    if (lane == 0) {
+        uint32_t bar = wr.bars + (wr.issued % DEC_NST) * 8;
+        mbar_expect_tx(bar, CH);
+        bulk_g2s(wr.ring + (wr.issued % DEC_NST) * CH, prod.ptr, CH, bar);
+    }
+    wr.issued++;
+    prod.kb++;
+    prod.ptr += CH;
+    if (prod.kb == prod.kb_end) {
+        prod.task += P;
+        int d0, d1, d2;
+        if (prod.task < ph.ntask) dec_task_setup<CH>(prod, ph, a, sh, d0, d1, d2);
+    }
+}
+
+// Consumes every task of the phase that belongs to this warp. `prod` must have
+// been initialised (and possibly primed) by the caller.
+template <int MODE>
+__device__ __forceinline__ bool dec_consume_phase(WarpRing &wr, DecIter &prod, const DecPhase &ph,
+                                                  const DecodeArgs &a, const DecShared *sh, int p0, int P,
+                                                  int lane) {
+    constexpr int CH = CODE_BYTES + (MODE == SC_H16 ? 256 : MODE == SC_F32 ? 512 : MODE == SC_MX ? 128 : 0);
+    const int g = lane >> 2, t = lane & 3;
+    DecIter cons;
+    cons.task = p0;
+    while (cons.task < ph.ntask) {
+        int seg_i, tile, kpart;
+        dec_task_setup<CH>(cons, ph, a, sh, seg_i, tile, kpart);
+        const DecPass &ps = sh->pass[ph.which == 1 ? (seg_i >> 1) : seg_i];
+        const int nrows = ps.nrows, nkb = ph.nkb;
+        const int rb = g >> 1;
+        const bool bvalid = rb < nrows;
+        const int rid_b = bvalid ? (ph.which == 1 ? ps.rowid[rb] : ps.pos0 + rb) : 0;
+        const __half *bptr = ph.bq + (size_t)rid_b * nkb * 256 + (g & 1) * 32 + t * 8;
+        const bool svalid = t < nrows;
+        const int rid_s = svalid ? (ph.which == 1 ? ps.rowid[t] : ps.pos0 + t) : 0;
+        const float *sptr = ph.bscale + (size_t)rid_s * nkb;
+        float R[2][4];
+#pragma unroll
+        for (int s = 0; s < 2; s++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) R[s][i] = 0.f;
+        for (int kb = cons.kb; kb < cons.kb_end; kb++) {
+            const int stage = wr.consumed % DEC_NST;
+            const uint32_t st = wr.ring + stage * CH;
+            float ixs = svalid ? sptr[kb] : 0.f;
+            if (!mbar_wait_bounded(wr.bars + stage * 8, (wr.consumed / DEC_NST) & 1)) return false;
+            uint4 w[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) w[j] = lds128(st + j * 512 + lane * 16);
+            uint4 sc16[2];
+            uint4 sc32[2][2];
+            uint2 sc8[2];
+            if (MODE == SC_H16) {
+#pragma unroll
+                for (int s = 0; s < 2; s++) sc16[s] = lds128(st + CODE_BYTES + (s * 8 + g) * 16);
+            } else if (MODE == SC_F32) {
+#pragma unroll
+                for (int s = 0; s < 2; s++) {
+                    sc32[s][0] = lds128(st + CODE_BYTES + (s * 8 + g) * 32);
+                    sc32[s][1] = lds128(st + CODE_BYTES + (s * 8 + g) * 32 + 16);
+                }
+            } else if (MODE == SC_MX) {
+#pragma unroll
+                for (int s = 0; s < 2; s++) sc8[s] = lds64(st + CODE_BYTES + (s * 8 + g) * 8);
+            }
+            float bacc[2][4];
+#pragma unroll
+            for (int s = 0; s < 2; s++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) bacc[s][i] = 0.f;
+#pragma unroll
+            for (int grp = 0; grp < 4; grp++) {
+                uint4 b = bvalid ? ldg128(bptr + (size_t)kb * 256 + grp * 64) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+                for (int s = 0; s < 2; s++) {
+                    uint32_t a_lo[4], a_hi[4];
+                    decode_word<MODE>(word_of(w[s * 2 + 0], grp), a_lo);
+                    decode_word<MODE>(word_of(w[s * 2 + 1], grp), a_hi);
+                    float s0 = 1.f, s1 = 1.f;
+                    if (MODE == SC_H16) {
+                        uint32_t p0w = grp < 2 ? sc16[s].x : sc16[s].y;
+                        uint32_t p1w = grp < 2 ? sc16[s].z : sc16[s].w;
+                        __half2 h0 = u32_as_h2(p0w), h1 = u32_as_h2(p1w);
+                        s0 = (grp & 1) ? __high2float(h0) : __low2float(h0);
+                        s1 = (grp & 1) ? __high2float(h1) : __low2float(h1);
+                    } else if (MODE == SC_F32) {
+                        s0 = __uint_as_float(word_of(sc32[s][0], grp));
+                        s1 = __uint_as_float(word_of(sc32[s][1], grp));
+                    } else if (MODE == SC_MX) {
+                        s0 = __uint_as_float(((sc8[s].x >> (8 * grp)) & 0xFFu) << 23);
+                        s1 = __uint_as_float(((sc8[s].y >> (8 * grp)) & 0xFFu) << 23);
+                    }
+                    float c[4] = {0.f, 0.f, 0.f, 0.f};
+                    mma_f16(c, a_lo[0], a_hi[0], a_lo[1], a_hi[1], b.x, b.y);
+                    mma_f16(c, a_lo[2], a_hi[2], a_lo[3], a_hi[3], b.z, b.w);
+                    if (MODE == SC_ROW) {
+                        bacc[s][0] += c[0]; bacc[s][1] += c[1]; bacc[s][2] += c[2]; bacc[s][3] += c[3];
+                    } else {
+                        bacc[s][0] = fmaf(c[0], s0, bacc[s][0]);
+                        bacc[s][1] = fmaf(c[1], s0, bacc[s][1]);
+                        bacc[s][2] = fmaf(c[2], s1, bacc[s][2]);
+                        bacc[s][3] = fmaf(c[3], s1, bacc[s][3]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int s = 0; s < 2; s++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) R[s][i] = fmaf(bacc[s][i], ixs, R[s][i]);
+            wr.consumed++;
+            __syncwarp();
+            dec_issue_one<CH>(wr, prod, ph, a, sh, P, lane);
+        }
+        const float mx_fix = (MODE == SC_MX) ? 16384.f : 1.f;
+        if (t < nrows) {
+            const float *rowscale = nullptr;
+            float *outp;
+            if (ph.which == 1) {
+                outp = (seg_i & 1) ? a.partU : a.partG;
+                if (MODE == SC_ROW) rowscale = ps.e >= 0 ? ((seg_i & 1) ? a.tab.up_rs[ps.e] : a.tab.gate_rs[ps.e])
+                                                         : ((seg_i & 1) ? a.tab.sh_up_rs : a.tab.sh_gate_rs);
+            } else {
+                outp = a.partD;
+                if (MODE == SC_ROW) rowscale = ps.e >= 0 ? a.tab.down_rs[ps.e] : a.tab.sh_down_rs;
+            }
+#pragma unroll
+            for (int s = 0; s < 2; s++) {
+                int o = tile * TILE_ROWS + s * 16 + g;
+                float v0 = (R[s][0] + R[s][1]) * mx_fix;
+                float v1 = (R[s][2] + R[s][3]) * mx_fix;
+                if (MODE == SC_ROW) { v0 *= rowscale[o]; v1 *= rowscale[o + 8]; }
+                float *dst = outp + ((size_t)kpart * ph.npos + ps.pos0 + t) * ph.O + o;
+                dst[0] = v0;
+                dst[8] = v1;
+            }
+        }
+        cons.task += P;
+    }
+    return true;
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) {
+    constexpr int CH = CODE_BYTES + (MODE == SC_H16 ? 256 : MODE == SC_F32 ? 512 : MODE == SC_MX ? 128 : 0);
+    extern __shared__ __align__(128) uint8_t smem[];
+    // layout: rings | mbarriers | DecShared | routing scratch (M * 2E floats)
+    DecShared *sh = reinterpret_cast<DecShared *>(smem + DEC_WARPS * DEC_NST * (CH + 8));
+    float *rscratch = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(sh) + ((sizeof(DecShared) + 15) & ~15));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+    const RouteRule &r = a.rule;
+    const int E = r.E, K = r.K, M = a.M, D = r.D, I = r.I;
+    WarpRing wr;
+    wr.ring = smem_u32(smem) + warp * (DEC_NST * CH);
+    wr.bars = smem_u32(smem) + DEC_WARPS * DEC_NST * CH + warp * DEC_NST * 8;
+    wr.issued = 0; wr.consumed = 0;
+    if (lane == 0) {
+        for (int s = 0; s < DEC_NST; s++) mbar_init(wr.bars + s * 8, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (tid == 0) sh->failed = 0;
+    for (int e = tid; e < E; e += blockDim.x) { sh->first[e] = 0x7fffffff; sh->cnt[e] = 0; }
+    __syncthreads();
+
+    // ---- routing, redundantly in every CTA -----------------------------------
+    if (warp < M)
+        route_row_warp(a.logits + (size_t)warp * E, a.router_bias, r, rscratch + (size_t)warp * 2 * E,
+                       rscratch + (size_t)warp * 2 * E + E, sh->idx + warp * K, sh->w + warp * K,
+                       sh->keff + warp, lane);
+    __syncthreads();
+    for (int i = tid; i < M * K; i += blockDim.x) {
+        int s = i / K, kk = i - s * K;
+        if (kk < sh->keff[s]) { int e = sh->idx[i]; atomicMin(&sh->first[e], i); atomicAdd(&sh->cnt[e], 1); }
+    }
+    if (tid == 0) sh->nu = 0;
+    __syncthreads();
+    for (int e = tid; e < E; e += blockDim.x) {
+        if (sh->cnt[e] > 0) {
+            int rank = 0;
+            for (int o = 0; o < E; o++) rank += (sh->cnt[o] > 0 && sh->first[o] < sh->first[e]);
+            sh->uniq[rank] = e;
+            atomicAdd(&sh->nu, 1);
+        }
+    }
+    __syncthreads();
+    const int nu = sh->nu;
+    for (int j = tid; j < nu; j += blockDim.x) {
+        int pos = 0, np = 0;
+        for (int q = 0; q < j; q++) { int c = sh->cnt[sh->uniq[q]]; pos += c; np += (c + 3) >> 2; }
+        int e = sh->uniq[j];
+        sh->base[e] = pos; sh->passbase[e] = np;
+        if (j == nu - 1) {
+            int c = sh->cnt[e];
+            int spos = pos + c, npass = np + ((c + 3) >> 2);
+            sh->shared_pos0 = spos;
+            if (a.tab.sh_gate_pk) {
+                for (int p = 0; p < (M + 3) / 4; p++) {
+                    DecPass &ps = sh->pass[npass + p];
+                    ps.e = -1; ps.pos0 = spos + 4 * p; ps.nrows = min(4, M - 4 * p);
+                    for (int q = 0; q < ps.nrows; q++) ps.rowid[q] = 4 * p + q;
+                }
+                npass += (M + 3) / 4; spos += M;
+            }
+            sh->npass = npass; sh->npos = spos;
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < M * K; i += blockDim.x) {
+        int s = i / K, kk = i - s * K;
+        if (kk < sh->keff[s]) {
+            int e = sh->idx[i], rr = 0;
+            for (int s2 = 0; s2 < s; s2++)
+                for (int k2 = 0; k2 < sh->keff[s2]; k2++) rr += (sh->idx[s2 * K + k2] == e);
+            int pos = sh->base[e] + rr;
+            sh->pos_of[i] = pos;
+            DecPass &ps = sh->pass[sh->passbase[e] + (rr >> 2)];
+            ps.rowid[rr & 3] = s;
+            if ((rr & 3) == 0) { ps.e = e; ps.pos0 = pos; ps.nrows = min(4, sh->cnt[e] - (rr & ~3)); }
+        }
+    }
+    __syncthreads();
+    if (blockIdx.x == 0) {
+        for (int i = tid; i < M * K; i += blockDim.x) {
+            if (a.idx_out) a.idx_out[i] = sh->idx[i];
+            if (a.w_out) a.w_out[i] = sh->w[i];
+        }
+        if (a.keff_out) for (int s = tid; s < M; s += blockDim.x) a.keff_out[s] = sh->keff[s];
+    }
+    const int npass = sh->npass, npos = sh->npos;
+    const int P = gridDim.x * DEC_WARPS, p0 = blockIdx.x * DEC_WARPS + warp;
+    const unsigned long long bar_base = a.epoch * DEC_NBAR * gridDim.x;
+
+    DecPhase ph1, ph2;
+    ph1.which = 1; ph1.ntiles = I / TILE_ROWS; ph1.nkb = D / BLOCK_K; ph1.nkpart = a.nkp1;
+    ph1.kb_per_part = ph1.nkb / a.nkp1; ph1.tps = ph1.ntiles * a.nkp1; ph1.ntask = 2 * npass * ph1.tps;
+    ph1.O = I; ph1.npos = npos; ph1.bq = a.xq; ph1.bscale = a.xs;
+    ph2.which = 2; ph2.ntiles = D / TILE_ROWS; ph2.nkb = I / BLOCK_K; ph2.nkpart = a.nkp2;
+    ph2.kb_per_part = ph2.nkb / a.nkp2; ph2.tps = ph2.ntiles * a.nkp2; ph2.ntask = npass * ph2.tps;
+    ph2.O = D; ph2.npos = npos; ph2.bq = a.hq; ph2.bscale = a.hs;
+
+    // ---- start the gate/up weight stream, then split the activations ---------
+    DecIter prod;
+    prod.task = p0;
+    int d0, d1, d2;
+    if (prod.task < ph1.ntask) dec_task_setup<CH>(prod, ph1, a, sh, d0, d1, d2);
+    for (int s = 0; s < DEC_NST; s++) dec_issue_one<CH>(wr, prod, ph1, a, sh, P, lane);
+    {
+        const int nkb = D / BLOCK_K;
+        for (int wid = p0; wid < M * nkb; wid += P) {
+            int row = wid / nkb, kb = wid - row * nkb;
+            float4 v = *reinterpret_cast<const float4 *>(a.x + (size_t)row * D + kb * BLOCK_K + lane * 4);
+            float m = warp_max(fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+            float s = block_scale_from_max(m);
+            store_split4(a.xq + ((size_t)row * nkb + kb) * 256, lane, v, s);
+            if (lane == 0) a.xs[(size_t)row * nkb + kb] = 1.f / s;
+        }
+    }
+    bool ok = grid_barrier(a.bar, bar_base + 1ULL * gridDim.x, &sh->failed);
+    // ---- gate / up ------------------------------------------------------------
+    if (ok) ok = dec_consume_phase<MODE>(wr, prod, ph1, a, sh, p0, P, lane);
+    if (!ok) sh->failed = 1;
+    // start the down weight stream before waiting for the other CTAs
+    prod.task = p0;
+    if (ok && prod.task < ph2.ntask) dec_task_setup<CH>(prod, ph2, a, sh, d0, d1, d2);
+    if (ok) for (int s = 0; s < DEC_NST; s++) dec_issue_one<CH>(wr, prod, ph2, a, sh, P, lane);
+    ok = grid_barrier(a.bar, bar_base + 2ULL * gridDim.x, &sh->failed) && ok;
+    // ---- SwiGLU + split of h, distributed ----------------------------------------
+    if (ok) {
+        const int nkb = I / BLOCK_K;
+        for (int wid = p0; wid < npos * nkb; wid += P) {
+            int pos = wid / nkb, kb = wid - pos * nkb;
+            float4 gs = make_float4(0, 0, 0, 0), us = gs;
+            for (int kp = 0; kp < a.nkp1; kp++) {
+                size_t off = ((size_t)kp * npos + pos) * I + kb * BLOCK_K + lane * 4;
+                float4 ga = *reinterpret_cast<const float4 *>(a.partG + off);
+                float4 ua = *reinterpret_cast<const float4 *>(a.partU + off);
+                gs.x += ga.x; gs.y += ga.y; gs.z += ga.z; gs.w += ga.w;
+                us.x += ua.x; us.y += ua.y; us.z += ua.z; us.w += ua.w;
+            }
+            float4 h;
+            h.x = (gs.x / (1.0f + expf(-gs.x))) * us.x;
+            h.y = (gs.y / (1.0f + expf(-gs.y))) * us.y;
+            h.z = (gs.z / (1.0f + expf(-gs.z))) * us.z;
+            h.w = (gs.w / (1.0f + expf(-gs.w))) * us.w;
+            float m = warp_max(fmaxf(fmaxf(fabsf(h.x), fabsf(h.y)), fmaxf(fabsf(h.z), fabsf(h.w))));
+            float s = block_scale_from_max(m);
+            store_split4(a.hq + ((size_t)pos * nkb + kb) * 256, lane, h, s);
+            if (lane == 0) a.hs[(size_t)pos * nkb + kb] = 1.f / s;
+        }
+    }
+    ok = grid_barrier(a.bar, bar_base + 3ULL * gridDim.x, &sh->failed) && ok;
+    // ---- down -------------------------------------------------------------------
+    if (ok) ok = dec_consume_phase<MODE>(wr, prod, ph2, a, sh, p0, P, lane);
+    if (!ok) sh->failed = 1;
+    ok = grid_barrier(a.bar, bar_base + 4ULL * gridDim.x, &sh->failed) && ok;
+    // ---- weighted combine: selection order per row, shared expert last ------------
+    if (ok) {
+        const int dq = D / 4;
+        for (int i = blockIdx.x * blockDim.x + tid; i < M * dq; i += gridDim.x * blockDim.x) {
+            int s = i / dq, d4 = i - s * dq;
+            float4 acc = make_float4(0, 0, 0, 0);
+            int ke = sh->keff[s];
+            for (int kk = 0; kk < ke; kk++) {
+                int pos = sh->pos_of[s * K + kk];
+                float wgt = sh->w[s * K + kk];
+                float4 y = make_float4(0, 0, 0, 0);
+                for (int kp = 0; kp < a.nkp2; kp++) {
+                    float4 v = reinterpret_cast<const float4 *>(a.partD + ((size_t)kp * npos + pos) * D)[d4];
+                    y.x += v.x; y.y += v.y; y.z += v.z; y.w += v.w;
+                }
+                acc.x += wgt * y.x; acc.y += wgt * y.y; acc.z += wgt * y.z; acc.w += wgt * y.w;
+            }
+            if (a.tab.sh_gate_pk) {
+                int pos = sh->shared_pos0 + s;
+                float4 y = make_float4(0, 0, 0, 0);
+                for (int kp = 0; kp < a.nkp2; kp++) {
+                    float4 v = reinterpret_cast<const float4 *>(a.partD + ((size_t)kp * npos + pos) * D)[d4];
+                    y.x += v.x; y.y += v.y; y.z += v.z; y.w += v.w;
+                }
+                acc.x += y.x; acc.y += y.y; acc.z += y.z; acc.w += y.w;
+            }
+            reinterpret_cast<float4 *>(a.out)[i] = acc;
+        }
+    }
+    if (!ok) {
+        if (tid == 0) atomicExch(a.status, sh->failed ? KSTAT_GRID_TIMEOUT : KSTAT_MBAR_TIMEOUT);
+        // drain copies still in flight before the shared memory goes away (bounded)
+        for (int i = wr.consumed; i < wr.issued; i++)
+            if (!mbar_wait_bounded(wr.bars + (i % DEC_NST) * 8, (i / DEC_NST) & 1)) break;
+    }
+}

@@ -95,6 +95,9 @@ extern "C" void coli_cuda_moe_layer_free(ColiCudaMoeLayer *L) {
     delete L;
 }
 
+static int g_fused_decode = 1;
+extern "C" void coli_cuda_set_fused_decode(int enabled) { g_fused_decode = enabled ? 1 : 0; }
+
 struct LayerPlan {
     int nc, rpp, nkp1, nkp2, seg_cap, npos_cap;
 };
@@ -146,6 +149,38 @@ static int layer_run(ColiCudaMoeLayer *L, DeviceCtx *c, float *out_dev, const fl
         k_router_logits<<<(n + 63) / 64, 64, 0, c->stream>>>((float *)L->logits.p, x_dev, L->router_w, M, r.D, r.E);
         c->last_launches++;
         lg = (const float *)L->logits.p;
+    }
+    if (!route_only && g_fused_decode && M <= DEC_MAX_M && r.E <= DEC_MAX_E && L->mode_gu == L->mode_d) {
+        // one cooperative kernel for the whole layer
+        LayerPlan q = p;
+        long passes = (long)(M * r.K < r.E ? M * r.K : r.E) + (L->has_shared ? (M + 3) / 4 : 0);
+        q.nkp1 = pick_nkpart(nkb1, 2 * passes * (r.I / TILE_ROWS), c->sms);
+        q.nkp2 = pick_nkpart(nkb2, passes * (r.D / TILE_ROWS), c->sms);
+        if (!reserve(c, &L->pg, (size_t)q.nkp1 * p.npos_cap * r.I * sizeof(float)) ||
+            !reserve(c, &L->pu, (size_t)q.nkp1 * p.npos_cap * r.I * sizeof(float)) ||
+            !reserve(c, &L->pd, (size_t)q.nkp2 * p.npos_cap * r.D * sizeof(float))) return 0;
+        DecodeArgs a;
+        a.rule = r; a.tab = L->tab;
+        a.x = x_dev; a.logits = lg; a.router_bias = L->router_bias;
+        a.out = out_dev; a.idx_out = idx_dev; a.w_out = w_dev; a.keff_out = keff_dev;
+        a.xq = (__half *)L->xq.p; a.xs = (float *)L->xs.p;
+        a.partG = (float *)L->pg.p; a.partU = (float *)L->pu.p;
+        a.hq = (__half *)L->hq.p; a.hs = (float *)L->hs.p; a.partD = (float *)L->pd.p;
+        a.bar = c->gridbar; a.epoch = c->epoch++; a.status = c->status;
+        a.M = M; a.nkp1 = q.nkp1; a.nkp2 = q.nkp2;
+        void *args[] = {&a};
+        const void *fn = L->mode_gu == SC_ROW ? (const void *)k_moe_decode<SC_ROW>
+                       : L->mode_gu == SC_H16 ? (const void *)k_moe_decode<SC_H16>
+                       : L->mode_gu == SC_F32 ? (const void *)k_moe_decode<SC_F32>
+                                              : (const void *)k_moe_decode<SC_MX>;
+        cudaEvent_t e0 = nullptr, e1 = nullptr;
+        kernel_event_pair(c, &e0, &e1);
+        if (e0) cudaEventRecord(e0, c->stream);
+        cudaError_t err = cudaLaunchCooperativeKernel(fn, dim3(c->sms), dim3(DEC_WARPS * 32), args,
+                                                      (size_t)decode_smem_bytes(L->mode_gu), c->stream);
+        if (e1) cudaEventRecord(e1, c->stream);
+        c->last_launches++;
+        return cuda_ok(err, "fused decode launch");
     }
     {
         const int warps = 4;

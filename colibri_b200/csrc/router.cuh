@@ -165,7 +165,7 @@ __global__ void k_route_build(const int *__restrict__ idx, const int *__restrict
     extern __shared__ int sm_build[];
     const int E = rule.E, K = rule.K, D = rule.D, I = rule.I;
     int *first = sm_build, *cnt = first + E, *base = cnt + E, *uniq = base + E, *passbase = uniq + E;
-    __shared__ int s_nu, s_npos, s_npass;
+    __shared__ int s_nu, s_npass;
     const int tid = threadIdx.x, nth = blockDim.x;
     for (int e = tid; e < E; e += nth) { first[e] = 0x7fffffff; cnt[e] = 0; }
     if (tid == 0) s_nu = 0;
@@ -201,10 +201,12 @@ __global__ void k_route_build(const int *__restrict__ idx, const int *__restrict
         int np_routed = np;
         if (tab.sh_gate_pk) { pos += M; np += (M + rpp - 1) / rpp; }
         if (np > seg_cap) np = seg_cap;   // capacity is sized for the worst case; never exceeded
-        s_npos = pos; s_npass = np;
+        s_npass = np;
         *out.npos = pos; *out.shared_pos0 = shared_pos0; *out.nu = nu;
         out.ctl1->nseg = 2 * np; out.ctl1->ntask = 2 * np * (I / TILE_ROWS) * nkpart1; out.ctl1->npos = pos;
+        out.ctl1->tasks_per_seg = (I / TILE_ROWS) * nkpart1;
         out.ctl2->nseg = np; out.ctl2->ntask = np * (D / TILE_ROWS) * nkpart2; out.ctl2->npos = pos;
+        out.ctl2->tasks_per_seg = (D / TILE_ROWS) * nkpart2;
         // shared expert segments
         if (tab.sh_gate_pk) {
             for (int p = 0; p < (M + rpp - 1) / rpp && np_routed + p < seg_cap; p++) {

@@ -222,8 +222,12 @@ int coli_cuda_last_timing(int device, float *kernel_ms, int *launches);
 /* Enables (1) or disables (0) that per-call event timing; off by default. */
 void coli_cuda_set_timing(int enabled);
 
+/* Decode-sized layer calls (M <= 8) normally run as one fused cooperative
+ * kernel; 0 routes them through the multi-kernel path instead (A/B testing). */
+void coli_cuda_set_fused_decode(int enabled);
+
 /* Per-kernel timing of the dominant kernel: while enabled, every launch of the
- * streaming GEMV is bracketed by a CUDA event pair on the backend's stream.
+ * streaming GEMV and of the fused decode kernel is bracketed by a CUDA event pair on the backend's stream.
  * coli_cuda_kernel_events synchronises, returns the summed duration and the
  * number of launches since the last query, and clears the list. */
 void coli_cuda_set_kernel_events(int enabled);

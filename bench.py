@@ -82,9 +82,14 @@ def gen_layer_host(torch, cfg, seed, device):
     """-> lists of QTensor (gate, up, down) for one layer."""
     D, I, E = cfg["D"], cfg["I"], cfg["E"]
     out = []
+    chunk = max(1, min(E, (1 << 28) // (D * I)))     # bound the f32 temporary to ~1 GiB
     for k, (O, K) in enumerate(((I, D), (I, D), (D, I))):
-        pk, sc = gen_int4_g32_torch(torch, E, O, K, seed * 10 + k, device)
-        out.append([QTensor(pk[e], sc[e], 4, K, O, 32) for e in range(E)])
+        ts = []
+        for e0 in range(0, E, chunk):
+            n = min(chunk, E - e0)
+            pk, sc = gen_int4_g32_torch(torch, n, O, K, (seed * 10 + k) * 1000 + e0, device)
+            ts += [QTensor(pk[e], sc[e], 4, K, O, 32) for e in range(n)]
+        out.append(ts)
     return out
 
 

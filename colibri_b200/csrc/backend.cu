@@ -42,7 +42,8 @@ struct DeviceCtx {
     int group_pending = 0;
     int *status = nullptr;                    // device int: sticky kernel status
     unsigned long long *gridbar = nullptr;    // arrival counter of the fused decode kernel's grid barrier
-    unsigned long long epoch = 0;             // launches of that kernel since the counter was zeroed
+    unsigned long long epoch = 0;             // arrivals expected at that counter so far
+    int sticky_status = 0;                    // last non-zero kernel status seen by the host
     float last_ms = 0.f;
     int last_launches = 0;
     int have_timing = 0;
@@ -138,8 +139,9 @@ static void setup_mode() { setup_one<MODE, 1>(); setup_one<MODE, 2>(); setup_one
 extern "C" void coli_cuda_shutdown(void);
 
 static int decode_smem_bytes(int mode) {
-    return DEC_WARPS * DEC_NST * (chunk_bytes_of(mode) + 8) + (int)((sizeof(DecShared) + 15) & ~15) +
-           DEC_MAX_M * 2 * DEC_MAX_E * (int)sizeof(float);
+    const int nst = mode == SC_F32 ? 3 : 4;
+    return DEC_WARPS * nst * (chunk_bytes_of(mode) + 8) + (int)((sizeof(DecShared) + 127) & ~127) +
+           DEC_ACT_BYTES + 2048;
 }
 
 extern "C" int coli_cuda_init(const int *devices, int count) {
@@ -278,7 +280,7 @@ extern "C" int coli_cuda_kernel_status(int device) {
     if (!select_ctx(c)) return -1;
     int v = 0;
     if (!cuda_ok(cudaMemcpy(&v, c->status, sizeof(int), cudaMemcpyDeviceToHost), "status read")) return -1;
-    return v;
+    return v ? v : c->sticky_status;
 }
 
 // ---------------------------------------------------------------------------
@@ -624,7 +626,9 @@ static int check_status(DeviceCtx *c) {
         std::fprintf(stderr, "[CUDA] kernel wait guard expired (status %d)\n", v);
         // the grid barrier's arrival count is no longer a multiple of the grid: start over
         cudaMemsetAsync(c->gridbar, 0, sizeof(unsigned long long), c->stream);
+        cudaMemsetAsync(c->status, 0, sizeof(int), c->stream);
         c->epoch = 0;
+        c->sticky_status = v;
         return 0;
     }
     return 1;

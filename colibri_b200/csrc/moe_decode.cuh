@@ -18,9 +18,19 @@
 // The GEMV inner loop is the one of gemv_stream.cuh with one 8-column set
 // (4 rows per pass; an expert with more rows takes two passes).
 //
-// Grid barrier: an arrival counter in global memory that only grows; launch
-// number `epoch` waits for (epoch*NBAR + k + 1) * gridDim.x arrivals at its k-th
-// barrier. Every spin is bounded (about a second); on expiry the CTA records
+// Activations: when they are small enough (M*D*4 bytes <= 64 KB, and the slice
+// of h one task needs <= 4 KB) they never touch global memory: every CTA splits
+// x into fp16 hi/lo fragments in its own shared memory while its first warps
+// route, and each warp computes the SwiGLU slice of its down-projection task
+// from the gate/up partial sums into a private shared-memory slot. That removes
+// two grid barriers and takes the B-operand loads of the inner loop from
+// L2 latency to shared-memory latency. Otherwise the split activations go
+// through global memory with a barrier after each producer step.
+//
+// Grid barrier: an arrival counter in global memory that only grows; the host
+// passes the number of arrivals expected before the launch, and the k-th barrier
+// of the launch waits for that plus (k+1) * gridDim.x. Every spin is bounded
+// (about 20 ms); on expiry the CTA records
 // KSTAT_GRID_TIMEOUT, drains its copies and returns. The kernel is launched
 // cooperatively so that all CTAs are co-resident.
 #pragma once
@@ -35,7 +45,9 @@
 #define DEC_MAX_PASS 80          // <= 64 distinct experts + second passes + shared passes
 #define DEC_NBAR 4
 #define DEC_WARPS 16
-#define DEC_NST 4
+#define DEC_ACT_BYTES 65536       // shared-memory activation region (x fragments, then h slots)
+#define DEC_SLOT_BYTES 4160       // per-warp h slot in phase 2: 8 blocks of fragments + their scales
+#define DEC_NPROBE 12
 
 struct DecPass {
     int e;            // expert id, or -1 for the shared expert
@@ -54,9 +66,11 @@ struct DecodeArgs {
     __half *hq; float *hs;            // [npos][nkb2][256], [npos][nkb2]
     float *partD;                     // [nkp2][npos][D]
     unsigned long long *bar;
-    unsigned long long epoch;
+    unsigned long long bar_base;      // arrivals expected before this launch (host-side running total)
     int *status;
     int M, nkp1, nkp2;
+    int act_smem;                     // 1: activations stay in shared memory (see above)
+    unsigned long long *probe;        // optional [gridDim.x][DEC_NPROBE] phase timestamps (ns), or NULL
 };
 
 struct DecShared {
@@ -68,7 +82,24 @@ struct DecShared {
     int uniq[DEC_MAX_E];
     DecPass pass[DEC_MAX_PASS];
     int nu, npass, npos, shared_pos0, failed;
+    unsigned long long exp_tab[32];
 };
+
+__device__ __forceinline__ void dec_probe(const DecodeArgs &a, int slot) {
+    if (a.probe && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        a.probe[(size_t)blockIdx.x * DEC_NPROBE + slot] = t;
+    }
+}
+
+__device__ __forceinline__ void dec_probe_lane(const DecodeArgs &a, int slot) {   // any one lane
+    if (a.probe) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        a.probe[(size_t)blockIdx.x * DEC_NPROBE + slot] = t;
+    }
+}
 
 __device__ __forceinline__ uint4 ldg128(const void *p) {
     uint4 v;
@@ -81,59 +112,88 @@ __device__ __forceinline__ bool grid_barrier(unsigned long long *counter, unsign
                                              int *s_failed) {
     __syncthreads();
     if (threadIdx.x == 0) {
-        __threadfence();
-        atomicAdd(counter, 1ULL);
+        // release-add (orders this CTA's earlier writes, made visible to thread 0 by
+        // the CTA barrier above), then acquire-poll
+        asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(counter), "l"(1ULL) : "memory");
         long long t0 = clock64();
         for (;;) {
             unsigned long long v;
             asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(counter) : "memory");
             if (v >= target) break;
-            if (clock64() - t0 > 2000000000LL) { *s_failed = 1; break; }
+            if (clock64() - t0 > 40000000LL) { *s_failed = 1; break; }   // ~20 ms: a barrier takes microseconds
         }
-        __threadfence();
     }
     __syncthreads();
     return *s_failed == 0;
 }
 
-// One row of routing by one warp: the body of k_route_topk with shared-memory outputs.
+// One row of routing by one warp, outputs in shared memory. `tab` is the 2^(i/32)
+// table of expf_exact.h (shared memory here, so that 32 lanes with 32 different
+// indices do not serialise on the constant cache).
+//
+// Selection: the engine makes K passes of "largest untaken by strict '>', lowest
+// index wins ties". When every candidate is an ordinary number above -1e30 that is
+// the same as ranking: rank(e) = #{e' : c[e'] > c[e] or (c[e'] == c[e] and e' < e)},
+// and slot kk holds the element of rank kk. Each lane ranks its own elements against
+// all E values (independent shared-memory reads, no cross-lane traffic). Rows with a
+// NaN or a value <= -1e30 take the pass-by-pass form, which also reproduces the
+// engine's "nothing found -> expert kk" degradation.
 __device__ __forceinline__ void route_row_warp(const float *z, const float *bias, const RouteRule &rule,
                                                float *score, float *choice, int *idx, float *wk,
-                                               int *keff, int lane) {
+                                               int *keff, int lane, const uint64_t *tab) {
     const int E = rule.E, K = rule.K;
     if (rule.gating == 0) {
         float m = -1e30f;
         for (int e = lane; e < E; e += 32) { float v = z[e]; if (v > m) m = v; }
 #pragma unroll
         for (int off = 16; off; off >>= 1) { float o = __shfl_xor_sync(0xffffffffu, m, off); if (o > m) m = o; }
-        for (int e = lane; e < E; e += 32) score[e] = expf_host_exact(__fsub_rn(z[e], m));
+        for (int e = lane; e < E; e += 32) score[e] = coli_expf_exact(__fsub_rn(z[e], m), tab);
         __syncwarp();
         float tot = 0.f;
-        if (lane == 0) for (int e = 0; e < E; e++) tot = __fadd_rn(tot, score[e]);
+        if (lane == 0) {     // the engine's serial ascending sum; loads batched four at a time
+            int e = 0;
+            for (; e + 4 <= E; e += 4) {
+                float4 v = *reinterpret_cast<const float4 *>(score + e);
+                tot = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(tot, v.x), v.y), v.z), v.w);
+            }
+            for (; e < E; e++) tot = __fadd_rn(tot, score[e]);
+        }
         tot = __shfl_sync(0xffffffffu, tot, 0);
         for (int e = lane; e < E; e += 32) { float p = __fdiv_rn(score[e], tot); score[e] = p; choice[e] = p; }
     } else {
         for (int e = lane; e < E; e += 32) {
-            float sg = __fdiv_rn(1.f, __fadd_rn(1.f, expf_host_exact(-z[e])));
+            float sg = __fdiv_rn(1.f, __fadd_rn(1.f, coli_expf_exact(-z[e], tab)));
             score[e] = sg;
             choice[e] = bias ? __fadd_rn(sg, bias[e]) : sg;
         }
     }
     __syncwarp();
-    for (int kk = 0; kk < K; kk++) {
-        int best = -1;
-        float bv = -1e30f;
-        for (int e = lane; e < E; e += 32) { float c = choice[e]; if (c > bv) { bv = c; best = e; } }
-#pragma unroll
-        for (int off = 16; off; off >>= 1) {
-            float ov = __shfl_xor_sync(0xffffffffu, bv, off);
-            int ob = __shfl_xor_sync(0xffffffffu, best, off);
-            bool take = ob >= 0 && (best < 0 || ov > bv || (ov == bv && ob < best));
-            if (take) { bv = ov; best = ob; }
+    bool odd = false;
+    for (int e = lane; e < E; e += 32) { float c = choice[e]; odd |= !(c > -1e30f); }
+    if (!__any_sync(0xffffffffu, odd)) {
+        for (int e = lane; e < E; e += 32) {
+            const float c = choice[e];
+            int rank = 0;
+            for (int o = 0; o < E; o++) { float v = choice[o]; rank += (v > c) || (v == c && o < e); }
+            if (rank < K) { idx[rank] = e; wk[rank] = score[e]; }
         }
-        if (best < 0) best = kk < E ? kk : 0;
-        if (lane == 0) { idx[kk] = best; wk[kk] = score[best]; choice[best] = __uint_as_float(0x7fc00000u); }
         __syncwarp();
+    } else {
+        for (int kk = 0; kk < K; kk++) {
+            int best = -1;
+            float bv = -1e30f;
+            for (int e = lane; e < E; e += 32) { float c = choice[e]; if (c > bv) { bv = c; best = e; } }
+#pragma unroll
+            for (int off = 16; off; off >>= 1) {
+                float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+                int ob = __shfl_xor_sync(0xffffffffu, best, off);
+                bool take = ob >= 0 && (best < 0 || ov > bv || (ov == bv && ob < best));
+                if (take) { bv = ov; best = ob; }
+            }
+            if (best < 0) best = kk < E ? kk : 0;
+            if (lane == 0) { idx[kk] = best; wk[kk] = score[best]; choice[best] = __uint_as_float(0x7fc00000u); }
+            __syncwarp();
+        }
     }
     if (lane == 0) {
         int Ke = K;
@@ -167,8 +227,6 @@ __device__ __forceinline__ void route_row_warp(const float *z, const float *bias
 struct DecPhase {
     int which;        // 1: gate/up (segments alternate gate, up), 2: down
     int ntask, tps, ntiles, nkb, nkpart, kb_per_part, O, npos;
-    const __half *bq;
-    const float *bscale;
 };
 
 struct DecIter {
@@ -202,15 +260,15 @@ struct WarpRing {
     int issued, consumed;
 };
 
-template <int CH>
+template <int CH, int NST>
 __device__ __forceinline__ void dec_issue_one(WarpRing &wr, DecIter &prod, const DecPhase &ph,
                                               const DecodeArgs &a, const DecShared *sh, int P, int lane) {
     if (prod.task >= ph.ntask) return;
-    if (wr.issued - wr.consumed >= DEC_NST) return;
+    if (wr.issued - wr.consumed >= NST) return;
     if (lane == 0) {
-        uint32_t bar = wr.bars + (wr.issued % DEC_NST) * 8;
+        uint32_t bar = wr.bars + (wr.issued % NST) * 8;
         mbar_expect_tx(bar, CH);
-        bulk_g2s(wr.ring + (wr.issued % DEC_NST) * CH, prod.ptr, CH, bar);
+        bulk_g2s(wr.ring + (wr.issued % NST) * CH, prod.ptr, CH, bar);
     }
     wr.issued++;
     prod.kb++;
@@ -222,12 +280,55 @@ __device__ __forceinline__ void dec_issue_one(WarpRing &wr, DecIter &prod, const
     }
 }
 
+// SwiGLU of one 128-wide block of one packed row from the gate/up partial sums,
+// split into fp16 hi/lo fragments at `dst` (256 halfs); returns the inverse scale.
+__device__ __forceinline__ float dec_swiglu_block(const DecodeArgs &a, int npos, int pos, int kb, int lane,
+                                                  __half *dst) {
+    const int I = a.rule.I;
+    float4 gs = make_float4(0, 0, 0, 0), us = gs;
+    // all loads of up to 8 partial sums are issued before the first add (one memory
+    // round trip instead of one per slice); the sum stays in ascending slice order
+    for (int k0 = 0; k0 < a.nkp1; k0 += 8) {
+        float4 ga[8], ua[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            if (k0 + j < a.nkp1) {
+                size_t off = ((size_t)(k0 + j) * npos + pos) * I + kb * BLOCK_K + lane * 4;
+                ga[j] = *reinterpret_cast<const float4 *>(a.partG + off);
+                ua[j] = *reinterpret_cast<const float4 *>(a.partU + off);
+            } else {
+                ga[j] = make_float4(0, 0, 0, 0); ua[j] = ga[j];
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            gs.x += ga[j].x; gs.y += ga[j].y; gs.z += ga[j].z; gs.w += ga[j].w;
+            us.x += ua[j].x; us.y += ua[j].y; us.z += ua[j].z; us.w += ua[j].w;
+        }
+    }
+    float4 h;
+    h.x = (gs.x / (1.0f + expf(-gs.x))) * us.x;
+    h.y = (gs.y / (1.0f + expf(-gs.y))) * us.y;
+    h.z = (gs.z / (1.0f + expf(-gs.z))) * us.z;
+    h.w = (gs.w / (1.0f + expf(-gs.w))) * us.w;
+    float m = warp_max(fmaxf(fmaxf(fabsf(h.x), fabsf(h.y)), fmaxf(fabsf(h.z), fabsf(h.w))));
+    float s = block_scale_from_max(m);
+    store_split4(dst, lane, h, s);
+    return 1.f / s;
+}
+
 // Consumes every task of the phase that belongs to this warp. `prod` must have
 // been initialised (and possibly primed) by the caller.
-template <int MODE>
+//   bq / bscale : B operand fragments and inverse block scales (generic pointers:
+//                 global memory, or this CTA's shared memory)
+//   slot        : when non-null (phase 2, activations in shared memory) the warp first
+//                 computes the SwiGLU slice of each task into this private slot
+//                 ([row][block][256 halfs], then the scales) and reads B from it
+template <int MODE, int NST>
 __device__ __forceinline__ bool dec_consume_phase(WarpRing &wr, DecIter &prod, const DecPhase &ph,
                                                   const DecodeArgs &a, const DecShared *sh, int p0, int P,
-                                                  int lane) {
+                                                  int lane, const __half *bq, const float *bscale,
+                                                  uint8_t *slot) {
     constexpr int CH = CODE_BYTES + (MODE == SC_H16 ? 256 : MODE == SC_F32 ? 512 : MODE == SC_MX ? 128 : 0);
     const int g = lane >> 2, t = lane & 3;
     DecIter cons;
@@ -236,24 +337,48 @@ __device__ __forceinline__ bool dec_consume_phase(WarpRing &wr, DecIter &prod, c
         int seg_i, tile, kpart;
         dec_task_setup<CH>(cons, ph, a, sh, seg_i, tile, kpart);
         const DecPass &ps = sh->pass[ph.which == 1 ? (seg_i >> 1) : seg_i];
-        const int nrows = ps.nrows, nkb = ph.nkb;
+        const int nrows = ps.nrows;
+        int b_nkb = ph.nkb, b_kb0 = 0;     // B operand addressing: row stride in blocks, first block
         const int rb = g >> 1;
         const bool bvalid = rb < nrows;
-        const int rid_b = bvalid ? (ph.which == 1 ? ps.rowid[rb] : ps.pos0 + rb) : 0;
-        const __half *bptr = ph.bq + (size_t)rid_b * nkb * 256 + (g & 1) * 32 + t * 8;
         const bool svalid = t < nrows;
-        const int rid_s = svalid ? (ph.which == 1 ? ps.rowid[t] : ps.pos0 + t) : 0;
-        const float *sptr = ph.bscale + (size_t)rid_s * nkb;
+        int rid_b = bvalid ? (ph.which == 1 ? ps.rowid[rb] : ps.pos0 + rb) : 0;
+        int rid_s = svalid ? (ph.which == 1 ? ps.rowid[t] : ps.pos0 + t) : 0;
+        const __half *bbase = bq;
+        const float *sbase = bscale;
+        if (slot) {
+            const int kbpp = ph.kb_per_part;
+            __half *hq = reinterpret_cast<__half *>(slot);
+            float *hs = reinterpret_cast<float *>(slot + 4096);
+            __syncwarp();
+            for (int r = 0; r < nrows; r++)
+                for (int j = 0; j < kbpp; j++) {
+                    float inv = dec_swiglu_block(a, ph.npos, ps.pos0 + r, cons.kb + j, lane,
+                                                 hq + (size_t)(r * kbpp + j) * 256);
+                    if (lane == 0) hs[r * kbpp + j] = inv;
+                }
+            __syncwarp();
+            b_nkb = kbpp; b_kb0 = cons.kb;
+            rid_b = rb; rid_s = t;
+            bbase = hq; sbase = hs;
+        }
+        const __half *bptr = bbase + ((size_t)rid_b * b_nkb - b_kb0) * 256 + (g & 1) * 32 + t * 8;
+        const float *sptr = sbase + (size_t)rid_s * b_nkb - b_kb0;
         float R[2][4];
 #pragma unroll
         for (int s = 0; s < 2; s++)
 #pragma unroll
             for (int i = 0; i < 4; i++) R[s][i] = 0.f;
         for (int kb = cons.kb; kb < cons.kb_end; kb++) {
-            const int stage = wr.consumed % DEC_NST;
+            const int stage = wr.consumed % NST;
             const uint32_t st = wr.ring + stage * CH;
             float ixs = svalid ? sptr[kb] : 0.f;
-            if (!mbar_wait_bounded(wr.bars + stage * 8, (wr.consumed / DEC_NST) & 1)) return false;
+            uint4 b[4];
+#pragma unroll
+            for (int grp = 0; grp < 4; grp++)
+                b[grp] = bvalid ? *reinterpret_cast<const uint4 *>(bptr + (size_t)kb * 256 + grp * 64)
+                                : make_uint4(0, 0, 0, 0);
+            if (!mbar_wait_bounded(wr.bars + stage * 8, (wr.consumed / NST) & 1)) return false;
             uint4 w[4];
 #pragma unroll
             for (int j = 0; j < 4; j++) w[j] = lds128(st + j * 512 + lane * 16);
@@ -280,7 +405,6 @@ __device__ __forceinline__ bool dec_consume_phase(WarpRing &wr, DecIter &prod, c
                 for (int i = 0; i < 4; i++) bacc[s][i] = 0.f;
 #pragma unroll
             for (int grp = 0; grp < 4; grp++) {
-                uint4 b = bvalid ? ldg128(bptr + (size_t)kb * 256 + grp * 64) : make_uint4(0, 0, 0, 0);
 #pragma unroll
                 for (int s = 0; s < 2; s++) {
                     uint32_t a_lo[4], a_hi[4];
@@ -301,8 +425,8 @@ __device__ __forceinline__ bool dec_consume_phase(WarpRing &wr, DecIter &prod, c
                         s1 = __uint_as_float(((sc8[s].y >> (8 * grp)) & 0xFFu) << 23);
                     }
                     float c[4] = {0.f, 0.f, 0.f, 0.f};
-                    mma_f16(c, a_lo[0], a_hi[0], a_lo[1], a_hi[1], b.x, b.y);
-                    mma_f16(c, a_lo[2], a_hi[2], a_lo[3], a_hi[3], b.z, b.w);
+                    mma_f16(c, a_lo[0], a_hi[0], a_lo[1], a_hi[1], b[grp].x, b[grp].y);
+                    mma_f16(c, a_lo[2], a_hi[2], a_lo[3], a_hi[3], b[grp].z, b[grp].w);
                     if (MODE == SC_ROW) {
                         bacc[s][0] += c[0]; bacc[s][1] += c[1]; bacc[s][2] += c[2]; bacc[s][3] += c[3];
                     } else {
@@ -319,7 +443,7 @@ __device__ __forceinline__ bool dec_consume_phase(WarpRing &wr, DecIter &prod, c
                 for (int i = 0; i < 4; i++) R[s][i] = fmaf(bacc[s][i], ixs, R[s][i]);
             wr.consumed++;
             __syncwarp();
-            dec_issue_one<CH>(wr, prod, ph, a, sh, P, lane);
+            dec_issue_one<CH, NST>(wr, prod, ph, a, sh, P, lane);
         }
         const float mx_fix = (MODE == SC_MX) ? 16384.f : 1.f;
         if (t < nrows) {
@@ -349,45 +473,82 @@ __device__ __forceinline__ bool dec_consume_phase(WarpRing &wr, DecIter &prod, c
     return true;
 }
 
+template <int MODE> struct DecCfg { static constexpr int NST = MODE == SC_F32 ? 3 : 4; };
+
 template <int MODE>
 __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) {
     constexpr int CH = CODE_BYTES + (MODE == SC_H16 ? 256 : MODE == SC_F32 ? 512 : MODE == SC_MX ? 128 : 0);
+    constexpr int NST = DecCfg<MODE>::NST;
     extern __shared__ __align__(128) uint8_t smem[];
-    // layout: rings | mbarriers | DecShared | routing scratch (M * 2E floats)
-    DecShared *sh = reinterpret_cast<DecShared *>(smem + DEC_WARPS * DEC_NST * (CH + 8));
-    float *rscratch = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(sh) + ((sizeof(DecShared) + 15) & ~15));
+    // layout: rings | mbarriers | DecShared | activation region (act_smem only)
+    // The routing scratch (2E floats per routed row) lives in the routing warp's own
+    // ring, which carries no data before the first copy is issued.
+    DecShared *sh = reinterpret_cast<DecShared *>(smem + DEC_WARPS * NST * (CH + 8));
+    uint8_t *act = reinterpret_cast<uint8_t *>(sh) + ((sizeof(DecShared) + 127) & ~127);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
     const RouteRule &r = a.rule;
     const int E = r.E, K = r.K, M = a.M, D = r.D, I = r.I;
+    const int nkb1 = D / BLOCK_K, nkb2 = I / BLOCK_K;
     WarpRing wr;
-    wr.ring = smem_u32(smem) + warp * (DEC_NST * CH);
-    wr.bars = smem_u32(smem) + DEC_WARPS * DEC_NST * CH + warp * DEC_NST * 8;
+    wr.ring = smem_u32(smem) + warp * (NST * CH);
+    wr.bars = smem_u32(smem) + DEC_WARPS * NST * CH + warp * NST * 8;
     wr.issued = 0; wr.consumed = 0;
+    dec_probe(a, 0);
     if (lane == 0) {
-        for (int s = 0; s < DEC_NST; s++) mbar_init(wr.bars + s * 8, 1);
+        for (int s = 0; s < NST; s++) mbar_init(wr.bars + s * 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (tid == 0) sh->failed = 0;
+    if (tid == 0) { sh->failed = 0; sh->nu = 0; }
+    if (warp == DEC_WARPS - 1) sh->exp_tab[lane] = c_exp2_tab[lane];
     for (int e = tid; e < E; e += blockDim.x) { sh->first[e] = 0x7fffffff; sh->cnt[e] = 0; }
     __syncthreads();
 
-    // ---- routing, redundantly in every CTA -----------------------------------
-    if (warp < M)
-        route_row_warp(a.logits + (size_t)warp * E, a.router_bias, r, rscratch + (size_t)warp * 2 * E,
-                       rscratch + (size_t)warp * 2 * E + E, sh->idx + warp * K, sh->w + warp * K,
-                       sh->keff + warp, lane);
+    // ---- routing in warps 0..M-1 (redundantly in every CTA); meanwhile the other
+    // warps split x into this CTA's shared memory when the activations live there ----
+    __half *xq_s = reinterpret_cast<__half *>(act);
+    float *xs_s = reinterpret_cast<float *>(act + (size_t)M * nkb1 * 512);
+    if (warp < M) {
+        float *scratch = reinterpret_cast<float *>(smem + (size_t)warp * (NST * CH));
+        route_row_warp(a.logits + (size_t)warp * E, a.router_bias, r, scratch, scratch + E, sh->idx + warp * K,
+                       sh->w + warp * K, sh->keff + warp, lane, reinterpret_cast<const uint64_t *>(sh->exp_tab));
+        if (warp == 0 && lane == 0) dec_probe_lane(a, 10);
+    }
+    if (a.act_smem) {
+        const int nhelp = DEC_WARPS > M ? DEC_WARPS - M : DEC_WARPS;
+        const int me = DEC_WARPS > M ? warp - M : warp;
+        if (me >= 0)
+            for (int wid = me; wid < M * nkb1; wid += nhelp) {
+                int row = wid / nkb1, kb = wid - row * nkb1;
+                float4 v = *reinterpret_cast<const float4 *>(a.x + (size_t)row * D + kb * BLOCK_K + lane * 4);
+                float m = warp_max(fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+                float s = block_scale_from_max(m);
+                store_split4(xq_s + ((size_t)row * nkb1 + kb) * 256, lane, v, s);
+                if (lane == 0) xs_s[(size_t)row * nkb1 + kb] = 1.f / s;
+            }
+        if (me == 0 && lane == 0) dec_probe_lane(a, 11);
+    }
     __syncthreads();
+    if (a.act_smem) dec_probe(a, 2);   // rows routed, x split
+    // the routing scratch was written through the generic proxy into memory that the
+    // bulk copies (async proxy) overwrite next
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     for (int i = tid; i < M * K; i += blockDim.x) {
         int s = i / K, kk = i - s * K;
         if (kk < sh->keff[s]) { int e = sh->idx[i]; atomicMin(&sh->first[e], i); atomicAdd(&sh->cnt[e], 1); }
     }
-    if (tid == 0) sh->nu = 0;
     __syncthreads();
-    for (int e = tid; e < E; e += blockDim.x) {
-        if (sh->cnt[e] > 0) {
+    // union in first-appearance order: entry i opens a new expert iff it is that
+    // expert's first entry; its rank is the number of such entries before it
+    for (int i = tid; i < M * K; i += blockDim.x) {
+        int s = i / K, kk = i - s * K;
+        sh->pos_of[i] = (kk < sh->keff[s] && sh->first[sh->idx[i]] == i) ? 1 : 0;
+    }
+    __syncthreads();
+    for (int i = tid; i < M * K; i += blockDim.x) {
+        if (sh->pos_of[i]) {
             int rank = 0;
-            for (int o = 0; o < E; o++) rank += (sh->cnt[o] > 0 && sh->first[o] < sh->first[e]);
-            sh->uniq[rank] = e;
+            for (int q = 0; q < i; q++) rank += sh->pos_of[q];
+            sh->uniq[rank] = sh->idx[i];
             atomicAdd(&sh->nu, 1);
         }
     }
@@ -435,106 +596,139 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
         }
         if (a.keff_out) for (int s = tid; s < M; s += blockDim.x) a.keff_out[s] = sh->keff[s];
     }
+    dec_probe(a, 1);   // routing and tables done
     const int npass = sh->npass, npos = sh->npos;
-    const int P = gridDim.x * DEC_WARPS, p0 = blockIdx.x * DEC_WARPS + warp;
-    const unsigned long long bar_base = a.epoch * DEC_NBAR * gridDim.x;
+    // task t goes to CTA t % grid, so every SM gets the same number of tasks (+-1)
+    const int P = gridDim.x * DEC_WARPS, p0 = warp * gridDim.x + blockIdx.x;
+    unsigned long long bar_target = a.bar_base;
 
     DecPhase ph1, ph2;
-    ph1.which = 1; ph1.ntiles = I / TILE_ROWS; ph1.nkb = D / BLOCK_K; ph1.nkpart = a.nkp1;
-    ph1.kb_per_part = ph1.nkb / a.nkp1; ph1.tps = ph1.ntiles * a.nkp1; ph1.ntask = 2 * npass * ph1.tps;
-    ph1.O = I; ph1.npos = npos; ph1.bq = a.xq; ph1.bscale = a.xs;
-    ph2.which = 2; ph2.ntiles = D / TILE_ROWS; ph2.nkb = I / BLOCK_K; ph2.nkpart = a.nkp2;
-    ph2.kb_per_part = ph2.nkb / a.nkp2; ph2.tps = ph2.ntiles * a.nkp2; ph2.ntask = npass * ph2.tps;
-    ph2.O = D; ph2.npos = npos; ph2.bq = a.hq; ph2.bscale = a.hs;
+    ph1.which = 1; ph1.ntiles = I / TILE_ROWS; ph1.nkb = nkb1; ph1.nkpart = a.nkp1;
+    ph1.kb_per_part = nkb1 / a.nkp1; ph1.tps = ph1.ntiles * a.nkp1; ph1.ntask = 2 * npass * ph1.tps;
+    ph1.O = I; ph1.npos = npos;
+    ph2.which = 2; ph2.ntiles = D / TILE_ROWS; ph2.nkb = nkb2; ph2.nkpart = a.nkp2;
+    ph2.kb_per_part = nkb2 / a.nkp2; ph2.tps = ph2.ntiles * a.nkp2; ph2.ntask = npass * ph2.tps;
+    ph2.O = D; ph2.npos = npos;
 
-    // ---- start the gate/up weight stream, then split the activations ---------
+    // ---- start the gate/up weight stream ------------------------------------------
     DecIter prod;
     prod.task = p0;
     int d0, d1, d2;
     if (prod.task < ph1.ntask) dec_task_setup<CH>(prod, ph1, a, sh, d0, d1, d2);
-    for (int s = 0; s < DEC_NST; s++) dec_issue_one<CH>(wr, prod, ph1, a, sh, P, lane);
-    {
-        const int nkb = D / BLOCK_K;
-        for (int wid = p0; wid < M * nkb; wid += P) {
-            int row = wid / nkb, kb = wid - row * nkb;
+    for (int s = 0; s < NST; s++) dec_issue_one<CH, NST>(wr, prod, ph1, a, sh, P, lane);
+    bool ok = true;
+    if (!a.act_smem) {
+        // activations through global memory: distributed split, then a barrier
+        for (int wid = p0; wid < M * nkb1; wid += P) {
+            int row = wid / nkb1, kb = wid - row * nkb1;
             float4 v = *reinterpret_cast<const float4 *>(a.x + (size_t)row * D + kb * BLOCK_K + lane * 4);
             float m = warp_max(fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
             float s = block_scale_from_max(m);
-            store_split4(a.xq + ((size_t)row * nkb + kb) * 256, lane, v, s);
-            if (lane == 0) a.xs[(size_t)row * nkb + kb] = 1.f / s;
+            store_split4(a.xq + ((size_t)row * nkb1 + kb) * 256, lane, v, s);
+            if (lane == 0) a.xs[(size_t)row * nkb1 + kb] = 1.f / s;
         }
+        dec_probe(a, 2);
+        bar_target += gridDim.x;
+        ok = grid_barrier(a.bar, bar_target, &sh->failed);
     }
-    bool ok = grid_barrier(a.bar, bar_base + 1ULL * gridDim.x, &sh->failed);
-    // ---- gate / up ------------------------------------------------------------
-    if (ok) ok = dec_consume_phase<MODE>(wr, prod, ph1, a, sh, p0, P, lane);
+    dec_probe(a, 3);
+    // ---- gate / up ------------------------------------------------------------------
+    if (ok) ok = dec_consume_phase<MODE, NST>(wr, prod, ph1, a, sh, p0, P, lane, a.act_smem ? xq_s : a.xq,
+                                              a.act_smem ? xs_s : a.xs, nullptr);
     if (!ok) sh->failed = 1;
     // start the down weight stream before waiting for the other CTAs
     prod.task = p0;
     if (ok && prod.task < ph2.ntask) dec_task_setup<CH>(prod, ph2, a, sh, d0, d1, d2);
-    if (ok) for (int s = 0; s < DEC_NST; s++) dec_issue_one<CH>(wr, prod, ph2, a, sh, P, lane);
-    ok = grid_barrier(a.bar, bar_base + 2ULL * gridDim.x, &sh->failed) && ok;
-    // ---- SwiGLU + split of h, distributed ----------------------------------------
-    if (ok) {
-        const int nkb = I / BLOCK_K;
-        for (int wid = p0; wid < npos * nkb; wid += P) {
-            int pos = wid / nkb, kb = wid - pos * nkb;
-            float4 gs = make_float4(0, 0, 0, 0), us = gs;
-            for (int kp = 0; kp < a.nkp1; kp++) {
-                size_t off = ((size_t)kp * npos + pos) * I + kb * BLOCK_K + lane * 4;
-                float4 ga = *reinterpret_cast<const float4 *>(a.partG + off);
-                float4 ua = *reinterpret_cast<const float4 *>(a.partU + off);
-                gs.x += ga.x; gs.y += ga.y; gs.z += ga.z; gs.w += ga.w;
-                us.x += ua.x; us.y += ua.y; us.z += ua.z; us.w += ua.w;
+    if (ok) for (int s = 0; s < NST; s++) dec_issue_one<CH, NST>(wr, prod, ph2, a, sh, P, lane);
+    dec_probe(a, 4);   // gate/up consumed, down stream primed
+    bar_target += gridDim.x;
+    ok = grid_barrier(a.bar, bar_target, &sh->failed) && ok;
+    dec_probe(a, 5);
+    if (!a.act_smem) {
+        // SwiGLU + split of h, distributed, then a barrier
+        if (ok)
+            for (int wid = p0; wid < npos * nkb2; wid += P) {
+                int pos = wid / nkb2, kb = wid - pos * nkb2;
+                float inv = dec_swiglu_block(a, npos, pos, kb, lane, a.hq + ((size_t)pos * nkb2 + kb) * 256);
+                if (lane == 0) a.hs[(size_t)pos * nkb2 + kb] = inv;
             }
-            float4 h;
-            h.x = (gs.x / (1.0f + expf(-gs.x))) * us.x;
-            h.y = (gs.y / (1.0f + expf(-gs.y))) * us.y;
-            h.z = (gs.z / (1.0f + expf(-gs.z))) * us.z;
-            h.w = (gs.w / (1.0f + expf(-gs.w))) * us.w;
-            float m = warp_max(fmaxf(fmaxf(fabsf(h.x), fabsf(h.y)), fmaxf(fabsf(h.z), fabsf(h.w))));
-            float s = block_scale_from_max(m);
-            store_split4(a.hq + ((size_t)pos * nkb + kb) * 256, lane, h, s);
-            if (lane == 0) a.hs[(size_t)pos * nkb + kb] = 1.f / s;
-        }
+        dec_probe(a, 6);
+        bar_target += gridDim.x;
+        ok = grid_barrier(a.bar, bar_target, &sh->failed) && ok;
     }
-    ok = grid_barrier(a.bar, bar_base + 3ULL * gridDim.x, &sh->failed) && ok;
-    // ---- down -------------------------------------------------------------------
-    if (ok) ok = dec_consume_phase<MODE>(wr, prod, ph2, a, sh, p0, P, lane);
+    dec_probe(a, 7);
+    // ---- down -------------------------------------------------------------------------
+    if (ok) ok = dec_consume_phase<MODE, NST>(wr, prod, ph2, a, sh, p0, P, lane, a.hq, a.hs,
+                                              a.act_smem ? act + (size_t)warp * DEC_SLOT_BYTES : nullptr);
     if (!ok) sh->failed = 1;
-    ok = grid_barrier(a.bar, bar_base + 4ULL * gridDim.x, &sh->failed) && ok;
-    // ---- weighted combine: selection order per row, shared expert last ------------
+    dec_probe(a, 8);   // down consumed
+    bar_target += gridDim.x;
+    ok = grid_barrier(a.bar, bar_target, &sh->failed) && ok;
+    // ---- weighted combine: selection order per row, shared expert last ------------------
+    // One warp per float4 of the output; its lanes take the (selected expert, slice)
+    // terms w*partial round-robin (the shared expert's slices last, weight 1) and a
+    // fixed shuffle tree adds the lanes: deterministic, and every load is in flight at once.
     if (ok) {
         const int dq = D / 4;
-        for (int i = blockIdx.x * blockDim.x + tid; i < M * dq; i += gridDim.x * blockDim.x) {
+        const int gw = blockIdx.x * DEC_WARPS + warp;
+        for (int i = gw; i < M * dq; i += P) {
             int s = i / dq, d4 = i - s * dq;
+            const int ke = sh->keff[s];
+            const int nterm = (ke + (a.tab.sh_gate_pk ? 1 : 0)) * a.nkp2;
             float4 acc = make_float4(0, 0, 0, 0);
-            int ke = sh->keff[s];
-            for (int kk = 0; kk < ke; kk++) {
-                int pos = sh->pos_of[s * K + kk];
-                float wgt = sh->w[s * K + kk];
-                float4 y = make_float4(0, 0, 0, 0);
-                for (int kp = 0; kp < a.nkp2; kp++) {
-                    float4 v = reinterpret_cast<const float4 *>(a.partD + ((size_t)kp * npos + pos) * D)[d4];
-                    y.x += v.x; y.y += v.y; y.z += v.z; y.w += v.w;
-                }
-                acc.x += wgt * y.x; acc.y += wgt * y.y; acc.z += wgt * y.z; acc.w += wgt * y.w;
+            for (int term = lane; term < nterm; term += 32) {
+                int kk = term / a.nkp2, kp = term - kk * a.nkp2;
+                int pos; float wgt;
+                if (kk < ke) { pos = sh->pos_of[s * K + kk]; wgt = sh->w[s * K + kk]; }
+                else { pos = sh->shared_pos0 + s; wgt = 1.f; }
+                float4 v = reinterpret_cast<const float4 *>(a.partD + ((size_t)kp * npos + pos) * D)[d4];
+                acc.x = fmaf(wgt, v.x, acc.x); acc.y = fmaf(wgt, v.y, acc.y);
+                acc.z = fmaf(wgt, v.z, acc.z); acc.w = fmaf(wgt, v.w, acc.w);
             }
-            if (a.tab.sh_gate_pk) {
-                int pos = sh->shared_pos0 + s;
-                float4 y = make_float4(0, 0, 0, 0);
-                for (int kp = 0; kp < a.nkp2; kp++) {
-                    float4 v = reinterpret_cast<const float4 *>(a.partD + ((size_t)kp * npos + pos) * D)[d4];
-                    y.x += v.x; y.y += v.y; y.z += v.z; y.w += v.w;
-                }
-                acc.x += y.x; acc.y += y.y; acc.z += y.z; acc.w += y.w;
+#pragma unroll
+            for (int off = 16; off; off >>= 1) {
+                acc.x += __shfl_xor_sync(0xffffffffu, acc.x, off);
+                acc.y += __shfl_xor_sync(0xffffffffu, acc.y, off);
+                acc.z += __shfl_xor_sync(0xffffffffu, acc.z, off);
+                acc.w += __shfl_xor_sync(0xffffffffu, acc.w, off);
             }
-            reinterpret_cast<float4 *>(a.out)[i] = acc;
+            if (lane == 0) reinterpret_cast<float4 *>(a.out)[i] = acc;
         }
     }
+    dec_probe(a, 9);
     if (!ok) {
         if (tid == 0) atomicExch(a.status, sh->failed ? KSTAT_GRID_TIMEOUT : KSTAT_MBAR_TIMEOUT);
         // drain copies still in flight before the shared memory goes away (bounded)
         for (int i = wr.consumed; i < wr.issued; i++)
-            if (!mbar_wait_bounded(wr.bars + (i % DEC_NST) * 8, (i / DEC_NST) & 1)) break;
+            if (!mbar_wait_bounded(wr.bars + (i % NST) * 8, (i / NST) & 1)) break;
+    }
+}
+
+// Stand-alone routing kernel of the multi-kernel path: one warp per row, E <= 1024,
+// K <= 64; the same routing function as the fused kernel.
+__global__ void k_route_topk(const float *__restrict__ logits, const float *__restrict__ bias,
+                             RouteRule rule, int M, int *__restrict__ idx_out,
+                             float *__restrict__ w_out, int *__restrict__ keff_out) {
+    extern __shared__ float sm_route[];
+    __shared__ unsigned long long s_tab[32];
+    const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int E = rule.E, K = rule.K;
+    if (threadIdx.x < 32) s_tab[threadIdx.x] = c_exp2_tab[threadIdx.x];
+    __syncthreads();
+    float *score = sm_route + (size_t)warp * (2 * E + 2 * ROUTE_MAX_K);
+    float *choice = score + E;
+    int *idx = reinterpret_cast<int *>(choice + E);
+    float *wk = reinterpret_cast<float *>(idx + ROUTE_MAX_K);
+    __shared__ int s_keff[32];
+    int s = blockIdx.x * warps + warp;
+    if (s >= M) return;
+    route_row_warp(logits + (size_t)s * E, bias, rule, score, choice, idx, wk, &s_keff[warp], lane,
+                   reinterpret_cast<const uint64_t *>(s_tab));
+    if (lane == 0) {
+        for (int kk = 0; kk < K; kk++) {
+            idx_out[(size_t)s * K + kk] = idx[kk];
+            w_out[(size_t)s * K + kk] = wk[kk];
+        }
+        keff_out[s] = s_keff[warp];
     }
 }

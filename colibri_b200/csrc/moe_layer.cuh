@@ -96,7 +96,9 @@ extern "C" void coli_cuda_moe_layer_free(ColiCudaMoeLayer *L) {
 }
 
 static int g_fused_decode = 1;
-extern "C" void coli_cuda_set_fused_decode(int enabled) { g_fused_decode = enabled ? 1 : 0; }
+static unsigned long long *g_decode_probe = nullptr;
+extern "C" void coli_cuda_set_decode_probe(void *dev_buffer) { g_decode_probe = static_cast<unsigned long long *>(dev_buffer); }
+extern "C" void coli_cuda_set_fused_decode(int enabled) { g_fused_decode = enabled; }
 
 struct LayerPlan {
     int nc, rpp, nkp1, nkp2, seg_cap, npos_cap;
@@ -156,6 +158,16 @@ static int layer_run(ColiCudaMoeLayer *L, DeviceCtx *c, float *out_dev, const fl
         long passes = (long)(M * r.K < r.E ? M * r.K : r.E) + (L->has_shared ? (M + 3) / 4 : 0);
         q.nkp1 = pick_nkpart(nkb1, 2 * passes * (r.I / TILE_ROWS), c->sms);
         q.nkp2 = pick_nkpart(nkb2, passes * (r.D / TILE_ROWS), c->sms);
+        // activations in shared memory: x fragments (M*D*4 B + scales) must fit the region, and
+        // the h slice of one down task (rows <= min(M,4), nkb2/nkp2 blocks of 512 B) its slot
+        int act_smem = (size_t)M * r.D * 4 + (size_t)M * nkb1 * 4 <= DEC_ACT_BYTES + 2048;
+        if (act_smem) {
+            int rows = M < 4 ? M : 4;
+            int nk = q.nkp2;
+            while (nk < nkb2 && (nkb2 % nk || rows * (nkb2 / nk) > 8)) nk++;
+            if (nkb2 % nk == 0 && rows * (nkb2 / nk) <= 8) q.nkp2 = nk;
+            else act_smem = 0;
+        }
         if (!reserve(c, &L->pg, (size_t)q.nkp1 * p.npos_cap * r.I * sizeof(float)) ||
             !reserve(c, &L->pu, (size_t)q.nkp1 * p.npos_cap * r.I * sizeof(float)) ||
             !reserve(c, &L->pd, (size_t)q.nkp2 * p.npos_cap * r.D * sizeof(float))) return 0;
@@ -166,8 +178,9 @@ static int layer_run(ColiCudaMoeLayer *L, DeviceCtx *c, float *out_dev, const fl
         a.xq = (__half *)L->xq.p; a.xs = (float *)L->xs.p;
         a.partG = (float *)L->pg.p; a.partU = (float *)L->pu.p;
         a.hq = (__half *)L->hq.p; a.hs = (float *)L->hs.p; a.partD = (float *)L->pd.p;
-        a.bar = c->gridbar; a.epoch = c->epoch++; a.status = c->status;
-        a.M = M; a.nkp1 = q.nkp1; a.nkp2 = q.nkp2;
+        a.bar = c->gridbar; a.bar_base = c->epoch; a.status = c->status;
+        c->epoch += (unsigned long long)(act_smem ? 2 : 4) * (unsigned long long)c->sms;
+        a.M = M; a.nkp1 = q.nkp1; a.nkp2 = q.nkp2; a.act_smem = act_smem; a.probe = g_decode_probe;
         void *args[] = {&a};
         const void *fn = L->mode_gu == SC_ROW ? (const void *)k_moe_decode<SC_ROW>
                        : L->mode_gu == SC_H16 ? (const void *)k_moe_decode<SC_H16>
@@ -176,8 +189,11 @@ static int layer_run(ColiCudaMoeLayer *L, DeviceCtx *c, float *out_dev, const fl
         cudaEvent_t e0 = nullptr, e1 = nullptr;
         kernel_event_pair(c, &e0, &e1);
         if (e0) cudaEventRecord(e0, c->stream);
-        cudaError_t err = cudaLaunchCooperativeKernel(fn, dim3(c->sms), dim3(DEC_WARPS * 32), args,
-                                                      (size_t)decode_smem_bytes(L->mode_gu), c->stream);
+        // g_fused_decode == 2: plain launch (experiment; the grid still fits the device)
+        cudaError_t err = g_fused_decode == 2
+            ? cudaLaunchKernel(fn, dim3(c->sms), dim3(DEC_WARPS * 32), args, (size_t)decode_smem_bytes(L->mode_gu), c->stream)
+            : cudaLaunchCooperativeKernel(fn, dim3(c->sms), dim3(DEC_WARPS * 32), args,
+                                          (size_t)decode_smem_bytes(L->mode_gu), c->stream);
         if (e1) cudaEventRecord(e1, c->stream);
         c->last_launches++;
         return cuda_ok(err, "fused decode launch");

@@ -45,100 +45,8 @@ __global__ void k_router_logits(float *__restrict__ logits, const float *__restr
     logits[i] = a;
 }
 
-// One warp per row. E <= 1024, K <= 64. Scores live in shared memory.
-// Selection: K passes; each lane scans its strided candidates for the largest
-// value above -1e30 (strict '>' in ascending index order keeps the lowest index
-// among equals), then a shuffle reduction keeps the larger value, or the lower
-// index on equal values. A pass that finds nothing (all NaN) degrades to
-// expert kk, as the engine does.
 #define ROUTE_MAX_E 1024
 #define ROUTE_MAX_K 64
-__global__ void k_route_topk(const float *__restrict__ logits, const float *__restrict__ bias,
-                             RouteRule rule, int M, int *__restrict__ idx_out,
-                             float *__restrict__ w_out, int *__restrict__ keff_out) {
-    extern __shared__ float sm_route[];
-    const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int E = rule.E, K = rule.K;
-    float *score = sm_route + (size_t)warp * (2 * E + 2 * ROUTE_MAX_K);   // value used as weight
-    float *choice = score + E;                                           // value used for selection
-    int *idx = reinterpret_cast<int *>(choice + E);
-    float *wk = reinterpret_cast<float *>(idx + ROUTE_MAX_K);
-    int s = blockIdx.x * warps + warp;
-    if (s >= M) return;
-    const float *z = logits + (size_t)s * E;
-
-    if (rule.gating == 0) {
-        float m = -1e30f;
-        for (int e = lane; e < E; e += 32) { float v = z[e]; if (v > m) m = v; }
-#pragma unroll
-        for (int off = 16; off; off >>= 1) { float o = __shfl_xor_sync(0xffffffffu, m, off); if (o > m) m = o; }
-        for (int e = lane; e < E; e += 32) score[e] = expf_host_exact(__fsub_rn(z[e], m));
-        __syncwarp();
-        float tot = 0.f;
-        if (lane == 0) for (int e = 0; e < E; e++) tot = __fadd_rn(tot, score[e]);
-        tot = __shfl_sync(0xffffffffu, tot, 0);
-        for (int e = lane; e < E; e += 32) { float p = __fdiv_rn(score[e], tot); score[e] = p; choice[e] = p; }
-    } else {
-        for (int e = lane; e < E; e += 32) {
-            float sg = __fdiv_rn(1.f, __fadd_rn(1.f, expf_host_exact(-z[e])));
-            score[e] = sg;
-            choice[e] = bias ? __fadd_rn(sg, bias[e]) : sg;
-        }
-    }
-    __syncwarp();
-    for (int kk = 0; kk < K; kk++) {
-        int best = -1;
-        float bv = -1e30f;
-        for (int e = lane; e < E; e += 32) {
-            float c = choice[e];
-            if (c > bv) { bv = c; best = e; }
-        }
-#pragma unroll
-        for (int off = 16; off; off >>= 1) {
-            float ov = __shfl_xor_sync(0xffffffffu, bv, off);
-            int ob = __shfl_xor_sync(0xffffffffu, best, off);
-            bool take = ob >= 0 && (best < 0 || ov > bv || (ov == bv && ob < best));
-            if (take) { bv = ov; best = ob; }
-        }
-        if (best < 0) best = kk < E ? kk : 0;
-        if (lane == 0) {
-            idx[kk] = best;
-            wk[kk] = score[best];
-            choice[best] = __uint_as_float(0x7fc00000u);   // taken: NaN never compares greater
-        }
-        __syncwarp();
-    }
-    if (lane == 0) {
-        int Ke = K;
-        if (rule.gating == 1 && rule.topp > 0.f && rule.topp < 1.f) {
-            for (int a = 1; a < K; a++) {
-                int ii = idx[a]; float ww = wk[a]; int b = a - 1;
-                while (b >= 0 && wk[b] < ww) { wk[b + 1] = wk[b]; idx[b + 1] = idx[b]; b--; }
-                wk[b + 1] = ww; idx[b + 1] = ii;
-            }
-            float tot = 1e-20f;
-            for (int kk = 0; kk < K; kk++) tot = __fadd_rn(tot, wk[kk]);
-            float cum = 0.f;
-            for (int kk = 0; kk < K; kk++) {
-                cum = __fadd_rn(cum, wk[kk]);
-                if (cum >= __fmul_rn(rule.topp, tot)) { Ke = kk + 1; break; }
-            }
-        }
-        if (rule.norm_topk) {
-            float sm = 0.f;
-            for (int kk = 0; kk < Ke; kk++) sm = __fadd_rn(sm, wk[kk]);
-            if (rule.gating == 1) sm = __fadd_rn(sm, 1e-20f);
-            for (int kk = 0; kk < Ke; kk++) wk[kk] = __fdiv_rn(wk[kk], sm);
-        }
-        if (rule.gating == 1)
-            for (int kk = 0; kk < Ke; kk++) wk[kk] = __fmul_rn(wk[kk], rule.routed_scale);
-        for (int kk = 0; kk < K; kk++) {
-            idx_out[(size_t)s * K + kk] = idx[kk];
-            w_out[(size_t)s * K + kk] = wk[kk];
-        }
-        keff_out[s] = Ke;
-    }
-}
 
 // Per-layer device tables the build kernel reads.
 struct LayerTables {

@@ -226,6 +226,13 @@ void coli_cuda_set_timing(int enabled);
  * kernel; 0 routes them through the multi-kernel path instead (A/B testing). */
 void coli_cuda_set_fused_decode(int enabled);
 
+/* Phase probe of the fused decode kernel: with a device buffer of
+ * (#SMs x 12) 64-bit words set, thread 0 of every CTA stores the global
+ * nanosecond timer at each phase boundary of the next launches (start, routed,
+ * split written, barrier, gate/up done, barrier, SwiGLU written, barrier, down
+ * done, end, routing warp done, first helper warp's split done). NULL (the default) turns it off. */
+void coli_cuda_set_decode_probe(void *dev_buffer);
+
 /* Per-kernel timing of the dominant kernel: while enabled, every launch of the
  * streaming GEMV and of the fused decode kernel is bracketed by a CUDA event pair on the backend's stream.
  * coli_cuda_kernel_events synchronises, returns the summed duration and the

@@ -27,7 +27,9 @@
 // (j, lane, grp) carries row sub*16+h*8+g, columns grp*32 + 8t + {0..7}, as
 // eight 4-bit fields in the order {0,2,4,6,1,3,5,7} (field f at bits 4f..4f+3),
 // which lets two mask operations split a word into the (k, k+1) half2 pairs
-// the fragment wants.
+// the fragment wants. (A group-major order with 32-bit loads and a rolled loop
+// over the groups was measured slower: the kernels are bound by the integer
+// pipe, so fewer, wider loads win over a smaller instruction footprint.)
 //   int4 (fmt 2, 4): a field is the stored offset-binary nibble (value+8).
 //   MXFP4 (fmt 7):   the four (k,k+1) pairs A,B,C,D of a word are re-encoded so
 //                    that each decodes with shifts and masks straight into

@@ -31,6 +31,7 @@
 #pragma once
 #include "common.cuh"
 
+
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return (uint32_t)__cvta_generic_to_shared(p);
 }
@@ -119,6 +120,81 @@ __device__ __forceinline__ void decode_word(uint32_t q, uint32_t (&v)[4]) {
 
 __device__ __forceinline__ uint32_t word_of(const uint4 &v, int i) {
     return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w;
+}
+
+// One 32x128 block (in shared memory at `st`) against NC 8-column sets:
+// four 128-bit loads give every A fragment of the lane, then per 32-column group
+// decode, two MMAs per 16-row half and column set, and the flush into `bacc` with
+// the group's scales. loadB(grp, cs) returns the B fragments of a group.
+template <int MODE, int NC, class LoadB>
+__device__ __forceinline__ void block_mma(uint32_t st, int lane, int g, LoadB loadB, float (&bacc)[NC][2][4]) {
+    uint4 w[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) w[j] = lds128(st + j * 512 + lane * 16);
+    // scales of rows g (h=0) and g+8 (h=1) of both 16-row halves
+    uint4 sc16[2];
+    uint4 sc32[2][2];
+    uint2 sc8[2];
+    if (MODE == SC_H16) {
+#pragma unroll
+        for (int s = 0; s < 2; s++) sc16[s] = lds128(st + CODE_BYTES + (s * 8 + g) * 16);
+    } else if (MODE == SC_F32) {
+#pragma unroll
+        for (int s = 0; s < 2; s++) {
+            sc32[s][0] = lds128(st + CODE_BYTES + (s * 8 + g) * 32);
+            sc32[s][1] = lds128(st + CODE_BYTES + (s * 8 + g) * 32 + 16);
+        }
+    } else if (MODE == SC_MX) {
+#pragma unroll
+        for (int s = 0; s < 2; s++) sc8[s] = lds64(st + CODE_BYTES + (s * 8 + g) * 8);
+    }
+#pragma unroll
+    for (int cs = 0; cs < NC; cs++)
+#pragma unroll
+        for (int s = 0; s < 2; s++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) bacc[cs][s][i] = 0.f;
+#pragma unroll
+    for (int grp = 0; grp < 4; grp++) {
+        uint4 b[NC];
+#pragma unroll
+        for (int cs = 0; cs < NC; cs++) b[cs] = loadB(grp, cs);
+#pragma unroll
+        for (int s = 0; s < 2; s++) {
+            uint32_t a_lo[4], a_hi[4];
+            decode_word<MODE>(word_of(w[s * 2 + 0], grp), a_lo);   // row g
+            decode_word<MODE>(word_of(w[s * 2 + 1], grp), a_hi);   // row g+8
+            float s0 = 1.f, s1 = 1.f;
+            if (MODE == SC_H16) {
+                uint32_t p0w = grp < 2 ? sc16[s].x : sc16[s].y;
+                uint32_t p1w = grp < 2 ? sc16[s].z : sc16[s].w;
+                __half2 h0 = u32_as_h2(p0w), h1 = u32_as_h2(p1w);
+                s0 = (grp & 1) ? __high2float(h0) : __low2float(h0);
+                s1 = (grp & 1) ? __high2float(h1) : __low2float(h1);
+            } else if (MODE == SC_F32) {
+                s0 = __uint_as_float(word_of(sc32[s][0], grp));
+                s1 = __uint_as_float(word_of(sc32[s][1], grp));
+            } else if (MODE == SC_MX) {
+                s0 = __uint_as_float(((sc8[s].x >> (8 * grp)) & 0xFFu) << 23);
+                s1 = __uint_as_float(((sc8[s].y >> (8 * grp)) & 0xFFu) << 23);
+            }
+#pragma unroll
+            for (int cs = 0; cs < NC; cs++) {
+                float c[4] = {0.f, 0.f, 0.f, 0.f};
+                mma_f16(c, a_lo[0], a_hi[0], a_lo[1], a_hi[1], b[cs].x, b[cs].y);
+                mma_f16(c, a_lo[2], a_hi[2], a_lo[3], a_hi[3], b[cs].z, b[cs].w);
+                if (MODE == SC_ROW) {
+                    bacc[cs][s][0] += c[0]; bacc[cs][s][1] += c[1];
+                    bacc[cs][s][2] += c[2]; bacc[cs][s][3] += c[3];
+                } else {
+                    bacc[cs][s][0] = fmaf(c[0], s0, bacc[cs][s][0]);
+                    bacc[cs][s][1] = fmaf(c[1], s0, bacc[cs][s][1]);
+                    bacc[cs][s][2] = fmaf(c[2], s1, bacc[cs][s][2]);
+                    bacc[cs][s][3] = fmaf(c[3], s1, bacc[cs][s][3]);
+                }
+            }
+        }
+    }
 }
 
 struct TaskPos {
@@ -234,77 +310,23 @@ k_gemv_stream(const GemvSeg *__restrict__ segs, const GemvCtl *__restrict__ ctl,
             float ixs[NC];
 #pragma unroll
             for (int cs = 0; cs < NC; cs++) ixs[cs] = svalid[cs] ? __ldg(sptr[cs] + kb) : 0.f;
-            if (!mbar_wait_bounded(bars + stage * 8, (consumed / NST) & 1)) { failed = true; break; }
-            uint4 w[4];
-#pragma unroll
-            for (int j = 0; j < 4; j++) w[j] = lds128(st + j * 512 + lane * 16);
-            // scales of rows g (h=0) and g+8 (h=1) of both 16-row halves
-            uint4 sc16[2];
-            uint4 sc32[2][2];
-            uint2 sc8[2];
-            if (MODE == SC_H16) {
-#pragma unroll
-                for (int s = 0; s < 2; s++) sc16[s] = lds128(st + CODE_BYTES + (s * 8 + g) * 16);
-            } else if (MODE == SC_F32) {
-#pragma unroll
-                for (int s = 0; s < 2; s++) {
-                    sc32[s][0] = lds128(st + CODE_BYTES + (s * 8 + g) * 32);
-                    sc32[s][1] = lds128(st + CODE_BYTES + (s * 8 + g) * 32 + 16);
-                }
-            } else if (MODE == SC_MX) {
-#pragma unroll
-                for (int s = 0; s < 2; s++) sc8[s] = lds64(st + CODE_BYTES + (s * 8 + g) * 8);
-            }
             float bacc[NC][2][4];
+            if (NC == 1) {
+                // the B fragments do not depend on the chunk: fetch them before waiting for it
+                uint4 bpre[4];
 #pragma unroll
-            for (int cs = 0; cs < NC; cs++)
-#pragma unroll
-                for (int s = 0; s < 2; s++)
-#pragma unroll
-                    for (int i = 0; i < 4; i++) bacc[cs][s][i] = 0.f;
-
-#pragma unroll
-            for (int grp = 0; grp < 4; grp++) {
-                uint4 b[NC];
-#pragma unroll
-                for (int cs = 0; cs < NC; cs++)
-                    b[cs] = bvalid[cs] ? ldg_nc128(bptr[cs] + (size_t)kb * 256 + grp * 64)
-                                       : make_uint4(0, 0, 0, 0);
-#pragma unroll
-                for (int s = 0; s < 2; s++) {
-                    uint32_t a_lo[4], a_hi[4];
-                    decode_word<MODE>(word_of(w[s * 2 + 0], grp), a_lo);   // row g
-                    decode_word<MODE>(word_of(w[s * 2 + 1], grp), a_hi);   // row g+8
-                    float s0 = 1.f, s1 = 1.f;
-                    if (MODE == SC_H16) {
-                        uint32_t p0w = grp < 2 ? sc16[s].x : sc16[s].y;
-                        uint32_t p1w = grp < 2 ? sc16[s].z : sc16[s].w;
-                        __half2 h0 = u32_as_h2(p0w), h1 = u32_as_h2(p1w);
-                        s0 = (grp & 1) ? __high2float(h0) : __low2float(h0);
-                        s1 = (grp & 1) ? __high2float(h1) : __low2float(h1);
-                    } else if (MODE == SC_F32) {
-                        s0 = __uint_as_float(word_of(sc32[s][0], grp));
-                        s1 = __uint_as_float(word_of(sc32[s][1], grp));
-                    } else if (MODE == SC_MX) {
-                        s0 = __uint_as_float(((sc8[s].x >> (8 * grp)) & 0xFFu) << 23);
-                        s1 = __uint_as_float(((sc8[s].y >> (8 * grp)) & 0xFFu) << 23);
-                    }
-#pragma unroll
-                    for (int cs = 0; cs < NC; cs++) {
-                        float c[4] = {0.f, 0.f, 0.f, 0.f};
-                        mma_f16(c, a_lo[0], a_hi[0], a_lo[1], a_hi[1], b[cs].x, b[cs].y);
-                        mma_f16(c, a_lo[2], a_hi[2], a_lo[3], a_hi[3], b[cs].z, b[cs].w);
-                        if (MODE == SC_ROW) {
-                            bacc[cs][s][0] += c[0]; bacc[cs][s][1] += c[1];
-                            bacc[cs][s][2] += c[2]; bacc[cs][s][3] += c[3];
-                        } else {
-                            bacc[cs][s][0] = fmaf(c[0], s0, bacc[cs][s][0]);
-                            bacc[cs][s][1] = fmaf(c[1], s0, bacc[cs][s][1]);
-                            bacc[cs][s][2] = fmaf(c[2], s1, bacc[cs][s][2]);
-                            bacc[cs][s][3] = fmaf(c[3], s1, bacc[cs][s][3]);
-                        }
-                    }
-                }
+                for (int grp = 0; grp < 4; grp++)
+                    bpre[grp] = bvalid[0] ? ldg_nc128(bptr[0] + (size_t)kb * 256 + grp * 64) : make_uint4(0, 0, 0, 0);
+                if (!mbar_wait_bounded(bars + stage * 8, (consumed / NST) & 1)) { failed = true; break; }
+                block_mma<MODE, NC>(st, lane, g, [&](int grp, int) { return bpre[grp]; }, bacc);
+            } else {
+                if (!mbar_wait_bounded(bars + stage * 8, (consumed / NST) & 1)) { failed = true; break; }
+                block_mma<MODE, NC>(st, lane, g,
+                                    [&](int grp, int cs) {
+                                        return bvalid[cs] ? ldg_nc128(bptr[cs] + (size_t)kb * 256 + grp * 64)
+                                                          : make_uint4(0, 0, 0, 0);
+                                    },
+                                    bacc);
             }
 #pragma unroll
             for (int cs = 0; cs < NC; cs++)

@@ -18,13 +18,14 @@
 // The GEMV inner loop is the one of gemv_stream.cuh with one 8-column set
 // (4 rows per pass; an expert with more rows takes two passes).
 //
-// Activations: when they are small enough (M*D*4 bytes <= 64 KB, and the slice
-// of h one task needs <= 4 KB) they never touch global memory: every CTA splits
-// x into fp16 hi/lo fragments in its own shared memory while its first warps
-// route, and each warp computes the SwiGLU slice of its down-projection task
-// from the gate/up partial sums into a private shared-memory slot. That removes
-// two grid barriers and takes the B-operand loads of the inner loop from
-// L2 latency to shared-memory latency. Otherwise the split activations go
+// Activations: when they are small enough (M*D*4 bytes <= 64 KB and the h slices
+// of a CTA's down tasks fit the same region) they never touch global memory:
+// every CTA splits x into fp16 hi/lo fragments in its own shared memory while the
+// first gate/up chunks are in flight, and after the gate/up barrier the warps of a
+// CTA compute, once, the SwiGLU slices their down tasks need (tasks are dealt to
+// CTAs in contiguous ranges, so a CTA touches one or two (expert, slice) groups).
+// That removes two grid barriers and takes the B-operand loads of the inner loop
+// from L2 latency to shared-memory latency. Otherwise the split activations go
 // through global memory with a barrier after each producer step.
 //
 // Grid barrier: an arrival counter in global memory that only grows; the host
@@ -46,7 +47,6 @@
 #define DEC_NBAR 4
 #define DEC_WARPS 16
 #define DEC_ACT_BYTES 65536       // shared-memory activation region (x fragments, then h slots)
-#define DEC_SLOT_BYTES 4160       // per-warp h slot in phase 2: 8 blocks of fragments + their scales
 #define DEC_NPROBE 12
 
 struct DecPass {
@@ -82,6 +82,8 @@ struct DecShared {
     int uniq[DEC_MAX_E];
     DecPass pass[DEC_MAX_PASS];
     int nu, npass, npos, shared_pos0, failed;
+    float rowtmp[2 * DEC_MAX_M];
+    int rowflag[DEC_MAX_M];
     unsigned long long exp_tab[32];
 };
 
@@ -223,10 +225,121 @@ __device__ __forceinline__ void route_row_warp(const float *z, const float *bias
     __syncwarp();
 }
 
-// Description of one GEMV phase of the fused kernel.
+// CTA-parallel routing of M rows (all threads of the CTA). score/choice: [M*E] floats
+// of scratch; outputs idx/wk [M*K], keff [M] in shared memory. Same arithmetic, element
+// for element, as route_row_warp.
+__device__ __forceinline__ void route_rows_cta(const float *logits, const float *bias, const RouteRule &rule,
+                                               int M, float *score, float *choice, float *rowtmp,
+                                               int *rowflag, int *idx, float *wk, int *keff,
+                                               const uint64_t *tab) {
+    const int E = rule.E, K = rule.K, tid = threadIdx.x, nth = blockDim.x;
+    const int warp = tid >> 5, lane = tid & 31;
+    if (rule.gating == 0) {
+        if (warp < M) {
+            const float *z = logits + (size_t)warp * E;
+            float m = -1e30f;
+            for (int e = lane; e < E; e += 32) { float v = z[e]; if (v > m) m = v; }
+#pragma unroll
+            for (int off = 16; off; off >>= 1) { float o = __shfl_xor_sync(0xffffffffu, m, off); if (o > m) m = o; }
+            if (lane == 0) rowtmp[warp] = m;
+        }
+        __syncthreads();
+        for (int i = tid; i < M * E; i += nth) score[i] = coli_expf_exact(__fsub_rn(logits[i], rowtmp[i / E]), tab);
+        __syncthreads();
+        if (tid < M) {      // the engine's serial ascending sum, one thread per row
+            const float *sc = score + (size_t)tid * E;
+            float tot = 0.f;
+            int e = 0;
+            for (; e + 4 <= E; e += 4) {
+                float4 v = *reinterpret_cast<const float4 *>(sc + e);
+                tot = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(tot, v.x), v.y), v.z), v.w);
+            }
+            for (; e < E; e++) tot = __fadd_rn(tot, sc[e]);
+            rowtmp[DEC_MAX_M + tid] = tot;
+        }
+        __syncthreads();
+        for (int i = tid; i < M * E; i += nth) {
+            float p = __fdiv_rn(score[i], rowtmp[DEC_MAX_M + i / E]);
+            score[i] = p; choice[i] = p;
+        }
+    } else {
+        for (int i = tid; i < M * E; i += nth) {
+            float sg = __fdiv_rn(1.f, __fadd_rn(1.f, coli_expf_exact(-logits[i], tab)));
+            score[i] = sg;
+            choice[i] = bias ? __fadd_rn(sg, bias[i % E]) : sg;
+        }
+    }
+    if (tid < M) rowflag[tid] = 0;
+    __syncthreads();
+    for (int i = tid; i < M * E; i += nth) if (!(choice[i] > -1e30f)) rowflag[i / E] = 1;
+    __syncthreads();
+    for (int i = tid; i < M * E; i += nth) {
+        const int s = i / E, e = i - s * E;
+        if (rowflag[s]) continue;
+        const float c = choice[i];
+        const float *row = choice + (size_t)s * E;
+        int rank = 0;
+        for (int o = 0; o < E; o++) { float v = row[o]; rank += (v > c) || (v == c && o < e); }
+        if (rank < K) { idx[s * K + rank] = e; wk[s * K + rank] = score[i]; }
+    }
+    __syncthreads();
+    if (warp < M && rowflag[warp]) {     // a row with NaN / -inf candidates: pass by pass
+        float *ch = choice + (size_t)warp * E;
+        const float *sc = score + (size_t)warp * E;
+        for (int kk = 0; kk < K; kk++) {
+            int best = -1;
+            float bv = -1e30f;
+            for (int e = lane; e < E; e += 32) { float c = ch[e]; if (c > bv) { bv = c; best = e; } }
+#pragma unroll
+            for (int off = 16; off; off >>= 1) {
+                float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+                int ob = __shfl_xor_sync(0xffffffffu, best, off);
+                bool take = ob >= 0 && (best < 0 || ov > bv || (ov == bv && ob < best));
+                if (take) { bv = ov; best = ob; }
+            }
+            if (best < 0) best = kk < E ? kk : 0;
+            if (lane == 0) { idx[warp * K + kk] = best; wk[warp * K + kk] = sc[best]; ch[best] = __uint_as_float(0x7fc00000u); }
+            __syncwarp();
+        }
+    }
+    __syncthreads();
+    if (tid < M) {
+        int *ix = idx + tid * K;
+        float *w = wk + tid * K;
+        int Ke = K;
+        if (rule.gating == 1 && rule.topp > 0.f && rule.topp < 1.f) {
+            for (int a = 1; a < K; a++) {
+                int ii = ix[a]; float ww = w[a]; int b = a - 1;
+                while (b >= 0 && w[b] < ww) { w[b + 1] = w[b]; ix[b + 1] = ix[b]; b--; }
+                w[b + 1] = ww; ix[b + 1] = ii;
+            }
+            float tot = 1e-20f;
+            for (int kk = 0; kk < K; kk++) tot = __fadd_rn(tot, w[kk]);
+            float cum = 0.f;
+            for (int kk = 0; kk < K; kk++) {
+                cum = __fadd_rn(cum, w[kk]);
+                if (cum >= __fmul_rn(rule.topp, tot)) { Ke = kk + 1; break; }
+            }
+        }
+        if (rule.norm_topk) {
+            float sm = 0.f;
+            for (int kk = 0; kk < Ke; kk++) sm = __fadd_rn(sm, w[kk]);
+            if (rule.gating == 1) sm = __fadd_rn(sm, 1e-20f);
+            for (int kk = 0; kk < Ke; kk++) w[kk] = __fdiv_rn(w[kk], sm);
+        }
+        if (rule.gating == 1) for (int kk = 0; kk < Ke; kk++) w[kk] = __fmul_rn(w[kk], rule.routed_scale);
+        keff[tid] = Ke;
+    }
+    __syncthreads();
+}
+
+// Description of one GEMV phase of the fused kernel. Tasks are numbered
+// ((segment * nkpart + kpart) * ntiles + tile); this CTA owns [t0, t1) and its warp w
+// takes t0 + w, t0 + w + 16, ...
 struct DecPhase {
     int which;        // 1: gate/up (segments alternate gate, up), 2: down
     int ntask, tps, ntiles, nkb, nkpart, kb_per_part, O, npos;
+    int t0, t1;
 };
 
 struct DecIter {
@@ -262,8 +375,8 @@ struct WarpRing {
 
 template <int CH, int NST>
 __device__ __forceinline__ void dec_issue_one(WarpRing &wr, DecIter &prod, const DecPhase &ph,
-                                              const DecodeArgs &a, const DecShared *sh, int P, int lane) {
-    if (prod.task >= ph.ntask) return;
+                                              const DecodeArgs &a, const DecShared *sh, int lane) {
+    if (prod.task >= ph.t1) return;
     if (wr.issued - wr.consumed >= NST) return;
     if (lane == 0) {
         uint32_t bar = wr.bars + (wr.issued % NST) * 8;
@@ -274,9 +387,9 @@ __device__ __forceinline__ void dec_issue_one(WarpRing &wr, DecIter &prod, const
     prod.kb++;
     prod.ptr += CH;
     if (prod.kb == prod.kb_end) {
-        prod.task += P;
+        prod.task += DEC_WARPS;
         int d0, d1, d2;
-        if (prod.task < ph.ntask) dec_task_setup<CH>(prod, ph, a, sh, d0, d1, d2);
+        if (prod.task < ph.t1) dec_task_setup<CH>(prod, ph, a, sh, d0, d1, d2);
     }
 }
 
@@ -317,23 +430,26 @@ __device__ __forceinline__ float dec_swiglu_block(const DecodeArgs &a, int npos,
     return 1.f / s;
 }
 
+// Bytes of one (expert pass, contraction slice) group of h in shared memory:
+// up to 4 rows x kb_per_part blocks of fragments, then their inverse scales.
+__device__ __host__ inline int dec_slice_bytes(int kbpp) { return 4 * kbpp * 512 + ((4 * kbpp * 4 + 15) & ~15); }
+
 // Consumes every task of the phase that belongs to this warp. `prod` must have
 // been initialised (and possibly primed) by the caller.
-//   bq / bscale : B operand fragments and inverse block scales (generic pointers:
-//                 global memory, or this CTA's shared memory)
-//   slot        : when non-null (phase 2, activations in shared memory) the warp first
-//                 computes the SwiGLU slice of each task into this private slot
-//                 ([row][block][256 halfs], then the scales) and reads B from it
+//   bq / bscale : B operand fragments and inverse block scales in global memory, or
+//                 (phase 1, activations in shared memory) this CTA's copy of x
+//   slices      : when non-null (phase 2, activations in shared memory) the h slices of
+//                 this CTA's groups, group (task / ntiles) at index gidx - first group
 template <int MODE, int NST>
 __device__ __forceinline__ bool dec_consume_phase(WarpRing &wr, DecIter &prod, const DecPhase &ph,
-                                                  const DecodeArgs &a, const DecShared *sh, int p0, int P,
+                                                  const DecodeArgs &a, const DecShared *sh, int warp,
                                                   int lane, const __half *bq, const float *bscale,
-                                                  uint8_t *slot) {
+                                                  const uint8_t *slices) {
     constexpr int CH = CODE_BYTES + (MODE == SC_H16 ? 256 : MODE == SC_F32 ? 512 : MODE == SC_MX ? 128 : 0);
     const int g = lane >> 2, t = lane & 3;
     DecIter cons;
-    cons.task = p0;
-    while (cons.task < ph.ntask) {
+    cons.task = ph.t0 + warp;
+    while (cons.task < ph.t1) {
         int seg_i, tile, kpart;
         dec_task_setup<CH>(cons, ph, a, sh, seg_i, tile, kpart);
         const DecPass &ps = sh->pass[ph.which == 1 ? (seg_i >> 1) : seg_i];
@@ -346,21 +462,13 @@ __device__ __forceinline__ bool dec_consume_phase(WarpRing &wr, DecIter &prod, c
         int rid_s = svalid ? (ph.which == 1 ? ps.rowid[t] : ps.pos0 + t) : 0;
         const __half *bbase = bq;
         const float *sbase = bscale;
-        if (slot) {
+        if (slices) {
             const int kbpp = ph.kb_per_part;
-            __half *hq = reinterpret_cast<__half *>(slot);
-            float *hs = reinterpret_cast<float *>(slot + 4096);
-            __syncwarp();
-            for (int r = 0; r < nrows; r++)
-                for (int j = 0; j < kbpp; j++) {
-                    float inv = dec_swiglu_block(a, ph.npos, ps.pos0 + r, cons.kb + j, lane,
-                                                 hq + (size_t)(r * kbpp + j) * 256);
-                    if (lane == 0) hs[r * kbpp + j] = inv;
-                }
-            __syncwarp();
+            const uint8_t *sl = slices + (size_t)(cons.task / ph.ntiles - ph.t0 / ph.ntiles) * dec_slice_bytes(kbpp);
+            bbase = reinterpret_cast<const __half *>(sl);
+            sbase = reinterpret_cast<const float *>(sl + 4 * kbpp * 512);
             b_nkb = kbpp; b_kb0 = cons.kb;
             rid_b = rb; rid_s = t;
-            bbase = hq; sbase = hs;
         }
         const __half *bptr = bbase + ((size_t)rid_b * b_nkb - b_kb0) * 256 + (g & 1) * 32 + t * 8;
         const float *sptr = sbase + (size_t)rid_s * b_nkb - b_kb0;
@@ -373,77 +481,22 @@ __device__ __forceinline__ bool dec_consume_phase(WarpRing &wr, DecIter &prod, c
             const int stage = wr.consumed % NST;
             const uint32_t st = wr.ring + stage * CH;
             float ixs = svalid ? sptr[kb] : 0.f;
-            uint4 b[4];
+            // the B fragments do not depend on the chunk: fetch them before waiting for it
+            uint4 bpre[4];
 #pragma unroll
             for (int grp = 0; grp < 4; grp++)
-                b[grp] = bvalid ? *reinterpret_cast<const uint4 *>(bptr + (size_t)kb * 256 + grp * 64)
-                                : make_uint4(0, 0, 0, 0);
+                bpre[grp] = bvalid ? *reinterpret_cast<const uint4 *>(bptr + (size_t)kb * 256 + grp * 64)
+                                   : make_uint4(0, 0, 0, 0);
             if (!mbar_wait_bounded(wr.bars + stage * 8, (wr.consumed / NST) & 1)) return false;
-            uint4 w[4];
-#pragma unroll
-            for (int j = 0; j < 4; j++) w[j] = lds128(st + j * 512 + lane * 16);
-            uint4 sc16[2];
-            uint4 sc32[2][2];
-            uint2 sc8[2];
-            if (MODE == SC_H16) {
-#pragma unroll
-                for (int s = 0; s < 2; s++) sc16[s] = lds128(st + CODE_BYTES + (s * 8 + g) * 16);
-            } else if (MODE == SC_F32) {
-#pragma unroll
-                for (int s = 0; s < 2; s++) {
-                    sc32[s][0] = lds128(st + CODE_BYTES + (s * 8 + g) * 32);
-                    sc32[s][1] = lds128(st + CODE_BYTES + (s * 8 + g) * 32 + 16);
-                }
-            } else if (MODE == SC_MX) {
-#pragma unroll
-                for (int s = 0; s < 2; s++) sc8[s] = lds64(st + CODE_BYTES + (s * 8 + g) * 8);
-            }
-            float bacc[2][4];
+            float bacc[1][2][4];
+            block_mma<MODE, 1>(st, lane, g, [&](int grp, int) { return bpre[grp]; }, bacc);
 #pragma unroll
             for (int s = 0; s < 2; s++)
 #pragma unroll
-                for (int i = 0; i < 4; i++) bacc[s][i] = 0.f;
-#pragma unroll
-            for (int grp = 0; grp < 4; grp++) {
-#pragma unroll
-                for (int s = 0; s < 2; s++) {
-                    uint32_t a_lo[4], a_hi[4];
-                    decode_word<MODE>(word_of(w[s * 2 + 0], grp), a_lo);
-                    decode_word<MODE>(word_of(w[s * 2 + 1], grp), a_hi);
-                    float s0 = 1.f, s1 = 1.f;
-                    if (MODE == SC_H16) {
-                        uint32_t p0w = grp < 2 ? sc16[s].x : sc16[s].y;
-                        uint32_t p1w = grp < 2 ? sc16[s].z : sc16[s].w;
-                        __half2 h0 = u32_as_h2(p0w), h1 = u32_as_h2(p1w);
-                        s0 = (grp & 1) ? __high2float(h0) : __low2float(h0);
-                        s1 = (grp & 1) ? __high2float(h1) : __low2float(h1);
-                    } else if (MODE == SC_F32) {
-                        s0 = __uint_as_float(word_of(sc32[s][0], grp));
-                        s1 = __uint_as_float(word_of(sc32[s][1], grp));
-                    } else if (MODE == SC_MX) {
-                        s0 = __uint_as_float(((sc8[s].x >> (8 * grp)) & 0xFFu) << 23);
-                        s1 = __uint_as_float(((sc8[s].y >> (8 * grp)) & 0xFFu) << 23);
-                    }
-                    float c[4] = {0.f, 0.f, 0.f, 0.f};
-                    mma_f16(c, a_lo[0], a_hi[0], a_lo[1], a_hi[1], b[grp].x, b[grp].y);
-                    mma_f16(c, a_lo[2], a_hi[2], a_lo[3], a_hi[3], b[grp].z, b[grp].w);
-                    if (MODE == SC_ROW) {
-                        bacc[s][0] += c[0]; bacc[s][1] += c[1]; bacc[s][2] += c[2]; bacc[s][3] += c[3];
-                    } else {
-                        bacc[s][0] = fmaf(c[0], s0, bacc[s][0]);
-                        bacc[s][1] = fmaf(c[1], s0, bacc[s][1]);
-                        bacc[s][2] = fmaf(c[2], s1, bacc[s][2]);
-                        bacc[s][3] = fmaf(c[3], s1, bacc[s][3]);
-                    }
-                }
-            }
-#pragma unroll
-            for (int s = 0; s < 2; s++)
-#pragma unroll
-                for (int i = 0; i < 4; i++) R[s][i] = fmaf(bacc[s][i], ixs, R[s][i]);
+                for (int i = 0; i < 4; i++) R[s][i] = fmaf(bacc[0][s][i], ixs, R[s][i]);
             wr.consumed++;
             __syncwarp();
-            dec_issue_one<CH, NST>(wr, prod, ph, a, sh, P, lane);
+            dec_issue_one<CH, NST>(wr, prod, ph, a, sh, lane);
         }
         const float mx_fix = (MODE == SC_MX) ? 16384.f : 1.f;
         if (t < nrows) {
@@ -468,21 +521,29 @@ __device__ __forceinline__ bool dec_consume_phase(WarpRing &wr, DecIter &prod, c
                 dst[8] = v1;
             }
         }
-        cons.task += P;
+        cons.task += DEC_WARPS;
     }
     return true;
 }
 
 template <int MODE> struct DecCfg { static constexpr int NST = MODE == SC_F32 ? 3 : 4; };
 
+// This CTA's contiguous share [t0, t1) of ntask tasks: sizes differ by at most one.
+__device__ __forceinline__ void dec_cta_range(int ntask, int &t0, int &t1) {
+    const int G = gridDim.x, b = blockIdx.x;
+    const int q = ntask / G, r = ntask - q * G;
+    t0 = b * q + (b < r ? b : r);
+    t1 = t0 + q + (b < r ? 1 : 0);
+}
+
 template <int MODE>
 __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) {
     constexpr int CH = CODE_BYTES + (MODE == SC_H16 ? 256 : MODE == SC_F32 ? 512 : MODE == SC_MX ? 128 : 0);
     constexpr int NST = DecCfg<MODE>::NST;
     extern __shared__ __align__(128) uint8_t smem[];
-    // layout: rings | mbarriers | DecShared | activation region (act_smem only)
-    // The routing scratch (2E floats per routed row) lives in the routing warp's own
-    // ring, which carries no data before the first copy is issued.
+    // layout: rings | mbarriers | DecShared | activation region
+    // The activation region holds, in turn: the routing scratch (2*M*E floats), the
+    // fp16 fragments of x (act_smem), the h slices of this CTA's down tasks (act_smem).
     DecShared *sh = reinterpret_cast<DecShared *>(smem + DEC_WARPS * NST * (CH + 8));
     uint8_t *act = reinterpret_cast<uint8_t *>(sh) + ((sizeof(DecShared) + 127) & ~127);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
@@ -503,35 +564,14 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
     for (int e = tid; e < E; e += blockDim.x) { sh->first[e] = 0x7fffffff; sh->cnt[e] = 0; }
     __syncthreads();
 
-    // ---- routing in warps 0..M-1 (redundantly in every CTA); meanwhile the other
-    // warps split x into this CTA's shared memory when the activations live there ----
-    __half *xq_s = reinterpret_cast<__half *>(act);
-    float *xs_s = reinterpret_cast<float *>(act + (size_t)M * nkb1 * 512);
-    if (warp < M) {
-        float *scratch = reinterpret_cast<float *>(smem + (size_t)warp * (NST * CH));
-        route_row_warp(a.logits + (size_t)warp * E, a.router_bias, r, scratch, scratch + E, sh->idx + warp * K,
-                       sh->w + warp * K, sh->keff + warp, lane, reinterpret_cast<const uint64_t *>(sh->exp_tab));
-        if (warp == 0 && lane == 0) dec_probe_lane(a, 10);
+    // ---- routing, redundantly in every CTA, all threads -----------------------------
+    {
+        float *score = reinterpret_cast<float *>(act);
+        float *choice = score + (size_t)M * E;
+        route_rows_cta(a.logits, a.router_bias, r, M, score, choice, sh->rowtmp, sh->rowflag, sh->idx, sh->w,
+                       sh->keff, reinterpret_cast<const uint64_t *>(sh->exp_tab));
     }
-    if (a.act_smem) {
-        const int nhelp = DEC_WARPS > M ? DEC_WARPS - M : DEC_WARPS;
-        const int me = DEC_WARPS > M ? warp - M : warp;
-        if (me >= 0)
-            for (int wid = me; wid < M * nkb1; wid += nhelp) {
-                int row = wid / nkb1, kb = wid - row * nkb1;
-                float4 v = *reinterpret_cast<const float4 *>(a.x + (size_t)row * D + kb * BLOCK_K + lane * 4);
-                float m = warp_max(fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
-                float s = block_scale_from_max(m);
-                store_split4(xq_s + ((size_t)row * nkb1 + kb) * 256, lane, v, s);
-                if (lane == 0) xs_s[(size_t)row * nkb1 + kb] = 1.f / s;
-            }
-        if (me == 0 && lane == 0) dec_probe_lane(a, 11);
-    }
-    __syncthreads();
-    if (a.act_smem) dec_probe(a, 2);   // rows routed, x split
-    // the routing scratch was written through the generic proxy into memory that the
-    // bulk copies (async proxy) overwrite next
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    dec_probe(a, 10);
     for (int i = tid; i < M * K; i += blockDim.x) {
         int s = i / K, kk = i - s * K;
         if (kk < sh->keff[s]) { int e = sh->idx[i]; atomicMin(&sh->first[e], i); atomicAdd(&sh->cnt[e], 1); }
@@ -598,28 +638,57 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
     }
     dec_probe(a, 1);   // routing and tables done
     const int npass = sh->npass, npos = sh->npos;
-    // task t goes to CTA t % grid, so every SM gets the same number of tasks (+-1)
-    const int P = gridDim.x * DEC_WARPS, p0 = warp * gridDim.x + blockIdx.x;
+    const int P = gridDim.x * DEC_WARPS;
     unsigned long long bar_target = a.bar_base;
 
     DecPhase ph1, ph2;
     ph1.which = 1; ph1.ntiles = I / TILE_ROWS; ph1.nkb = nkb1; ph1.nkpart = a.nkp1;
     ph1.kb_per_part = nkb1 / a.nkp1; ph1.tps = ph1.ntiles * a.nkp1; ph1.ntask = 2 * npass * ph1.tps;
     ph1.O = I; ph1.npos = npos;
+    dec_cta_range(ph1.ntask, ph1.t0, ph1.t1);
     ph2.which = 2; ph2.ntiles = D / TILE_ROWS; ph2.nkb = nkb2; ph2.nkpart = a.nkp2;
     ph2.kb_per_part = nkb2 / a.nkp2; ph2.tps = ph2.ntiles * a.nkp2; ph2.ntask = npass * ph2.tps;
     ph2.O = D; ph2.npos = npos;
+    dec_cta_range(ph2.ntask, ph2.t0, ph2.t1);
 
-    // ---- start the gate/up weight stream ------------------------------------------
+    // ---- start the gate/up weight stream, then split x while it is in flight ----------
     DecIter prod;
-    prod.task = p0;
+    prod.task = ph1.t0 + warp;
     int d0, d1, d2;
-    if (prod.task < ph1.ntask) dec_task_setup<CH>(prod, ph1, a, sh, d0, d1, d2);
-    for (int s = 0; s < NST; s++) dec_issue_one<CH, NST>(wr, prod, ph1, a, sh, P, lane);
+    if (prod.task < ph1.t1) dec_task_setup<CH>(prod, ph1, a, sh, d0, d1, d2);
+    for (int s = 0; s < NST; s++) dec_issue_one<CH, NST>(wr, prod, ph1, a, sh, lane);
     bool ok = true;
-    if (!a.act_smem) {
+    __half *xq_s = reinterpret_cast<__half *>(act);
+    float *xs_s = reinterpret_cast<float *>(act + (size_t)M * nkb1 * 512);
+    if (a.act_smem) {
+        // four blocks per warp at a time: their loads are in flight together
+        for (int w0 = warp; w0 < M * nkb1; w0 += 4 * DEC_WARPS) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                int wid = w0 + u * DEC_WARPS;
+                if (wid < M * nkb1) {
+                    int row = wid / nkb1, kb = wid - row * nkb1;
+                    v[u] = *reinterpret_cast<const float4 *>(a.x + (size_t)row * D + kb * BLOCK_K + lane * 4);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                int wid = w0 + u * DEC_WARPS;
+                if (wid < M * nkb1) {
+                    int row = wid / nkb1, kb = wid - row * nkb1;
+                    float m = warp_max(fmaxf(fmaxf(fabsf(v[u].x), fabsf(v[u].y)), fmaxf(fabsf(v[u].z), fabsf(v[u].w))));
+                    float sc = block_scale_from_max(m);
+                    store_split4(xq_s + ((size_t)row * nkb1 + kb) * 256, lane, v[u], sc);
+                    if (lane == 0) xs_s[(size_t)row * nkb1 + kb] = 1.f / sc;
+                }
+            }
+        }
+        __syncthreads();
+        dec_probe(a, 2);
+    } else {
         // activations through global memory: distributed split, then a barrier
-        for (int wid = p0; wid < M * nkb1; wid += P) {
+        for (int wid = blockIdx.x * DEC_WARPS + warp; wid < M * nkb1; wid += P) {
             int row = wid / nkb1, kb = wid - row * nkb1;
             float4 v = *reinterpret_cast<const float4 *>(a.x + (size_t)row * D + kb * BLOCK_K + lane * 4);
             float m = warp_max(fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
@@ -633,21 +702,42 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
     }
     dec_probe(a, 3);
     // ---- gate / up ------------------------------------------------------------------
-    if (ok) ok = dec_consume_phase<MODE, NST>(wr, prod, ph1, a, sh, p0, P, lane, a.act_smem ? xq_s : a.xq,
+    if (ok) ok = dec_consume_phase<MODE, NST>(wr, prod, ph1, a, sh, warp, lane, a.act_smem ? xq_s : a.xq,
                                               a.act_smem ? xs_s : a.xs, nullptr);
     if (!ok) sh->failed = 1;
     // start the down weight stream before waiting for the other CTAs
-    prod.task = p0;
-    if (ok && prod.task < ph2.ntask) dec_task_setup<CH>(prod, ph2, a, sh, d0, d1, d2);
-    if (ok) for (int s = 0; s < NST; s++) dec_issue_one<CH, NST>(wr, prod, ph2, a, sh, P, lane);
+    prod.task = ph2.t0 + warp;
+    if (ok && prod.task < ph2.t1) dec_task_setup<CH>(prod, ph2, a, sh, d0, d1, d2);
+    if (ok) for (int s = 0; s < NST; s++) dec_issue_one<CH, NST>(wr, prod, ph2, a, sh, lane);
     dec_probe(a, 4);   // gate/up consumed, down stream primed
     bar_target += gridDim.x;
     ok = grid_barrier(a.bar, bar_target, &sh->failed) && ok;
     dec_probe(a, 5);
-    if (!a.act_smem) {
+    if (a.act_smem) {
+        // SwiGLU slices of this CTA's groups, one block per warp at a time, into the
+        // activation region (x is no longer needed: every warp passed the barrier)
+        if (ok && ph2.t1 > ph2.t0) {
+            const int kbpp = ph2.kb_per_part, slb = dec_slice_bytes(kbpp);
+            const int g0 = ph2.t0 / ph2.ntiles, g1 = (ph2.t1 - 1) / ph2.ntiles;
+            const int per = 4 * kbpp;                          // block slots per group
+            for (int w = warp; w < (g1 - g0 + 1) * per; w += DEC_WARPS) {
+                int gi = w / per, rem = w - gi * per, rr = rem / kbpp, j = rem - rr * kbpp;
+                int grp_id = g0 + gi, seg = grp_id / a.nkp2, kp = grp_id - seg * a.nkp2;
+                const DecPass &ps = sh->pass[seg];
+                if (rr < ps.nrows) {
+                    uint8_t *sl = act + (size_t)gi * slb;
+                    float inv = dec_swiglu_block(a, npos, ps.pos0 + rr, kp * kbpp + j, lane,
+                                                 reinterpret_cast<__half *>(sl) + (size_t)(rr * kbpp + j) * 256);
+                    if (lane == 0) reinterpret_cast<float *>(sl + 4 * kbpp * 512)[rr * kbpp + j] = inv;
+                }
+            }
+        }
+        __syncthreads();
+        dec_probe(a, 6);
+    } else {
         // SwiGLU + split of h, distributed, then a barrier
         if (ok)
-            for (int wid = p0; wid < npos * nkb2; wid += P) {
+            for (int wid = blockIdx.x * DEC_WARPS + warp; wid < npos * nkb2; wid += P) {
                 int pos = wid / nkb2, kb = wid - pos * nkb2;
                 float inv = dec_swiglu_block(a, npos, pos, kb, lane, a.hq + ((size_t)pos * nkb2 + kb) * 256);
                 if (lane == 0) a.hs[(size_t)pos * nkb2 + kb] = inv;
@@ -658,13 +748,12 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
     }
     dec_probe(a, 7);
     // ---- down -------------------------------------------------------------------------
-    if (ok) ok = dec_consume_phase<MODE, NST>(wr, prod, ph2, a, sh, p0, P, lane, a.hq, a.hs,
-                                              a.act_smem ? act + (size_t)warp * DEC_SLOT_BYTES : nullptr);
+    if (ok) ok = dec_consume_phase<MODE, NST>(wr, prod, ph2, a, sh, warp, lane, a.hq, a.hs,
+                                              a.act_smem ? act : nullptr);
     if (!ok) sh->failed = 1;
     dec_probe(a, 8);   // down consumed
     bar_target += gridDim.x;
     ok = grid_barrier(a.bar, bar_target, &sh->failed) && ok;
-    // ---- weighted combine: selection order per row, shared expert last ------------------
     // One warp per float4 of the output; its lanes take the (selected expert, slice)
     // terms w*partial round-robin (the shared expert's slices last, weight 1) and a
     // fixed shuffle tree adds the lanes: deterministic, and every load is in flight at once.

@@ -158,16 +158,17 @@ static int layer_run(ColiCudaMoeLayer *L, DeviceCtx *c, float *out_dev, const fl
         long passes = (long)(M * r.K < r.E ? M * r.K : r.E) + (L->has_shared ? (M + 3) / 4 : 0);
         q.nkp1 = pick_nkpart(nkb1, 2 * passes * (r.I / TILE_ROWS), c->sms);
         q.nkp2 = pick_nkpart(nkb2, passes * (r.D / TILE_ROWS), c->sms);
-        // activations in shared memory: x fragments (M*D*4 B + scales) must fit the region, and
-        // the h slice of one down task (rows <= min(M,4), nkb2/nkp2 blocks of 512 B) its slot
-        int act_smem = (size_t)M * r.D * 4 + (size_t)M * nkb1 * 4 <= DEC_ACT_BYTES + 2048;
+        // activations in shared memory: the routing scratch (2*M*E floats), the x fragments
+        // (M*D*4 B + scales) and the h slices of one CTA's down tasks must each fit the region
+        const size_t act_cap = DEC_ACT_BYTES + 2048;
+        int act_smem = (size_t)M * r.D * 4 + (size_t)M * nkb1 * 4 <= act_cap;
         if (act_smem) {
-            int rows = M < 4 ? M : 4;
-            int nk = q.nkp2;
-            while (nk < nkb2 && (nkb2 % nk || rows * (nkb2 / nk) > 8)) nk++;
-            if (nkb2 % nk == 0 && rows * (nkb2 / nk) <= 8) q.nkp2 = nk;
-            else act_smem = 0;
+            long t2 = passes * (r.D / TILE_ROWS) * q.nkp2;
+            long chunk = (t2 + c->sms - 1) / c->sms;
+            long groups = chunk / (r.D / TILE_ROWS) + 2;
+            if ((size_t)groups * dec_slice_bytes(nkb2 / q.nkp2) > act_cap) act_smem = 0;
         }
+        if ((size_t)2 * M * r.E * sizeof(float) > act_cap) return 0;
         if (!reserve(c, &L->pg, (size_t)q.nkp1 * p.npos_cap * r.I * sizeof(float)) ||
             !reserve(c, &L->pu, (size_t)q.nkp1 * p.npos_cap * r.I * sizeof(float)) ||
             !reserve(c, &L->pd, (size_t)q.nkp2 * p.npos_cap * r.D * sizeof(float))) return 0;

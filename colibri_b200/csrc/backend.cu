@@ -1045,3 +1045,93 @@ extern "C" int coli_cuda_expert_group_resident_take(int home_device, const int *
 }
 
 #include "moe_layer.cuh"
+
+// ---------------------------------------------------------------------------
+// Allocation-free matmul on device pointers (no counterpart in the reference).
+//
+// Some callers may not allocate device memory when they reach the backend: an
+// engine that has already handed every free byte of HBM to its KV cache and
+// expert tier (a cudaMalloc would fail or force an eviction), or a decode loop
+// that cannot afford the device-wide synchronisation a cudaMalloc / cudaFree
+// implies. coli_cuda_pipe_gemm normally grows per-device workspaces on demand;
+// this variant keeps all of its scratch (segment descriptors, the fp16 hi/lo
+// split of the activations, their block scales and the partial sums of the
+// contraction slices) in one fixed file-scope device array instead.
+//
+// The array is per device (every device that loads this library holds its
+// 8 MiB until the process exits) and is shared by all calls: it keeps whatever
+// the last call left there (nothing in it has to start at zero: every word a
+// call reads it has written first), and two calls that overlap on the GPU, e.g.
+// from two host threads or on two streams, race on it. The first call on a
+// device looks up the array's device address (cudaGetSymbolAddress, with that
+// device current); make that first call before any stream capture begins.
+// ---------------------------------------------------------------------------
+#define NOALLOC_SCRATCH_BYTES (8u << 20)
+#define NOALLOC_MAX_ROWS 32
+#define NOALLOC_HEADER_BYTES 4096          // one segment descriptor + the control block
+#define NOALLOC_SCALE_BYTES 16384          // inverse block scales: rows * (I/128) floats
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+static unsigned char *g_noalloc_dev[64];   // device address of the array, per CUDA ordinal
+
+extern "C" int coli_cuda_pipe_gemm_noalloc(ColiCudaTensor *t, float *y_dev, const float *x_dev, int S) {
+    if (!t || !y_dev || !x_dev || S < 1) return 0;
+    DeviceCtx *c = find_ctx(t->device);
+    if (!select_ctx(c)) return 0;
+    if (!t->packed) {
+        std::fprintf(stderr, "[CUDA] pipe_gemm_noalloc: tensor is not in the packed layout "
+                             "(needs fmt 2/4/7, I %% 128 == 0, O %% 32 == 0)\n");
+        return 0;
+    }
+    if (t->device < 0 || t->device >= 64) return 0;
+    if (S > NOALLOC_MAX_ROWS) {
+        std::fprintf(stderr, "[CUDA] pipe_gemm_noalloc: %d rows exceed the limit of %d\n", S, NOALLOC_MAX_ROWS);
+        return 0;
+    }
+    const int nkb = t->I / BLOCK_K;
+    const int nc = pick_nc(S);
+    const int nkpart = pick_nkpart(nkb, (long)(t->O / TILE_ROWS), c->sms);
+    const size_t bs_bytes = (size_t)S * nkb * sizeof(float);
+    const size_t bq_bytes = (size_t)S * t->I * 2 * sizeof(__half);
+    const size_t pd_bytes = (size_t)nkpart * S * t->O * sizeof(float);
+    const size_t need = NOALLOC_HEADER_BYTES + NOALLOC_SCALE_BYTES + bq_bytes + pd_bytes;
+    if (bs_bytes > NOALLOC_SCALE_BYTES || need > NOALLOC_SCRATCH_BYTES) {
+        std::fprintf(stderr, "[CUDA] pipe_gemm_noalloc: S=%d I=%d O=%d needs %zu bytes of scratch, the fixed "
+                             "array holds %u\n", S, t->I, t->O, need, NOALLOC_SCRATCH_BYTES);
+        return 0;
+    }
+    if (!g_noalloc_dev[t->device]) {
+        // once per device, with that device current (select_ctx above)
+        void *p = nullptr;
+        if (!cuda_ok(cudaGetSymbolAddress(&p, g_noalloc_scratch), "static scratch address") || !p) return 0;
+        g_noalloc_dev[t->device] = static_cast<unsigned char *>(p);
+    }
+    unsigned char *base = g_noalloc_dev[t->device];
+    GemvSeg *seg_dev = reinterpret_cast<GemvSeg *>(base);
+    GemvCtl *ctl_dev = reinterpret_cast<GemvCtl *>(base + NOALLOC_HEADER_BYTES - 256);
+    float *bs_dev = reinterpret_cast<float *>(base + NOALLOC_HEADER_BYTES);
+    __half *bq_dev = reinterpret_cast<__half *>(base + NOALLOC_HEADER_BYTES + NOALLOC_SCALE_BYTES);
+    float *pd_dev = reinterpret_cast<float *>(base + NOALLOC_HEADER_BYTES + NOALLOC_SCALE_BYTES + bq_bytes);
+    // descriptor and control block from the stack (pageable source: captured before the call returns)
+    struct { GemvSeg seg; } hs;
+    GemvCtl hc;
+    std::memset(&hs, 0, sizeof(hs));
+    hs.seg.w = t->pk; hs.seg.rowscale = t->rowscale; hs.seg.out = pd_dev;
+    for (int r = 0; r < S; r++) hs.seg.rowid[r] = r;
+    hs.seg.nrows = S; hs.seg.pos0 = 0;
+    hs.seg.O = t->O; hs.seg.ntiles = t->O / TILE_ROWS; hs.seg.nkb = nkb;
+    hs.seg.nkpart = nkpart; hs.seg.kb_per_part = nkb / nkpart; hs.seg.task0 = 0;
+    hc.nseg = 1; hc.ntask = hs.seg.ntiles * nkpart; hc.npos = S; hc.tasks_per_seg = hc.ntask;
+    if (!cuda_ok(cudaMemcpyAsync(seg_dev, &hs.seg, sizeof(GemvSeg), cudaMemcpyHostToDevice, c->stream), "noalloc segment") ||
+        !cuda_ok(cudaMemcpyAsync(ctl_dev, &hc, sizeof(GemvCtl), cudaMemcpyHostToDevice, c->stream), "noalloc control")) return 0;
+    const int nw = S * nkb;
+    k_prep_rows<<<(nw * 32 + 255) / 256, 256, 0, c->stream>>>(bq_dev, bs_dev, x_dev, nullptr, S, t->I);
+    switch (t->mode) {
+    case SC_ROW: launch_mode<SC_ROW>(c, nc, seg_dev, ctl_dev, bq_dev, bs_dev); break;
+    case SC_H16: launch_mode<SC_H16>(c, nc, seg_dev, ctl_dev, bq_dev, bs_dev); break;
+    case SC_F32: launch_mode<SC_F32>(c, nc, seg_dev, ctl_dev, bq_dev, bs_dev); break;
+    default: launch_mode<SC_MX>(c, nc, seg_dev, ctl_dev, bq_dev, bs_dev); break;
+    }
+    const size_t n4 = (size_t)S * t->O / 4;
+    k_reduce_parts<<<(unsigned)((n4 + 255) / 256), 256, 0, c->stream>>>(y_dev, pd_dev, S, t->O, nkpart);
+    return cuda_ok(cudaGetLastError(), "pipe_gemm_noalloc launch");
+}

@@ -211,6 +211,20 @@ int coli_cuda_moe_route_dev(ColiCudaMoeLayer *layer, const float *x_dev, const f
                             int M, int *idx_dev, float *w_dev, int *keff_dev, int *uniq_dev,
                             int *nu_dev);
 
+/* No counterpart in the reference. coli_cuda_pipe_gemm for callers that must not
+ * allocate device memory at call time (an engine that has given all free HBM to
+ * its caches, or a decode loop that cannot take the device-wide synchronisation
+ * of cudaMalloc/cudaFree): y_dev[S,O] = x_dev[S,I] @ W^T for a resident tensor in
+ * the packed layout (fmt 2/4/7, I % 128 == 0, O % 32 == 0), with every byte of
+ * scratch in a fixed 8 MiB device array that each GPU holds from library load to
+ * process exit. Limits: S <= 32 and 20 KiB + S*I*4 + slices*S*O*4 bytes <= 8 MiB
+ * (slices <= I/256); a call beyond them prints the reason and returns 0. All
+ * calls on a device share the array, so calls that overlap on the GPU race. The
+ * first call on a device resolves the array's address and should be made before
+ * any stream capture. Runs on the backend's stream for the device; returns
+ * after enqueueing. */
+int coli_cuda_pipe_gemm_noalloc(ColiCudaTensor *t, float *y_dev, const float *x_dev, int S);
+
 /* Physical device bytes held by resident tensors after repacking (the logical
  * figure is coli_cuda_stats). */
 size_t coli_cuda_physical_bytes(int device);

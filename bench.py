@@ -78,27 +78,51 @@ def gen_int4_g32_torch(torch, E, O, I, seed, device):
     return packed.cpu().numpy(), s.view(E, O * (I // 32)).cpu().numpy()
 
 
-def gen_layer_host(torch, cfg, seed, device):
-    """-> lists of QTensor (gate, up, down) for one layer."""
-    D, I, E = cfg["D"], cfg["I"], cfg["E"]
+def gen_mxfp4_torch(torch, E, O, I, seed, device):
+    """E2M1 + UE8M0 per 32 columns, the rule of c/tools/make_deepseek_v4_tiny.py:97-121."""
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    w = torch.randn((E, O, I), generator=g, device=device, dtype=torch.float32) * 0.02
+    wr = w.view(E, O, I // 32, 32)
+    amax = wr.abs().amax(dim=3, keepdim=True)
+    e = torch.where(amax > 0, torch.ceil(torch.log2(amax.double() / 6.0)), torch.full_like(amax, -127).double())
+    e = e.clamp(-127, 127)
+    scale = torch.pow(torch.tensor(2.0, device=device, dtype=torch.float64), e).float()
+    norm = (wr / scale).clamp(-6.0, 6.0)
+    lut = torch.tensor([0, .5, 1, 1.5, 2, 3, 4, 6, -0.0, -.5, -1, -1.5, -2, -3, -4, -6], device=device)
+    code = (norm.unsqueeze(-1) - lut).abs().argmin(dim=-1).to(torch.int32).view(E, O, I)
+    packed = (code[:, :, 0::2] | (code[:, :, 1::2] << 4)).to(torch.uint8)
+    return packed.cpu().numpy(), (e.view(E, O, I // 32) + 127).to(torch.uint8).cpu().numpy()
+
+
+def gen_layer_host(torch, cfg, seed, device, n_experts=None):
+    """-> lists of QTensor (gate, up, down) for n_experts experts of one layer."""
+    D, I = cfg["D"], cfg["I"]
+    E = n_experts if n_experts is not None else cfg["E"]
+    fmt = cfg["fmt"]
     out = []
-    chunk = max(1, min(E, (1 << 28) // (D * I)))     # bound the f32 temporary to ~1 GiB
+    per = D * I * (20 if fmt == 7 else 1)
+    chunk = max(1, min(E, (1 << 28) // per))     # bound the temporaries to ~1-2 GiB
     for k, (O, K) in enumerate(((I, D), (I, D), (D, I))):
         ts = []
         for e0 in range(0, E, chunk):
             n = min(chunk, E - e0)
-            pk, sc = gen_int4_g32_torch(torch, n, O, K, (seed * 10 + k) * 1000 + e0, device)
-            ts += [QTensor(pk[e], sc[e], 4, K, O, 32) for e in range(n)]
+            if fmt == 7:
+                pk, sc = gen_mxfp4_torch(torch, n, O, K, (seed * 10 + k) * 1000 + e0, device)
+                ts += [QTensor(pk[e], sc[e], 7, K, O, 0) for e in range(n)]
+            else:
+                pk, sc = gen_int4_g32_torch(torch, n, O, K, (seed * 10 + k) * 1000 + e0, device)
+                ts += [QTensor(pk[e], sc[e], 4, K, O, 32) for e in range(n)]
         out.append(ts)
     return out
 
 
 def expert_bytes_device(cfg):
     """Algorithmic bytes of one expert as stored on the device: nibbles + fp16
-    scales for int4 g32 (4.5 bits per weight)."""
+    scales for int4 g32 (4.5 bits per weight), nibbles + ue8m0 bytes for MXFP4."""
     D, I = cfg["D"], cfg["I"]
     per_w = 3 * D * I
-    return per_w // 2 + (per_w // 32) * 2
+    return per_w // 2 + (per_w // 32) * (1 if cfg["fmt"] == 7 else 2)
 
 
 class ClockSampler:
@@ -152,37 +176,51 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def route_counts(oracle, logits, K, E):
-    idx, _, _ = oracle.route_softmax(logits, K, False)
+def route_counts(oracle, cfg, logits, bias):
+    if cfg["gating"] == 0:
+        idx, _, _ = oracle.route_softmax(logits, cfg["K"], False)
+    else:
+        idx, _, _, _ = oracle.route_sigmoid(logits, bias, cfg["K"], 0.0, bool(cfg["norm_topk"]), ROUTED_SCALE)
     return int(len(np.unique(idx)))
+
+
+ROUTED_SCALE = 2.5   # sigmoid-gated configurations (GLM / DeepSeek-V3 style)
 
 
 # ---------------------------------------------------------------------------
 # CPU arm (reference kernels)
 # ---------------------------------------------------------------------------
-def cpu_step(ref, oracle, cfg, layers_host, xs, logits, layer_ids):
+def cpu_step(ref, oracle, cfg, layers_host, xs, logits, layer_ids, biases=None):
     """One pass over `layer_ids` with the reference's CPU kernels in the engine's
-    per-expert order (c/colibri.c:4731-4786); returns the bytes it touched."""
+    per-expert order (c/colibri.c:4731-4786, shared expert last :4940-5001);
+    returns the bytes it touched."""
     K, E, D = cfg["K"], cfg["E"], cfg["D"]
     nbytes = 0
     eb = expert_bytes_device(cfg)
     for li in layer_ids:
-        gate, up, down = layers_host[li]
+        gate, up, down, shared = layers_host[li]
         x, lg = xs[li], logits[li]
-        idx, val, _ = oracle.route_softmax(lg, K, False)
-        uniq = oracle.union(idx, np.full(x.shape[0], K, np.int32), E)
+        if cfg["gating"] == 0:
+            idx, val, _ = oracle.route_softmax(lg, K, False)
+            keff = np.full(x.shape[0], K, np.int32)
+        else:
+            idx, val, keff, _ = oracle.route_sigmoid(lg, biases[li] if biases else None, K, 0.0,
+                                                     bool(cfg["norm_topk"]), ROUTED_SCALE)
+        uniq = oracle.union(idx, keff, E)
         out = np.zeros_like(x)
         for e in uniq:
             rows, col = np.nonzero(idx == e)
             y = ref.expert_mlp(x[rows], gate[e], up[e], down[e])
             out[rows] += val[rows, col][:, None] * y
-        nbytes += len(uniq) * eb + 2 * x.nbytes
+        if shared is not None:
+            out += ref.expert_mlp(x, *shared)
+        nbytes += (len(uniq) + (1 if shared is not None else 0)) * eb + 2 * x.nbytes
     return nbytes
 
 
 def run_reference_arm(args):
     from oracle.oracle import Oracle, RefCpu
-    cfg = W.CONFIGS["c2"]
+    cfg = W.CONFIGS[args.workload.split("_")[0]]
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -199,22 +237,29 @@ def run_reference_arm(args):
     M = args.M
     xs = [W.activations(M, cfg["D"], 100 + li) for li in range(L)]
     lgs = [W.router_logits(M, cfg["E"], 200 + li) for li in range(L)]
-    layers_host = []
+    layers_host, biases = [], []
     for li in range(L):
-        idx, _, _ = oracle.route_softmax(lgs[li], cfg["K"], False)
+        bias = None
+        if cfg["gating"] == 0:
+            idx, _, _ = oracle.route_softmax(lgs[li], cfg["K"], False)
+        else:
+            bias = (np.random.default_rng(31 + li).standard_normal(cfg["E"]) * 0.01).astype(np.float32)
+            idx, _, _, _ = oracle.route_sigmoid(lgs[li], bias, cfg["K"], 0.0, bool(cfg["norm_topk"]), ROUTED_SCALE)
+        biases.append(bias)
         need = set(np.unique(idx).tolist())
         gate, up, down = {}, {}, {}
         for e in need:
-            g, u, d = W.expert_weights(cfg["D"], cfg["I"], 4, 32, 9000 + li * 64 + e)
+            g, u, d = W.expert_weights(cfg["D"], cfg["I"], cfg["fmt"], cfg["gs"], 9000 + li * cfg["E"] + e)
             gate[e], up[e], down[e] = g, u, d
-        layers_host.append((gate, up, down))
+        shared = W.expert_weights(cfg["D"], cfg["I"], cfg["fmt"], cfg["gs"], 8000 + li) if cfg["shared"] else None
+        layers_host.append((gate, up, down, shared))
     ids = list(range(L))
     for _ in range(args.warmup):
-        cpu_step(ref, oracle, cfg, layers_host, xs, lgs, ids)
+        cpu_step(ref, oracle, cfg, layers_host, xs, lgs, ids, biases)
     t0 = time.perf_counter()
     nbytes = 0
     for _ in range(args.steps):
-        nbytes += cpu_step(ref, oracle, cfg, layers_host, xs, lgs, ids)
+        nbytes += cpu_step(ref, oracle, cfg, layers_host, xs, lgs, ids, biases)
     dt = time.perf_counter() - t0
     gbs = nbytes / dt / 1e9
     line = {
@@ -222,7 +267,9 @@ def run_reference_arm(args):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic", "impl": "reference",
-        "config": {"workload": f"c2_decode: OLMoE-shape MoE layer op, int4 g32, M={M}, {L} layers per step"},
+        "config": {"workload": f"{args.workload}: MoE layer op (D={cfg['D']}, I={cfg['I']}, E={cfg['E']}, "
+                               f"top-{cfg['K']}), {'int4 g32' if cfg['fmt'] == 4 else 'MXFP4'}, M={M}, "
+                               f"{L} layers per step"},
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": ref.threads(), "kind": kind,
                          "sample": f"{args.steps} steps x {L} layers, routed experts only"},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -246,33 +293,46 @@ def run_gpu_arm(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    cfg = W.CONFIGS["c2"]
+    cfg = dict(W.CONFIGS[args.workload.split("_")[0]])
+    if args.experts:
+        cfg["E"] = args.experts          # profiling subsets only; the default is the full configuration
     D, I, E, K = cfg["D"], cfg["I"], cfg["E"], cfg["K"]
     L, M = args.layers, args.M
+    fmt, gs = cfg["fmt"], cfg["gs"]
 
     be = Backend()
     if be.init_devices((local,)) != 1:
         raise RuntimeError("coli_cuda_init failed: the CUDA backend is required (no CPU fallback)")
-    layers, handles, host_keep = [], [], []
+    layers, handles, host_keep, biases = [], [], [], []
+    up = lambda t: be.upload(t.w, t.s, t.fmt, t.I, t.O, local, t.gs)
     for li in range(L):
-        gate, up, down = gen_layer_host(torch, cfg, 1000 * (rank + 1) + li, dev)
-        hg = [be.upload(t.w, t.s, 4, t.I, t.O, local, 32) for t in gate]
-        hu = [be.upload(t.w, t.s, 4, t.I, t.O, local, 32) for t in up]
-        hd = [be.upload(t.w, t.s, 4, t.I, t.O, local, 32) for t in down]
-        if not all(hg + hu + hd):
+        gate, upw, down = gen_layer_host(torch, cfg, 1000 * (rank + 1) + li, dev)
+        hg, hu, hd = [up(t) for t in gate], [up(t) for t in upw], [up(t) for t in down]
+        shared = None
+        sh_host = None
+        if cfg["shared"]:
+            sg, su, sd = gen_layer_host(torch, cfg, 777000 + 1000 * (rank + 1) + li, dev, n_experts=1)
+            sh_host = (sg[0], su[0], sd[0])
+            shared = tuple(up(t) for t in sh_host)
+        if not all(hg + hu + hd + list(shared or ())):
             raise RuntimeError("tensor upload failed")
-        handles.append((hg, hu, hd))
-        layers.append(MoeLayer(be, D, I, E, K, hg, hu, hd, 0, 0, max_rows=max(M, 8)))
-        if rank == 0 and li < args.cpu_layers:
-            host_keep.append((gate, up, down))
-        del gate, up, down
+        handles.append((hg, hu, hd, shared))
+        bias = None
+        if cfg["gating"] == 1:
+            bias = (np.random.default_rng(31 + li).standard_normal(E) * 0.01).astype(np.float32)
+        biases.append(bias)
+        layers.append(MoeLayer(be, D, I, E, K, hg, hu, hd, cfg["gating"], cfg["norm_topk"], ROUTED_SCALE, 0.0,
+                               router_bias=bias, shared=shared, max_rows=max(M, 8)))
+        if rank == 0 and li < args.cpu_layers and not args.quick:
+            host_keep.append((gate, upw, down, sh_host))
+        del gate, upw, down
     torch.cuda.synchronize()
 
     xs = [W.activations(M, D, 100 + li + 1000 * rank) for li in range(L)]
     lgs = [W.router_logits(M, E, 200 + li + 1000 * rank) for li in range(L)]
     from oracle.oracle import Oracle   # routing counts for the byte accounting only
     orc = Oracle()
-    nus = [route_counts(orc, lgs[li], K, E) for li in range(L)]
+    nus = [route_counts(orc, cfg, lgs[li], biases[li]) + (1 if cfg["shared"] else 0) for li in range(L)]
     eb = expert_bytes_device(cfg)
     act_bytes = 2 * M * D * 4
     step_bytes = sum(nu * eb + act_bytes for nu in nus)
@@ -335,14 +395,16 @@ def run_gpu_arm(args):
     def step_host():
         for li in range(L):
             layers[li](xs[li], lgs[li], want_route=False)
-    for _ in range(max(args.warmup, 3)):
-        step_host()
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        step_host()
-    torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
+    e2e_s = float("nan")
+    if not args.quick:
+        for _ in range(max(args.warmup, 3)):
+            step_host()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            step_host()
+        torch.cuda.synchronize()
+        e2e_s = time.perf_counter() - t0
 
     tmax = torch.tensor([ms, e2e_s * 1e3], device=dev, dtype=torch.float64)
     if world > 1:
@@ -362,6 +424,8 @@ def run_gpu_arm(args):
         # CPU baseline on a bounded sample (first cpu_layers layers of the step)
         cpu = None
         try:
+            if args.quick:
+                raise RuntimeError("skipped (--quick)")
             from oracle.oracle import RefCpu
             ref = RefCpu() if RefCpu.available() else None
             kind = "reference" if ref else "port"
@@ -371,11 +435,11 @@ def run_gpu_arm(args):
                     def threads(self): return orc.threads()
                 ref = Port()
             ids = list(range(len(host_keep)))
-            cpu_step(ref, orc, cfg, host_keep, xs, lgs, ids)
+            cpu_step(ref, orc, cfg, host_keep, xs, lgs, ids, biases)
             t0 = time.perf_counter()
             nb, reps = 0, 0
             while time.perf_counter() - t0 < args.cpu_seconds:
-                nb += cpu_step(ref, orc, cfg, host_keep, xs, lgs, ids)
+                nb += cpu_step(ref, orc, cfg, host_keep, xs, lgs, ids, biases)
                 reps += 1
             dt = time.perf_counter() - t0
             cpu = {"value": nb / dt / 1e9, "unit": "GB/s", "cores": ref.threads(), "kind": kind,
@@ -387,8 +451,11 @@ def run_gpu_arm(args):
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_all / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
-            "config": {"workload": f"c2_decode: OLMoE-shape MoE layer op (D={D}, I={I}, E={E}, top-{K} softmax), "
-                                   f"int4 g32 fp16-valued scales, M={M} rows, {L} distinct layers per step",
+            "config": {"workload": f"{args.workload}: MoE layer op (D={D}, I={I}, E={E}"
+                                   f"{'+1 shared' if cfg['shared'] else ''}, top-{K} "
+                                   f"{'softmax' if cfg['gating'] == 0 else 'sigmoid'}), "
+                                   f"{'int4 g32 fp16-valued scales' if fmt == 4 else 'MXFP4'}, M={M} rows, "
+                                   f"{L} distinct layers per step",
                        "l2": f"{L} distinct layers, {weight_bytes_step / 1e6:.0f} MB of weights touched per step "
                              f"(> 126 MB L2); no flush needed",
                        "bytes_per_step": step_bytes, "distinct_experts_per_layer": nus,
@@ -407,8 +474,8 @@ def run_gpu_arm(args):
         print(json.dumps(line), flush=True)
     for lay in layers:
         lay.free()
-    for hg, hu, hd in handles:
-        for t in hg + hu + hd:
+    for hg, hu, hd, sh in handles:
+        for t in hg + hu + hd + list(sh or ()):
             be.tensor_free(t)
     be.shutdown()
     if world > 1:
@@ -421,7 +488,11 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2_decode", choices=["c2_decode", "c3_decode", "c4_decode"],
+                    help="layer shape and weight format (configuration 2, 3 or 4 of the benchmark)")
     ap.add_argument("--M", type=int, default=1, help="rows per layer call")
+    ap.add_argument("--experts", type=int, default=0, help="override the expert count (profiling subsets)")
+    ap.add_argument("--quick", action="store_true", help="device-resident timing only (no e2e, no CPU baseline)")
     ap.add_argument("--layers", type=int, default=16)
     ap.add_argument("--cpu-layers", type=int, default=4, help="layers kept on the host for the CPU baseline sample")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)

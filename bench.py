@@ -482,13 +482,135 @@ def run_gpu_arm(args):
         dist.destroy_process_group()
 
 
+# ---------------------------------------------------------------------------
+# expert-parallel workload (configuration 5)
+# ---------------------------------------------------------------------------
+def run_ep_arm(args):
+    """Configuration 5: GLM-scale layer (D 6144, I 2048, 256 routed experts + 1 shared,
+    top-8 sigmoid, MXFP4), 4 layers, M = 2048 rows in total, Zipf(1.1)-skewed logits;
+    experts sharded over the ranks, dispatch and combine as NCCL all-to-all. Strong
+    scaling: the total work is fixed. value = algorithmic weight bytes of all ranks
+    (distinct experts actually used + one shared expert per rank) + activations, per
+    step / max-over-ranks time."""
+    import torch
+    import torch.distributed as dist
+    from colibri_b200.backend import Backend
+    from colibri_b200.ep import CudaEpLayer, ep_moe_layer
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = dict(W.CONFIGS["c5"])
+    if args.experts:
+        cfg["E"] = args.experts
+    D, I, E, K = cfg["D"], cfg["I"], cfg["E"], cfg["K"]
+    L = args.layers if args.layers != 16 else 4
+    M = args.M if args.M != 1 else 2048
+    assert E % world == 0 and M % world == 0
+    e_loc, m = E // world, M // world
+    be = Backend()
+    if be.init_devices((local,)) != 1:
+        raise RuntimeError("coli_cuda_init failed: the CUDA backend is required (no CPU fallback)")
+    up = lambda t: be.upload(t.w, t.s, t.fmt, t.I, t.O, local, t.gs)
+    layers = []
+    for li in range(L):
+        hs = [[], [], []]
+        for e in range(rank * e_loc, (rank + 1) * e_loc):
+            for k, (O, Kd) in enumerate(((I, D), (I, D), (D, I))):
+                pk, sc = gen_mxfp4_torch(torch, 1, O, Kd, ((li * 1024 + e) * 4 + k) * 7 + 5, dev)
+                hs[k].append(up(QTensor(pk[0], sc[0], 7, Kd, O, 0)))
+        sh = []
+        for k, (O, Kd) in enumerate(((I, D), (I, D), (D, I))):
+            pk, sc = gen_mxfp4_torch(torch, 1, O, Kd, ((li * 1024 + 1000) * 4 + k) * 7 + 5, dev)
+            sh.append(up(QTensor(pk[0], sc[0], 7, Kd, O, 0)))
+        if not all(hs[0] + hs[1] + hs[2] + sh):
+            raise RuntimeError("tensor upload failed")
+        bias = torch.from_numpy((np.random.default_rng(31 + li).standard_normal(E) * 0.01).astype(np.float32)).to(dev)
+        layers.append(CudaEpLayer(be, local, cfg, hs[0], hs[1], hs[2], tuple(sh), bias, rank * e_loc, ROUTED_SCALE))
+    xs = [torch.from_numpy(W.activations(M, D, 500 + li)[rank * m:(rank + 1) * m].copy()).to(dev) for li in range(L)]
+    lg_all = [W.router_logits(M, E, 600 + li, zipf=1.1) for li in range(L)]
+    lgs = [torch.from_numpy(l[rank * m:(rank + 1) * m].copy()).to(dev) for l in lg_all]
+    # byte accounting from the routing of all rows (CPU oracle, accounting only)
+    from oracle.oracle import Oracle
+    orc = Oracle()
+    eb = expert_bytes_device(cfg)
+    step_bytes = 0
+    for li in range(L):
+        b = (np.random.default_rng(31 + li).standard_normal(E) * 0.01).astype(np.float32)
+        idx, _, _, _ = orc.route_sigmoid(lg_all[li], b, K, 0.0, True, ROUTED_SCALE)
+        step_bytes += (len(np.unique(idx)) + world) * eb + 2 * M * D * 4
+    torch.cuda.synchronize()
+
+    def step():
+        outs = []
+        for li in range(L):
+            lay = layers[li]
+            lay.logits = lgs[li]
+            out, _ = ep_moe_layer(xs[li], lay.route, lay.experts, lay.shared_fn, E)
+            outs.append(out)
+        return outs
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_all = float(t.item())
+    if be.kernel_status(local) != 0:
+        raise RuntimeError("a kernel wait guard expired")
+    if rank == 0:
+        peak, which = measured_peaks()
+        value = step_bytes * args.steps / (ms_all * 1e-3) / 1e9
+        line = {
+            "metric": "moe_expert_ffn_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_all / args.steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": f"c5_ep: expert-parallel MoE layer (D={D}, I={I}, E={E}+1 shared, top-{K} sigmoid, "
+                                   f"MXFP4), M={M} rows in total, {L} layers per step, Zipf(1.1) logit bias, "
+                                   f"experts sharded over {world} rank(s), NCCL all-to-all dispatch/combine (f32 rows)",
+                       "l2": "weights touched per step exceed L2 (126 MB)", "bytes_per_step": step_bytes,
+                       "a2a_bytes_per_rank_per_layer": int(2 * (M // world) * K * D * 4 * (world - 1) / max(world, 1))},
+            "e2e": None, "gpu_launches": None, "clocks": clocks,
+            "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s",
+                         "frac": value / world / peak, "traffic": None, "kernel": "k_gemv_stream (whole layer, per GPU)",
+                         "peak_source": which},
+            "cpu_baseline": None,
+        }
+        print(json.dumps(line), flush=True)
+    be.shutdown()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2_decode", choices=["c2_decode", "c3_decode", "c4_decode"],
+    ap.add_argument("--workload", default="c2_decode", choices=["c2_decode", "c3_decode", "c4_decode", "c5_ep"],
                     help="layer shape and weight format (configuration 2, 3 or 4 of the benchmark)")
     ap.add_argument("--M", type=int, default=1, help="rows per layer call")
     ap.add_argument("--experts", type=int, default=0, help="override the expert count (profiling subsets)")
@@ -497,7 +619,13 @@ def main():
     ap.add_argument("--cpu-layers", type=int, default=4, help="layers kept on the host for the CPU baseline sample")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.workload == "c5_ep":
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the reference has no expert-parallel path "
+                              "(no collective library); its CPU arm is timed on the default workload"}))
+        else:
+            run_ep_arm(args)
+    elif args.impl == "reference":
         run_reference_arm(args)
     else:
         run_gpu_arm(args)

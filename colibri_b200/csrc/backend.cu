@@ -1046,6 +1046,38 @@ extern "C" int coli_cuda_expert_group_resident_take(int home_device, const int *
 
 #include "moe_layer.cuh"
 
+// Device-pointer form of coli_cuda_expert_group (additive): x_dev and y_dev hold
+// sum(rows) consecutive [D] rows in call order on the tensors' device; experts with
+// zero rows are allowed and skipped; count is not limited to 64. Enqueues on the
+// backend's stream and returns. Used by the expert-parallel layer, whose rows arrive
+// from other ranks already in device memory.
+extern "C" int coli_cuda_expert_group_dev(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
+                                          ColiCudaTensor *const *downs, const int *rows, int count,
+                                          float *y_dev, const float *x_dev) {
+    if (fault_injected()) return 0;
+    if (!gates || !ups || !downs || !rows || !x_dev || !y_dev || count < 1) return 0;
+    std::vector<ColiCudaTensor *> g, u, d;
+    std::vector<int> r;
+    for (int e = 0; e < count; e++) {
+        if (rows[e] < 0) return 0;
+        if (rows[e] == 0) continue;
+        g.push_back(gates[e]); u.push_back(ups[e]); d.push_back(downs[e]); r.push_back(rows[e]);
+    }
+    if (g.empty()) return 1;
+    int device, D, I, total, max_rows, all_packed, any_packed;
+    if (!group_shape_ok(g.data(), u.data(), d.data(), r.data(), (int)g.size(), &device, &D, &I, &total,
+                        &max_rows, &all_packed, &any_packed)) return 0;
+    if (!all_packed && any_packed) return 0;
+    DeviceCtx *c = find_ctx(device);
+    if (!select_ctx(c)) return 0;
+    timing_begin(c);
+    int ok = group_device(c, g.data(), u.data(), d.data(), r.data(), (int)g.size(), D, I, total, max_rows,
+                          all_packed, y_dev, x_dev, nullptr);
+    timing_end(c);
+    if (ok) count_group(c, (int)g.size(), total);
+    return ok;
+}
+
 // ---------------------------------------------------------------------------
 // Allocation-free matmul on device pointers (no counterpart in the reference).
 //

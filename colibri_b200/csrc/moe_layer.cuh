@@ -312,3 +312,19 @@ extern "C" int coli_cuda_moe_layer(ColiCudaMoeLayer *L, float *out, const float 
     }
     return 1;
 }
+
+// Routing alone for callers that hold no layer handle (an expert-parallel rank owns
+// only a slice of the experts): logits_dev [M,E] -> idx/w [M,K], keff [M] on `device`,
+// same arithmetic as the layer entry points. bias_dev may be NULL.
+extern "C" int coli_cuda_route_topk_dev(int device, const float *logits_dev, const float *bias_dev, int M,
+                                        int E, int K, int gating, int norm_topk, float routed_scale,
+                                        float topp, int *idx_dev, float *w_dev, int *keff_dev) {
+    DeviceCtx *c = find_ctx(device);
+    if (!logits_dev || !idx_dev || !w_dev || !keff_dev || M < 1 || E < 1 || E > ROUTE_MAX_E || K < 1 ||
+        K > ROUTE_MAX_K || K > E || !select_ctx(c)) return 0;
+    RouteRule r{0, 0, E, K, gating, norm_topk, routed_scale, topp};
+    const int warps = 4;
+    size_t sm = (size_t)warps * (2 * E + 2 * ROUTE_MAX_K) * sizeof(float);
+    k_route_topk<<<(M + warps - 1) / warps, warps * 32, sm, c->stream>>>(logits_dev, bias_dev, r, M, idx_dev, w_dev, keff_dev);
+    return cuda_ok(cudaGetLastError(), "route launch");
+}

@@ -211,6 +211,13 @@ int coli_cuda_moe_route_dev(ColiCudaMoeLayer *layer, const float *x_dev, const f
                             int M, int *idx_dev, float *w_dev, int *keff_dev, int *uniq_dev,
                             int *nu_dev);
 
+/* coli_cuda_expert_group with DEVICE buffers (x_dev, y_dev: sum(rows) consecutive
+ * [D] rows in call order on the tensors' device). Experts with rows[e] == 0 are
+ * skipped and count may exceed 64. Enqueues on the backend's stream and returns. */
+int coli_cuda_expert_group_dev(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
+                               ColiCudaTensor *const *downs, const int *rows, int count, float *y_dev,
+                               const float *x_dev);
+
 /* No counterpart in the reference. coli_cuda_pipe_gemm for callers that must not
  * allocate device memory at call time (an engine that has given all free HBM to
  * its caches, or a decode loop that cannot take the device-wide synchronisation
@@ -224,6 +231,13 @@ int coli_cuda_moe_route_dev(ColiCudaMoeLayer *layer, const float *x_dev, const f
  * any stream capture. Runs on the backend's stream for the device; returns
  * after enqueueing. */
 int coli_cuda_pipe_gemm_noalloc(ColiCudaTensor *t, float *y_dev, const float *x_dev, int S);
+
+/* Routing without a layer handle (an expert-parallel rank owns only some of the
+ * experts): logits_dev [M,E] (+ optional bias_dev [E]) -> idx_dev, w_dev [M,K],
+ * keff_dev [M], same rules and arithmetic as coli_cuda_moe_layer. */
+int coli_cuda_route_topk_dev(int device, const float *logits_dev, const float *bias_dev, int M, int E,
+                             int K, int gating, int norm_topk, float routed_scale, float topp,
+                             int *idx_dev, float *w_dev, int *keff_dev);
 
 /* Physical device bytes held by resident tensors after repacking (the logical
  * figure is coli_cuda_stats). */

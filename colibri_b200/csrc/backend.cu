@@ -10,6 +10,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <cmath>
 #include <mutex>
 #include <vector>
 
@@ -18,6 +19,7 @@
 #include "kernels_misc.cuh"
 #include "router.cuh"
 #include "moe_decode.cuh"
+#include "gemm_tc.cuh"
 
 // ---------------------------------------------------------------------------
 // Context
@@ -136,6 +138,11 @@ static void setup_one() {
 template <int MODE>
 static void setup_mode() { setup_one<MODE, 1>(); setup_one<MODE, 2>(); setup_one<MODE, 4>(); setup_one<MODE, 8>(); }
 
+template <int MODE>
+static int tc_smem_bytes() {
+    return 2 * ((MODE == SC_H16 ? 2 : 1) * TC_M * TC_KB * 2 + 2 * TC_NMAX * TC_KB * 2) + 1024;
+}
+
 extern "C" void coli_cuda_shutdown(void);
 
 static int decode_smem_bytes(int mode) {
@@ -182,6 +189,8 @@ extern "C" int coli_cuda_init(const int *devices, int count) {
         setup_mode<SC_ROW>(); setup_mode<SC_H16>(); setup_mode<SC_F32>(); setup_mode<SC_MX>();
         set_smem(k_moe_decode<SC_ROW>, decode_smem_bytes(SC_ROW)); set_smem(k_moe_decode<SC_H16>, decode_smem_bytes(SC_H16));
         set_smem(k_moe_decode<SC_F32>, decode_smem_bytes(SC_F32)); set_smem(k_moe_decode<SC_MX>, decode_smem_bytes(SC_MX));
+        set_smem(k_expert_gemm_tc<SC_ROW>, tc_smem_bytes<SC_ROW>()); set_smem(k_expert_gemm_tc<SC_H16>, tc_smem_bytes<SC_H16>());
+        set_smem(k_expert_gemm_tc<SC_MX>, tc_smem_bytes<SC_MX>());
         if (!cuda_ok(cudaGetLastError(), "kernel attributes")) { g_nctx = i + 1; coli_cuda_shutdown(); return 0; }
     }
     g_nctx = count;
@@ -294,6 +303,51 @@ static int scales_fit_half(const float *s, size_t n) {
     return 1;
 }
 
+// Decides whether the tensor-core path can carry this tensor exactly and with which
+// power-of-two pre-multiplier (gemm_tc.cuh):
+//   SC_ROW  integer codes, no shift
+//   SC_H16  scale * 2^shift puts the largest scale in [2^10, 2^11); every non-zero scale must
+//           lie within 2^-12 of the largest so that the hi/lo split keeps its low bits
+//   SC_MX   2^(e - 127 + 14 + shift) must be an fp16 power of two >= 2^-9 for every group
+//           that holds a non-zero code: shift = 128 - e_max, spread e_max - e <= 24
+static void tensor_tc_params(ColiCudaTensor *t, const void *weights, const void *scales) {
+    t->tc_ok = 0; t->tc_shift = 0;
+    if (!t->packed || (t->O % 128) || (t->I % 128)) return;
+    const size_t scount = (size_t)t->O * (size_t)t->ng;
+    if (t->mode == SC_ROW) { t->tc_ok = 1; return; }
+    if (t->mode == SC_H16) {
+        const float *s = static_cast<const float *>(scales);
+        float smax = 0.f, smin = 0.f;
+        for (size_t i = 0; i < scount; i++) {
+            float a = std::fabs(s[i]);
+            if (!(a <= 65504.f)) return;          // inf / nan
+            if (a > smax) smax = a;
+            if (a > 0.f && (smin == 0.f || a < smin)) smin = a;
+        }
+        if (smax == 0.f) { t->tc_ok = 1; return; }
+        if (smin < smax * (1.0f / 4096.0f)) return;
+        int ex; std::frexp(smax, &ex);             // smax = m * 2^ex, m in [0.5, 1)
+        int shift = 11 - ex;                       // smax * 2^shift in [2^10, 2^11)
+        if (shift < 0 || shift > 30) return;
+        t->tc_shift = shift; t->tc_ok = 1;
+        return;
+    }
+    if (t->mode == SC_MX) {
+        const uint8_t *e8 = static_cast<const uint8_t *>(scales);
+        const uint8_t *q = static_cast<const uint8_t *>(weights);
+        int emax = 0;
+        for (size_t i = 0; i < scount; i++) { if (e8[i] == 255) return; if (e8[i] > emax) emax = e8[i]; }
+        const size_t rb = (size_t)t->I / 2;
+        for (size_t i = 0; i < scount; i++) {
+            if (emax - (int)e8[i] <= 24) continue;
+            const size_t row = i / t->ng, g = i % t->ng;
+            const uint8_t *c = q + row * rb + g * 16;
+            for (int b = 0; b < 16; b++) if (c[b] & 0x77) return;   // a live group below the exact range
+        }
+        t->tc_shift = 128 - emax; t->tc_ok = 1;
+    }
+}
+
 static void tensor_release(ColiCudaTensor *t) {
     if (t->raw_w) cudaFree(t->raw_w);
     if (t->raw_s) cudaFree(t->raw_s);
@@ -329,6 +383,7 @@ static int tensor_fill(DeviceCtx *c, ColiCudaTensor *t, const void *weights, con
                !scales_fit_half(static_cast<const float *>(scales), scount)) {
         return 0;   // the refreshed scales no longer fit the storage chosen at upload
     }
+    tensor_tc_params(t, weights, scales);
     const int ch = chunk_bytes_of(mode);
     const size_t nblk = (size_t)(t->O / TILE_ROWS) * (t->I / BLOCK_K);
     const size_t pkbytes = nblk * ch;
@@ -699,10 +754,139 @@ static int group_shape_ok(ColiCudaTensor *const *gates, ColiCudaTensor *const *u
     return 1;
 }
 
+
+// ---------------------------------------------------------------------------
+// Tensor-core path of the expert group (gemm_tc.cuh): taken when some expert has
+// more rows than one streaming pass holds and every tensor qualifies.
+// ---------------------------------------------------------------------------
+static int g_tc_enabled = 1;
+extern "C" void coli_cuda_set_tensor_core(int enabled) { g_tc_enabled = enabled ? 1 : 0; }
+#define TC_MIN_ROWS 33
+
+template <int MODE>
+static void launch_tc_mode(DeviceCtx *c, const TcSeg *segs, const TcCtl *ctl, int ntask) {
+    int grid = ntask < c->sms ? ntask : c->sms;
+    k_expert_gemm_tc<MODE><<<grid, TC_THREADS, tc_smem_bytes<MODE>(), c->stream>>>(segs, ctl, c->status);
+    c->last_launches++;
+}
+
+struct TcSegs {
+    std::vector<TcSeg> v[4];
+    int ntask[4] = {0, 0, 0, 0};
+};
+static void add_tc_seg(TcSegs *ts, const ColiCudaTensor *t, float *out, const __half *bq, const float *binv,
+                       int nrows, int npad, int pos0) {
+    TcSeg s;
+    std::memset(&s, 0, sizeof(s));
+    s.w = t->pk; s.rowscale = t->rowscale; s.bq = bq; s.binv = binv; s.out = out;
+    s.nrows = nrows; s.npad = npad; s.pos0 = pos0;
+    s.O = t->O; s.nkb64 = t->I / TC_KB;
+    s.task0 = ts->ntask[t->mode];
+    s.shift = t->tc_shift;
+    s.out_scale = std::ldexp(1.0f, -t->tc_shift);
+    ts->ntask[t->mode] += t->O / TC_M;
+    ts->v[t->mode].push_back(s);
+}
+static int run_tc_segs(DeviceCtx *c, TcSegs *ts, Buf *segbuf) {
+    size_t total = 0;
+    for (int m = 0; m < 4; m++) total += ts->v[m].size();
+    const size_t seg_bytes = total * sizeof(TcSeg), need = seg_bytes + 4 * sizeof(TcCtl);
+    if (!reserve(c, segbuf, need)) return 0;
+    std::vector<uint8_t> stage(need);   // pageable: captured by the copy call before it returns
+    uint8_t *hp = stage.data(), *dp = static_cast<uint8_t *>(segbuf->p);
+    size_t off = 0, seg_off[4];
+    TcCtl ctl[4];
+    for (int m = 0; m < 4; m++) {
+        seg_off[m] = off;
+        size_t b = ts->v[m].size() * sizeof(TcSeg);
+        if (b) std::memcpy(hp + off, ts->v[m].data(), b);
+        off += b;
+        ctl[m].nseg = (int)ts->v[m].size(); ctl[m].ntask = ts->ntask[m];
+    }
+    std::memcpy(hp + seg_bytes, ctl, sizeof(ctl));
+    if (!cuda_ok(cudaMemcpyAsync(dp, hp, need, cudaMemcpyHostToDevice, c->stream), "segment upload")) return 0;
+    for (int m = 0; m < 4; m++) {
+        if (ts->v[m].empty()) continue;
+        const TcSeg *sp = reinterpret_cast<const TcSeg *>(dp + seg_off[m]);
+        const TcCtl *cp = reinterpret_cast<const TcCtl *>(dp + seg_bytes) + m;
+        if (m == SC_ROW) launch_tc_mode<SC_ROW>(c, sp, cp, ts->ntask[m]);
+        else if (m == SC_H16) launch_tc_mode<SC_H16>(c, sp, cp, ts->ntask[m]);
+        else if (m == SC_MX) launch_tc_mode<SC_MX>(c, sp, cp, ts->ntask[m]);
+        else return 0;
+    }
+    return cuda_ok(cudaGetLastError(), "tensor-core gemm launch");
+}
+
+static int group_tc_ok(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
+                       ColiCudaTensor *const *downs, int count, int max_rows) {
+    if (!g_tc_enabled || max_rows < TC_MIN_ROWS) return 0;
+    for (int e = 0; e < count; e++)
+        if (!gates[e]->tc_ok || !ups[e]->tc_ok || !downs[e]->tc_ok) return 0;
+    return 1;
+}
+
+// x_dev [total (or 1 when bcast), D] -> y_dev [total, D]; passes of up to 128 rows per expert.
+static int group_device_tc(DeviceCtx *c, ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
+                           ColiCudaTensor *const *downs, const int *rows, int count, int D, int I,
+                           int total, float *y_dev, const float *x_dev, int bcast) {
+    std::vector<int> meta;            // [rowsrc | row_pass | row_n | pass_row0 | pass_npad]
+    std::vector<int> row_pass(total), row_n(total), pass_row0, pass_npad, pass_rows, pass_pos0, pass_expert;
+    int off = 0, padded = 0;
+    for (int e = 0; e < count; e++) {
+        const int re = rows ? rows[e] : 1;
+        for (int r0 = 0; r0 < re; r0 += TC_NMAX) {
+            const int nr = re - r0 < TC_NMAX ? re - r0 : TC_NMAX, npad = (nr + 15) & ~15;
+            const int p = (int)pass_row0.size();
+            for (int r = 0; r < nr; r++) { row_pass[off + r0 + r] = p; row_n[off + r0 + r] = r; }
+            pass_row0.push_back(padded); pass_npad.push_back(npad); pass_rows.push_back(nr);
+            pass_pos0.push_back(off + r0); pass_expert.push_back(e);
+            padded += npad;
+        }
+        off += re;
+    }
+    const int npass = (int)pass_row0.size();
+    meta.resize((size_t)3 * total + 2 * npass);
+    for (int r = 0; r < total; r++) { meta[r] = bcast ? 0 : r; meta[total + r] = row_pass[r]; meta[2 * total + r] = row_n[r]; }
+    for (int p = 0; p < npass; p++) { meta[3 * total + p] = pass_row0[p]; meta[3 * total + npass + p] = pass_npad[p]; }
+    if (!reserve(c, &c->misc, meta.size() * sizeof(int)) ||
+        !reserve(c, &c->bq, (size_t)padded * D * 2 * sizeof(__half)) ||
+        !reserve(c, &c->bs, (size_t)total * sizeof(float)) ||
+        !reserve(c, &c->pg, (size_t)total * I * sizeof(float)) ||
+        !reserve(c, &c->pu, (size_t)total * I * sizeof(float)) ||
+        !reserve(c, &c->hq, (size_t)padded * I * 2 * sizeof(__half)) ||
+        !reserve(c, &c->hs, (size_t)total * sizeof(float))) return 0;
+    if (!cuda_ok(cudaMemcpyAsync(c->misc.p, meta.data(), meta.size() * sizeof(int), cudaMemcpyHostToDevice, c->stream), "row table upload")) return 0;
+    const int *d_meta = static_cast<const int *>(c->misc.p);
+    const int *d_rowsrc = d_meta, *d_row_pass = d_meta + total, *d_row_n = d_meta + 2 * total;
+    const int *d_pass_row0 = d_meta + 3 * total, *d_pass_npad = d_pass_row0 + npass;
+    __half *bq = (__half *)c->bq.p, *hq = (__half *)c->hq.p;
+    float *binv = (float *)c->bs.p, *hinv = (float *)c->hs.p, *G = (float *)c->pg.p, *U = (float *)c->pu.p;
+    k_prep_umma<<<(total * 32 + 255) / 256, 256, 0, c->stream>>>(bq, binv, x_dev, nullptr, d_rowsrc, d_row_pass, d_row_n,
+                                                                 d_pass_row0, d_pass_npad, total, D);
+    c->last_launches++;
+    TcSegs t1, t2;
+    for (int p = 0; p < npass; p++) {
+        const int e = pass_expert[p];
+        const __half *bp = bq + (size_t)2 * D * pass_row0[p];
+        const __half *hp = hq + (size_t)2 * I * pass_row0[p];
+        add_tc_seg(&t1, gates[e], G, bp, binv + pass_pos0[p], pass_rows[p], pass_npad[p], pass_pos0[p]);
+        add_tc_seg(&t1, ups[e], U, bp, binv + pass_pos0[p], pass_rows[p], pass_npad[p], pass_pos0[p]);
+        add_tc_seg(&t2, downs[e], y_dev, hp, hinv + pass_pos0[p], pass_rows[p], pass_npad[p], pass_pos0[p]);
+    }
+    if (!run_tc_segs(c, &t1, &c->segs1)) return 0;
+    k_prep_umma<<<(total * 32 + 255) / 256, 256, 0, c->stream>>>(hq, hinv, G, U, nullptr, d_row_pass, d_row_n,
+                                                                 d_pass_row0, d_pass_npad, total, I);
+    c->last_launches++;
+    if (!run_tc_segs(c, &t2, &c->segs2)) return 0;
+    return cuda_ok(cudaGetLastError(), "expert group launch");
+}
+
 static int group_device(DeviceCtx *c, ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
                         ColiCudaTensor *const *downs, const int *rows, int count, int D, int I,
                         int total, int max_rows, int all_packed, float *y_dev, const float *x_dev,
                         const int *bcast_src /* optional: every row reads x row 0 */) {
+    if (all_packed && D % 128 == 0 && I % 128 == 0 && group_tc_ok(gates, ups, downs, count, max_rows))
+        return group_device_tc(c, gates, ups, downs, rows, count, D, I, total, y_dev, x_dev, bcast_src != nullptr);
     if (all_packed) {
         const int nc = pick_nc(max_rows), rpp = 4 * nc;
         long npass = 0;

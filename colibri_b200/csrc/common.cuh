@@ -68,6 +68,9 @@ struct ColiCudaTensor {
     int mode;                 // ScaleMode
     uint8_t *pk;              // tile streams
     float *rowscale;          // SC_ROW only
+    // tensor-core path (gemm_tc.cuh): usable for this tensor, and the power of two its
+    // fp16 weight terms are pre-multiplied with
+    int tc_ok, tc_shift;
 };
 
 // One matrix x one pass of rows for the streaming GEMV kernel.

@@ -254,6 +254,13 @@ void coli_cuda_set_timing(int enabled);
  * kernel; 0 routes them through the multi-kernel path instead (A/B testing). */
 void coli_cuda_set_fused_decode(int enabled);
 
+/* Expert groups in which some expert has more than 32 rows normally run on the
+ * tcgen05 tensor-core kernel (when every tensor of the group is int4 with per-row
+ * or fp16-exact group scales, or MXFP4, and D and I are multiples of 128);
+ * 0 keeps them on the streaming kernel instead (A/B testing). No counterpart in
+ * the reference. */
+void coli_cuda_set_tensor_core(int enabled);
+
 /* Phase probe of the fused decode kernel: with a device buffer of
  * (#SMs x 12) 64-bit words set, thread 0 of every CTA stores the global
  * nanosecond timer at each phase boundary of the next launches (start, routed,

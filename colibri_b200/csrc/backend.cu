@@ -139,9 +139,7 @@ template <int MODE>
 static void setup_mode() { setup_one<MODE, 1>(); setup_one<MODE, 2>(); setup_one<MODE, 4>(); setup_one<MODE, 8>(); }
 
 template <int MODE>
-static int tc_smem_bytes() {
-    return 2 * ((MODE == SC_H16 ? 2 : 1) * TC_M * TC_KB * 2 + 2 * TC_NMAX * TC_KB * 2) + 1024;
-}
+static int tc_smem_bytes() { return tc_smem_total(MODE); }
 
 extern "C" void coli_cuda_shutdown(void);
 
@@ -784,7 +782,7 @@ static void add_tc_seg(TcSegs *ts, const ColiCudaTensor *t, float *out, const __
     s.task0 = ts->ntask[t->mode];
     s.shift = t->tc_shift;
     s.out_scale = std::ldexp(1.0f, -t->tc_shift);
-    ts->ntask[t->mode] += t->O / TC_M;
+    ts->ntask[t->mode] += (t->O + TC_FEAT - 1) / TC_FEAT;
     ts->v[t->mode].push_back(s);
 }
 static int run_tc_segs(DeviceCtx *c, TcSegs *ts, Buf *segbuf) {
@@ -826,6 +824,7 @@ static int group_tc_ok(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
 }
 
 // x_dev [total (or 1 when bcast), D] -> y_dev [total, D]; passes of up to 128 rows per expert.
+// y_dev must be 16-byte aligned (the accumulators are stored as float4).
 static int group_device_tc(DeviceCtx *c, ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
                            ColiCudaTensor *const *downs, const int *rows, int count, int D, int I,
                            int total, float *y_dev, const float *x_dev, int bcast) {
@@ -834,8 +833,8 @@ static int group_device_tc(DeviceCtx *c, ColiCudaTensor *const *gates, ColiCudaT
     int off = 0, padded = 0;
     for (int e = 0; e < count; e++) {
         const int re = rows ? rows[e] : 1;
-        for (int r0 = 0; r0 < re; r0 += TC_NMAX) {
-            const int nr = re - r0 < TC_NMAX ? re - r0 : TC_NMAX, npad = (nr + 15) & ~15;
+        for (int r0 = 0; r0 < re; r0 += TC_ROWS) {
+            const int nr = re - r0 < TC_ROWS ? re - r0 : TC_ROWS, npad = (nr + 15) & ~15;
             const int p = (int)pass_row0.size();
             for (int r = 0; r < nr; r++) { row_pass[off + r0 + r] = p; row_n[off + r0 + r] = r; }
             pass_row0.push_back(padded); pass_npad.push_back(npad); pass_rows.push_back(nr);
@@ -885,7 +884,8 @@ static int group_device(DeviceCtx *c, ColiCudaTensor *const *gates, ColiCudaTens
                         ColiCudaTensor *const *downs, const int *rows, int count, int D, int I,
                         int total, int max_rows, int all_packed, float *y_dev, const float *x_dev,
                         const int *bcast_src /* optional: every row reads x row 0 */) {
-    if (all_packed && D % 128 == 0 && I % 128 == 0 && group_tc_ok(gates, ups, downs, count, max_rows))
+    if (all_packed && D % 128 == 0 && I % 128 == 0 && (reinterpret_cast<uintptr_t>(y_dev) & 15) == 0 &&
+        group_tc_ok(gates, ups, downs, count, max_rows))
         return group_device_tc(c, gates, ups, downs, rows, count, D, I, total, y_dev, x_dev, bcast_src != nullptr);
     if (all_packed) {
         const int nc = pick_nc(max_rows), rpp = 4 * nc;

@@ -2,11 +2,20 @@
 // in TMEM) for experts with many rows (prefill / batched decode), over the same
 // packed tile-stream weights as the streaming GEMV.
 //
-// Shape of one task: 128 output features x up to 128 rows of one expert, full
-// contraction. D[128 x N] (TMEM, f32) += A[128 x 16] (fp16, shared memory) x
-// B[N x 16]^T (fp16, shared memory), K-major operands in the no-swizzle
-// core-matrix layout (8 rows x 16 bytes contiguous; 8-row groups 128 B apart,
-// 8-column chunks one tile-column apart).
+// Shape of one task: up to 128 rows of one expert (a "pass") x 256 output features,
+// full contraction. D[128 rows x 256 features] (TMEM, f32) += X[128 x 16] (fp16,
+// shared memory, the A operand) x W[256 x 16]^T (fp16, shared memory, the B
+// operand), both K-major. One activation stage thus feeds 256 features, and one
+// instruction is 128 x 256 x 16: measured here, an MMA costs about 80 cycles however
+// narrow it is, so the widest shape is the only one that reaches the tensor rate.
+//   X tile: no-swizzle core-matrix layout (8 rows x 16 bytes contiguous; 8-row
+//           groups 128 B apart, 8-column chunks npad*16 B apart), which the
+//           preparation kernel writes to global memory as is, so a stage is one
+//           bulk copy. Rows >= npad of the 128 read whatever follows in shared
+//           memory; they only feed accumulator rows that are never read back.
+//   W tile: 128-byte-swizzle layout (rows of 64 fp16, 8-row groups of 1024 B, the
+//           16-byte chunk index XORed with the row index in the group), chosen so
+//           that the decode warps' 16-byte stores spread over all banks.
 //
 // Exactness: the CPU path multiplies f32 activations with exactly decoded
 // weights. Both operands are therefore expanded into fp16 terms whose products the
@@ -14,36 +23,63 @@
 //   activations  x*2^r  = hi + lo   (r per row: largest |x| lands in [2^13, 2^14))
 //   MXFP4 / per-row int4 weights: one exact fp16 term (e2m1 * 2^(e+shift), or n)
 //   grouped int4 with fp16 scales: n*s*2^shift = hi + lo exactly (hmul2 + fma residual)
-// so a 16-column step costs 2 MMAs (A x Bhi, A x Blo) or 3 (Ahi x Bhi, Ahi x Blo,
-// Alo x Bhi); the dropped Alo x Blo term is below 2^-22 of the product.
-// The row scale 2^-r, the tensor shift and a per-row weight scale are applied when
-// the accumulators are read back.
+// so a 16-column step costs 2 MMAs (Xhi x W, Xlo x W) or 3 (Xhi x Whi, Xlo x Whi,
+// Xhi x Wlo); the dropped Xlo x Wlo term is below 2^-22 of the product.
+// The row scale 2^-r, the tensor shift and a per-feature weight scale are applied
+// when the accumulators are read back.
 //
-// Pipeline per 64-column block, two shared-memory stages: all 256 threads decode
-// their share of the weight block into the A tile(s) and copy the pre-split
-// activation tile (cp.async), fence to the async proxy and meet at a CTA barrier;
-// one thread issues the block's MMAs and commits them to the stage's mbarrier,
-// which the threads wait on before they overwrite that stage two blocks later.
-// Every wait is bounded; on expiry the CTA records KSTAT_MBAR_TIMEOUT, frees its
-// TMEM columns and leaves.
+// Pipeline (one CTA per SM, 23 warps, every hand-over through an mbarrier):
+//   warp 0       weight producer: bulk copies of the raw packed chunks (8 tiles of 32
+//                features x 128 columns per stage) into a ring
+//   warp 1       activation producer: one bulk copy per 32-column block (both terms,
+//                contiguous in global memory) into a ring of 16 KB stages
+//   warp 2       one thread issues the MMAs of a 64-column block (descriptor high words
+//                constant, low words advanced by adds) and commits them to the barriers
+//                that free the activation stages and the W stage; after the last block it
+//                commits to the accumulator barrier
+//   warps 3-18   decode: raw chunk -> registers -> fp16 W tile(s) of a 2-stage ring (one
+//                16-byte shared store per 8 weights), fence to the async proxy, one
+//                arrival per warp
+//   warps 19-22  read the accumulators of a finished task (tcgen05.ld, lane = row),
+//                scale and store them while the next task's MMAs fill the other half of
+//                the 512 allocated TMEM columns
+// Every wait is bounded and also polls a CTA-wide abort flag; on expiry the CTA
+// records KSTAT_MBAR_TIMEOUT, waits (bounded) for its copies and MMAs in flight,
+// frees its TMEM columns and leaves.
 #pragma once
 #include "common.cuh"
 #include "gemv_stream.cuh"
 
-#define TC_M 128            // output features per task
-#define TC_NMAX 128         // rows per task (padded to a multiple of 16)
-#define TC_KB 64            // columns per pipeline step
-#define TC_THREADS 256
+#define TC_ROWS 128         // rows per pass (M of the MMA)
+#define TC_FEAT 256         // output features per task (N of the MMA)
+#define TC_KB 64            // columns per W stage
+#define TC_XKB 32           // columns per activation stage
+#define TC_NW 2             // W ring depth
+#define TC_DEC_WARPS 16
+#define TC_WARPS (3 + TC_DEC_WARPS + 4)
+#define TC_THREADS (TC_WARPS * 32)
+#define TC_X_STAGE (2 * 4 * TC_ROWS * 16)   // 16 KB: both terms of a 32-column block of 128 rows
+
+__host__ __device__ constexpr int tc_chunk_bytes(int mode) {
+    return CODE_BYTES + (mode == SC_H16 ? 256 : mode == SC_F32 ? 512 : mode == SC_MX ? 128 : 0);
+}
+__host__ __device__ constexpr int tc_nraw(int mode) { return mode == SC_H16 ? 2 : 3; }      // raw ring depth
+__host__ __device__ constexpr int tc_nx(int mode) { return mode == SC_H16 ? 3 : 6; }        // activation ring depth
+__host__ __device__ constexpr int tc_raw_stage_bytes(int mode) { return 8 * tc_chunk_bytes(mode); }
+__host__ __device__ constexpr int tc_w_stage_bytes(int mode) { return (mode == SC_H16 ? 2 : 1) * TC_FEAT * TC_KB * 2; }
+__host__ __device__ constexpr int tc_smem_total(int mode) {
+    return TC_NW * tc_w_stage_bytes(mode) + tc_nx(mode) * TC_X_STAGE + tc_nraw(mode) * tc_raw_stage_bytes(mode) + 1024;
+}
 
 struct TcSeg {
     const uint8_t *w;        // packed tensor
     const float *rowscale;   // SC_ROW: per output feature, else NULL
-    const __half *bq;        // activation tiles of this pass: [nkb64][2 terms][8 chunks][npad/8][8][8] halfs
+    const __half *bq;        // activation tiles of this pass: [K/32][2 terms][4 chunks][npad][8] halfs
     const float *binv;       // [nrows] 2^-r of the pass rows
     float *out;              // [.. , O] row-major; row (pos0 + n) receives feature o
     int nrows, npad, pos0;
     int O, nkb64;            // output features, 64-column blocks along the contraction
-    int task0;               // first task of this segment (tasks = O / 128)
+    int task0;               // first task of this segment (tasks = ceil(O / 256))
     float out_scale;         // 2^-shift of the tensor
     int shift;               // tensor shift: fp16 weight terms carry value * 2^shift
 };
@@ -52,44 +88,37 @@ struct TcCtl {
     int nseg, ntask;
 };
 
-__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    // K-major, no swizzle: start address, leading (K direction) and stride (8-row group)
-    // byte offsets in 16-byte units, descriptor version 1 (Blackwell)
-    uint64_t d = 0;
-    d |= (uint64_t)((saddr >> 4) & 0x3FFFu);
-    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
-    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
-    d |= (uint64_t)1 << 46;
-    return d;
-}
 __device__ __forceinline__ uint32_t umma_idesc_f16(int M, int N) {
     // D f32 (1 << 4), A f16 (0 << 7), B f16 (0 << 10), both K-major, N >> 3 at bit 17, M >> 4 at bit 24
     return (1u << 4) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                         uint32_t accumulate) {
+// One MMA, descriptors given as 32-bit halves: the issuing thread is a single dependent
+// instruction stream, so the loop keeps the constant high words in registers and only
+// adds to the low words (start address field).
+//   low word : start address >> 4 | (leading byte offset >> 4) << 16
+//   high word: stride byte offset >> 4 | version 1 << 14 | layout type << 29 (0 none, 2 128-byte swizzle)
+__device__ __forceinline__ void umma_f16_split(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                               uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u)
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, {%7, %7, %7, %7}, p;\n\t}"
+        ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate), "r"(0u)
         : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
 
 // Activation preparation for the tensor-core path: one warp per row of the call.
 // Row n of pass p lives in the pass's tiles: halfs at
-//   base_p + ((kb*2 + term)*8 + kc) * npad*8 + (n/8)*64 + (n%8)*8 + (k%8),   kb = k/64, kc = (k%64)/8
+//   base_p + ((kb*2 + term)*4 + kc) * npad*8 + (n/8)*64 + (n%8)*8 + (k%8),   kb = k/32, kc = (k%32)/8
 // with base_p = 2*K*pass_row0[p] (pass_row0 = padded rows of all earlier passes). Rows
-// n >= nrows of a pass are never written: they only feed accumulator columns that are
-// never read back. The row scale is taken over the whole row; 2^-r goes to binv.
-// rowsrc: optional gather (row -> source row of x). u: when set, the row is
-// silu(x)*u (the SwiGLU of complete gate/up sums) instead of x.
+// n >= nrows of a pass are never written. The row scale is taken over the whole row;
+// 2^-r goes to binv. rowsrc: optional gather (row -> source row of x). u: when set, the
+// row is silu(x)*u (the SwiGLU of complete gate/up sums) instead of x.
 __device__ __forceinline__ float4 tc_row_vals(const float *xr, const float *ur, int k) {
     float4 v = *reinterpret_cast<const float4 *>(xr + k);
     if (ur) {
@@ -125,9 +154,9 @@ __global__ void k_prep_umma(__half *__restrict__ bq, float *__restrict__ binv, c
         __half hi[4], lo[4];
 #pragma unroll
         for (int i = 0; i < 4; i++) { hi[i] = __float2half_rn(xv[i]); lo[i] = __float2half_rn(xv[i] - __half2float(hi[i])); }
-        const int kb = k >> 6, kc = (k & 63) >> 3, ki = k & 7;
-        size_t o_hi = ((size_t)((kb * 2 + 0) * 8 + kc) * npad) * 8 + (size_t)(n >> 3) * 64 + (n & 7) * 8 + ki;
-        size_t o_lo = ((size_t)((kb * 2 + 1) * 8 + kc) * npad) * 8 + (size_t)(n >> 3) * 64 + (n & 7) * 8 + ki;
+        const int kb = k >> 5, kc = (k & 31) >> 3, ki = k & 7;
+        size_t o_hi = ((size_t)((kb * 2 + 0) * 4 + kc) * npad) * 8 + (size_t)(n >> 3) * 64 + (n & 7) * 8 + ki;
+        size_t o_lo = ((size_t)((kb * 2 + 1) * 4 + kc) * npad) * 8 + (size_t)(n >> 3) * 64 + (n & 7) * 8 + ki;
         *reinterpret_cast<uint2 *>(base + o_hi) = make_uint2(
             (uint32_t)__half_as_ushort(hi[0]) | ((uint32_t)__half_as_ushort(hi[1]) << 16),
             (uint32_t)__half_as_ushort(hi[2]) | ((uint32_t)__half_as_ushort(hi[3]) << 16));
@@ -137,202 +166,322 @@ __global__ void k_prep_umma(__half *__restrict__ bq, float *__restrict__ binv, c
     }
 }
 
+#define TC_MAX_RING 6
+struct TcBars {
+    unsigned long long raw_full[4], raw_empty[4];
+    unsigned long long x_full[TC_MAX_RING], x_empty[TC_MAX_RING];
+    unsigned long long w_full[TC_NW], w_empty[TC_NW];
+    unsigned long long acc_full[2], acc_empty[2];
+    unsigned long long drain;
+};
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Bounded wait that also gives up as soon as another role of the CTA has given up.
+__device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (*abort_flag) return false;
+        if (clock64() - t0 > 400000000LL) { *abort_flag = 1; return false; }
+    }
+    return true;
+}
+__device__ __forceinline__ const TcSeg *tc_find_seg(const TcSeg *segs, int nseg, int task) {
+    int lo = 0, hi = nseg - 1;
+    while (lo < hi) { int mid = (lo + hi + 1) >> 1; if (segs[mid].task0 <= task) lo = mid; else hi = mid - 1; }
+    return segs + lo;
+}
+// Ring position with the parity its "full" barrier is waited with; the matching "empty"
+// barrier of a slot that has been used before is waited with the opposite parity.
+struct TcRing {
+    int s; uint32_t par; bool wrapped;
+    __device__ TcRing() : s(0), par(0), wrapped(false) {}
+    __device__ __forceinline__ void next(int n) { if (++s == n) { s = 0; par ^= 1; wrapped = true; } }
+};
+
 template <int MODE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 k_expert_gemm_tc(const TcSeg *__restrict__ segs, const TcCtl *__restrict__ ctl, int *status) {
-    constexpr int CH = CODE_BYTES + (MODE == SC_H16 ? 256 : MODE == SC_F32 ? 512 : MODE == SC_MX ? 128 : 0);
-    constexpr bool TWO_A = (MODE == SC_H16);             // weights need a hi and a lo term
-    constexpr int A_BYTES = TC_M * TC_KB * 2;            // 16 KB per term
-    constexpr int B_BYTES = TC_NMAX * TC_KB * 2;         // 16 KB per term
-    constexpr int STAGE = (TWO_A ? 2 : 1) * A_BYTES + 2 * B_BYTES;
-    extern __shared__ __align__(1024) uint8_t smem[];
-    __shared__ __align__(8) unsigned long long s_bar[3];   // [0],[1]: stage free; [2]: accumulator complete
+    constexpr int CH = tc_chunk_bytes(MODE);
+    constexpr bool TWO_W = (MODE == SC_H16);             // weights need a hi and a lo term
+    constexpr int W_BYTES = TC_FEAT * TC_KB * 2;         // 32 KB per term
+    constexpr int RAW_STAGE = tc_raw_stage_bytes(MODE);
+    constexpr int W_STAGE = tc_w_stage_bytes(MODE);
+    constexpr int NRAW = tc_nraw(MODE), NX = tc_nx(MODE);
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ TcBars s_bars;
     __shared__ uint32_t s_tmem;
+    __shared__ int s_abort;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t sbase = (smem_u32(smem) + 1023u) & ~1023u;
-    const uint32_t bar0 = smem_u32(&s_bar[0]);
+    const uint32_t w0 = sbase, x0 = w0 + TC_NW * W_STAGE, raw0 = x0 + NX * TC_X_STAGE;
+    const uint32_t bar_raw_full = smem_u32(s_bars.raw_full), bar_raw_empty = smem_u32(s_bars.raw_empty);
+    const uint32_t bar_x_full = smem_u32(s_bars.x_full), bar_x_empty = smem_u32(s_bars.x_empty);
+    const uint32_t bar_w_full = smem_u32(s_bars.w_full), bar_w_empty = smem_u32(s_bars.w_empty);
+    const uint32_t bar_acc_full = smem_u32(s_bars.acc_full), bar_acc_empty = smem_u32(s_bars.acc_empty);
+    const uint32_t bar_drain = smem_u32(&s_bars.drain);
+    volatile int *abort_flag = &s_abort;
     if (tid == 0) {
-        mbar_init(bar0, 1); mbar_init(bar0 + 8, 1); mbar_init(bar0 + 16, 1);
+        for (int i = 0; i < NRAW; i++) { mbar_init(bar_raw_full + i * 8, 1); mbar_init(bar_raw_empty + i * 8, TC_DEC_WARPS); }
+        for (int i = 0; i < NX; i++) { mbar_init(bar_x_full + i * 8, 1); mbar_init(bar_x_empty + i * 8, 1); }
+        for (int i = 0; i < TC_NW; i++) { mbar_init(bar_w_full + i * 8, TC_DEC_WARPS); mbar_init(bar_w_empty + i * 8, 1); }
+        for (int i = 0; i < 2; i++) { mbar_init(bar_acc_full + i * 8, 1); mbar_init(bar_acc_empty + i * 8, 4); }
+        mbar_init(bar_drain, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        s_abort = 0;
     }
     if (warp == 0) {
         __syncwarp();
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(128u) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = s_tmem;
-    uint32_t par_stage[2] = {0, 0}, par_acc = 0;
-    int uses[2] = {0, 0};        // commits on each stage not yet waited for, plus one per use in this task
-
     const int ntask = ctl->ntask, nseg = ctl->nseg;
-    // thread -> weights: packed 32-row tile t4, lane fl of the fragment order, slot pair jh
-    const int t4 = tid >> 6, fl = tid & 31, jh = (tid >> 5) & 1;
-    const int fg = fl >> 2, ft = fl & 3;
-    bool failed = false;         // CTA-uniform: only ever set from a __syncthreads_or result
 
-    for (int task = blockIdx.x; task < ntask && !failed; task += gridDim.x) {
-        int si = 0;
-        { int lo = 0, hi = nseg - 1; while (lo < hi) { int mid = (lo + hi + 1) >> 1; if (segs[mid].task0 <= task) lo = mid; else hi = mid - 1; } si = lo; }
-        const TcSeg &sg = segs[si];
-        const int mt = task - sg.task0;                  // 128-feature tile
-        const int npad = sg.npad, nkb64 = sg.nkb64, nkb128 = nkb64 >> 1;
-        const uint32_t idesc = umma_idesc_f16(TC_M, npad);
-        const uint8_t *wtile = sg.w + ((size_t)(mt * 4 + t4) * nkb128) * CH;   // this thread's 32-row tile stream
-        // grouped int4: fp16 scale * 2^shift in two exact steps (shift may exceed the fp16 exponent range)
-        const int sh_a = sg.shift > 15 ? 15 : sg.shift, sh_b = sg.shift - sh_a;
-        const __half2 f_a = __half2half2(__ushort_as_half((unsigned short)((15 + sh_a) << 10)));
-        const __half2 f_b = __half2half2(__ushort_as_half((unsigned short)((15 + sh_b) << 10)));
-        uint2 codes[2];
-        uint32_t scl[2];
-        auto fetch = [&](int kb) {
-            const uint8_t *ch = wtile + (size_t)(kb >> 1) * CH;
-            const int g0 = (kb & 1) * 2;
-#pragma unroll
-            for (int q = 0; q < 2; q++) {
-                const int j = jh * 2 + q;
-                codes[q] = *reinterpret_cast<const uint2 *>(ch + j * 512 + fl * 16 + g0 * 4);
-                if (MODE == SC_H16)
-                    scl[q] = *reinterpret_cast<const uint32_t *>(ch + CODE_BYTES + ((((j >> 1) * 8 + fg) * 2 + (j & 1)) * 4 + g0) * 2);
-                else if (MODE == SC_MX)
-                    scl[q] = *reinterpret_cast<const uint16_t *>(ch + CODE_BYTES + (((j >> 1) * 8 + fg) * 2 + (j & 1)) * 4 + g0);
-                else
-                    scl[q] = 0;
-            }
-        };
-        fetch(0);
-        for (int kb = 0; kb < nkb64; kb++) {
-            const int s = kb & 1;
-            const uint32_t stage = sbase + s * STAGE;
+    if (warp == 0) {
+        // ---- weight producer ------------------------------------------------------------------
+        if (lane == 0) {
+            TcRing r;
+            int issued = 0;
             bool ok = true;
-            if (uses[s] > 0) {            // the MMAs that read this stage last must be done
-                ok = mbar_wait_bounded(bar0 + s * 8, par_stage[s]);
-                par_stage[s] ^= 1;
-            }
-            // activation tile: hi and lo terms, npad rows, contiguous in global memory
-            {
-                const uint8_t *src = reinterpret_cast<const uint8_t *>(sg.bq) + (size_t)kb * 2 * 8 * npad * 16;
-                const uint32_t dstB = stage + (TWO_A ? 2 : 1) * A_BYTES;
-                const int per_term = 8 * npad;           // 16-byte units: [chunk][row]
-                for (int u = tid; u < 2 * per_term; u += TC_THREADS) {
-                    const int term = u >= per_term;
-                    cp_async16(dstB + term * B_BYTES + (u - term * per_term) * 16, src + (size_t)u * 16);
+            for (int task = blockIdx.x; task < ntask && ok; task += gridDim.x) {
+                const TcSeg *sg = tc_find_seg(segs, nseg, task);
+                const int ft = task - sg->task0, nkb128 = sg->nkb64 >> 1;
+                const int ntile = min(8, sg->O / TILE_ROWS - ft * 8);       // packed 32-feature tiles of this task
+                const uint8_t *wbase = sg->w + (size_t)(ft * 8) * nkb128 * CH;
+                for (int kb = 0; kb < nkb128; kb++, issued++) {
+                    if (r.wrapped && !tc_wait(bar_raw_empty + r.s * 8, r.par ^ 1, abort_flag)) { ok = false; break; }
+                    mbar_expect_tx(bar_raw_full + r.s * 8, ntile * CH);
+                    for (int t = 0; t < ntile; t++)
+                        bulk_g2s(raw0 + r.s * RAW_STAGE + t * CH, wbase + ((size_t)t * nkb128 + kb) * CH, CH, bar_raw_full + r.s * 8);
+                    r.next(NRAW);
                 }
-                asm volatile("cp.async.commit_group;" ::: "memory");
             }
-            // weights: decode this thread's four words into the A tile(s)
+            if (!ok)      // copies still in flight must land before the CTA's shared memory is given up
+                for (int k = issued > NRAW ? issued - NRAW : 0; k < issued; k++)
+                    mbar_wait_bounded(bar_raw_full + (k % NRAW) * 8, (k / NRAW) & 1);
+        }
+    } else if (warp == 1) {
+        // ---- activation producer --------------------------------------------------------------
+        if (lane == 0) {
+            TcRing r;
+            int issued = 0;
+            bool ok = true;
+            for (int task = blockIdx.x; task < ntask && ok; task += gridDim.x) {
+                const TcSeg *sg = tc_find_seg(segs, nseg, task);
+                const uint32_t xbytes = (uint32_t)sg->npad * 128u;          // 2 terms x 4 chunks x npad rows x 16 B
+                const uint8_t *src = reinterpret_cast<const uint8_t *>(sg->bq);
+                const int nkb32 = sg->nkb64 * 2;
+                for (int kb = 0; kb < nkb32; kb++, issued++) {
+                    if (r.wrapped && !tc_wait(bar_x_empty + r.s * 8, r.par ^ 1, abort_flag)) { ok = false; break; }
+                    mbar_expect_tx(bar_x_full + r.s * 8, xbytes);
+                    bulk_g2s(x0 + r.s * TC_X_STAGE, src + (size_t)kb * xbytes, xbytes, bar_x_full + r.s * 8);
+                    r.next(NX);
+                }
+            }
+            if (!ok)
+                for (int k = issued > NX ? issued - NX : 0; k < issued; k++)
+                    mbar_wait_bounded(bar_x_full + (k % NX) * 8, (k / NX) & 1);
+        }
+    } else if (warp == 2) {
+        // ---- MMA issue ------------------------------------------------------------------------
+        if (lane == 0) {
+            TcRing rw, rx;
+            int tc = 0;
+            bool ok = true;
+            // descriptor high words: stride offset | version 1 (| 128-byte swizzle for W)
+            const uint32_t desc_x_hi = (128u >> 4) | (1u << 14);
+            const uint32_t desc_w_hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+            for (int task = blockIdx.x; task < ntask && ok; task += gridDim.x, tc++) {
+                const TcSeg *sg = tc_find_seg(segs, nseg, task);
+                const int npad = sg->npad, nkb64 = sg->nkb64;
+                const int nfeat = min(TC_FEAT, sg->O - (task - sg->task0) * TC_FEAT);
+                const uint32_t idesc = umma_idesc_f16(TC_ROWS, nfeat);
+                const int ab = tc & 1;
+                if (tc >= 2 && !tc_wait(bar_acc_empty + ab * 8, ((tc >> 1) + 1) & 1, abort_flag)) { ok = false; break; }
+                const uint32_t d_tmem = tmem + (uint32_t)ab * 256u;
+                const uint32_t lbo_x = (uint32_t)npad * 16u;                // bytes between 8-column chunks
+                const uint32_t x_term = (uint32_t)npad * 4u;                // hi -> lo term, 16-byte units (4 chunks)
+                uint32_t acc = 0;
+                for (int kb = 0; kb < nkb64 && ok; kb++) {
+                    if (!tc_wait(bar_w_full + rw.s * 8, rw.par, abort_flag)) { ok = false; break; }
+                    const uint32_t wl = ((w0 + rw.s * W_STAGE) >> 4) | (1u << 16);
 #pragma unroll
-            for (int q = 0; q < 2; q++) {
-                const int j = jh * 2 + q;
-                const int row = t4 * 32 + (j >> 1) * 16 + (j & 1) * 8 + fg;
+                    for (int h = 0; h < 2; h++) {
+                        if (!tc_wait(bar_x_full + rx.s * 8, rx.par, abort_flag)) { ok = false; break; }
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const uint32_t xl = ((x0 + rx.s * TC_X_STAGE) >> 4) | ((lbo_x >> 4) << 16);
 #pragma unroll
-                for (int gi = 0; gi < 2; gi++) {
-                    const uint32_t wv = gi ? codes[q].y : codes[q].x;
-                    uint32_t v[4];
-                    decode_word<MODE>(wv, v);
-                    const int kc = gi * 4 + ft;
-                    const uint32_t off = ((uint32_t)(kc * 16 + (row >> 3)) * 8 + (row & 7)) * 16;
-                    if (MODE == SC_H16) {
-                        const __half sh = __ushort_as_half((unsigned short)(gi ? (scl[q] >> 16) : (scl[q] & 0xFFFFu)));
-                        const __half2 s2 = __hmul2(__hmul2(__half2half2(sh), f_a), f_b);
-                        uint32_t hi[4], lo[4];
-#pragma unroll
-                        for (int i = 0; i < 4; i++) {
-                            __half2 n2 = u32_as_h2(v[i]);
-                            __half2 h = __hmul2(n2, s2);
-                            __half2 l = __hfma2(n2, s2, __hneg2(h));
-                            hi[i] = h2_as_u32(h); lo[i] = h2_as_u32(l);
+                        for (int k2 = 0; k2 < 2; k2++) {
+                            // a 16-column step: 2 chunks further in the X stage, 32 B further inside the W rows
+                            const uint32_t x_k = xl + (uint32_t)(2 * k2) * (lbo_x >> 4);
+                            const uint32_t w_k = wl + (uint32_t)(h * 2 + k2) * 2u;
+                            umma_f16_split(d_tmem, x_k, desc_x_hi, w_k, desc_w_hi, idesc, acc);
+                            umma_f16_split(d_tmem, x_k + x_term, desc_x_hi, w_k, desc_w_hi, idesc, 1u);
+                            if (TWO_W) umma_f16_split(d_tmem, x_k, desc_x_hi, w_k + (W_BYTES >> 4), desc_w_hi, idesc, 1u);
+                            acc = 1u;
                         }
-                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(stage + off), "r"(hi[0]), "r"(hi[1]), "r"(hi[2]), "r"(hi[3]) : "memory");
-                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(stage + A_BYTES + off), "r"(lo[0]), "r"(lo[1]), "r"(lo[2]), "r"(lo[3]) : "memory");
-                    } else if (MODE == SC_MX) {
-                        // decoded fields are e2m1 * 2^-14; the group factor 2^(e - 127 + 14 + shift) is an
-                        // fp16 power of two for every group the upload check admitted (else 0)
-                        const int e = (int)((scl[q] >> (8 * gi)) & 0xFFu) - 127 + 14 + sg.shift;
-                        const unsigned short fb = (e >= -14 && e <= 15) ? (unsigned short)((e + 15) << 10) : 0;
-                        const __half2 f2 = __half2half2(__ushort_as_half(fb));
-                        uint32_t a[4];
+                        umma_commit(bar_x_empty + rx.s * 8);
+                        rx.next(NX);
+                    }
+                    umma_commit(bar_w_empty + rw.s * 8);
+                    rw.next(TC_NW);
+                }
+                if (ok) umma_commit(bar_acc_full + ab * 8);
+            }
+            if (!ok) {     // MMAs in flight read shared memory and write TMEM: let them finish
+                umma_commit(bar_drain);
+                mbar_wait_bounded(bar_drain, 0);
+            }
+        }
+    } else if (warp < 3 + TC_DEC_WARPS) {
+        // ---- decode: raw chunk -> W tile(s) -----------------------------------------------------
+        const int dw = warp - 3;                         // 0..15
+        const int t8 = dw >> 1, jh = dw & 1;             // packed 32-feature tile of the task, slot pair
+        // lane -> fragment row g and 8-column chunk t of the packed words it decodes. A quarter
+        // warp holds t = 0..3 of an even row and of an odd row that differ in bit 2, which keeps
+        // both the 128-bit loads of the raw chunk and the swizzled 128-bit stores of the W tile
+        // free of bank conflicts.
+        const int ft = lane & 3, fg = (lane & 4) ? (((lane >> 3) * 2 + 5) & 7) : (lane >> 3) * 2;
+        const int fl = fg * 4 + ft;
+        TcRing rr, rw;
+        bool ok = true;
+        for (int task = blockIdx.x; task < ntask && ok; task += gridDim.x) {
+            const TcSeg *sg = tc_find_seg(segs, nseg, task);
+            const int nkb128 = sg->nkb64 >> 1, shift = sg->shift;
+            const bool live = t8 < sg->O / TILE_ROWS - (task - sg->task0) * 8;     // this warp's tile exists
+            // grouped int4: fp16 scale * 2^shift in two exact steps (shift may exceed the fp16 exponent range)
+            const int sh_a = shift > 15 ? 15 : shift, sh_b = shift - sh_a;
+            const __half2 f_a = __half2half2(__ushort_as_half((unsigned short)((15 + sh_a) << 10)));
+            const __half2 f_b = __half2half2(__ushort_as_half((unsigned short)((15 + sh_b) << 10)));
+            for (int kb = 0; kb < nkb128 && ok; kb++) {
+                if (!tc_wait(bar_raw_full + rr.s * 8, rr.par, abort_flag)) { ok = false; break; }
+                const uint32_t rbase = raw0 + rr.s * RAW_STAGE + t8 * CH;
+                uint4 w[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+                uint2 sc[2] = {make_uint2(0, 0), make_uint2(0, 0)};
+                if (live) {
 #pragma unroll
-                        for (int i = 0; i < 4; i++) a[i] = h2_as_u32(__hmul2(u32_as_h2(v[i]), f2));
-                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(stage + off), "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]) : "memory");
-                    } else {
-                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(stage + off), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]) : "memory");
+                    for (int q = 0; q < 2; q++) {
+                        const int j = jh * 2 + q;
+                        w[q] = lds128(rbase + j * 512 + fl * 16);
+                        const int slot = (((j >> 1) * 8 + fg) * 2 + (j & 1)) * 4;
+                        if (MODE == SC_H16) sc[q] = lds64(rbase + CODE_BYTES + slot * 2);
+                        else if (MODE == SC_MX) { uint32_t v; asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(rbase + CODE_BYTES + slot)); sc[q] = make_uint2(v, 0); }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_raw_empty + rr.s * 8);
+                rr.next(NRAW);
+#pragma unroll
+                for (int half = 0; half < 2; half++) {
+                    if (rw.wrapped && !tc_wait(bar_w_empty + rw.s * 8, rw.par ^ 1, abort_flag)) { ok = false; break; }
+                    const uint32_t stage = w0 + rw.s * W_STAGE;
+                    if (live) {
+#pragma unroll
+                        for (int q = 0; q < 2; q++) {
+                            const int j = jh * 2 + q;
+                            const int rg = t8 * 4 + j;                           // 8-row group of the W tile; row in group = fg
+#pragma unroll
+                            for (int gi = 0; gi < 2; gi++) {
+                                const int grp = half * 2 + gi;
+                                uint32_t v[4];
+                                decode_word<MODE>(word_of(w[q], grp), v);
+                                const int kc = gi * 4 + ft;
+                                const uint32_t off = (uint32_t)rg * 1024u + (uint32_t)fg * 128u + (uint32_t)((kc ^ fg) * 16);
+                                if (MODE == SC_H16) {
+                                    const uint32_t sw = half ? sc[q].y : sc[q].x;
+                                    const __half sh = __ushort_as_half((unsigned short)(gi ? (sw >> 16) : (sw & 0xFFFFu)));
+                                    const __half2 s2 = __hmul2(__hmul2(__half2half2(sh), f_a), f_b);
+                                    uint32_t hi[4], lo[4];
+#pragma unroll
+                                    for (int i = 0; i < 4; i++) {
+                                        __half2 n2 = u32_as_h2(v[i]);
+                                        __half2 h = __hmul2(n2, s2);
+                                        __half2 l = __hfma2(n2, s2, __hneg2(h));
+                                        hi[i] = h2_as_u32(h); lo[i] = h2_as_u32(l);
+                                    }
+                                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(stage + off), "r"(hi[0]), "r"(hi[1]), "r"(hi[2]), "r"(hi[3]) : "memory");
+                                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(stage + W_BYTES + off), "r"(lo[0]), "r"(lo[1]), "r"(lo[2]), "r"(lo[3]) : "memory");
+                                } else if (MODE == SC_MX) {
+                                    // decoded fields are e2m1 * 2^-14; the group factor 2^(e - 127 + 14 + shift) is an
+                                    // fp16 power of two for every group the upload check admitted (else 0)
+                                    const int e = (int)((sc[q].x >> (8 * grp)) & 0xFFu) - 127 + 14 + shift;
+                                    const unsigned short fb = (e >= -14 && e <= 15) ? (unsigned short)((e + 15) << 10) : 0;
+                                    const __half2 f2 = __half2half2(__ushort_as_half(fb));
+                                    uint32_t a[4];
+#pragma unroll
+                                    for (int i = 0; i < 4; i++) a[i] = h2_as_u32(__hmul2(u32_as_h2(v[i]), f2));
+                                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(stage + off), "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]) : "memory");
+                                } else {
+                                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(stage + off), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]) : "memory");
+                                }
+                            }
+                        }
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_w_full + rw.s * 8);
+                    rw.next(TC_NW);
+                }
+            }
+        }
+    } else {
+        // ---- accumulators -> global: lane = row of the pass, columns = features -----------------
+        const int q4 = warp & 3;                         // the TMEM lane quarter this warp may read
+        int tc = 0;
+        bool ok = true;
+        for (int task = blockIdx.x; task < ntask && ok; task += gridDim.x, tc++) {
+            const TcSeg *sg = tc_find_seg(segs, nseg, task);
+            const int f0 = (task - sg->task0) * TC_FEAT, nrows = sg->nrows, O = sg->O;
+            const int nfeat = min(TC_FEAT, O - f0);
+            const int ab = tc & 1;
+            if (!tc_wait(bar_acc_full + ab * 8, (tc >> 1) & 1, abort_flag)) { ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int n = q4 * 32 + lane;
+            if (q4 * 32 < nrows) {                       // warp-uniform: some row of this quarter is live
+                // two factors, applied one after the other: their product alone could underflow
+                const float bi = n < nrows ? sg->binv[n] : 0.f, fs = sg->out_scale;
+                float *outp = sg->out + (size_t)(sg->pos0 + n) * O + f0;
+                const float *rsc = MODE == SC_ROW ? sg->rowscale + f0 : nullptr;
+                for (int c0 = 0; c0 < nfeat; c0 += 16) {
+                    uint32_t r[16];
+                    const uint32_t taddr = tmem + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(ab * 256 + c0);
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                        : "r"(taddr));
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (n < nrows) {
+#pragma unroll
+                        for (int i = 0; i < 16; i += 4) {
+                            float4 o4;
+                            o4.x = __uint_as_float(r[i]) * bi * fs; o4.y = __uint_as_float(r[i + 1]) * bi * fs;
+                            o4.z = __uint_as_float(r[i + 2]) * bi * fs; o4.w = __uint_as_float(r[i + 3]) * bi * fs;
+                            if (MODE == SC_ROW) {
+                                const float4 rs = *reinterpret_cast<const float4 *>(rsc + c0 + i);
+                                o4.x *= rs.x; o4.y *= rs.y; o4.z *= rs.z; o4.w *= rs.w;
+                            }
+                            *reinterpret_cast<float4 *>(outp + c0 + i) = o4;
+                        }
                     }
                 }
             }
-            if (kb + 1 < nkb64) fetch(kb + 1);
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            if (__syncthreads_or(!ok)) { failed = true; break; }
-            if (tid == 0) {
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_hi = stage, a_lo = stage + A_BYTES;
-                const uint32_t b_hi = stage + (TWO_A ? 2 : 1) * A_BYTES, b_lo = b_hi + B_BYTES;
-                const uint32_t lboA = 16 * 128, lboB = (uint32_t)(npad / 8) * 128;
-#pragma unroll
-                for (int ks = 0; ks < TC_KB / 16; ks++) {
-                    // a 16-column step = 8-column chunks 2ks and 2ks+1
-                    const uint64_t dah = umma_smem_desc(a_hi + (uint32_t)(2 * ks) * lboA, lboA, 128);
-                    const uint64_t dbh = umma_smem_desc(b_hi + (uint32_t)(2 * ks) * lboB, lboB, 128);
-                    const uint64_t dbl = umma_smem_desc(b_lo + (uint32_t)(2 * ks) * lboB, lboB, 128);
-                    umma_f16(tmem, dah, dbh, idesc, (kb > 0 || ks > 0) ? 1u : 0u);
-                    umma_f16(tmem, dah, dbl, idesc, 1u);
-                    if (TWO_A) {
-                        const uint64_t dal = umma_smem_desc(a_lo + (uint32_t)(2 * ks) * lboA, lboA, 128);
-                        umma_f16(tmem, dal, dbh, idesc, 1u);
-                    }
-                }
-                umma_commit(bar0 + s * 8);
-                if (kb == nkb64 - 1) umma_commit(bar0 + 16);
-            }
-            uses[s]++;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_acc_empty + ab * 8);
         }
-        if (failed) break;
-        // ---- accumulators -> global: lane = feature, columns = rows of the pass ------------------
-        {
-            const bool ok = mbar_wait_bounded(bar0 + 16, par_acc);
-            par_acc ^= 1;
-            if (__syncthreads_or(!ok)) { failed = true; break; }
-        }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        {
-            const int q4 = warp & 3, half = warp >> 2;            // TMEM lane quarter, column half
-            const int o = mt * TC_M + q4 * 32 + lane;
-            float fs = sg.out_scale;
-            if (MODE == SC_ROW) fs *= sg.rowscale[o];
-            for (int c0 = half * 16; c0 < npad; c0 += 32) {
-                uint32_t r[16];
-                const uint32_t taddr = tmem + ((uint32_t)(q4 * 32) << 16) + (uint32_t)c0;
-                asm volatile(
-                    "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                      "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                    : "r"(taddr));
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                for (int i = 0; i < 16; i++) {
-                    const int n = c0 + i;
-                    if (n < sg.nrows)
-                        sg.out[(size_t)(sg.pos0 + n) * sg.O + o] = __uint_as_float(r[i]) * fs * sg.binv[n];
-                }
-            }
-        }
-        // the last commit of each stage completed before the accumulator barrier fired: consume
-        // those phases so that the next task starts with both stages free
-        bool ok2 = true;
-#pragma unroll
-        for (int s = 0; s < 2; s++)
-            if (uses[s] > 0) { ok2 = mbar_wait_bounded(bar0 + s * 8, par_stage[s]) && ok2; par_stage[s] ^= 1; uses[s] = 0; }
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        // every read of the accumulators is done before the next task overwrites them
-        if (__syncthreads_or(!ok2)) { failed = true; break; }
     }
-    if (failed && tid == 0) atomicExch(status, KSTAT_MBAR_TIMEOUT);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 0)
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(128u) : "memory");
+    if (tid == 0 && s_abort) atomicExch(status, KSTAT_MBAR_TIMEOUT);
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
 }

@@ -825,9 +825,10 @@ static int group_tc_ok(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
 
 // x_dev [total (or 1 when bcast), D] -> y_dev [total, D]; passes of up to 128 rows per expert.
 // y_dev must be 16-byte aligned (the accumulators are stored as float4).
+// rowsrc (host, optional): source row of x for every row of the call (a gather).
 static int group_device_tc(DeviceCtx *c, ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
                            ColiCudaTensor *const *downs, const int *rows, int count, int D, int I,
-                           int total, float *y_dev, const float *x_dev, int bcast) {
+                           int total, float *y_dev, const float *x_dev, int bcast, const int *rowsrc = nullptr) {
     std::vector<int> meta;            // [rowsrc | row_pass | row_n | pass_row0 | pass_npad]
     std::vector<int> row_pass(total), row_n(total), pass_row0, pass_npad, pass_rows, pass_pos0, pass_expert;
     int off = 0, padded = 0;
@@ -845,7 +846,7 @@ static int group_device_tc(DeviceCtx *c, ColiCudaTensor *const *gates, ColiCudaT
     }
     const int npass = (int)pass_row0.size();
     meta.resize((size_t)3 * total + 2 * npass);
-    for (int r = 0; r < total; r++) { meta[r] = bcast ? 0 : r; meta[total + r] = row_pass[r]; meta[2 * total + r] = row_n[r]; }
+    for (int r = 0; r < total; r++) { meta[r] = rowsrc ? rowsrc[r] : bcast ? 0 : r; meta[total + r] = row_pass[r]; meta[2 * total + r] = row_n[r]; }
     for (int p = 0; p < npass; p++) { meta[3 * total + p] = pass_row0[p]; meta[3 * total + npass + p] = pass_npad[p]; }
     if (!reserve(c, &c->misc, meta.size() * sizeof(int)) ||
         !reserve(c, &c->bq, (size_t)padded * D * 2 * sizeof(__half)) ||

@@ -28,7 +28,19 @@
 // The row scale 2^-r, the tensor shift and a per-feature weight scale are applied
 // when the accumulators are read back.
 //
-// Pipeline (one CTA per SM, 23 warps, every hand-over through an mbarrier):
+// Accumulation: the tensor core adds into its f32 accumulator with truncation, so a
+// long chain of MMAs drifts toward zero by about half an ulp of the running sum per
+// instruction (measured: 1.4e-5 of the output's rms after 384 instructions). The
+// contraction is therefore cut into partial sums of 8 blocks of 64 columns (64 or 96
+// instructions) in TMEM columns 0..255; after each, the read-back warps add the
+// partial sum to a running sum in TMEM columns 256..511 with ordinary rounded f32 adds
+// (tcgen05.ld, FADD, tcgen05.st), and the MMAs of the next partial sum start when they
+// are done (about a microsecond per ten of MMA time). The last partial sum goes to the
+// output together with the running sum. Keeping the running sum in global memory
+// instead (even L2-resident, evict-last) was measured 1.5x slower: ordinary loads
+// queue behind the bulk copies.
+//
+// Pipeline (one CTA per SM, 19 warps, every hand-over through an mbarrier):
 //   warp 0       weight producer: bulk copies of the raw packed chunks (8 tiles of 32
 //                features x 128 columns per stage) into a ring
 //   warp 1       activation producer: one bulk copy per 32-column block (both terms,
@@ -37,12 +49,12 @@
 //                constant, low words advanced by adds) and commits them to the barriers
 //                that free the activation stages and the W stage; after the last block it
 //                commits to the accumulator barrier
-//   warps 3-18   decode: raw chunk -> registers -> fp16 W tile(s) of a 2-stage ring (one
-//                16-byte shared store per 8 weights), fence to the async proxy, one
-//                arrival per warp
-//   warps 19-22  read the accumulators of a finished task (tcgen05.ld, lane = row),
-//                scale and store them while the next task's MMAs fill the other half of
-//                the 512 allocated TMEM columns
+//   warps 3-10   decode, one warp per packed tile: raw chunk -> registers -> fp16 W tile(s)
+//                of a 2-stage ring (one 16-byte shared store per 8 weights), fence to the
+//                async proxy, one arrival per warp
+//   warps 11-18  read back a finished partial sum (tcgen05.ld, lane = row; two warps per
+//                TMEM lane quarter, half of the feature columns each) and add it to the
+//                running sum, or scale and store the total after the last one
 // Every wait is bounded and also polls a CTA-wide abort flag; on expiry the CTA
 // records KSTAT_MBAR_TIMEOUT, waits (bounded) for its copies and MMAs in flight,
 // frees its TMEM columns and leaves.
@@ -55,8 +67,10 @@
 #define TC_KB 64            // columns per W stage
 #define TC_XKB 32           // columns per activation stage
 #define TC_NW 2             // W ring depth
-#define TC_DEC_WARPS 16
-#define TC_WARPS (3 + TC_DEC_WARPS + 4)
+#define TC_FLUSH_KB 8        // 64-column blocks per partial sum (see "Accumulation" above)
+#define TC_DEC_WARPS 8
+#define TC_EPI_WARPS 8
+#define TC_WARPS (3 + TC_DEC_WARPS + TC_EPI_WARPS)
 #define TC_THREADS (TC_WARPS * 32)
 #define TC_X_STAGE (2 * 4 * TC_ROWS * 16)   // 16 KB: both terms of a 32-column block of 128 rows
 
@@ -110,6 +124,22 @@ __device__ __forceinline__ void umma_f16_split(uint32_t tmem_d, uint32_t a_lo, u
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// 16 consecutive 32-bit TMEM columns of this thread's lane <-> registers.
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
 }
 
 // Activation preparation for the tensor-core path: one warp per row of the call.
@@ -227,7 +257,7 @@ k_expert_gemm_tc(const TcSeg *__restrict__ segs, const TcCtl *__restrict__ ctl, 
         for (int i = 0; i < NRAW; i++) { mbar_init(bar_raw_full + i * 8, 1); mbar_init(bar_raw_empty + i * 8, TC_DEC_WARPS); }
         for (int i = 0; i < NX; i++) { mbar_init(bar_x_full + i * 8, 1); mbar_init(bar_x_empty + i * 8, 1); }
         for (int i = 0; i < TC_NW; i++) { mbar_init(bar_w_full + i * 8, TC_DEC_WARPS); mbar_init(bar_w_empty + i * 8, 1); }
-        for (int i = 0; i < 2; i++) { mbar_init(bar_acc_full + i * 8, 1); mbar_init(bar_acc_empty + i * 8, 4); }
+        mbar_init(bar_acc_full, 1); mbar_init(bar_acc_empty, TC_EPI_WARPS);
         mbar_init(bar_drain, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         s_abort = 0;
@@ -297,18 +327,21 @@ k_expert_gemm_tc(const TcSeg *__restrict__ segs, const TcCtl *__restrict__ ctl, 
             // descriptor high words: stride offset | version 1 (| 128-byte swizzle for W)
             const uint32_t desc_x_hi = (128u >> 4) | (1u << 14);
             const uint32_t desc_w_hi = (1024u >> 4) | (1u << 14) | (2u << 29);
-            for (int task = blockIdx.x; task < ntask && ok; task += gridDim.x, tc++) {
+            for (int task = blockIdx.x; task < ntask && ok; task += gridDim.x) {
                 const TcSeg *sg = tc_find_seg(segs, nseg, task);
                 const int npad = sg->npad, nkb64 = sg->nkb64;
                 const int nfeat = min(TC_FEAT, sg->O - (task - sg->task0) * TC_FEAT);
                 const uint32_t idesc = umma_idesc_f16(TC_ROWS, nfeat);
-                const int ab = tc & 1;
-                if (tc >= 2 && !tc_wait(bar_acc_empty + ab * 8, ((tc >> 1) + 1) & 1, abort_flag)) { ok = false; break; }
-                const uint32_t d_tmem = tmem + (uint32_t)ab * 256u;
                 const uint32_t lbo_x = (uint32_t)npad * 16u;                // bytes between 8-column chunks
                 const uint32_t x_term = (uint32_t)npad * 4u;                // hi -> lo term, 16-byte units (4 chunks)
                 uint32_t acc = 0;
+                const uint32_t d_tmem = tmem;                               // partial sum: columns 0..255
                 for (int kb = 0; kb < nkb64 && ok; kb++) {
+                    if (kb % TC_FLUSH_KB == 0) {      // a new partial sum, once the previous one has been read back
+                        if (tc >= 1 && !tc_wait(bar_acc_empty, (tc + 1) & 1, abort_flag)) { ok = false; break; }
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        acc = 0;
+                    }
                     if (!tc_wait(bar_w_full + rw.s * 8, rw.par, abort_flag)) { ok = false; break; }
                     const uint32_t wl = ((w0 + rw.s * W_STAGE) >> 4) | (1u << 16);
 #pragma unroll
@@ -331,8 +364,8 @@ k_expert_gemm_tc(const TcSeg *__restrict__ segs, const TcCtl *__restrict__ ctl, 
                     }
                     umma_commit(bar_w_empty + rw.s * 8);
                     rw.next(TC_NW);
+                    if (ok && (kb % TC_FLUSH_KB == TC_FLUSH_KB - 1 || kb == nkb64 - 1)) { umma_commit(bar_acc_full); tc++; }
                 }
-                if (ok) umma_commit(bar_acc_full + ab * 8);
             }
             if (!ok) {     // MMAs in flight read shared memory and write TMEM: let them finish
                 umma_commit(bar_drain);
@@ -341,8 +374,7 @@ k_expert_gemm_tc(const TcSeg *__restrict__ segs, const TcCtl *__restrict__ ctl, 
         }
     } else if (warp < 3 + TC_DEC_WARPS) {
         // ---- decode: raw chunk -> W tile(s) -----------------------------------------------------
-        const int dw = warp - 3;                         // 0..15
-        const int t8 = dw >> 1, jh = dw & 1;             // packed 32-feature tile of the task, slot pair
+        const int t8 = warp - 3;                         // packed 32-feature tile of the task
         // lane -> fragment row g and 8-column chunk t of the packed words it decodes. A quarter
         // warp holds t = 0..3 of an even row and of an odd row that differ in bit 2, which keeps
         // both the 128-bit loads of the raw chunk and the swizzled 128-bit stores of the W tile
@@ -362,12 +394,14 @@ k_expert_gemm_tc(const TcSeg *__restrict__ segs, const TcCtl *__restrict__ ctl, 
             for (int kb = 0; kb < nkb128 && ok; kb++) {
                 if (!tc_wait(bar_raw_full + rr.s * 8, rr.par, abort_flag)) { ok = false; break; }
                 const uint32_t rbase = raw0 + rr.s * RAW_STAGE + t8 * CH;
-                uint4 w[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
-                uint2 sc[2] = {make_uint2(0, 0), make_uint2(0, 0)};
+                uint4 w[4];
+                uint2 sc[4];
+#pragma unroll
+                for (int q = 0; q < 4; q++) { w[q] = make_uint4(0, 0, 0, 0); sc[q] = make_uint2(0, 0); }
                 if (live) {
 #pragma unroll
-                    for (int q = 0; q < 2; q++) {
-                        const int j = jh * 2 + q;
+                    for (int q = 0; q < 4; q++) {
+                        const int j = q;
                         w[q] = lds128(rbase + j * 512 + fl * 16);
                         const int slot = (((j >> 1) * 8 + fg) * 2 + (j & 1)) * 4;
                         if (MODE == SC_H16) sc[q] = lds64(rbase + CODE_BYTES + slot * 2);
@@ -383,8 +417,8 @@ k_expert_gemm_tc(const TcSeg *__restrict__ segs, const TcCtl *__restrict__ ctl, 
                     const uint32_t stage = w0 + rw.s * W_STAGE;
                     if (live) {
 #pragma unroll
-                        for (int q = 0; q < 2; q++) {
-                            const int j = jh * 2 + q;
+                        for (int q = 0; q < 4; q++) {
+                            const int j = q;
                             const int rg = t8 * 4 + j;                           // 8-row group of the W tile; row in group = fg
 #pragma unroll
                             for (int gi = 0; gi < 2; gi++) {
@@ -433,48 +467,59 @@ k_expert_gemm_tc(const TcSeg *__restrict__ segs, const TcCtl *__restrict__ ctl, 
     } else {
         // ---- accumulators -> global: lane = row of the pass, columns = features -----------------
         const int q4 = warp & 3;                         // the TMEM lane quarter this warp may read
+        const int chalf = (warp - 3 - TC_DEC_WARPS) >> 2; // which half of the task's feature columns
         int tc = 0;
         bool ok = true;
-        for (int task = blockIdx.x; task < ntask && ok; task += gridDim.x, tc++) {
+        for (int task = blockIdx.x; task < ntask && ok; task += gridDim.x) {
             const TcSeg *sg = tc_find_seg(segs, nseg, task);
             const int f0 = (task - sg->task0) * TC_FEAT, nrows = sg->nrows, O = sg->O;
             const int nfeat = min(TC_FEAT, O - f0);
-            const int ab = tc & 1;
-            if (!tc_wait(bar_acc_full + ab * 8, (tc >> 1) & 1, abort_flag)) { ok = false; break; }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int nchunk = (sg->nkb64 + TC_FLUSH_KB - 1) / TC_FLUSH_KB;
             const int n = q4 * 32 + lane;
-            if (q4 * 32 < nrows) {                       // warp-uniform: some row of this quarter is live
-                // two factors, applied one after the other: their product alone could underflow
-                const float bi = n < nrows ? sg->binv[n] : 0.f, fs = sg->out_scale;
-                float *outp = sg->out + (size_t)(sg->pos0 + n) * O + f0;
-                const float *rsc = MODE == SC_ROW ? sg->rowscale + f0 : nullptr;
-                for (int c0 = 0; c0 < nfeat; c0 += 16) {
-                    uint32_t r[16];
-                    const uint32_t taddr = tmem + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(ab * 256 + c0);
-                    asm volatile(
-                        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                        : "r"(taddr));
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (n < nrows) {
+            // two factors, applied one after the other: their product alone could underflow
+            const float bi = n < nrows ? sg->binv[n] : 0.f, fs = sg->out_scale;
+            float *outp = sg->out + (size_t)(sg->pos0 + n) * O + f0;
+            const float *rsc = MODE == SC_ROW ? sg->rowscale + f0 : nullptr;
+            const int cbeg = chalf * (nfeat >> 1), cend = cbeg + (nfeat >> 1);
+            const bool live = q4 * 32 < nrows;               // warp-uniform: some row of this quarter is live
+            for (int ch = 0; ch < nchunk && ok; ch++, tc++) {
+                if (!tc_wait(bar_acc_full, tc & 1, abort_flag)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (live) {
+                    const bool last = ch == nchunk - 1;
+                    for (int c0 = cbeg; c0 < cend; c0 += 16) {
+                        uint32_t pr[16], rr[16];
+                        const uint32_t tp = tmem + ((uint32_t)(q4 * 32) << 16) + (uint32_t)c0;   // partial sum
+                        const uint32_t tr = tp + 256u;                                              // running sum
+                        tmem_ld16(tp, pr);
+                        if (ch > 0) tmem_ld16(tr, rr);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        if (ch > 0) {
 #pragma unroll
-                        for (int i = 0; i < 16; i += 4) {
-                            float4 o4;
-                            o4.x = __uint_as_float(r[i]) * bi * fs; o4.y = __uint_as_float(r[i + 1]) * bi * fs;
-                            o4.z = __uint_as_float(r[i + 2]) * bi * fs; o4.w = __uint_as_float(r[i + 3]) * bi * fs;
-                            if (MODE == SC_ROW) {
-                                const float4 rs = *reinterpret_cast<const float4 *>(rsc + c0 + i);
-                                o4.x *= rs.x; o4.y *= rs.y; o4.z *= rs.z; o4.w *= rs.w;
+                            for (int i = 0; i < 16; i++) pr[i] = __float_as_uint(__uint_as_float(pr[i]) + __uint_as_float(rr[i]));
+                        }
+                        if (!last) {
+                            tmem_st16(tr, pr);
+                        } else if (n < nrows) {
+#pragma unroll
+                            for (int i = 0; i < 16; i += 4) {
+                                float4 o4;
+                                o4.x = __uint_as_float(pr[i]) * bi * fs; o4.y = __uint_as_float(pr[i + 1]) * bi * fs;
+                                o4.z = __uint_as_float(pr[i + 2]) * bi * fs; o4.w = __uint_as_float(pr[i + 3]) * bi * fs;
+                                if (MODE == SC_ROW) {
+                                    const float4 rs = *reinterpret_cast<const float4 *>(rsc + c0 + i);
+                                    o4.x *= rs.x; o4.y *= rs.y; o4.z *= rs.z; o4.w *= rs.w;
+                                }
+                                *reinterpret_cast<float4 *>(outp + c0 + i) = o4;
                             }
-                            *reinterpret_cast<float4 *>(outp + c0 + i) = o4;
                         }
                     }
+                    if (!last) asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_acc_empty);
             }
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_acc_empty + ab * 8);
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");

@@ -14,6 +14,12 @@ struct ColiCudaMoeLayer {
     Buf x, out, logits, idx, w, keff, pos_of, uniq, scal, xq, xs, pg, pu, hq, hs, pd, seg1, seg2, ctl;
     float *host_io;                          // pinned staging
     size_t host_io_cap;
+    // tensor handles (host arrays of E entries; shared: one each or NULL) for the paths that
+    // build their work lists on the host
+    ColiCudaTensor **h_gates, **h_ups, **h_downs;
+    ColiCudaTensor *h_shared[3];
+    int tc_ok;                               // every tensor of the layer qualifies for the tensor-core path
+    int *host_route;                         // pinned: idx [max_rows*K] + keff [max_rows]
 };
 
 static int layer_mode_of(const ColiCudaTensor *t) { return t && t->packed ? t->mode : -1; }
@@ -62,6 +68,17 @@ extern "C" int coli_cuda_moe_layer_create(ColiCudaMoeLayer **layer, const ColiCu
         ok = cuda_ok(cudaMalloc((void **)&L->router_bias, (size_t)E * sizeof(float)), "router bias") &&
              cuda_ok(cudaMemcpy(L->router_bias, d->router_bias, (size_t)E * sizeof(float), cudaMemcpyHostToDevice), "router bias");
     }
+    L->h_gates = new ColiCudaTensor *[E]; L->h_ups = new ColiCudaTensor *[E]; L->h_downs = new ColiCudaTensor *[E];
+    L->tc_ok = (d->D % 128 == 0 && d->I % 128 == 0);
+    for (int e = 0; e < E; e++) {
+        L->h_gates[e] = d->gates[e]; L->h_ups[e] = d->ups[e]; L->h_downs[e] = d->downs[e];
+        L->tc_ok &= d->gates[e]->tc_ok && d->ups[e]->tc_ok && d->downs[e]->tc_ok;
+    }
+    if (has_shared) {
+        L->h_shared[0] = d->shared_gate; L->h_shared[1] = d->shared_up; L->h_shared[2] = d->shared_down;
+        L->tc_ok &= d->shared_gate->tc_ok && d->shared_up->tc_ok && d->shared_down->tc_ok;
+    }
+    if (ok) ok = cuda_ok(cudaMallocHost((void **)&L->host_route, ((size_t)max_rows * d->K + max_rows) * sizeof(int)), "pinned allocation");
     if (!ok) { coli_cuda_moe_layer_free(L); return 0; }
     const void *const *tp = static_cast<const void *const *>(L->table_mem);
     L->tab.gate_pk = reinterpret_cast<const uint8_t *const *>(tp);
@@ -90,8 +107,10 @@ extern "C" void coli_cuda_moe_layer_free(ColiCudaMoeLayer *L) {
         if (L->router_bias) cudaFree(L->router_bias);
         if (L->table_mem) cudaFree(L->table_mem);
         if (L->host_io) cudaFreeHost(L->host_io);
+        if (L->host_route) cudaFreeHost(L->host_route);
         (void)cudaGetLastError();
     }
+    delete[] L->h_gates; delete[] L->h_ups; delete[] L->h_downs;
     delete L;
 }
 
@@ -122,6 +141,46 @@ static LayerPlan layer_plan(const ColiCudaMoeLayer *L, const DeviceCtx *c, int M
     return p;
 }
 
+// Prefill-sized calls on the tensor cores: the routing result comes back to the host
+// (one synchronisation per call), rows are grouped per expert in ascending expert order
+// (row order kept inside an expert), the grouped GEMM runs with the row gather, and the
+// combine adds in each row's selection order, shared expert last.
+#define TC_LAYER_MIN_ROWS 64
+static int layer_run_tc(ColiCudaMoeLayer *L, DeviceCtx *c, float *out_dev, const float *x_dev, int M,
+                        const int *idx_dev, const float *w_dev, const int *keff_dev) {
+    const RouteRule &r = L->rule;
+    int *h_idx = L->host_route, *h_keff = L->host_route + (size_t)M * r.K;
+    if (!cuda_ok(cudaMemcpyAsync(h_idx, idx_dev, (size_t)M * r.K * sizeof(int), cudaMemcpyDeviceToHost, c->stream), "routing download") ||
+        !cuda_ok(cudaMemcpyAsync(h_keff, keff_dev, (size_t)M * sizeof(int), cudaMemcpyDeviceToHost, c->stream), "routing download") ||
+        !cuda_ok(cudaStreamSynchronize(c->stream), "routing download")) return 0;
+    std::vector<int> cnt(r.E, 0), start(r.E + 1, 0);
+    for (int s = 0; s < M; s++) for (int kk = 0; kk < h_keff[s]; kk++) cnt[h_idx[s * r.K + kk]]++;
+    for (int e = 0; e < r.E; e++) start[e + 1] = start[e] + cnt[e];
+    const int routed = start[r.E], npos = routed + (L->has_shared ? M : 0);
+    std::vector<int> pos_scal((size_t)M * r.K + 4, 0), rowsrc(npos), fill(start.begin(), start.end() - 1);
+    for (int s = 0; s < M; s++)
+        for (int kk = 0; kk < h_keff[s]; kk++) {
+            int pos = fill[h_idx[s * r.K + kk]]++;
+            pos_scal[(size_t)s * r.K + kk] = pos; rowsrc[pos] = s;
+        }
+    for (int s = 0; s < M && L->has_shared; s++) rowsrc[routed + s] = s;
+    pos_scal[(size_t)M * r.K + 1] = npos; pos_scal[(size_t)M * r.K + 2] = routed;
+    std::vector<ColiCudaTensor *> g, u, d;
+    std::vector<int> rows;
+    for (int e = 0; e < r.E; e++) if (cnt[e]) { g.push_back(L->h_gates[e]); u.push_back(L->h_ups[e]); d.push_back(L->h_downs[e]); rows.push_back(cnt[e]); }
+    if (L->has_shared) { g.push_back(L->h_shared[0]); u.push_back(L->h_shared[1]); d.push_back(L->h_shared[2]); rows.push_back(M); }
+    if (!reserve(c, &L->pos_of, pos_scal.size() * sizeof(int)) || !reserve(c, &L->pd, (size_t)npos * r.D * sizeof(float))) return 0;
+    if (!cuda_ok(cudaMemcpyAsync(L->pos_of.p, pos_scal.data(), pos_scal.size() * sizeof(int), cudaMemcpyHostToDevice, c->stream), "position table upload")) return 0;
+    if (npos > 0 && !group_device_tc(c, g.data(), u.data(), d.data(), rows.data(), (int)rows.size(), r.D, r.I, npos,
+                                     (float *)L->pd.p, x_dev, 0, rowsrc.data())) return 0;
+    const int *scal = (const int *)L->pos_of.p + (size_t)M * r.K;
+    size_t n4 = (size_t)M * r.D / 4;
+    k_combine<<<(unsigned)((n4 + 255) / 256), 256, 0, c->stream>>>(out_dev, (const float *)L->pd.p, (const int *)L->pos_of.p, w_dev,
+                                                                keff_dev, scal + 1, M, r.K, r.D, 1, L->has_shared ? scal + 2 : nullptr);
+    c->last_launches++;
+    return cuda_ok(cudaGetLastError(), "layer launch");
+}
+
 // Everything on c->stream with device buffers. idx/w/keff must be device
 // buffers of the layer or the caller ([M,K], [M,K], [M]).
 static int layer_run(ColiCudaMoeLayer *L, DeviceCtx *c, float *out_dev, const float *x_dev,
@@ -130,13 +189,14 @@ static int layer_run(ColiCudaMoeLayer *L, DeviceCtx *c, float *out_dev, const fl
     const RouteRule &r = L->rule;
     const LayerPlan p = layer_plan(L, c, M);
     const int nkb1 = r.D / BLOCK_K, nkb2 = r.I / BLOCK_K;
+    const bool use_tc = !route_only && !uniq_dev && g_tc_enabled && L->tc_ok && M >= TC_LAYER_MIN_ROWS;
     if (!reserve(c, &L->logits, (size_t)M * r.E * sizeof(float)) ||
         !reserve(c, &L->pos_of, (size_t)M * r.K * sizeof(int)) ||
         !reserve(c, &L->uniq, (size_t)r.E * sizeof(int)) || !reserve(c, &L->scal, 64) ||
         !reserve(c, &L->seg1, (size_t)2 * p.seg_cap * sizeof(GemvSeg)) ||
         !reserve(c, &L->seg2, (size_t)p.seg_cap * sizeof(GemvSeg)) ||
         !reserve(c, &L->ctl, 2 * sizeof(GemvCtl))) return 0;
-    if (!route_only &&
+    if (!route_only && !use_tc &&
         (!reserve(c, &L->xq, (size_t)M * r.D * 2 * sizeof(__half)) ||
          !reserve(c, &L->xs, (size_t)M * nkb1 * sizeof(float)) ||
          !reserve(c, &L->pg, (size_t)p.nkp1 * p.npos_cap * r.I * sizeof(float)) ||
@@ -205,6 +265,8 @@ static int layer_run(ColiCudaMoeLayer *L, DeviceCtx *c, float *out_dev, const fl
         k_route_topk<<<(M + warps - 1) / warps, warps * 32, sm, c->stream>>>(lg, L->router_bias, r, M, idx_dev, w_dev, keff_dev);
         c->last_launches++;
     }
+    if (use_tc)
+        return layer_run_tc(L, c, out_dev, x_dev, M, idx_dev, w_dev, keff_dev);
     int *scal = (int *)L->scal.p;   // [0]=nu [1]=npos [2]=shared_pos0
     BuildOut bo;
     bo.seg1 = (GemvSeg *)L->seg1.p; bo.seg2 = (GemvSeg *)L->seg2.p;

@@ -101,3 +101,70 @@ def test_tc_mxfp4_scale_spread_falls_back(be, oracle):
     assert np.array_equal(y_tc.view(np.uint32), y_st.view(np.uint32))
     want = oracle.expert_mlp(x, *e)
     assert max_rel_err(y_tc, want) <= 1e-3
+
+
+@pytest.mark.parametrize("name,M", [("c2_small", 64), ("c3_small", 200), ("c4_small", 333)])
+def test_tc_layer_matches_oracle_and_streaming(be, oracle, name, M):
+    # prefill-sized layer call: routing on the device, rows grouped per expert on the host,
+    # grouped GEMM on the tensor cores, combine in selection order
+    from colibri_b200 import workloads as W
+    from colibri_b200.backend import MoeLayer
+    from tests.util import upload_layer, free_layer, host_layer
+    cfg = W.CONFIGS[name]
+    L = W.HostLayerWeights(cfg, 77)
+    h = upload_layer(be, L)
+    g, u, d, sh = h
+    scale = 2.5 if cfg["gating"] else 1.0
+    lay = MoeLayer(be, cfg["D"], cfg["I"], cfg["E"], cfg["K"], g, u, d, cfg["gating"], cfg["norm_topk"],
+                   scale, 0.0, router_bias=L.router_bias, shared=sh, max_rows=M)
+    x = W.activations(M, cfg["D"], 9)
+    lg = W.router_logits(M, cfg["E"], 10, zipf=1.1)
+    try:
+        be.set_tensor_core(1)
+        out_tc, idx, w, keff = lay(x, lg)
+        be.set_tensor_core(0)
+        out_st, idx2, w2, keff2 = lay(x, lg)
+    finally:
+        be.set_tensor_core(1)
+    want, oi, ow, ok_, _ = oracle.moe_layer(host_layer(cfg, L, scale, 0.0, 1, False), x, lg)
+    assert np.array_equal(keff, ok_) and np.array_equal(idx, idx2) and np.array_equal(w.view(np.uint32), w2.view(np.uint32))
+    for s in range(M):
+        assert np.array_equal(idx[s, :keff[s]], oi[s, :ok_[s]]), s
+    assert max_rel_err(out_tc, want) <= 1e-3
+    assert max_rel_err(out_st, want) <= 1e-3
+    assert be.kernel_status(0) == 0
+    lay.free()
+    free_layer(be, h)
+
+
+def test_tc_many_tasks_per_cta(be, oracle):
+    # more tasks than SMs: every CTA runs several tasks back to back, so the rings, the two
+    # accumulator halves and their barriers wrap around
+    D, I = 256, 256
+    rng = np.random.default_rng(21)
+    rows = [33 + (7 * e) % 60 for e in range(200)]
+    base = [(rand_qt(rng, I, D, 4, 32, half=True), rand_qt(rng, I, D, 4, 32, half=True),
+             rand_qt(rng, D, I, 4, 32, half=True)) for _ in range(8)]
+    experts = [base[e % 8] for e in range(200)]
+    total = int(np.sum(rows))
+    x = ((rng.random((total, D)) - 0.5) * 2).astype(np.float32)
+    hs = [[upload_qt(be, t) for t in e] for e in base]
+    g = [hs[e % 8][0] for e in range(200)]; u = [hs[e % 8][1] for e in range(200)]; d = [hs[e % 8][2] for e in range(200)]
+    # the host entry point takes at most 64 experts per call
+    y = np.empty_like(x)
+    off = 0
+    for c0 in range(0, 200, 50):
+        n = int(np.sum(rows[c0:c0 + 50]))
+        ok, yc = be.run_expert_group(g[c0:c0 + 50], u[c0:c0 + 50], d[c0:c0 + 50], rows[c0:c0 + 50], x[off:off + n], D)
+        assert ok
+        y[off:off + n] = yc
+        off += n
+    assert be.kernel_status(0) == 0
+    off = 0
+    for e, r in zip(experts, rows):
+        want = oracle.expert_mlp(x[off:off + r], *e)
+        assert max_rel_err(y[off:off + r], want) <= 1e-3, (off, r)
+        off += r
+    for h in hs:
+        for t in h:
+            be.tensor_free(t)

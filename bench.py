@@ -59,6 +59,36 @@ def measured_peaks():
     return 6650.0, "fallback"
 
 
+TC_MEAN_ROWS = 12     # the backend's rule for prefill-sized layer calls: mean rows per expert
+
+
+def measured_tensor_peak():
+    """Dense bf16 TFLOP/s of this pool's B200s, the sustained figure (the kernel is timed
+    inside a long step); the stated fallback when the driver's file is absent."""
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            d = json.load(open(p))
+            return float(d["bf16_tflops_sustained"]), "measured (sustained)"
+        except Exception:
+            pass
+    return 1400.0, "fallback (sustained)"
+
+
+def tensor_roofline(useful_flop, kernel_ms, launches, terms, kernel="k_expert_gemm_tc"):
+    """roofline object of the tensor-core grouped GEMM: achieved = algorithmic FLOPs
+    (rows x 3 matrices x 2*D*I) / event time of its launches. The kernel issues `terms`
+    fp16 MMAs per algorithmic product (exact f32-equivalent operands), so the tensor
+    pipe does terms x this much work."""
+    peak, which = measured_tensor_peak()
+    ach = useful_flop / (kernel_ms * 1e-3) / 1e12 if kernel_ms > 0 else None
+    return {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s",
+            "frac": (ach / peak) if ach else None, "traffic": None, "kernel": kernel, "launches": launches,
+            "avg_launch_us": (kernel_ms / launches * 1e3) if launches else None, "peak_source": which,
+            "mma_terms_per_product": terms,
+            "tensor_pipe_frac": (ach * terms / peak) if ach else None}
+
+
 # ---------------------------------------------------------------------------
 # synthetic weights, generated on the GPU with torch (fast) in the reference
 # converter's rules (colibri_b200.quant restates the same rules in numpy; the
@@ -303,6 +333,7 @@ def run_gpu_arm(args):
     be = Backend()
     if be.init_devices((local,)) != 1:
         raise RuntimeError("coli_cuda_init failed: the CUDA backend is required (no CPU fallback)")
+    be.set_tensor_core(args.tc)
     layers, handles, host_keep, biases = [], [], [], []
     up = lambda t: be.upload(t.w, t.s, t.fmt, t.I, t.O, local, t.gs)
     for li in range(L):
@@ -464,11 +495,14 @@ def run_gpu_arm(args):
                     "d2h_bytes_per_step": L * M * D * 4, "ms_per_step": e2e_ms_all / args.steps},
             "gpu_launches": launches,
             "clocks": clocks,
-            "roofline": {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s",
-                         "frac": (ach / peak) if ach else None, "traffic": None,
-                         "kernel": "k_moe_decode" if M <= 8 else "k_gemv_stream", "launches": k_n.value,
-                         "avg_launch_us": (k_ms.value / k_n.value * 1e3) if k_n.value else None,
-                         "peak_source": which},
+            "roofline": (tensor_roofline(sum((M * K + (M if cfg["shared"] else 0)) * 6.0 * D * I for _ in range(L)) * args.steps,
+                                         k_ms.value, k_n.value, 3 if fmt == 4 else 2)
+                         if M >= 32 and (args.tc == 2 or (args.tc == 1 and M * K >= TC_MEAN_ROWS * E)) else
+                         {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s",
+                          "frac": (ach / peak) if ach else None, "traffic": None,
+                          "kernel": "k_moe_decode" if M <= 8 else "k_gemv_stream", "launches": k_n.value,
+                          "avg_launch_us": (k_ms.value / k_n.value * 1e3) if k_n.value else None,
+                          "peak_source": which}),
             "cpu_baseline": cpu,
         }
         print(json.dumps(line), flush=True)
@@ -551,7 +585,7 @@ def run_ep_arm(args):
         for li in range(L):
             lay = layers[li]
             lay.logits = lgs[li]
-            out, _ = ep_moe_layer(xs[li], lay.route, lay.experts, lay.shared_fn, E)
+            out, _ = ep_moe_layer(xs[li], lay.route, lay.experts, lay.shared_fn, E, combine=lay.combine)
             outs.append(out)
         return outs
 
@@ -572,11 +606,40 @@ def run_ep_arm(args):
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1)
+    # kernels launched per step, and the grouped-GEMM kernel time, from one more step
+    n0 = be.launch_total(local)
+    be.set_kernel_events(1)
+    step()
+    k_ms, k_n = C.c_float(), C.c_int()
+    be.kernel_events(local, C.byref(k_ms), C.byref(k_n))
+    be.set_kernel_events(0)
+    launches_step = int(be.launch_total(local) - n0)
     clocks = sampler.stop() if rank == 0 else None
-    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    # end to end: rows and logits start in pinned host memory, the result is read back
+    x_pin = [x.cpu().pin_memory() for x in xs]
+    lg_pin = [l.cpu().pin_memory() for l in lgs]
+    out_pin = torch.empty((m, D), dtype=torch.float32).pin_memory()
+
+    def step_host():
+        for li in range(L):
+            lay = layers[li]
+            xd = x_pin[li].to(dev, non_blocking=True)
+            lay.logits = lg_pin[li].to(dev, non_blocking=True)
+            out, _ = ep_moe_layer(xd, lay.route, lay.experts, lay.shared_fn, E, combine=lay.combine)
+            out_pin.copy_(out, non_blocking=True)
+        torch.cuda.synchronize()
+    for _ in range(2):
+        step_host()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step_host()
+    barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+    t = torch.tensor([ms, e2e_ms, k_ms.value], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_all = float(t.item())
+    ms_all, e2e_all, k_ms_all = float(t[0].item()), float(t[1].item()), float(t[2].item())
     if be.kernel_status(local) != 0:
         raise RuntimeError("a kernel wait guard expired")
     if rank == 0:
@@ -592,10 +655,12 @@ def run_ep_arm(args):
                                    f"experts sharded over {world} rank(s), NCCL all-to-all dispatch/combine (f32 rows)",
                        "l2": "weights touched per step exceed L2 (126 MB)", "bytes_per_step": step_bytes,
                        "a2a_bytes_per_rank_per_layer": int(2 * (M // world) * K * D * 4 * (world - 1) / max(world, 1))},
-            "e2e": None, "gpu_launches": None, "clocks": clocks,
-            "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s",
-                         "frac": value / world / peak, "traffic": None, "kernel": "k_gemv_stream (whole layer, per GPU)",
-                         "peak_source": which},
+            "e2e": {"value": step_bytes * args.steps / (e2e_all * 1e-3) / 1e9, "unit": "GB/s",
+                    "h2d_bytes_per_step": L * world * (m * D * 4 + m * E * 4), "d2h_bytes_per_step": L * world * m * D * 4,
+                    "ms_per_step": e2e_all / args.steps},
+            "gpu_launches": launches_step * args.steps * world, "clocks": clocks,
+            # per GPU: this rank's share of the rows (an even share is assumed for the FLOP count)
+            "roofline": tensor_roofline((M * K / world + m) * 6.0 * D * I * L, k_ms_all, k_n.value, 2),
             "cpu_baseline": None,
         }
         print(json.dumps(line), flush=True)
@@ -618,6 +683,8 @@ def main():
     ap.add_argument("--layers", type=int, default=16)
     ap.add_argument("--cpu-layers", type=int, default=4, help="layers kept on the host for the CPU baseline sample")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--tc", type=int, default=1, choices=[0, 1, 2],
+                    help="tensor-core path: 0 never, 1 when it pays (default), 2 whenever possible")
     args = ap.parse_args()
     if args.workload == "c5_ep":
         if args.impl == "reference":

@@ -48,6 +48,7 @@ struct DeviceCtx {
     int sticky_status = 0;                    // last non-zero kernel status seen by the host
     float last_ms = 0.f;
     int last_launches = 0;
+    unsigned long long total_launches = 0;   // kernels launched by earlier calls (see coli_cuda_launch_total)
     int have_timing = 0;
     std::vector<cudaEvent_t> *kev = nullptr;   // per-launch event pairs of the streaming GEMV
     int kev_used = 0;
@@ -277,6 +278,10 @@ extern "C" int coli_cuda_last_timing(int device, float *kernel_ms, int *launches
     if (kernel_ms) *kernel_ms = c->last_ms;
     if (launches) *launches = c->last_launches;
     return 1;
+}
+extern "C" unsigned long long coli_cuda_launch_total(int device) {
+    DeviceCtx *c = find_ctx(device);
+    return c ? c->total_launches + (unsigned long long)c->last_launches : 0;
 }
 extern "C" void *coli_cuda_stream(int device) {
     DeviceCtx *c = find_ctx(device);
@@ -563,6 +568,7 @@ static int pick_nkpart(int nkb, long base_tasks, int sms) {
 }
 
 static void timing_begin(DeviceCtx *c) {
+    c->total_launches += (unsigned long long)c->last_launches;
     c->last_launches = 0;
     c->have_timing = 0;
     if (g_timing) cudaEventRecord(c->ev0, c->stream);
@@ -757,14 +763,26 @@ static int group_shape_ok(ColiCudaTensor *const *gates, ColiCudaTensor *const *u
 // Tensor-core path of the expert group (gemm_tc.cuh): taken when some expert has
 // more rows than one streaming pass holds and every tensor qualifies.
 // ---------------------------------------------------------------------------
+// 0: never; 1: when it pays (below); 2: whenever the tensors and shapes allow it (tests).
+// A pass of the tensor-core kernel costs the same for 1 or 128 rows (the MMA is 128 rows
+// tall) while the streaming kernel's cost grows with the rows (it is bound by instruction
+// issue, one set of MMAs per 4 rows). Measured crossover on both benchmark shapes: a mean
+// of about 12 rows per expert (OLMoE shape: 3.2 vs 5.2 ms per 16 layers at 8 rows per
+// expert, 6.1 vs 5.2 ms at 16; DeepSeek-V3 shape: 8.1 vs 9.4 ms per 2 layers at 8, 18.8 vs
+// 10.2 ms at 16).
 static int g_tc_enabled = 1;
-extern "C" void coli_cuda_set_tensor_core(int enabled) { g_tc_enabled = enabled ? 1 : 0; }
-#define TC_MIN_ROWS 33
+extern "C" void coli_cuda_set_tensor_core(int enabled) { g_tc_enabled = enabled < 0 ? 0 : enabled > 2 ? 2 : enabled; }
+#define TC_MIN_ROWS 13
+#define TC_MEAN_ROWS 12
 
 template <int MODE>
 static void launch_tc_mode(DeviceCtx *c, const TcSeg *segs, const TcCtl *ctl, int ntask) {
     int grid = ntask < c->sms ? ntask : c->sms;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    kernel_event_pair(c, &e0, &e1);
+    if (e0) cudaEventRecord(e0, c->stream);
     k_expert_gemm_tc<MODE><<<grid, TC_THREADS, tc_smem_bytes<MODE>(), c->stream>>>(segs, ctl, c->status);
+    if (e1) cudaEventRecord(e1, c->stream);
     c->last_launches++;
 }
 
@@ -816,8 +834,9 @@ static int run_tc_segs(DeviceCtx *c, TcSegs *ts, Buf *segbuf) {
 }
 
 static int group_tc_ok(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
-                       ColiCudaTensor *const *downs, int count, int max_rows) {
+                       ColiCudaTensor *const *downs, int count, int max_rows, int total) {
     if (!g_tc_enabled || max_rows < TC_MIN_ROWS) return 0;
+    if (g_tc_enabled == 1 && (long)total < (long)TC_MEAN_ROWS * count) return 0;
     for (int e = 0; e < count; e++)
         if (!gates[e]->tc_ok || !ups[e]->tc_ok || !downs[e]->tc_ok) return 0;
     return 1;
@@ -886,7 +905,7 @@ static int group_device(DeviceCtx *c, ColiCudaTensor *const *gates, ColiCudaTens
                         int total, int max_rows, int all_packed, float *y_dev, const float *x_dev,
                         const int *bcast_src /* optional: every row reads x row 0 */) {
     if (all_packed && D % 128 == 0 && I % 128 == 0 && (reinterpret_cast<uintptr_t>(y_dev) & 15) == 0 &&
-        group_tc_ok(gates, ups, downs, count, max_rows))
+        group_tc_ok(gates, ups, downs, count, max_rows, total))
         return group_device_tc(c, gates, ups, downs, rows, count, D, I, total, y_dev, x_dev, bcast_src != nullptr);
     if (all_packed) {
         const int nc = pick_nc(max_rows), rpp = 4 * nc;
@@ -1261,6 +1280,23 @@ extern "C" int coli_cuda_expert_group_dev(ColiCudaTensor *const *gates, ColiCuda
     timing_end(c);
     if (ok) count_group(c, (int)g.size(), total);
     return ok;
+}
+
+// Weighted combine of an expert-parallel layer on device buffers: out[s] = sum over the
+// first keff[s] selections of w[s,kk] * y[entry_of[s,kk]], then + shared[s] when given.
+// entry_of and keff are 64-bit integers. Enqueues on the backend's stream.
+extern "C" int coli_cuda_moe_combine_dev(int device, float *out_dev, const float *y_dev,
+                                         const long long *entry_of_dev, const float *w_dev,
+                                         const long long *keff_dev, const float *shared_dev, int M, int K,
+                                         int D) {
+    DeviceCtx *c = find_ctx(device);
+    if (!out_dev || !entry_of_dev || !w_dev || !keff_dev || M < 1 || K < 1 || D < 4 || D % 4 || !select_ctx(c)) return 0;
+    if ((reinterpret_cast<uintptr_t>(out_dev) | reinterpret_cast<uintptr_t>(y_dev) | reinterpret_cast<uintptr_t>(shared_dev)) & 15) return 0;
+    size_t n4 = (size_t)M * D / 4;
+    k_combine_rows<<<(unsigned)((n4 + 255) / 256), 256, 0, c->stream>>>(out_dev, y_dev, entry_of_dev, w_dev, keff_dev,
+                                                                     shared_dev, M, K, D);
+    c->last_launches++;
+    return cuda_ok(cudaGetLastError(), "combine launch");
 }
 
 // ---------------------------------------------------------------------------

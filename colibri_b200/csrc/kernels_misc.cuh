@@ -217,6 +217,32 @@ __global__ void k_combine(float *__restrict__ out, const float *__restrict__ par
     reinterpret_cast<float4 *>(out)[i] = acc;
 }
 
+// Weighted combine over separate buffers (expert-parallel layer): for row s,
+//   out[s] = sum_{kk<keff[s]} w[s,kk] * y[entry_of[s*K+kk]]  (+ shared[s]),
+// selection order, shared expert last. entry_of is 64-bit (a torch index tensor).
+__global__ void k_combine_rows(float *__restrict__ out, const float *__restrict__ y,
+                               const long long *__restrict__ entry_of, const float *__restrict__ wts,
+                               const long long *__restrict__ keff, const float *__restrict__ shared, int M,
+                               int K, int D) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int dq = D / 4;
+    if (i >= (size_t)M * dq) return;
+    int s = i / dq, d4 = i - (size_t)s * dq;
+    float4 acc = make_float4(0, 0, 0, 0);
+    int ke = (int)keff[s];
+    for (int kk = 0; kk < ke; kk++) {
+        long long pos = entry_of[s * K + kk];
+        float wgt = wts[s * K + kk];
+        float4 a = reinterpret_cast<const float4 *>(y + (size_t)pos * D)[d4];
+        acc.x += wgt * a.x; acc.y += wgt * a.y; acc.z += wgt * a.z; acc.w += wgt * a.w;
+    }
+    if (shared) {
+        float4 a = reinterpret_cast<const float4 *>(shared + (size_t)s * D)[d4];
+        acc.x += a.x; acc.y += a.y; acc.z += a.z; acc.w += a.w;
+    }
+    reinterpret_cast<float4 *>(out)[i] = acc;
+}
+
 // ---------------------------------------------------------------------------
 // Generic matmul for raw tensors (any fmt 0,1,2,3,4,7, any shape): one warp per
 // output row o and chunk of up to 8 input rows; lanes stride over columns,

@@ -145,7 +145,7 @@ static LayerPlan layer_plan(const ColiCudaMoeLayer *L, const DeviceCtx *c, int M
 // (one synchronisation per call), rows are grouped per expert in ascending expert order
 // (row order kept inside an expert), the grouped GEMM runs with the row gather, and the
 // combine adds in each row's selection order, shared expert last.
-#define TC_LAYER_MIN_ROWS 64
+#define TC_LAYER_MIN_ROWS 32
 static int layer_run_tc(ColiCudaMoeLayer *L, DeviceCtx *c, float *out_dev, const float *x_dev, int M,
                         const int *idx_dev, const float *w_dev, const int *keff_dev) {
     const RouteRule &r = L->rule;
@@ -189,7 +189,9 @@ static int layer_run(ColiCudaMoeLayer *L, DeviceCtx *c, float *out_dev, const fl
     const RouteRule &r = L->rule;
     const LayerPlan p = layer_plan(L, c, M);
     const int nkb1 = r.D / BLOCK_K, nkb2 = r.I / BLOCK_K;
-    const bool use_tc = !route_only && !uniq_dev && g_tc_enabled && L->tc_ok && M >= TC_LAYER_MIN_ROWS;
+    // worth it from a mean of TC_MEAN_ROWS rows per routed expert (see group_tc_ok)
+    const bool use_tc = !route_only && !uniq_dev && L->tc_ok && M >= TC_LAYER_MIN_ROWS &&
+                        (g_tc_enabled == 2 || (g_tc_enabled == 1 && (long)M * r.K >= (long)TC_MEAN_ROWS * r.E));
     if (!reserve(c, &L->logits, (size_t)M * r.E * sizeof(float)) ||
         !reserve(c, &L->pos_of, (size_t)M * r.K * sizeof(int)) ||
         !reserve(c, &L->uniq, (size_t)r.E * sizeof(int)) || !reserve(c, &L->scal, 64) ||
@@ -388,5 +390,6 @@ extern "C" int coli_cuda_route_topk_dev(int device, const float *logits_dev, con
     const int warps = 4;
     size_t sm = (size_t)warps * (2 * E + 2 * ROUTE_MAX_K) * sizeof(float);
     k_route_topk<<<(M + warps - 1) / warps, warps * 32, sm, c->stream>>>(logits_dev, bias_dev, r, M, idx_dev, w_dev, keff_dev);
+    c->last_launches++;
     return cuda_ok(cudaGetLastError(), "route launch");
 }

@@ -37,22 +37,21 @@ class DispatchPlan:
         self.m, self.K, self.E, self.world = m, K, E, world
         self.e_loc = E // world
         dev = idx.device
-        kk = torch.arange(K, device=dev).unsqueeze(0).expand(m, K)
-        valid = kk < keff.view(m, 1)
-        flat_e = idx[valid]                                  # expert of every live entry, row-major order
-        self.entry_of = torch.full((m, K), -1, dtype=torch.int64, device=dev)
-        n = int(flat_e.numel())
-        # stable sort by expert id: experts ascend (so owner ranks ascend), row order kept inside an expert
-        order = torch.sort(flat_e, stable=True).indices
-        self.order = order                                   # sorted position -> entry number
-        pos = torch.empty(n, dtype=torch.int64, device=dev)
-        pos[order] = torch.arange(n, device=dev)
-        self.entry_of[valid] = pos                           # (row, kk) -> position in the send buffer
-        rows = torch.arange(m, device=dev).unsqueeze(1).expand(m, K)[valid]
-        self.send_rows = rows[order]                         # source row of every sent entry
-        self.counts = torch.bincount(flat_e, minlength=E).view(world, self.e_loc)   # [dest rank, local expert]
-        self.send_splits = self.counts.sum(dim=1)            # rows per destination rank
-        self.n = n
+        kk = torch.arange(K, device=dev).unsqueeze(0)
+        valid = (kk < keff.view(m, 1)).reshape(-1)
+        # dead entries (kk >= keff) get the key E and sort behind every live one; the stable sort
+        # makes experts ascend (so owner ranks ascend) and keeps row order inside an expert
+        key = torch.where(valid, idx.reshape(-1), torch.full_like(idx.reshape(-1), E))
+        order = torch.sort(key, stable=True).indices           # sorted position -> flat (row*K + kk)
+        pos = torch.empty(m * K, dtype=torch.int64, device=dev)
+        pos[order] = torch.arange(m * K, device=dev)
+        self.entry_of = torch.where(valid, pos, torch.full_like(pos, -1)).view(m, K)   # (row, kk) -> send position
+        counts = torch.bincount(key, minlength=E + 1)[:E]
+        self.counts = counts.view(world, self.e_loc)           # [dest rank, local expert]
+        self.counts_host = self.counts.tolist()                # the one host synchronisation of the plan
+        self.send_splits = [int(sum(r)) for r in self.counts_host]
+        self.n = int(sum(self.send_splits))
+        self.send_rows = torch.div(order[:self.n], K, rounding_mode="floor")   # source row of every sent entry
 
 
 def _all_to_all_rows(send: torch.Tensor, send_splits, recv_splits, group):
@@ -65,54 +64,68 @@ def _all_to_all_rows(send: torch.Tensor, send_splits, recv_splits, group):
     return recv
 
 
-def ep_moe_layer(x: torch.Tensor, route, experts, shared, E: int, group=None):
+def _combine_torch(got, entry_of, w, keff, ys):
+    """Step 7 with tensor ops (CPU tests): selection order, shared expert last."""
+    m, K = entry_of.shape
+    out = torch.zeros((m, got.shape[1]), dtype=got.dtype, device=got.device)
+    for kk in range(K):
+        ent = entry_of[:, kk]
+        live = ent >= 0
+        contrib = got.index_select(0, ent.clamp(min=0)) * w[:, kk].unsqueeze(1)
+        out = out + torch.where(live.unsqueeze(1), contrib, torch.zeros_like(contrib))
+    return out if ys is None else out + ys
+
+
+def ep_moe_layer(x: torch.Tensor, route, experts, shared, E: int, group=None, combine=None):
     """One expert-parallel MoE layer for this rank's rows x [m, D]. Returns out [m, D]
-    and the routing (idx, w, keff)."""
+    and the routing (idx, w, keff). combine(got, entry_of, w, keff, ys) -> out replaces
+    the tensor-op combine (the CUDA layer passes its kernel)."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     m, D = x.shape
     idx, w, keff = route(x)
     plan = DispatchPlan(idx, keff, E, world)
-    # 3. counts: recv_counts[src, local expert]
-    send_counts = plan.counts.to(torch.int64).contiguous()
-    recv_counts = torch.empty_like(send_counts)
-    if world > 1:
-        dist.all_to_all_single(recv_counts.view(-1), send_counts.view(-1), group=group)
-    else:
-        recv_counts.copy_(send_counts)
-    send_splits = [int(v) for v in plan.send_splits.tolist()]
-    recv_splits = [int(v) for v in recv_counts.sum(dim=1).tolist()]
     # 4. rows out, grouped by (dest rank, expert, row order)
     send_x = x.index_select(0, plan.send_rows)
-    recv_x = _all_to_all_rows(send_x, send_splits, recv_splits, group)
-    # received rows are ordered (source rank, local expert, row order); the expert call wants
-    # (local expert, source rank, row order)
-    rc = recv_counts                                           # [src, e_loc]
-    seg_start = torch.cumsum(rc.reshape(-1), 0) - rc.reshape(-1)    # start of segment (src, e) in recv order
-    by_expert = rc.t().contiguous()                            # [e_loc, src]
-    dst_start = torch.cumsum(by_expert.reshape(-1), 0) - by_expert.reshape(-1)
-    n_recv = int(rc.sum())
-    src_n, e_n = rc.shape
-    lengths = by_expert.reshape(-1)                                       # segments in (expert, source) order
-    src_starts = seg_start.view(src_n, e_n).t().reshape(-1)               # where each starts in recv order
-    perm = (torch.repeat_interleave(src_starts - dst_start, lengths) +
-            torch.arange(n_recv, device=x.device))                        # expert-order position -> recv position
-    rows_per_expert = [int(v) for v in by_expert.sum(dim=1).tolist()]
-    xe = recv_x.index_select(0, perm)
-    # 5. local experts
-    ye = experts(rows_per_expert, xe)
-    # 6. results back along the same plan
-    back = torch.empty_like(ye)
-    back[perm] = ye
-    got = _all_to_all_rows(back, recv_splits, send_splits, group)   # [n, D] in send-buffer order
+    if world == 1:
+        # one rank: the send buffer already is the expert-order buffer
+        got = experts(plan.counts_host[0], send_x)
+    else:
+        # 3. counts: recv_counts[src, local expert]
+        send_counts = plan.counts.to(torch.int64).contiguous()
+        recv_counts = torch.empty_like(send_counts)
+        dist.all_to_all_single(recv_counts.view(-1), send_counts.view(-1), group=group)
+        rc_host = recv_counts.tolist()                             # [src][local expert]
+        recv_splits = [int(sum(r)) for r in rc_host]
+        recv_x = _all_to_all_rows(send_x, plan.send_splits, recv_splits, group)
+        # received rows are ordered (source rank, local expert, row order); the expert call wants
+        # (local expert, source rank, row order)
+        src_n, e_n = len(rc_host), len(rc_host[0])
+        seg_start, acc = [[0] * e_n for _ in range(src_n)], 0
+        for s_ in range(src_n):
+            for e_ in range(e_n):
+                seg_start[s_][e_] = acc
+                acc += rc_host[s_][e_]
+        n_recv = acc
+        starts, lengths = [], []
+        for e_ in range(e_n):
+            for s_ in range(src_n):
+                starts.append(seg_start[s_][e_]); lengths.append(rc_host[s_][e_])
+        lengths_t = torch.tensor(lengths, dtype=torch.int64, device=x.device)
+        starts_t = torch.tensor(starts, dtype=torch.int64, device=x.device)
+        dst_start = torch.cumsum(lengths_t, 0) - lengths_t
+        perm = (torch.repeat_interleave(starts_t - dst_start, lengths_t, output_size=n_recv) +
+                torch.arange(n_recv, device=x.device))            # expert-order position -> recv position
+        rows_per_expert = [sum(rc_host[s_][e_] for s_ in range(src_n)) for e_ in range(e_n)]
+        xe = recv_x.index_select(0, perm)
+        # 5. local experts
+        ye = experts(rows_per_expert, xe)
+        # 6. results back along the same plan
+        back = torch.empty_like(ye)
+        back[perm] = ye
+        got = _all_to_all_rows(back, recv_splits, plan.send_splits, group)   # [n, D] in send-buffer order
     # 7. weighted combine in selection order, shared expert last
-    out = torch.zeros_like(x)
-    for kk in range(plan.K):
-        ent = plan.entry_of[:, kk]
-        live = ent >= 0
-        contrib = got.index_select(0, ent.clamp(min=0)) * w[:, kk].unsqueeze(1)
-        out = out + torch.where(live.unsqueeze(1), contrib, torch.zeros_like(contrib))
-    if shared is not None:
-        out = out + shared(x)
+    ys = shared(x) if shared is not None else None
+    out = (combine or _combine_torch)(got, plan.entry_of, w, keff, ys)
     return out, (idx, w, keff)
 
 
@@ -165,6 +178,17 @@ class CudaEpLayer:
 
     def experts(self, rows, xe):
         return self._group(self.g, self.u, self.d, rows, xe.contiguous())
+
+    def combine(self, got, entry_of, w, keff, ys):
+        out = torch.empty((entry_of.shape[0], got.shape[1]), dtype=torch.float32, device=got.device)
+        if got.shape[0] == 0:
+            got = out                        # no live entry: the pointer is never read
+        ok = self.be.moe_combine_dev(self.device, out.data_ptr(), got.data_ptr(), entry_of.data_ptr(),
+                                     w.data_ptr(), keff.data_ptr(), ys.data_ptr() if ys is not None else None,
+                                     entry_of.shape[0], entry_of.shape[1], got.shape[1])
+        if not ok:
+            raise RuntimeError("coli_cuda_moe_combine_dev failed")
+        return out
 
     def shared_fn(self, x):
         return self._group(self.sg, self.su, self.sd, [x.shape[0]], x.contiguous())

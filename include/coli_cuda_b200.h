@@ -239,6 +239,16 @@ int coli_cuda_route_topk_dev(int device, const float *logits_dev, const float *b
                              int K, int gating, int norm_topk, float routed_scale, float topp,
                              int *idx_dev, float *w_dev, int *keff_dev);
 
+/* Weighted combine of an expert-parallel layer on device buffers:
+ *   out[s] = sum_{kk < keff[s]} w[s,kk] * y[entry_of[s*K+kk]]   (+ shared[s] when shared_dev != NULL)
+ * added in selection order, shared expert last (the order of c/colibri.c:4819-4839).
+ * entry_of [M,K] and keff [M] are 64-bit integers; y rows and out rows have D floats
+ * (D % 4 == 0, pointers 16-byte aligned). Enqueues on the backend's stream. No
+ * counterpart in the reference, which combines on the host. */
+int coli_cuda_moe_combine_dev(int device, float *out_dev, const float *y_dev, const long long *entry_of_dev,
+                              const float *w_dev, const long long *keff_dev, const float *shared_dev, int M,
+                              int K, int D);
+
 /* Physical device bytes held by resident tensors after repacking (the logical
  * figure is coli_cuda_stats). */
 size_t coli_cuda_physical_bytes(int device);
@@ -254,12 +264,20 @@ void coli_cuda_set_timing(int enabled);
  * kernel; 0 routes them through the multi-kernel path instead (A/B testing). */
 void coli_cuda_set_fused_decode(int enabled);
 
-/* Expert groups in which some expert has more than 32 rows normally run on the
- * tcgen05 tensor-core kernel (when every tensor of the group is int4 with per-row
- * or fp16-exact group scales, or MXFP4, and D and I are multiples of 128);
- * 0 keeps them on the streaming kernel instead (A/B testing). No counterpart in
- * the reference. */
+/* Expert groups and layer calls with many rows per expert run on the tcgen05
+ * tensor-core kernel when every tensor involved is int4 with per-row or fp16-exact
+ * group scales, or MXFP4, and D and I are multiples of 128:
+ *   1 (default)  when it pays: a mean of at least 12 rows per expert of the call
+ *                (layer calls: M >= 32 and M*K >= 12*E), the measured crossover with
+ *                the streaming kernel
+ *   2            whenever the tensors and shapes allow it (tests)
+ *   0            never: the streaming kernel takes every size (A/B testing)
+ * No counterpart in the reference. */
 void coli_cuda_set_tensor_core(int enabled);
+
+/* Kernels this backend has launched on `device` since coli_cuda_init (every compute
+ * entry point counts its own launches). No counterpart in the reference. */
+unsigned long long coli_cuda_launch_total(int device);
 
 /* Phase probe of the fused decode kernel: with a device buffer of
  * (#SMs x 12) 64-bit words set, thread 0 of every CTA stores the global

@@ -91,5 +91,5 @@ def test_dispatch_plan_orders_by_rank_expert_row():
     # live entries: r0:(5,1,6) r1:(1,7) r2:(6,5,2) -> sorted by expert: 1(r0),1(r1),2(r2),5(r0),5(r2),6(r0),6(r2),7(r1)
     assert p.send_rows.tolist() == [0, 1, 2, 0, 2, 0, 2, 1]
     assert p.counts.tolist() == [[0, 2, 1, 0], [0, 2, 2, 1]]
-    assert p.send_splits.tolist() == [3, 5]
+    assert p.send_splits == [3, 5]
     assert p.entry_of.tolist() == [[3, 0, 5], [1, 7, -1], [6, 4, 2]]

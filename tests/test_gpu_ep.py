@@ -22,7 +22,7 @@ def test_ep_layer_world1_matches_oracle(be, oracle, name, M):
     x = W.activations(M, cfg["D"], 5)
     lg = W.router_logits(M, cfg["E"], 6, zipf=1.1)
     lay.logits = torch.from_numpy(lg).to(dev)
-    out, (idx, w, keff) = ep_moe_layer(torch.from_numpy(x).to(dev), lay.route, lay.experts, lay.shared_fn, cfg["E"])
+    out, (idx, w, keff) = ep_moe_layer(torch.from_numpy(x).to(dev), lay.route, lay.experts, lay.shared_fn, cfg["E"], combine=lay.combine)
     torch.cuda.synchronize()
     want, oi, ow, ok_, _ = oracle.moe_layer(host_layer(cfg, L, 2.5), x, lg)
     assert np.array_equal(idx.cpu().numpy(), oi) and np.array_equal(keff.cpu().numpy(), ok_)

@@ -20,7 +20,7 @@ def group_both_ways(be, experts, rows, x, D):
     hs = [[upload_qt(be, t) for t in e] for e in experts]
     g, u, d = [h[0] for h in hs], [h[1] for h in hs], [h[2] for h in hs]
     try:
-        be.set_tensor_core(1)
+        be.set_tensor_core(2)
         ok, y_tc = be.run_expert_group(g, u, d, rows, x, D)
         assert ok
         be.set_tensor_core(0)
@@ -120,7 +120,7 @@ def test_tc_layer_matches_oracle_and_streaming(be, oracle, name, M):
     x = W.activations(M, cfg["D"], 9)
     lg = W.router_logits(M, cfg["E"], 10, zipf=1.1)
     try:
-        be.set_tensor_core(1)
+        be.set_tensor_core(2)
         out_tc, idx, w, keff = lay(x, lg)
         be.set_tensor_core(0)
         out_st, idx2, w2, keff2 = lay(x, lg)
@@ -153,12 +153,14 @@ def test_tc_many_tasks_per_cta(be, oracle):
     # the host entry point takes at most 64 experts per call
     y = np.empty_like(x)
     off = 0
+    be.set_tensor_core(2)
     for c0 in range(0, 200, 50):
         n = int(np.sum(rows[c0:c0 + 50]))
         ok, yc = be.run_expert_group(g[c0:c0 + 50], u[c0:c0 + 50], d[c0:c0 + 50], rows[c0:c0 + 50], x[off:off + n], D)
         assert ok
         y[off:off + n] = yc
         off += n
+    be.set_tensor_core(1)
     assert be.kernel_status(0) == 0
     off = 0
     for e, r in zip(experts, rows):

@@ -791,10 +791,10 @@ struct TcSegs {
     int ntask[4] = {0, 0, 0, 0};
 };
 static void add_tc_seg(TcSegs *ts, const ColiCudaTensor *t, float *out, const __half *bq, const float *binv,
-                       int nrows, int npad, int pos0) {
+                       const int *lo_flag, int nrows, int npad, int pos0) {
     TcSeg s;
     std::memset(&s, 0, sizeof(s));
-    s.w = t->pk; s.rowscale = t->rowscale; s.bq = bq; s.binv = binv; s.out = out;
+    s.w = t->pk; s.rowscale = t->rowscale; s.bq = bq; s.binv = binv; s.lo_flag = lo_flag; s.out = out;
     s.nrows = nrows; s.npad = npad; s.pos0 = pos0;
     s.O = t->O; s.nkb64 = t->I / TC_KB;
     s.task0 = ts->ntask[t->mode];
@@ -848,7 +848,7 @@ static int group_tc_ok(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
 static int group_device_tc(DeviceCtx *c, ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
                            ColiCudaTensor *const *downs, const int *rows, int count, int D, int I,
                            int total, float *y_dev, const float *x_dev, int bcast, const int *rowsrc = nullptr) {
-    std::vector<int> meta;            // [rowsrc | row_pass | row_n | pass_row0 | pass_npad]
+    std::vector<int> meta;            // [rowsrc | row_pass | row_n | pass_row0 | pass_npad | lo flags of x | lo flags of h]
     std::vector<int> row_pass(total), row_n(total), pass_row0, pass_npad, pass_rows, pass_pos0, pass_expert;
     int off = 0, padded = 0;
     for (int e = 0; e < count; e++) {
@@ -864,7 +864,7 @@ static int group_device_tc(DeviceCtx *c, ColiCudaTensor *const *gates, ColiCudaT
         off += re;
     }
     const int npass = (int)pass_row0.size();
-    meta.resize((size_t)3 * total + 2 * npass);
+    meta.resize((size_t)3 * total + 4 * npass, 0);
     for (int r = 0; r < total; r++) { meta[r] = rowsrc ? rowsrc[r] : bcast ? 0 : r; meta[total + r] = row_pass[r]; meta[2 * total + r] = row_n[r]; }
     for (int p = 0; p < npass; p++) { meta[3 * total + p] = pass_row0[p]; meta[3 * total + npass + p] = pass_npad[p]; }
     if (!reserve(c, &c->misc, meta.size() * sizeof(int)) ||
@@ -878,23 +878,24 @@ static int group_device_tc(DeviceCtx *c, ColiCudaTensor *const *gates, ColiCudaT
     const int *d_meta = static_cast<const int *>(c->misc.p);
     const int *d_rowsrc = d_meta, *d_row_pass = d_meta + total, *d_row_n = d_meta + 2 * total;
     const int *d_pass_row0 = d_meta + 3 * total, *d_pass_npad = d_pass_row0 + npass;
+    int *d_lo_x = static_cast<int *>(c->misc.p) + 3 * total + 2 * npass, *d_lo_h = d_lo_x + npass;
     __half *bq = (__half *)c->bq.p, *hq = (__half *)c->hq.p;
     float *binv = (float *)c->bs.p, *hinv = (float *)c->hs.p, *G = (float *)c->pg.p, *U = (float *)c->pu.p;
     k_prep_umma<<<(total * 32 + 255) / 256, 256, 0, c->stream>>>(bq, binv, x_dev, nullptr, d_rowsrc, d_row_pass, d_row_n,
-                                                                 d_pass_row0, d_pass_npad, total, D);
+                                                                 d_pass_row0, d_pass_npad, d_lo_x, total, D);
     c->last_launches++;
     TcSegs t1, t2;
     for (int p = 0; p < npass; p++) {
         const int e = pass_expert[p];
         const __half *bp = bq + (size_t)2 * D * pass_row0[p];
         const __half *hp = hq + (size_t)2 * I * pass_row0[p];
-        add_tc_seg(&t1, gates[e], G, bp, binv + pass_pos0[p], pass_rows[p], pass_npad[p], pass_pos0[p]);
-        add_tc_seg(&t1, ups[e], U, bp, binv + pass_pos0[p], pass_rows[p], pass_npad[p], pass_pos0[p]);
-        add_tc_seg(&t2, downs[e], y_dev, hp, hinv + pass_pos0[p], pass_rows[p], pass_npad[p], pass_pos0[p]);
+        add_tc_seg(&t1, gates[e], G, bp, binv + pass_pos0[p], d_lo_x + p, pass_rows[p], pass_npad[p], pass_pos0[p]);
+        add_tc_seg(&t1, ups[e], U, bp, binv + pass_pos0[p], d_lo_x + p, pass_rows[p], pass_npad[p], pass_pos0[p]);
+        add_tc_seg(&t2, downs[e], y_dev, hp, hinv + pass_pos0[p], d_lo_h + p, pass_rows[p], pass_npad[p], pass_pos0[p]);
     }
     if (!run_tc_segs(c, &t1, &c->segs1)) return 0;
     k_prep_umma<<<(total * 32 + 255) / 256, 256, 0, c->stream>>>(hq, hinv, G, U, nullptr, d_row_pass, d_row_n,
-                                                                 d_pass_row0, d_pass_npad, total, I);
+                                                                 d_pass_row0, d_pass_npad, d_lo_h, total, I);
     c->last_launches++;
     if (!run_tc_segs(c, &t2, &c->segs2)) return 0;
     return cuda_ok(cudaGetLastError(), "expert group launch");

@@ -24,7 +24,10 @@
 //   MXFP4 / per-row int4 weights: one exact fp16 term (e2m1 * 2^(e+shift), or n)
 //   grouped int4 with fp16 scales: n*s*2^shift = hi + lo exactly (hmul2 + fma residual)
 // so a 16-column step costs 2 MMAs (Xhi x W, Xlo x W) or 3 (Xhi x Whi, Xlo x Whi,
-// Xhi x Wlo); the dropped Xlo x Wlo term is below 2^-22 of the product.
+// Xhi x Wlo); the dropped Xlo x Wlo term is below 2^-22 of the product. When every lo
+// term of a pass is zero (activations that are exact in fp16 after the row scale, such as
+// bf16-valued inputs) the preparation kernel says so and the Xlo MMAs and copies are
+// skipped, which changes no result.
 // The row scale 2^-r, the tensor shift and a per-feature weight scale are applied
 // when the accumulators are read back.
 //
@@ -46,9 +49,10 @@
 //   warp 1       activation producer: one bulk copy per 32-column block (both terms,
 //                contiguous in global memory) into a ring of 16 KB stages
 //   warp 2       one thread issues the MMAs of a 64-column block (descriptor high words
-//                constant, low words advanced by adds) and commits them to the barriers
-//                that free the activation stages and the W stage; after the last block it
-//                commits to the accumulator barrier
+//                constant, low words advanced by adds) and commits them to the one barrier
+//                that frees the block's W stage and its two activation stages (a commit
+//                costs the issuing thread about 200 cycles, an MMA about 30); after the
+//                last block of a partial sum it commits to the accumulator barrier
 //   warps 3-10   decode, one warp per packed tile: raw chunk -> registers -> fp16 W tile(s)
 //                of a 2-stage ring (one 16-byte shared store per 8 weights), fence to the
 //                async proxy, one arrival per warp
@@ -66,7 +70,8 @@
 #define TC_FEAT 256         // output features per task (N of the MMA)
 #define TC_KB 64            // columns per W stage
 #define TC_XKB 32           // columns per activation stage
-#define TC_NW 2             // W ring depth
+#define TC_NW 2             // W ring depth = steps in flight; the activation ring holds the same two steps
+#define TC_NX 4             // activation stages (32 columns each)
 #define TC_FLUSH_KB 8        // 64-column blocks per partial sum (see "Accumulation" above)
 #define TC_DEC_WARPS 8
 #define TC_EPI_WARPS 8
@@ -77,12 +82,11 @@
 __host__ __device__ constexpr int tc_chunk_bytes(int mode) {
     return CODE_BYTES + (mode == SC_H16 ? 256 : mode == SC_F32 ? 512 : mode == SC_MX ? 128 : 0);
 }
-__host__ __device__ constexpr int tc_nraw(int mode) { return mode == SC_H16 ? 2 : 3; }      // raw ring depth
-__host__ __device__ constexpr int tc_nx(int mode) { return mode == SC_H16 ? 3 : 6; }        // activation ring depth
+__host__ __device__ constexpr int tc_nraw(int mode) { return mode == SC_H16 ? 1 : 3; }      // raw ring depth (what fits)
 __host__ __device__ constexpr int tc_raw_stage_bytes(int mode) { return 8 * tc_chunk_bytes(mode); }
 __host__ __device__ constexpr int tc_w_stage_bytes(int mode) { return (mode == SC_H16 ? 2 : 1) * TC_FEAT * TC_KB * 2; }
 __host__ __device__ constexpr int tc_smem_total(int mode) {
-    return TC_NW * tc_w_stage_bytes(mode) + tc_nx(mode) * TC_X_STAGE + tc_nraw(mode) * tc_raw_stage_bytes(mode) + 1024;
+    return TC_NW * tc_w_stage_bytes(mode) + TC_NX * TC_X_STAGE + tc_nraw(mode) * tc_raw_stage_bytes(mode) + 1024;
 }
 
 struct TcSeg {
@@ -90,6 +94,7 @@ struct TcSeg {
     const float *rowscale;   // SC_ROW: per output feature, else NULL
     const __half *bq;        // activation tiles of this pass: [K/32][2 terms][4 chunks][npad][8] halfs
     const float *binv;       // [nrows] 2^-r of the pass rows
+    const int *lo_flag;      // non-zero when some lo term of the pass is non-zero (else the lo MMAs are skipped)
     float *out;              // [.. , O] row-major; row (pos0 + n) receives feature o
     int nrows, npad, pos0;
     int O, nkb64;            // output features, 64-column blocks along the contraction
@@ -162,7 +167,7 @@ __global__ void k_prep_umma(__half *__restrict__ bq, float *__restrict__ binv, c
                             const float *__restrict__ u, const int *__restrict__ rowsrc,
                             const int *__restrict__ row_pass, const int *__restrict__ row_n,
                             const int *__restrict__ pass_row0, const int *__restrict__ pass_npad,
-                            int nrows_total, int K) {
+                            int *__restrict__ pass_lo, int nrows_total, int K) {
     const int wid = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (wid >= nrows_total) return;
     const int src = rowsrc ? rowsrc[wid] : wid;
@@ -178,12 +183,16 @@ __global__ void k_prep_umma(__half *__restrict__ bq, float *__restrict__ binv, c
     if (lane == 0) binv[wid] = 1.f / s;
     const int p = row_pass[wid], n = row_n[wid], npad = pass_npad[p];
     __half *base = bq + (size_t)2 * K * pass_row0[p];
+    unsigned lo_bits = 0;
     for (int k = lane * 4; k < K; k += 128) {
         float4 v = tc_row_vals(xr, ur, k);
         float xv[4] = {v.x * s, v.y * s, v.z * s, v.w * s};
         __half hi[4], lo[4];
 #pragma unroll
-        for (int i = 0; i < 4; i++) { hi[i] = __float2half_rn(xv[i]); lo[i] = __float2half_rn(xv[i] - __half2float(hi[i])); }
+        for (int i = 0; i < 4; i++) {
+            hi[i] = __float2half_rn(xv[i]); lo[i] = __float2half_rn(xv[i] - __half2float(hi[i]));
+            lo_bits |= __half_as_ushort(lo[i]) & 0x7FFFu;
+        }
         const int kb = k >> 5, kc = (k & 31) >> 3, ki = k & 7;
         size_t o_hi = ((size_t)((kb * 2 + 0) * 4 + kc) * npad) * 8 + (size_t)(n >> 3) * 64 + (n & 7) * 8 + ki;
         size_t o_lo = ((size_t)((kb * 2 + 1) * 4 + kc) * npad) * 8 + (size_t)(n >> 3) * 64 + (n & 7) * 8 + ki;
@@ -194,13 +203,17 @@ __global__ void k_prep_umma(__half *__restrict__ bq, float *__restrict__ binv, c
             (uint32_t)__half_as_ushort(lo[0]) | ((uint32_t)__half_as_ushort(lo[1]) << 16),
             (uint32_t)__half_as_ushort(lo[2]) | ((uint32_t)__half_as_ushort(lo[3]) << 16));
     }
+    // activations that are exact in fp16 after the row scale (bf16-valued inputs, for one)
+    // leave every lo term zero: the GEMM then skips the lo MMAs and the lo half of the copies
+    if (__any_sync(0xffffffffu, lo_bits != 0) && lane == 0) atomicOr(&pass_lo[p], 1);
 }
 
 #define TC_MAX_RING 6
 struct TcBars {
     unsigned long long raw_full[4], raw_empty[4];
-    unsigned long long x_full[TC_MAX_RING], x_empty[TC_MAX_RING];
-    unsigned long long w_full[TC_NW], w_empty[TC_NW];
+    unsigned long long x_full[TC_NX];
+    unsigned long long w_full[TC_NW];
+    unsigned long long step_free[TC_NW];     // the MMAs of a 64-column step are done: its W stage and X stages are free
     unsigned long long acc_full[2], acc_empty[2];
     unsigned long long drain;
 };
@@ -239,7 +252,7 @@ k_expert_gemm_tc(const TcSeg *__restrict__ segs, const TcCtl *__restrict__ ctl, 
     constexpr int W_BYTES = TC_FEAT * TC_KB * 2;         // 32 KB per term
     constexpr int RAW_STAGE = tc_raw_stage_bytes(MODE);
     constexpr int W_STAGE = tc_w_stage_bytes(MODE);
-    constexpr int NRAW = tc_nraw(MODE), NX = tc_nx(MODE);
+    constexpr int NRAW = tc_nraw(MODE), NX = TC_NX;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ TcBars s_bars;
     __shared__ uint32_t s_tmem;
@@ -248,15 +261,15 @@ k_expert_gemm_tc(const TcSeg *__restrict__ segs, const TcCtl *__restrict__ ctl, 
     const uint32_t sbase = (smem_u32(smem) + 1023u) & ~1023u;
     const uint32_t w0 = sbase, x0 = w0 + TC_NW * W_STAGE, raw0 = x0 + NX * TC_X_STAGE;
     const uint32_t bar_raw_full = smem_u32(s_bars.raw_full), bar_raw_empty = smem_u32(s_bars.raw_empty);
-    const uint32_t bar_x_full = smem_u32(s_bars.x_full), bar_x_empty = smem_u32(s_bars.x_empty);
-    const uint32_t bar_w_full = smem_u32(s_bars.w_full), bar_w_empty = smem_u32(s_bars.w_empty);
+    const uint32_t bar_x_full = smem_u32(s_bars.x_full), bar_w_full = smem_u32(s_bars.w_full);
+    const uint32_t bar_step_free = smem_u32(s_bars.step_free);
     const uint32_t bar_acc_full = smem_u32(s_bars.acc_full), bar_acc_empty = smem_u32(s_bars.acc_empty);
     const uint32_t bar_drain = smem_u32(&s_bars.drain);
     volatile int *abort_flag = &s_abort;
     if (tid == 0) {
         for (int i = 0; i < NRAW; i++) { mbar_init(bar_raw_full + i * 8, 1); mbar_init(bar_raw_empty + i * 8, TC_DEC_WARPS); }
-        for (int i = 0; i < NX; i++) { mbar_init(bar_x_full + i * 8, 1); mbar_init(bar_x_empty + i * 8, 1); }
-        for (int i = 0; i < TC_NW; i++) { mbar_init(bar_w_full + i * 8, TC_DEC_WARPS); mbar_init(bar_w_empty + i * 8, 1); }
+        for (int i = 0; i < NX; i++) mbar_init(bar_x_full + i * 8, 1);
+        for (int i = 0; i < TC_NW; i++) { mbar_init(bar_w_full + i * 8, TC_DEC_WARPS); mbar_init(bar_step_free + i * 8, 1); }
         mbar_init(bar_acc_full, 1); mbar_init(bar_acc_empty, TC_EPI_WARPS);
         mbar_init(bar_drain, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -299,18 +312,23 @@ k_expert_gemm_tc(const TcSeg *__restrict__ segs, const TcCtl *__restrict__ ctl, 
     } else if (warp == 1) {
         // ---- activation producer --------------------------------------------------------------
         if (lane == 0) {
-            TcRing r;
+            TcRing r, rs;
             int issued = 0;
             bool ok = true;
             for (int task = blockIdx.x; task < ntask && ok; task += gridDim.x) {
                 const TcSeg *sg = tc_find_seg(segs, nseg, task);
-                const uint32_t xbytes = (uint32_t)sg->npad * 128u;          // 2 terms x 4 chunks x npad rows x 16 B
+                const uint32_t xstride = (uint32_t)sg->npad * 128u;         // 2 terms x 4 chunks x npad rows x 16 B
+                const uint32_t xbytes = *sg->lo_flag ? xstride : xstride / 2;   // the hi term comes first
                 const uint8_t *src = reinterpret_cast<const uint8_t *>(sg->bq);
                 const int nkb32 = sg->nkb64 * 2;
                 for (int kb = 0; kb < nkb32; kb++, issued++) {
-                    if (r.wrapped && !tc_wait(bar_x_empty + r.s * 8, r.par ^ 1, abort_flag)) { ok = false; break; }
+                    // stages 2s and 2s+1 belong to step slot s: free once that step's MMAs are done
+                    if (!(kb & 1)) {
+                        if (rs.wrapped && !tc_wait(bar_step_free + rs.s * 8, rs.par ^ 1, abort_flag)) { ok = false; break; }
+                        rs.next(TC_NW);
+                    }
                     mbar_expect_tx(bar_x_full + r.s * 8, xbytes);
-                    bulk_g2s(x0 + r.s * TC_X_STAGE, src + (size_t)kb * xbytes, xbytes, bar_x_full + r.s * 8);
+                    bulk_g2s(x0 + r.s * TC_X_STAGE, src + (size_t)kb * xstride, xbytes, bar_x_full + r.s * 8);
                     r.next(NX);
                 }
             }
@@ -334,6 +352,7 @@ k_expert_gemm_tc(const TcSeg *__restrict__ segs, const TcCtl *__restrict__ ctl, 
                 const uint32_t idesc = umma_idesc_f16(TC_ROWS, nfeat);
                 const uint32_t lbo_x = (uint32_t)npad * 16u;                // bytes between 8-column chunks
                 const uint32_t x_term = (uint32_t)npad * 4u;                // hi -> lo term, 16-byte units (4 chunks)
+                const bool use_lo = *sg->lo_flag != 0;
                 uint32_t acc = 0;
                 const uint32_t d_tmem = tmem;                               // partial sum: columns 0..255
                 for (int kb = 0; kb < nkb64 && ok; kb++) {
@@ -355,14 +374,13 @@ k_expert_gemm_tc(const TcSeg *__restrict__ segs, const TcCtl *__restrict__ ctl, 
                             const uint32_t x_k = xl + (uint32_t)(2 * k2) * (lbo_x >> 4);
                             const uint32_t w_k = wl + (uint32_t)(h * 2 + k2) * 2u;
                             umma_f16_split(d_tmem, x_k, desc_x_hi, w_k, desc_w_hi, idesc, acc);
-                            umma_f16_split(d_tmem, x_k + x_term, desc_x_hi, w_k, desc_w_hi, idesc, 1u);
+                            if (use_lo) umma_f16_split(d_tmem, x_k + x_term, desc_x_hi, w_k, desc_w_hi, idesc, 1u);
                             if (TWO_W) umma_f16_split(d_tmem, x_k, desc_x_hi, w_k + (W_BYTES >> 4), desc_w_hi, idesc, 1u);
                             acc = 1u;
                         }
-                        umma_commit(bar_x_empty + rx.s * 8);
                         rx.next(NX);
                     }
-                    umma_commit(bar_w_empty + rw.s * 8);
+                    umma_commit(bar_step_free + rw.s * 8);      // one commit frees the W stage and both X stages
                     rw.next(TC_NW);
                     if (ok && (kb % TC_FLUSH_KB == TC_FLUSH_KB - 1 || kb == nkb64 - 1)) { umma_commit(bar_acc_full); tc++; }
                 }
@@ -413,7 +431,7 @@ k_expert_gemm_tc(const TcSeg *__restrict__ segs, const TcCtl *__restrict__ ctl, 
                 rr.next(NRAW);
 #pragma unroll
                 for (int half = 0; half < 2; half++) {
-                    if (rw.wrapped && !tc_wait(bar_w_empty + rw.s * 8, rw.par ^ 1, abort_flag)) { ok = false; break; }
+                    if (rw.wrapped && !tc_wait(bar_step_free + rw.s * 8, rw.par ^ 1, abort_flag)) { ok = false; break; }
                     const uint32_t stage = w0 + rw.s * W_STAGE;
                     if (live) {
 #pragma unroll

@@ -53,6 +53,7 @@ struct DecPass {
     int e;            // expert id, or -1 for the shared expert
     int rowid[4];     // token rows
     int nrows, pos0;
+    const uint8_t *wg, *wu, *wd;   // packed gate / up / down tensors of the expert
 };
 
 struct DecodeArgs {
@@ -355,13 +356,7 @@ __device__ __forceinline__ void dec_task_setup(DecIter &p, const DecPhase &ph, c
     kpart = local / ph.ntiles;
     tile = local - kpart * ph.ntiles;
     const DecPass &ps = sh->pass[ph.which == 1 ? (seg_i >> 1) : seg_i];
-    const uint8_t *w;
-    if (ph.which == 1) {
-        if (ps.e >= 0) w = (seg_i & 1) ? a.tab.up_pk[ps.e] : a.tab.gate_pk[ps.e];
-        else w = (seg_i & 1) ? a.tab.sh_up_pk : a.tab.sh_gate_pk;
-    } else {
-        w = ps.e >= 0 ? a.tab.down_pk[ps.e] : a.tab.sh_down_pk;
-    }
+    const uint8_t *w = ph.which == 1 ? ((seg_i & 1) ? ps.wu : ps.wg) : ps.wd;
     p.kb = kpart * ph.kb_per_part;
     p.kb_end = p.kb + ph.kb_per_part;
     p.ptr = w + ((size_t)tile * ph.nkb + p.kb) * CH;
@@ -555,6 +550,23 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
     wr.bars = smem_u32(smem) + DEC_WARPS * NST * CH + warp * NST * 8;
     wr.issued = 0; wr.consumed = 0;
     dec_probe(a, 0);
+    // Loads whose addresses do not depend on the routing are issued first and consumed after
+    // it, so their latency hides behind the routing: this thread's expert's tensor pointers
+    // (E <= 256 <= threads) and, when the activations live in shared memory, this warp's
+    // blocks of x (at most 8 per warp: M*D*4 B fit the 64 KB region).
+    const uint8_t *pre_g = nullptr, *pre_u = nullptr, *pre_d = nullptr;
+    if (tid < E) { pre_g = a.tab.gate_pk[tid]; pre_u = a.tab.up_pk[tid]; pre_d = a.tab.down_pk[tid]; }
+    float4 xpre[8];
+    if (a.act_smem) {
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            int wid = warp + u * DEC_WARPS;
+            if (wid < M * nkb1) {
+                int row = wid / nkb1, kb = wid - row * nkb1;
+                xpre[u] = *reinterpret_cast<const float4 *>(a.x + (size_t)row * D + kb * BLOCK_K + lane * 4);
+            }
+        }
+    }
     if (lane == 0) {
         for (int s = 0; s < NST; s++) mbar_init(wr.bars + s * 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -572,61 +584,92 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
                        sh->keff, reinterpret_cast<const uint64_t *>(sh->exp_tab));
     }
     dec_probe(a, 10);
-    for (int i = tid; i < M * K; i += blockDim.x) {
-        int s = i / K, kk = i - s * K;
-        if (kk < sh->keff[s]) { int e = sh->idx[i]; atomicMin(&sh->first[e], i); atomicAdd(&sh->cnt[e], 1); }
-    }
-    __syncthreads();
-    // union in first-appearance order: entry i opens a new expert iff it is that
-    // expert's first entry; its rank is the number of such entries before it
-    for (int i = tid; i < M * K; i += blockDim.x) {
-        int s = i / K, kk = i - s * K;
-        sh->pos_of[i] = (kk < sh->keff[s] && sh->first[sh->idx[i]] == i) ? 1 : 0;
-    }
-    __syncthreads();
-    for (int i = tid; i < M * K; i += blockDim.x) {
-        if (sh->pos_of[i]) {
-            int rank = 0;
-            for (int q = 0; q < i; q++) rank += sh->pos_of[q];
-            sh->uniq[rank] = sh->idx[i];
-            atomicAdd(&sh->nu, 1);
+    // the routing scratch is dead: park the preloaded tensor pointers there until the passes exist
+    const uint8_t **ptab = reinterpret_cast<const uint8_t **>(act);
+    if (tid < E) { ptab[tid] = pre_g; ptab[E + tid] = pre_u; ptab[2 * E + tid] = pre_d; }
+    if (M == 1 && sh->rowflag[0] == 0) {
+        // one row without NaN candidates: its selections are distinct experts, so entry kk is
+        // expert number kk of the union, pass kk, position kk
+        const int ke = sh->keff[0];
+        if (tid < ke) {
+            sh->pos_of[tid] = tid;
+            DecPass &ps = sh->pass[tid];
+            ps.e = sh->idx[tid]; ps.rowid[0] = 0; ps.nrows = 1; ps.pos0 = tid;
         }
-    }
-    __syncthreads();
-    const int nu = sh->nu;
-    for (int j = tid; j < nu; j += blockDim.x) {
-        int pos = 0, np = 0;
-        for (int q = 0; q < j; q++) { int c = sh->cnt[sh->uniq[q]]; pos += c; np += (c + 3) >> 2; }
-        int e = sh->uniq[j];
-        sh->base[e] = pos; sh->passbase[e] = np;
-        if (j == nu - 1) {
-            int c = sh->cnt[e];
-            int spos = pos + c, npass = np + ((c + 3) >> 2);
+        if (tid == 0) {
+            int npass = ke, spos = ke;
             sh->shared_pos0 = spos;
             if (a.tab.sh_gate_pk) {
-                for (int p = 0; p < (M + 3) / 4; p++) {
-                    DecPass &ps = sh->pass[npass + p];
-                    ps.e = -1; ps.pos0 = spos + 4 * p; ps.nrows = min(4, M - 4 * p);
-                    for (int q = 0; q < ps.nrows; q++) ps.rowid[q] = 4 * p + q;
-                }
-                npass += (M + 3) / 4; spos += M;
+                DecPass &ps = sh->pass[npass];
+                ps.e = -1; ps.pos0 = spos; ps.nrows = 1; ps.rowid[0] = 0;
+                npass++; spos++;
             }
-            sh->npass = npass; sh->npos = spos;
+            sh->npass = npass; sh->npos = spos; sh->nu = ke;
         }
+        __syncthreads();
+    } else {
+        for (int i = tid; i < M * K; i += blockDim.x) {
+            int s = i / K, kk = i - s * K;
+            if (kk < sh->keff[s]) { int e = sh->idx[i]; atomicMin(&sh->first[e], i); atomicAdd(&sh->cnt[e], 1); }
+        }
+        __syncthreads();
+        // union in first-appearance order: entry i opens a new expert iff it is that
+        // expert's first entry; its rank is the number of such entries before it
+        for (int i = tid; i < M * K; i += blockDim.x) {
+            int s = i / K, kk = i - s * K;
+            sh->pos_of[i] = (kk < sh->keff[s] && sh->first[sh->idx[i]] == i) ? 1 : 0;
+        }
+        __syncthreads();
+        for (int i = tid; i < M * K; i += blockDim.x) {
+            if (sh->pos_of[i]) {
+                int rank = 0;
+                for (int q = 0; q < i; q++) rank += sh->pos_of[q];
+                sh->uniq[rank] = sh->idx[i];
+                atomicAdd(&sh->nu, 1);
+            }
+        }
+        __syncthreads();
+        const int nu = sh->nu;
+        for (int j = tid; j < nu; j += blockDim.x) {
+            int pos = 0, np = 0;
+            for (int q = 0; q < j; q++) { int c = sh->cnt[sh->uniq[q]]; pos += c; np += (c + 3) >> 2; }
+            int e = sh->uniq[j];
+            sh->base[e] = pos; sh->passbase[e] = np;
+            if (j == nu - 1) {
+                int c = sh->cnt[e];
+                int spos = pos + c, npass = np + ((c + 3) >> 2);
+                sh->shared_pos0 = spos;
+                if (a.tab.sh_gate_pk) {
+                    for (int p = 0; p < (M + 3) / 4; p++) {
+                        DecPass &ps = sh->pass[npass + p];
+                        ps.e = -1; ps.pos0 = spos + 4 * p; ps.nrows = min(4, M - 4 * p);
+                        for (int q = 0; q < ps.nrows; q++) ps.rowid[q] = 4 * p + q;
+                    }
+                    npass += (M + 3) / 4; spos += M;
+                }
+                sh->npass = npass; sh->npos = spos;
+            }
+        }
+        __syncthreads();
+        for (int i = tid; i < M * K; i += blockDim.x) {
+            int s = i / K, kk = i - s * K;
+            if (kk < sh->keff[s]) {
+                int e = sh->idx[i], rr = 0;
+                for (int s2 = 0; s2 < s; s2++)
+                    for (int k2 = 0; k2 < sh->keff[s2]; k2++) rr += (sh->idx[s2 * K + k2] == e);
+                int pos = sh->base[e] + rr;
+                sh->pos_of[i] = pos;
+                DecPass &ps = sh->pass[sh->passbase[e] + (rr >> 2)];
+                ps.rowid[rr & 3] = s;
+                if ((rr & 3) == 0) { ps.e = e; ps.pos0 = pos; ps.nrows = min(4, sh->cnt[e] - (rr & ~3)); }
+            }
+        }
+        __syncthreads();
     }
-    __syncthreads();
-    for (int i = tid; i < M * K; i += blockDim.x) {
-        int s = i / K, kk = i - s * K;
-        if (kk < sh->keff[s]) {
-            int e = sh->idx[i], rr = 0;
-            for (int s2 = 0; s2 < s; s2++)
-                for (int k2 = 0; k2 < sh->keff[s2]; k2++) rr += (sh->idx[s2 * K + k2] == e);
-            int pos = sh->base[e] + rr;
-            sh->pos_of[i] = pos;
-            DecPass &ps = sh->pass[sh->passbase[e] + (rr >> 2)];
-            ps.rowid[rr & 3] = s;
-            if ((rr & 3) == 0) { ps.e = e; ps.pos0 = pos; ps.nrows = min(4, sh->cnt[e] - (rr & ~3)); }
-        }
+    for (int p = tid; p < sh->npass; p += blockDim.x) {
+        DecPass &ps = sh->pass[p];
+        if (ps.e >= 0) { ps.wg = ptab[ps.e]; ps.wu = ptab[E + ps.e]; ps.wd = ptab[2 * E + ps.e]; }
+        else { ps.wg = a.tab.sh_gate_pk; ps.wu = a.tab.sh_up_pk; ps.wd = a.tab.sh_down_pk; }
     }
     __syncthreads();
     if (blockIdx.x == 0) {
@@ -661,27 +704,16 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
     __half *xq_s = reinterpret_cast<__half *>(act);
     float *xs_s = reinterpret_cast<float *>(act + (size_t)M * nkb1 * 512);
     if (a.act_smem) {
-        // four blocks per warp at a time: their loads are in flight together
-        for (int w0 = warp; w0 < M * nkb1; w0 += 4 * DEC_WARPS) {
-            float4 v[4];
+        // the blocks were loaded before the routing
 #pragma unroll
-            for (int u = 0; u < 4; u++) {
-                int wid = w0 + u * DEC_WARPS;
-                if (wid < M * nkb1) {
-                    int row = wid / nkb1, kb = wid - row * nkb1;
-                    v[u] = *reinterpret_cast<const float4 *>(a.x + (size_t)row * D + kb * BLOCK_K + lane * 4);
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < 4; u++) {
-                int wid = w0 + u * DEC_WARPS;
-                if (wid < M * nkb1) {
-                    int row = wid / nkb1, kb = wid - row * nkb1;
-                    float m = warp_max(fmaxf(fmaxf(fabsf(v[u].x), fabsf(v[u].y)), fmaxf(fabsf(v[u].z), fabsf(v[u].w))));
-                    float sc = block_scale_from_max(m);
-                    store_split4(xq_s + ((size_t)row * nkb1 + kb) * 256, lane, v[u], sc);
-                    if (lane == 0) xs_s[(size_t)row * nkb1 + kb] = 1.f / sc;
-                }
+        for (int u = 0; u < 8; u++) {
+            int wid = warp + u * DEC_WARPS;
+            if (wid < M * nkb1) {
+                int row = wid / nkb1, kb = wid - row * nkb1;
+                float m = warp_max(fmaxf(fmaxf(fabsf(xpre[u].x), fabsf(xpre[u].y)), fmaxf(fabsf(xpre[u].z), fabsf(xpre[u].w))));
+                float sc = block_scale_from_max(m);
+                store_split4(xq_s + ((size_t)row * nkb1 + kb) * 256, lane, xpre[u], sc);
+                if (lane == 0) xs_s[(size_t)row * nkb1 + kb] = 1.f / sc;
             }
         }
         __syncthreads();

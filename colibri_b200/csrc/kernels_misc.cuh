@@ -311,7 +311,8 @@ __global__ void k_rows_add(float *x, const float *partial, const int *rows, int 
     const float *pr = partial + (size_t)blockIdx.x * D;
     for (int i = threadIdx.x; i < D; i += blockDim.x) xr[i] += pr[i];
 }
-// y = x * rsqrt(mean(x^2) + eps) * w, mean accumulated in double.
+// y = (x * r) * w with r = 1 / sqrtf((float)(sum(x^2) / D) + eps), the sum in double and the
+// rest in correctly rounded f32 operations (the arithmetic of c/colibri.c:1193-1196).
 __global__ void k_rmsnorm(float *y, const float *x, const float *w, int D, float eps, int xstride,
                           int ystride) {
     const float *xr = x + (size_t)blockIdx.x * xstride;
@@ -330,8 +331,8 @@ __global__ void k_rmsnorm(float *y, const float *x, const float *w, int D, float
         if (threadIdx.x == 0) sh[0] = b;
     }
     __syncthreads();
-    float r = rsqrtf((float)(sh[0] / D) + eps);
-    for (int i = threadIdx.x; i < D; i += blockDim.x) yr[i] = xr[i] * r * w[i];
+    float r = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn((float)(sh[0] / D), eps)));
+    for (int i = threadIdx.x; i < D; i += blockDim.x) yr[i] = __fmul_rn(__fmul_rn(xr[i], r), w[i]);
 }
 // out[i] = sum_c w[c] * y[c*D+i] in call order (resident group accumulate)
 __global__ void k_weighted_sum_rows(float *out, const float *y, const float *w, int count, int D) {

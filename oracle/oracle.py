@@ -189,6 +189,22 @@ class Oracle:
         return y
 
 
+def stack_forward(orc: "Oracle", embed, layers, post_ln, final_norm, lm_head, ids, eps):
+    """Logits [S, vocab] of a stack of MoE layers for S token ids, attention left out:
+    the glue of step_all / layer_forward_rows (c/colibri.c:5899-5910, 5696-5709):
+        x[s] = embed[ids[s]]
+        per layer:  x += moe(rmsnorm(x, post_ln))      (router from the normalised rows)
+        logits[s] = lm_head . rmsnorm(x[s], final_norm)
+    `layers` are HostLayer objects with router_w set; lm_head is an fmt-0 HostTensor."""
+    x = np.ascontiguousarray(embed[np.asarray(ids)], np.float32)
+    for L, ln in zip(layers, post_ln):
+        nrm = orc.rmsnorm(x, ln, eps)
+        out = orc.moe_layer(L, nrm, None)[0]
+        x = (x + out).astype(np.float32)
+    last = orc.rmsnorm(x, final_norm, eps)
+    return orc.matmul(last, lm_head)
+
+
 class HostLayer:
     """One MoE layer's weights and routing rules on the host."""
 

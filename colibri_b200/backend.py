@@ -98,6 +98,7 @@ ADDITIVE_ABI = [
     ("coli_cuda_moe_route_dev", C.c_int, [_vp, _vp, _vp, C.c_int, _vp, _vp, _vp, _vp, _vp]),
     ("coli_cuda_expert_group_dev", C.c_int, [C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), _i32p, C.c_int, _vp, _vp]),
     ("coli_cuda_pipe_gemm_noalloc", C.c_int, [_vp, _vp, _vp, C.c_int]),
+    ("coli_cuda_pipe_argmax", C.c_int, [C.c_int, _vp, _vp, C.c_int, C.c_int]),
     ("coli_cuda_moe_combine_dev", C.c_int, [C.c_int, _vp, _vp, _vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int]),
     ("coli_cuda_route_topk_dev", C.c_int, [C.c_int, _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_float, C.c_float, _vp, _vp, _vp]),
     ("coli_cuda_physical_bytes", C.c_size_t, [C.c_int]),

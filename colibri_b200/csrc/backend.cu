@@ -1283,6 +1283,15 @@ extern "C" int coli_cuda_expert_group_dev(ColiCudaTensor *const *gates, ColiCuda
     return ok;
 }
 
+// idx_dev[s] = argmax of row s of x_dev [S, N] with the engine's first-largest rule.
+extern "C" int coli_cuda_pipe_argmax(int device, int *idx_dev, const float *x_dev, int S, int N) {
+    DeviceCtx *c = find_ctx(device);
+    if (!idx_dev || !x_dev || S < 1 || N < 1 || !select_ctx(c)) return 0;
+    k_argmax_rows<<<S, 1024, 0, c->stream>>>(idx_dev, x_dev, N);
+    c->last_launches++;
+    return cuda_ok(cudaGetLastError(), "argmax launch");
+}
+
 // Weighted combine of an expert-parallel layer on device buffers: out[s] = sum over the
 // first keff[s] selections of w[s,kk] * y[entry_of[s,kk]], then + shared[s] when given.
 // entry_of and keff are 64-bit integers. Enqueues on the backend's stream.

@@ -349,3 +349,41 @@ __global__ void k_sum_slots(float *dst, const float *slots, int n, int D) {
         dst[i] = acc;
     }
 }
+
+// Row-wise argmax with the engine's scan semantics (c/olmoe.c:966-967, c/colibri.c greedy
+// pick): best = 0, then every i with x[i] > x[best] in ascending order, i.e. the first index
+// of the largest value, NaNs never winning; a NaN in x[0] keeps the answer at 0.
+__global__ void k_argmax_rows(int *__restrict__ out, const float *__restrict__ x, int N) {
+    const float *row = x + (size_t)blockIdx.x * N;
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < N; i += blockDim.x) {
+        float v = row[i];
+        if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+    }
+#pragma unroll
+    for (int off = 16; off; off >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+        int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = bv; si[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        const int nw = blockDim.x >> 5;
+        bv = threadIdx.x < nw ? sv[threadIdx.x] : -INFINITY;
+        bi = threadIdx.x < nw ? si[threadIdx.x] : 0x7fffffff;
+#pragma unroll
+        for (int off = 16; off; off >>= 1) {
+            float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+            int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (threadIdx.x == 0) {
+            const float first = row[0];
+            out[blockIdx.x] = (first != first || bi == 0x7fffffff) ? 0 : bi;
+        }
+    }
+}

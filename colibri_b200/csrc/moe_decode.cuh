@@ -549,6 +549,12 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
     wr.ring = smem_u32(smem) + warp * (NST * CH);
     wr.bars = smem_u32(smem) + DEC_WARPS * NST * CH + warp * NST * 8;
     wr.issued = 0; wr.consumed = 0;
+    // Programmatic dependent launch (when the host asked for it): let the next kernel of the
+    // stream be scheduled onto SMs as this grid's CTAs leave them, and wait here until the
+    // previous kernel has completed and its writes are visible. Both are no-ops in an
+    // ordinary launch.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     dec_probe(a, 0);
     // Loads whose addresses do not depend on the routing are issued first and consumed after
     // it, so their latency hides behind the routing: this thread's expert's tensor pointers

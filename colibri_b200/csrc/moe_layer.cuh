@@ -114,7 +114,7 @@ extern "C" void coli_cuda_moe_layer_free(ColiCudaMoeLayer *L) {
     delete L;
 }
 
-static int g_fused_decode = 1;
+static int g_fused_decode = 3;
 static unsigned long long *g_decode_probe = nullptr;
 extern "C" void coli_cuda_set_decode_probe(void *dev_buffer) { g_decode_probe = static_cast<unsigned long long *>(dev_buffer); }
 extern "C" void coli_cuda_set_fused_decode(int enabled) { g_fused_decode = enabled; }
@@ -252,11 +252,27 @@ static int layer_run(ColiCudaMoeLayer *L, DeviceCtx *c, float *out_dev, const fl
         cudaEvent_t e0 = nullptr, e1 = nullptr;
         kernel_event_pair(c, &e0, &e1);
         if (e0) cudaEventRecord(e0, c->stream);
-        // g_fused_decode == 2: plain launch (experiment; the grid still fits the device)
-        cudaError_t err = g_fused_decode == 2
-            ? cudaLaunchKernel(fn, dim3(c->sms), dim3(DEC_WARPS * 32), args, (size_t)decode_smem_bytes(L->mode_gu), c->stream)
-            : cudaLaunchCooperativeKernel(fn, dim3(c->sms), dim3(DEC_WARPS * 32), args,
-                                          (size_t)decode_smem_bytes(L->mode_gu), c->stream);
+        // 1: cooperative launch (co-residency of the grid guaranteed by the driver).
+        // 2: plain launch (the grid is one CTA per SM, so it still fits the device).
+        // 3: plain launch with programmatic stream serialisation: the next layer's CTAs are
+        //    scheduled as this grid's CTAs exit and wait at griddepcontrol.wait, which hides
+        //    most of the launch latency between back-to-back layer calls.
+        cudaError_t err;
+        if (g_fused_decode == 3) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(c->sms); cfg.blockDim = dim3(DEC_WARPS * 32);
+            cfg.dynamicSmemBytes = (size_t)decode_smem_bytes(L->mode_gu); cfg.stream = c->stream;
+            cudaLaunchAttribute at[1];
+            at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            at[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = at; cfg.numAttrs = 1;
+            err = cudaLaunchKernelExC(&cfg, fn, args);
+        } else if (g_fused_decode == 2) {
+            err = cudaLaunchKernel(fn, dim3(c->sms), dim3(DEC_WARPS * 32), args, (size_t)decode_smem_bytes(L->mode_gu), c->stream);
+        } else {
+            err = cudaLaunchCooperativeKernel(fn, dim3(c->sms), dim3(DEC_WARPS * 32), args,
+                                              (size_t)decode_smem_bytes(L->mode_gu), c->stream);
+        }
         if (e1) cudaEventRecord(e1, c->stream);
         c->last_launches++;
         return cuda_ok(err, "fused decode launch");

@@ -7,7 +7,7 @@ c/decode_batch.h) with attention left out, K candidate tokens per step.
                                                           coli_cuda_moe_layer_dev (router on the device),
                                                           coli_cuda_pipe_add
     logits[s] = lm_head . rmsnorm(x[s], final_norm)       coli_cuda_pipe_rmsnorm, coli_cuda_pipe_gemm
-    argmax on the host after one download
+    argmax[s]                                             coli_cuda_pipe_argmax (first largest)
 
 Every call is enqueued on the backend's stream; one synchronisation per step (the
 logits download)."""
@@ -33,6 +33,7 @@ class MoeStack:
         self.nrm = alloc(max_rows * D * 4)
         self.tmp = alloc(max_rows * D * 4)
         self.logits = alloc(max_rows * vocab * 4)
+        self.amax = alloc(max_rows * 4)
         self.ln = []
         for w in list(post_ln) + [final_norm]:
             w = np.ascontiguousarray(w, np.float32)
@@ -43,8 +44,9 @@ class MoeStack:
         if not (self.x and self.nrm and self.tmp and self.logits):
             raise RuntimeError("device allocation failed")
 
-    def step(self, ids):
-        """-> (logits [S, vocab] f32, argmax [S])"""
+    def step(self, ids, want_logits=True):
+        """-> (logits [S, vocab] f32 or None, argmax [S]); the argmax is taken on the device
+        (coli_cuda_pipe_argmax), so a decode loop that only needs the picks downloads S integers."""
         be, dev, D = self.be, self.dev, self.D
         ids = np.asarray(ids)
         S = len(ids)
@@ -57,15 +59,20 @@ class MoeStack:
             ok = ok and be.pipe_add(dev, self.x, self.tmp, S * D)
         ok = ok and be.pipe_rmsnorm(dev, self.nrm, self.x, self.ln[-1], S, D, C.c_float(self.eps))
         ok = ok and be.pipe_gemm(self.lm_head, self.logits, self.nrm, S)
-        out = np.empty((S, self.vocab), np.float32)
-        ok = ok and be.pipe_download(dev, self.logits, out.ctypes.data, S * self.vocab * 4)
+        ok = ok and be.pipe_argmax(dev, self.amax, self.logits, S, self.vocab)
+        pick = np.empty(S, np.int32)
+        ok = ok and be.pipe_download(dev, self.amax, pick.ctypes.data, S * 4)
+        out = None
+        if want_logits:
+            out = np.empty((S, self.vocab), np.float32)
+            ok = ok and be.pipe_download(dev, self.logits, out.ctypes.data, S * self.vocab * 4)
         if not ok:
             raise RuntimeError("a backend call of the stack step failed")
-        return out, out.argmax(axis=1)
+        return out, pick
 
     def free(self):
-        for p in [self.x, self.nrm, self.tmp, self.logits] + self.ln:
+        for p in [self.x, self.nrm, self.tmp, self.logits, self.amax] + self.ln:
             if p:
                 self.be.pipe_free(self.dev, p)
         self.ln = []
-        self.x = self.nrm = self.tmp = self.logits = None
+        self.x = self.nrm = self.tmp = self.logits = self.amax = None

@@ -239,6 +239,12 @@ int coli_cuda_route_topk_dev(int device, const float *logits_dev, const float *b
                              int K, int gating, int norm_topk, float routed_scale, float topp,
                              int *idx_dev, float *w_dev, int *keff_dev);
 
+/* Greedy pick on the device: idx_dev[s] = first index of the largest value of row s of
+ * x_dev [S, N] (the scan of c/olmoe.c:966-967: NaNs never win; a NaN in column 0 keeps
+ * the answer at 0). Lets a device-resident decode loop download S integers instead of
+ * S*N logits. Enqueues on the backend's stream. No counterpart in the reference. */
+int coli_cuda_pipe_argmax(int device, int *idx_dev, const float *x_dev, int S, int N);
+
 /* Weighted combine of an expert-parallel layer on device buffers:
  *   out[s] = sum_{kk < keff[s]} w[s,kk] * y[entry_of[s*K+kk]]   (+ shared[s] when shared_dev != NULL)
  * added in selection order, shared expert last (the order of c/colibri.c:4819-4839).
@@ -260,8 +266,17 @@ int coli_cuda_last_timing(int device, float *kernel_ms, int *launches);
 /* Enables (1) or disables (0) that per-call event timing; off by default. */
 void coli_cuda_set_timing(int enabled);
 
-/* Decode-sized layer calls (M <= 8) normally run as one fused cooperative
- * kernel; 0 routes them through the multi-kernel path instead (A/B testing). */
+/* Decode-sized layer calls (M <= 8) normally run as one fused kernel of one CTA per SM
+ * with grid barriers inside:
+ *   3 (default)  plain launch with programmatic stream serialisation: the next layer
+ *                call's CTAs are scheduled as this call's CTAs exit and wait (before
+ *                touching global memory) until it has completed, which hides most of
+ *                the launch latency between back-to-back layer calls
+ *   2            plain launch
+ *   1            cooperative launch (the driver guarantees the grid is co-resident)
+ *   0            the multi-kernel path instead (A/B testing)
+ * Every grid-barrier wait is bounded; a launch whose CTAs were not co-resident would end
+ * with the call returning 0, not with a hang. */
 void coli_cuda_set_fused_decode(int enabled);
 
 /* Expert groups and layer calls with many rows per expert run on the tcgen05

@@ -66,6 +66,7 @@ def test_stack_matches_oracle(be, oracle, K):
             want = stack_forward(oracle, embed, hosts, post_ln, final_norm, lm_t, ids, EPS)
             assert max_rel_err(got, want) <= 1e-3, step
             assert np.array_equal(am, want.argmax(axis=1)), step
+            assert np.array_equal(am, got.argmax(axis=1)), step      # device pick == first largest of its own logits
     finally:
         teardown(be, st, res)
 
@@ -135,3 +136,28 @@ def test_stack_full_shape_properties(be):
         for h in allh:
             be.tensor_free(h)
         be.tensor_free(lm_h)
+
+
+def test_device_argmax_rules(be):
+    import ctypes as C
+    rng = np.random.default_rng(2)
+    S, N = 5, 5000
+    x = rng.standard_normal((S, N)).astype(np.float32)
+    x[1, 77] = x[1, 4000] = 9.0            # tie: the first wins
+    x[2, 10] = np.nan; x[2, 20] = 8.0      # NaN never wins
+    x[3, 0] = np.nan                        # NaN in column 0 keeps the answer at 0
+    x[4, :] = -np.inf                       # nothing beats column 0
+    xd = be.pipe_alloc(0, x.nbytes); od = be.pipe_alloc(0, S * 4)
+    assert be.pipe_upload(0, xd, x.ctypes.data, x.nbytes)
+    assert be.pipe_argmax(0, od, xd, S, N)
+    got = np.empty(S, np.int32)
+    assert be.pipe_download(0, od, got.ctypes.data, S * 4)
+    be.pipe_free(0, xd); be.pipe_free(0, od)
+    want = []
+    for r in x:                             # the engine's scan
+        best = 0
+        for i in range(1, N):
+            if r[i] > r[best]:
+                best = i
+        want.append(best)
+    assert got.tolist() == want

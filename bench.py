@@ -59,6 +59,10 @@ def measured_peaks():
     return 6650.0, "fallback"
 
 
+# DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum of one
+# ncu capture, summarised in profiles/k_moe_decode_c2_m1.md and k_moe_decode_c4_e64_m1.md); other
+# workloads have no capture and report null.
+NCU_TRAFFIC_BYTES = {("c2_decode", 1, 64): 28.45e6}
 TC_MEAN_ROWS = 12     # the backend's rule for prefill-sized layer calls: mean rows per expert
 
 
@@ -499,7 +503,9 @@ def run_gpu_arm(args):
                                          k_ms.value, k_n.value, 3 if fmt == 4 else 2)
                          if M >= 32 and (args.tc == 2 or (args.tc == 1 and M * K >= TC_MEAN_ROWS * E)) else
                          {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s",
-                          "frac": (ach / peak) if ach else None, "traffic": None,
+                          "frac": (ach / peak) if ach else None,
+                          "traffic": NCU_TRAFFIC_BYTES.get((args.workload, M, E)),
+                          "algorithmic_bytes_per_launch": weight_bytes_step / L,
                           "kernel": "k_moe_decode" if M <= 8 else "k_gemv_stream", "launches": k_n.value,
                           "avg_launch_us": (k_ms.value / k_n.value * 1e3) if k_n.value else None,
                           "peak_source": which}),

@@ -494,6 +494,8 @@ def run_gpu_arm(args):
                        "l2": f"{L} distinct layers, {weight_bytes_step / 1e6:.0f} MB of weights touched per step "
                              f"(> 126 MB L2); no flush needed",
                        "bytes_per_step": step_bytes, "distinct_experts_per_layer": nus,
+                       # one step = the MoE FFNs of all layers for M tokens: the decode rate this path alone allows
+                       "moe_only_tokens_per_s": M * args.steps / (ms_all * 1e-3),
                        "vs_8tbs_nominal": value / world / 8000.0},
             "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": L * (M * D * 4 + M * E * 4),
                     "d2h_bytes_per_step": L * M * D * 4, "ms_per_step": e2e_ms_all / args.steps},

@@ -42,7 +42,7 @@ struct DeviceCtx {
     float *host_x = nullptr, *host_y = nullptr;
     size_t host_x_cap = 0, host_y_cap = 0;
     int group_pending = 0;
-    int *status = nullptr;                    // device int: sticky kernel status
+    int *status = nullptr;                    // pinned host int the kernels store into (kstat_set): sticky kernel status
     unsigned long long *gridbar = nullptr;    // arrival counter of the fused decode kernel's grid barrier
     unsigned long long epoch = 0;             // arrivals expected at that counter so far
     int sticky_status = 0;                    // last non-zero kernel status seen by the host
@@ -178,13 +178,13 @@ extern "C" int coli_cuda_init(const int *devices, int count) {
         if (!cuda_ok(cudaStreamCreate(&c->stream), "stream") ||
             !cuda_ok(cudaEventCreate(&c->ev0), "event") || !cuda_ok(cudaEventCreate(&c->ev1), "event") ||
             !cuda_ok(cudaEventCreateWithFlags(&c->ev_done, cudaEventDisableTiming), "event") ||
-            !cuda_ok(cudaMalloc((void **)&c->status, sizeof(int)), "status") ||
-            !cuda_ok(cudaMemset(c->status, 0, sizeof(int)), "status") ||
+            !cuda_ok(cudaHostAlloc((void **)&c->status, sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable), "status") ||
             !cuda_ok(cudaMalloc((void **)&c->gridbar, sizeof(unsigned long long)), "grid barrier") ||
             !cuda_ok(cudaMemset(c->gridbar, 0, sizeof(unsigned long long)), "grid barrier") ||
             !cuda_ok(cudaMemcpyToSymbol(c_exp2_tab, tab, sizeof(tab)), "exp table")) {
             g_nctx = i + 1; coli_cuda_shutdown(); return 0;
         }
+        *c->status = 0;
         setup_mode<SC_ROW>(); setup_mode<SC_H16>(); setup_mode<SC_F32>(); setup_mode<SC_MX>();
         set_smem(k_moe_decode<SC_ROW>, decode_smem_bytes(SC_ROW)); set_smem(k_moe_decode<SC_H16>, decode_smem_bytes(SC_H16));
         set_smem(k_moe_decode<SC_F32>, decode_smem_bytes(SC_F32)); set_smem(k_moe_decode<SC_MX>, decode_smem_bytes(SC_MX));
@@ -210,7 +210,7 @@ extern "C" void coli_cuda_shutdown(void) {
         for (int s = 0; s < 27; s++) free_buf(&c->pipe[s]);
         if (c->host_x) cudaFreeHost(c->host_x);
         if (c->host_y) cudaFreeHost(c->host_y);
-        if (c->status) cudaFree(c->status);
+        if (c->status) cudaFreeHost(c->status);
         if (c->gridbar) cudaFree(c->gridbar);
         if (c->ev0) cudaEventDestroy(c->ev0);
         if (c->ev1) cudaEventDestroy(c->ev1);
@@ -290,8 +290,8 @@ extern "C" void *coli_cuda_stream(int device) {
 extern "C" int coli_cuda_kernel_status(int device) {
     DeviceCtx *c = find_ctx(device);
     if (!select_ctx(c)) return -1;
-    int v = 0;
-    if (!cuda_ok(cudaMemcpy(&v, c->status, sizeof(int), cudaMemcpyDeviceToHost), "status read")) return -1;
+    if (!cuda_ok(cudaStreamSynchronize(c->stream), "synchronize")) return -1;
+    int v = *reinterpret_cast<volatile int *>(c->status);
     return v ? v : c->sticky_status;
 }
 
@@ -678,14 +678,13 @@ static int linear_any(DeviceCtx *c, const ColiCudaTensor *t, float *y_dev, const
 }
 
 static int check_status(DeviceCtx *c) {
-    int v = 0;
-    if (!cuda_ok(cudaMemcpyAsync(&v, c->status, sizeof(int), cudaMemcpyDeviceToHost, c->stream), "status read")) return 0;
     if (!cuda_ok(cudaStreamSynchronize(c->stream), "synchronize")) return 0;
+    const int v = *reinterpret_cast<volatile int *>(c->status);
     if (v) {
         std::fprintf(stderr, "[CUDA] kernel wait guard expired (status %d)\n", v);
         // the grid barrier's arrival count is no longer a multiple of the grid: start over
         cudaMemsetAsync(c->gridbar, 0, sizeof(unsigned long long), c->stream);
-        cudaMemsetAsync(c->status, 0, sizeof(int), c->stream);
+        *reinterpret_cast<volatile int *>(c->status) = 0;
         c->epoch = 0;
         c->sticky_status = v;
         return 0;

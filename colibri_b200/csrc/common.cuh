@@ -94,6 +94,14 @@ struct GemvCtl {
 
 #define KSTAT_MBAR_TIMEOUT 1
 
+// The status word lives in pinned host memory that the device addresses directly, so the
+// host reads it after a stream synchronisation without a copy. Kernels only ever store a
+// non-zero code into it (a plain store: no atomics across the bus are needed for that).
+__device__ __forceinline__ void kstat_set(int *status, int code) {
+    *reinterpret_cast<volatile int *>(status) = code;
+    __threadfence_system();
+}
+
 // Routing rule of a layer (device-visible mirror of ColiCudaMoeDesc).
 struct RouteRule {
     int D, I, E, K;

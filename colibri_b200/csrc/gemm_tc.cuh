@@ -542,7 +542,7 @@ k_expert_gemm_tc(const TcSeg *__restrict__ segs, const TcCtl *__restrict__ ctl, 
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (tid == 0 && s_abort) atomicExch(status, KSTAT_MBAR_TIMEOUT);
+    if (tid == 0 && s_abort) kstat_set(status, KSTAT_MBAR_TIMEOUT);
     if (warp == 0) {
         __syncwarp();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");

@@ -360,7 +360,7 @@ k_gemv_stream(const GemvSeg *__restrict__ segs, const GemvCtl *__restrict__ ctl,
         cons.task += P;
     }
     if (failed) {
-        if (lane == 0) atomicExch(status, KSTAT_MBAR_TIMEOUT);
+        if (lane == 0) kstat_set(status, KSTAT_MBAR_TIMEOUT);
         // drain whatever is still in flight before leaving (bounded)
         for (int i = consumed; i < issued; i++)
             if (!mbar_wait_bounded(bars + (i % NST) * 8, (i / NST) & 1)) break;

@@ -824,7 +824,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
     }
     dec_probe(a, 9);
     if (!ok) {
-        if (tid == 0) atomicExch(a.status, sh->failed ? KSTAT_GRID_TIMEOUT : KSTAT_MBAR_TIMEOUT);
+        if (tid == 0) kstat_set(a.status, sh->failed ? KSTAT_GRID_TIMEOUT : KSTAT_MBAR_TIMEOUT);
         // drain copies still in flight before the shared memory goes away (bounded)
         for (int i = wr.consumed; i < wr.issued; i++)
             if (!mbar_wait_bounded(wr.bars + (i % NST) * 8, (i / NST) & 1)) break;

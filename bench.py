@@ -258,7 +258,16 @@ def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # torchrun exports OMP_NUM_THREADS=1 to every rank; this arm is the CPU implementation with all
+    # the host threads, so the variable is put back before the OpenMP runtime starts, and the
+    # runtime is told again once it is loaded
+    ncpu = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    os.environ["OMP_NUM_THREADS"] = str(ncpu)
     oracle = Oracle()
+    try:
+        C.CDLL("libgomp.so.1").omp_set_num_threads(C.c_int(ncpu))
+    except OSError:
+        pass
     kind = "reference" if RefCpu.available() else "port"
     ref = RefCpu() if RefCpu.available() else None
     if ref is None:

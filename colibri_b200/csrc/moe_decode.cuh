@@ -279,8 +279,18 @@ __device__ __forceinline__ void route_rows_cta(const float *logits, const float 
         if (rowflag[s]) continue;
         const float c = choice[i];
         const float *row = choice + (size_t)s * E;
-        int rank = 0;
-        for (int o = 0; o < E; o++) { float v = row[o]; rank += (v > c) || (v == c && o < e); }
+        int rank = 0, o = 0;
+        if ((E & 3) == 0) {      // four candidates per shared-memory load (rows start 16-byte aligned then)
+#pragma unroll 4
+            for (; o < E; o += 4) {
+                const float4 v = *reinterpret_cast<const float4 *>(row + o);
+                rank += (v.x > c) || (v.x == c && o < e);
+                rank += (v.y > c) || (v.y == c && o + 1 < e);
+                rank += (v.z > c) || (v.z == c && o + 2 < e);
+                rank += (v.w > c) || (v.w == c && o + 3 < e);
+            }
+        }
+        for (; o < E; o++) { float v = row[o]; rank += (v > c) || (v == c && o < e); }
         if (rank < K) { idx[s * K + rank] = e; wk[s * K + rank] = score[i]; }
     }
     __syncthreads();
@@ -554,6 +564,21 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
     // previous kernel has completed and its writes are visible. Both are no-ops in an
     // ordinary launch.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // While the previous kernel drains: warm the TLB and L2 for the first addresses this CTA
+    // will read (prefetches carry no values, so it does not matter that the previous kernel
+    // may still be writing some of them; the first global access of a kernel otherwise costs
+    // about 2 us).
+    if (warp == 0) {
+        const char *pf = nullptr;
+        if (lane == 0) pf = reinterpret_cast<const char *>(a.logits);
+        else if (lane == 1) pf = reinterpret_cast<const char *>(a.x);
+        else if (lane == 2) pf = reinterpret_cast<const char *>(a.tab.gate_pk);
+        else if (lane == 3) pf = reinterpret_cast<const char *>(a.tab.up_pk);
+        else if (lane == 4) pf = reinterpret_cast<const char *>(a.tab.down_pk);
+        else if (lane == 5) pf = reinterpret_cast<const char *>(a.router_bias);
+        else if (lane == 6) pf = reinterpret_cast<const char *>(a.bar);
+        if (pf) asm volatile("prefetch.global.L2 [%0];" ::"l"(pf));
+    }
     asm volatile("griddepcontrol.wait;" ::: "memory");
     dec_probe(a, 0);
     // Loads whose addresses do not depend on the routing are issued first and consumed after

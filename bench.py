@@ -17,13 +17,19 @@ in and out) / step time.
   e2e       the same steps through coli_cuda_moe_layer with HOST buffers: every
             layer call copies its input rows and router logits to the device
             and its output rows back.
-  roofline  for the dominant kernel (the streaming dequant GEMV): algorithmic
+  roofline  for the dominant kernel: the streaming dequant GEMV (algorithmic
             weight bytes of its launches / their summed event-bracketed time,
-            against the measured copy bandwidth in MEASURED_PEAKS.json.
+            against the measured copy bandwidth in MEASURED_PEAKS.json) or, for
+            calls with many rows per expert, the tcgen05 grouped GEMM
+            (algorithmic FLOPs / time against the measured bf16 rate).
   cpu_baseline  the reference's own CPU kernels (oracle/_ref, c/quant.h compiled
             unchanged) on a bounded sample of the same steps, rank 0 only.
 
 `--impl reference` times that CPU implementation alone with the same metric.
+The distinct-expert counts of the byte accounting come from the device's own
+routing; the CPU oracle is used by the CPU legs only.
+Other workloads: `c3_decode` / `c4_decode` (DeepSeek-V3-style layer, MXFP4 /
+int4), `c5_ep` (expert-parallel layer over NCCL all-to-all, strong scaling).
 Multi-GPU (`--gpus N` under torchrun): the path has no exchange step at this
 configuration, so every rank decodes its own rows through its own replica
 (weak scaling); value = all ranks' bytes / max-over-ranks time.
@@ -210,14 +216,6 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def route_counts(oracle, cfg, logits, bias):
-    if cfg["gating"] == 0:
-        idx, _, _ = oracle.route_softmax(logits, cfg["K"], False)
-    else:
-        idx, _, _, _ = oracle.route_sigmoid(logits, bias, cfg["K"], 0.0, bool(cfg["norm_topk"]), ROUTED_SCALE)
-    return int(len(np.unique(idx)))
-
-
 ROUTED_SCALE = 2.5   # sigmoid-gated configurations (GLM / DeepSeek-V3 style)
 
 
@@ -374,9 +372,12 @@ def run_gpu_arm(args):
 
     xs = [W.activations(M, D, 100 + li + 1000 * rank) for li in range(L)]
     lgs = [W.router_logits(M, E, 200 + li + 1000 * rank) for li in range(L)]
-    from oracle.oracle import Oracle   # routing counts for the byte accounting only
-    orc = Oracle()
-    nus = [route_counts(orc, cfg, lgs[li], biases[li]) + (1 if cfg["shared"] else 0) for li in range(L)]
+    # distinct experts per layer call for the byte accounting, from the device's own routing
+    nus = []
+    for li in range(L):
+        _, ridx, _, rkeff = layers[li](xs[li], lgs[li])
+        live = np.concatenate([ridx[s, :rkeff[s]] for s in range(M)]) if M else np.zeros(0, np.int32)
+        nus.append(int(len(np.unique(live))) + (1 if cfg["shared"] else 0))
     eb = expert_bytes_device(cfg)
     act_bytes = 2 * M * D * 4
     step_bytes = sum(nu * eb + act_bytes for nu in nus)
@@ -472,7 +473,8 @@ def run_gpu_arm(args):
         try:
             if args.quick:
                 raise RuntimeError("skipped (--quick)")
-            from oracle.oracle import RefCpu
+            from oracle.oracle import Oracle, RefCpu
+            orc = Oracle()
             ref = RefCpu() if RefCpu.available() else None
             kind = "reference" if ref else "port"
             if ref is None:
@@ -588,15 +590,15 @@ def run_ep_arm(args):
     xs = [torch.from_numpy(W.activations(M, D, 500 + li)[rank * m:(rank + 1) * m].copy()).to(dev) for li in range(L)]
     lg_all = [W.router_logits(M, E, 600 + li, zipf=1.1) for li in range(L)]
     lgs = [torch.from_numpy(l[rank * m:(rank + 1) * m].copy()).to(dev) for l in lg_all]
-    # byte accounting from the routing of all rows (CPU oracle, accounting only)
-    from oracle.oracle import Oracle
-    orc = Oracle()
+    # byte accounting from the routing of all rows, done on this rank's GPU
     eb = expert_bytes_device(cfg)
     step_bytes = 0
     for li in range(L):
-        b = (np.random.default_rng(31 + li).standard_normal(E) * 0.01).astype(np.float32)
-        idx, _, _, _ = orc.route_sigmoid(lg_all[li], b, K, 0.0, True, ROUTED_SCALE)
-        step_bytes += (len(np.unique(idx)) + world) * eb + 2 * M * D * 4
+        lay = layers[li]
+        lay.logits = torch.from_numpy(lg_all[li]).to(dev)
+        ridx, _, rkeff = lay.route(torch.empty((M, 1), device=dev))
+        live = ridx[torch.arange(K, device=dev).unsqueeze(0) < rkeff.unsqueeze(1)]
+        step_bytes += (int(torch.unique(live).numel()) + world) * eb + 2 * M * D * 4
     torch.cuda.synchronize()
 
     def step():

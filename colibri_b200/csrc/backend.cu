@@ -847,25 +847,30 @@ static int group_tc_ok(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
 static int group_device_tc(DeviceCtx *c, ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
                            ColiCudaTensor *const *downs, const int *rows, int count, int D, int I,
                            int total, float *y_dev, const float *x_dev, int bcast, const int *rowsrc = nullptr) {
-    std::vector<int> meta;            // [rowsrc | row_pass | row_n | pass_row0 | pass_npad | lo flags of x | lo flags of h]
-    std::vector<int> row_pass(total), row_n(total), pass_row0, pass_npad, pass_rows, pass_pos0, pass_expert;
+    // device tables: [rowsrc (total) | per pass: row0, npad, pos0, rows, lo flag of x, lo flag of h | per row group: pass, rg]
+    std::vector<int> pass_row0, pass_npad, pass_rows, pass_pos0, pass_expert, grp_pass, grp_rg;
     int off = 0, padded = 0;
     for (int e = 0; e < count; e++) {
         const int re = rows ? rows[e] : 1;
         for (int r0 = 0; r0 < re; r0 += TC_ROWS) {
             const int nr = re - r0 < TC_ROWS ? re - r0 : TC_ROWS, npad = (nr + 15) & ~15;
             const int p = (int)pass_row0.size();
-            for (int r = 0; r < nr; r++) { row_pass[off + r0 + r] = p; row_n[off + r0 + r] = r; }
             pass_row0.push_back(padded); pass_npad.push_back(npad); pass_rows.push_back(nr);
             pass_pos0.push_back(off + r0); pass_expert.push_back(e);
+            for (int g = 0; g < npad / 8; g++) { grp_pass.push_back(p); grp_rg.push_back(g); }
             padded += npad;
         }
         off += re;
     }
-    const int npass = (int)pass_row0.size();
-    meta.resize((size_t)3 * total + 4 * npass, 0);
-    for (int r = 0; r < total; r++) { meta[r] = rowsrc ? rowsrc[r] : bcast ? 0 : r; meta[total + r] = row_pass[r]; meta[2 * total + r] = row_n[r]; }
-    for (int p = 0; p < npass; p++) { meta[3 * total + p] = pass_row0[p]; meta[3 * total + npass + p] = pass_npad[p]; }
+    const int npass = (int)pass_row0.size(), ngrp = (int)grp_pass.size();
+    std::vector<int> meta((size_t)total + 6 * npass + 2 * ngrp, 0);
+    for (int r = 0; r < total; r++) meta[r] = rowsrc ? rowsrc[r] : bcast ? 0 : r;
+    int *mp = meta.data() + total;
+    for (int p = 0; p < npass; p++) {
+        mp[p] = pass_row0[p]; mp[npass + p] = pass_npad[p]; mp[2 * npass + p] = pass_pos0[p]; mp[3 * npass + p] = pass_rows[p];
+    }
+    int *mg = mp + 6 * npass;
+    for (int g = 0; g < ngrp; g++) { mg[g] = grp_pass[g]; mg[ngrp + g] = grp_rg[g]; }
     if (!reserve(c, &c->misc, meta.size() * sizeof(int)) ||
         !reserve(c, &c->bq, (size_t)padded * D * 2 * sizeof(__half)) ||
         !reserve(c, &c->bs, (size_t)total * sizeof(float)) ||
@@ -874,14 +879,16 @@ static int group_device_tc(DeviceCtx *c, ColiCudaTensor *const *gates, ColiCudaT
         !reserve(c, &c->hq, (size_t)padded * I * 2 * sizeof(__half)) ||
         !reserve(c, &c->hs, (size_t)total * sizeof(float))) return 0;
     if (!cuda_ok(cudaMemcpyAsync(c->misc.p, meta.data(), meta.size() * sizeof(int), cudaMemcpyHostToDevice, c->stream), "row table upload")) return 0;
-    const int *d_meta = static_cast<const int *>(c->misc.p);
-    const int *d_rowsrc = d_meta, *d_row_pass = d_meta + total, *d_row_n = d_meta + 2 * total;
-    const int *d_pass_row0 = d_meta + 3 * total, *d_pass_npad = d_pass_row0 + npass;
-    int *d_lo_x = static_cast<int *>(c->misc.p) + 3 * total + 2 * npass, *d_lo_h = d_lo_x + npass;
+    int *d_meta = static_cast<int *>(c->misc.p);
+    const int *d_rowsrc = d_meta;
+    const int *d_pass_row0 = d_meta + total, *d_pass_npad = d_pass_row0 + npass, *d_pass_pos0 = d_pass_npad + npass,
+              *d_pass_rows = d_pass_pos0 + npass;
+    int *d_lo_x = d_meta + total + 4 * npass, *d_lo_h = d_lo_x + npass;
+    const int *d_grp_pass = d_meta + total + 6 * npass, *d_grp_rg = d_grp_pass + ngrp;
     __half *bq = (__half *)c->bq.p, *hq = (__half *)c->hq.p;
     float *binv = (float *)c->bs.p, *hinv = (float *)c->hs.p, *G = (float *)c->pg.p, *U = (float *)c->pu.p;
-    k_prep_umma<<<(total * 32 + 255) / 256, 256, 0, c->stream>>>(bq, binv, x_dev, nullptr, d_rowsrc, d_row_pass, d_row_n,
-                                                                 d_pass_row0, d_pass_npad, d_lo_x, total, D);
+    k_prep_umma<<<ngrp, 256, 0, c->stream>>>(bq, binv, x_dev, nullptr, d_rowsrc, d_grp_pass, d_grp_rg, d_pass_row0,
+                                             d_pass_npad, d_pass_pos0, d_pass_rows, d_lo_x, D);
     c->last_launches++;
     TcSegs t1, t2;
     for (int p = 0; p < npass; p++) {
@@ -893,8 +900,8 @@ static int group_device_tc(DeviceCtx *c, ColiCudaTensor *const *gates, ColiCudaT
         add_tc_seg(&t2, downs[e], y_dev, hp, hinv + pass_pos0[p], d_lo_h + p, pass_rows[p], pass_npad[p], pass_pos0[p]);
     }
     if (!run_tc_segs(c, &t1, &c->segs1)) return 0;
-    k_prep_umma<<<(total * 32 + 255) / 256, 256, 0, c->stream>>>(hq, hinv, G, U, nullptr, d_row_pass, d_row_n,
-                                                                 d_pass_row0, d_pass_npad, d_lo_h, total, I);
+    k_prep_umma<<<ngrp, 256, 0, c->stream>>>(hq, hinv, G, U, nullptr, d_grp_pass, d_grp_rg, d_pass_row0, d_pass_npad,
+                                             d_pass_pos0, d_pass_rows, d_lo_h, I);
     c->last_launches++;
     if (!run_tc_segs(c, &t2, &c->segs2)) return 0;
     return cuda_ok(cudaGetLastError(), "expert group launch");

@@ -147,11 +147,11 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
         : "memory");
 }
 
-// Activation preparation for the tensor-core path: one warp per row of the call.
+// Activation preparation for the tensor-core path.
 // Row n of pass p lives in the pass's tiles: halfs at
 //   base_p + ((kb*2 + term)*4 + kc) * npad*8 + (n/8)*64 + (n%8)*8 + (k%8),   kb = k/32, kc = (k%32)/8
-// with base_p = 2*K*pass_row0[p] (pass_row0 = padded rows of all earlier passes). Rows
-// n >= nrows of a pass are never written. The row scale is taken over the whole row;
+// with base_p = 2*K*pass_row0[p] (pass_row0 = padded rows of all earlier passes). The
+// row scale is taken over the whole row;
 // 2^-r goes to binv. rowsrc: optional gather (row -> source row of x). u: when set, the
 // row is silu(x)*u (the SwiGLU of complete gate/up sums) instead of x.
 __device__ __forceinline__ float4 tc_row_vals(const float *xr, const float *ur, int k) {
@@ -163,45 +163,69 @@ __device__ __forceinline__ float4 tc_row_vals(const float *xr, const float *ur, 
     }
     return v;
 }
-__global__ void k_prep_umma(__half *__restrict__ bq, float *__restrict__ binv, const float *__restrict__ x,
-                            const float *__restrict__ u, const int *__restrict__ rowsrc,
-                            const int *__restrict__ row_pass, const int *__restrict__ row_n,
-                            const int *__restrict__ pass_row0, const int *__restrict__ pass_npad,
-                            int *__restrict__ pass_lo, int nrows_total, int K) {
-    const int wid = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-    if (wid >= nrows_total) return;
-    const int src = rowsrc ? rowsrc[wid] : wid;
-    const float *xr = x + (size_t)src * K;
-    const float *ur = u ? u + (size_t)src * K : nullptr;
-    float m = 0.f;
-    for (int k = lane * 4; k < K; k += 128) {
-        float4 v = tc_row_vals(xr, ur, k);
-        m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
-    }
-    m = warp_max(m);
-    const float s = block_scale_from_max(m);
-    if (lane == 0) binv[wid] = 1.f / s;
-    const int p = row_pass[wid], n = row_n[wid], npad = pass_npad[p];
-    __half *base = bq + (size_t)2 * K * pass_row0[p];
-    unsigned lo_bits = 0;
-    for (int k = lane * 4; k < K; k += 128) {
-        float4 v = tc_row_vals(xr, ur, k);
-        float xv[4] = {v.x * s, v.y * s, v.z * s, v.w * s};
-        __half hi[4], lo[4];
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            hi[i] = __float2half_rn(xv[i]); lo[i] = __float2half_rn(xv[i] - __half2float(hi[i]));
-            lo_bits |= __half_as_ushort(lo[i]) & 0x7FFFu;
+// One block of 8 warps per group of 8 consecutive rows of a pass (one row of core matrices).
+// Phase 1: warp w finds the scale of row 8*rg + w. Phase 2: the block writes the group's
+// 16-byte pieces, 64 per 32-column block ([term][chunk][row]), four blocks per iteration, so
+// that 8 consecutive threads store 128 contiguous bytes. Rows beyond the pass's row count
+// (up to its padded count) are written as zeros.
+__global__ void __launch_bounds__(256) k_prep_umma(__half *__restrict__ bq, float *__restrict__ binv,
+                            const float *__restrict__ x, const float *__restrict__ u,
+                            const int *__restrict__ rowsrc, const int *__restrict__ grp_pass,
+                            const int *__restrict__ grp_rg, const int *__restrict__ pass_row0,
+                            const int *__restrict__ pass_npad, const int *__restrict__ pass_pos0,
+                            const int *__restrict__ pass_rows, int *__restrict__ pass_lo, int K) {
+    __shared__ float s_scale[8];
+    __shared__ int s_src[8];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int p = grp_pass[blockIdx.x], rg = grp_rg[blockIdx.x];
+    const int npad = pass_npad[p], nrows = pass_rows[p], pos0 = pass_pos0[p];
+    {
+        const int n = rg * 8 + warp;
+        float s = 0.f;
+        int src = -1;
+        if (n < nrows) {
+            const int wid = pos0 + n;
+            src = rowsrc ? rowsrc[wid] : wid;
+            const float *xr = x + (size_t)src * K;
+            const float *ur = u ? u + (size_t)src * K : nullptr;
+            float m = 0.f;
+            for (int k = lane * 4; k < K; k += 128) {
+                float4 v = tc_row_vals(xr, ur, k);
+                m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+            }
+            m = warp_max(m);
+            s = block_scale_from_max(m);
+            if (lane == 0) binv[wid] = 1.f / s;
         }
-        const int kb = k >> 5, kc = (k & 31) >> 3, ki = k & 7;
-        size_t o_hi = ((size_t)((kb * 2 + 0) * 4 + kc) * npad) * 8 + (size_t)(n >> 3) * 64 + (n & 7) * 8 + ki;
-        size_t o_lo = ((size_t)((kb * 2 + 1) * 4 + kc) * npad) * 8 + (size_t)(n >> 3) * 64 + (n & 7) * 8 + ki;
-        *reinterpret_cast<uint2 *>(base + o_hi) = make_uint2(
-            (uint32_t)__half_as_ushort(hi[0]) | ((uint32_t)__half_as_ushort(hi[1]) << 16),
-            (uint32_t)__half_as_ushort(hi[2]) | ((uint32_t)__half_as_ushort(hi[3]) << 16));
-        *reinterpret_cast<uint2 *>(base + o_lo) = make_uint2(
-            (uint32_t)__half_as_ushort(lo[0]) | ((uint32_t)__half_as_ushort(lo[1]) << 16),
-            (uint32_t)__half_as_ushort(lo[2]) | ((uint32_t)__half_as_ushort(lo[3]) << 16));
+        if (lane == 0) { s_scale[warp] = s; s_src[warp] = src; }
+    }
+    __syncthreads();
+    const int piece = threadIdx.x & 63, kb_in = threadIdx.x >> 6;
+    const int term = piece >> 5, kc = (piece >> 3) & 3, r = piece & 7;
+    const int src = s_src[r];
+    const float s = s_scale[r];
+    const float *xr = x + (size_t)(src < 0 ? 0 : src) * K;
+    const float *ur = u ? u + (size_t)(src < 0 ? 0 : src) * K : nullptr;
+    __half *base = bq + (size_t)2 * K * pass_row0[p] + (size_t)rg * 64 + r * 8;
+    unsigned lo_bits = 0;
+    for (int kb = kb_in; kb < K / 32; kb += 4) {
+        uint4 outv = make_uint4(0, 0, 0, 0);
+        if (src >= 0) {
+            const int k0 = kb * 32 + kc * 8;
+            const float4 a = tc_row_vals(xr, ur, k0), b = tc_row_vals(xr, ur, k0 + 4);
+            const float xv[8] = {a.x * s, a.y * s, a.z * s, a.w * s, b.x * s, b.y * s, b.z * s, b.w * s};
+            unsigned short h[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const __half hi = __float2half_rn(xv[i]);
+                const __half lo = __float2half_rn(xv[i] - __half2float(hi));
+                h[i] = __half_as_ushort(term ? lo : hi);
+                if (term) lo_bits |= h[i] & 0x7FFFu;
+            }
+            outv = make_uint4((uint32_t)h[0] | ((uint32_t)h[1] << 16), (uint32_t)h[2] | ((uint32_t)h[3] << 16),
+                              (uint32_t)h[4] | ((uint32_t)h[5] << 16), (uint32_t)h[6] | ((uint32_t)h[7] << 16));
+        }
+        *reinterpret_cast<uint4 *>(base + ((size_t)((kb * 2 + term) * 4 + kc) * npad) * 8) = outv;
     }
     // activations that are exact in fp16 after the row scale (bf16-valued inputs, for one)
     // leave every lo term zero: the GEMM then skips the lo MMAs and the lo half of the copies

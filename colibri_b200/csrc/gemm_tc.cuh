@@ -44,8 +44,7 @@
 // queue behind the bulk copies.
 //
 // Pipeline (one CTA per SM, 19 warps, every hand-over through an mbarrier):
-//   warp 0       weight producer: bulk copies of the raw packed chunks (8 tiles of 32
-//                features x 128 columns per stage) into a ring
+//   warp 0       owns the TMEM allocation
 //   warp 1       activation producer: one bulk copy per 32-column block (both terms,
 //                contiguous in global memory) into a ring of 16 KB stages
 //   warp 2       one thread issues the MMAs of a 64-column block (descriptor high words
@@ -53,9 +52,12 @@
 //                that frees the block's W stage and its two activation stages (a commit
 //                costs the issuing thread about 200 cycles, an MMA about 30); after the
 //                last block of a partial sum it commits to the accumulator barrier
-//   warps 3-10   decode, one warp per packed tile: raw chunk -> registers -> fp16 W tile(s)
-//                of a 2-stage ring (one 16-byte shared store per 8 weights), fence to the
-//                async proxy, one arrival per warp
+//   warps 3-10   decode, one warp per packed tile: packed words straight from global memory
+//                into registers (128-bit loads one 128-column block ahead, an L2 bulk
+//                prefetch four more blocks ahead: staging the raw chunks in shared memory
+//                cost a sixth of the shared-memory bandwidth, which bounds this kernel) ->
+//                fp16 W tile(s) of a 2-stage ring (one 16-byte shared store per 8 weights),
+//                fence to the async proxy, one arrival per warp
 //   warps 11-18  read back a finished partial sum (tcgen05.ld, lane = row; two warps per
 //                TMEM lane quarter, half of the feature columns each) and add it to the
 //                running sum, or scale and store the total after the last one
@@ -82,11 +84,9 @@
 __host__ __device__ constexpr int tc_chunk_bytes(int mode) {
     return CODE_BYTES + (mode == SC_H16 ? 256 : mode == SC_F32 ? 512 : mode == SC_MX ? 128 : 0);
 }
-__host__ __device__ constexpr int tc_nraw(int mode) { return mode == SC_H16 ? 1 : 3; }      // raw ring depth (what fits)
-__host__ __device__ constexpr int tc_raw_stage_bytes(int mode) { return 8 * tc_chunk_bytes(mode); }
 __host__ __device__ constexpr int tc_w_stage_bytes(int mode) { return (mode == SC_H16 ? 2 : 1) * TC_FEAT * TC_KB * 2; }
 __host__ __device__ constexpr int tc_smem_total(int mode) {
-    return TC_NW * tc_w_stage_bytes(mode) + TC_NX * TC_X_STAGE + tc_nraw(mode) * tc_raw_stage_bytes(mode) + 1024;
+    return TC_NW * tc_w_stage_bytes(mode) + TC_NX * TC_X_STAGE + 1024;
 }
 
 struct TcSeg {
@@ -232,9 +232,7 @@ __global__ void __launch_bounds__(256) k_prep_umma(__half *__restrict__ bq, floa
     if (__any_sync(0xffffffffu, lo_bits != 0) && lane == 0) atomicOr(&pass_lo[p], 1);
 }
 
-#define TC_MAX_RING 6
 struct TcBars {
-    unsigned long long raw_full[4], raw_empty[4];
     unsigned long long x_full[TC_NX];
     unsigned long long w_full[TC_NW];
     unsigned long long step_free[TC_NW];     // the MMAs of a 64-column step are done: its W stage and X stages are free
@@ -274,24 +272,21 @@ k_expert_gemm_tc(const TcSeg *__restrict__ segs, const TcCtl *__restrict__ ctl, 
     constexpr int CH = tc_chunk_bytes(MODE);
     constexpr bool TWO_W = (MODE == SC_H16);             // weights need a hi and a lo term
     constexpr int W_BYTES = TC_FEAT * TC_KB * 2;         // 32 KB per term
-    constexpr int RAW_STAGE = tc_raw_stage_bytes(MODE);
     constexpr int W_STAGE = tc_w_stage_bytes(MODE);
-    constexpr int NRAW = tc_nraw(MODE), NX = TC_NX;
+    constexpr int NX = TC_NX;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ TcBars s_bars;
     __shared__ uint32_t s_tmem;
     __shared__ int s_abort;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t sbase = (smem_u32(smem) + 1023u) & ~1023u;
-    const uint32_t w0 = sbase, x0 = w0 + TC_NW * W_STAGE, raw0 = x0 + NX * TC_X_STAGE;
-    const uint32_t bar_raw_full = smem_u32(s_bars.raw_full), bar_raw_empty = smem_u32(s_bars.raw_empty);
+    const uint32_t w0 = sbase, x0 = w0 + TC_NW * W_STAGE;
     const uint32_t bar_x_full = smem_u32(s_bars.x_full), bar_w_full = smem_u32(s_bars.w_full);
     const uint32_t bar_step_free = smem_u32(s_bars.step_free);
     const uint32_t bar_acc_full = smem_u32(s_bars.acc_full), bar_acc_empty = smem_u32(s_bars.acc_empty);
     const uint32_t bar_drain = smem_u32(&s_bars.drain);
     volatile int *abort_flag = &s_abort;
     if (tid == 0) {
-        for (int i = 0; i < NRAW; i++) { mbar_init(bar_raw_full + i * 8, 1); mbar_init(bar_raw_empty + i * 8, TC_DEC_WARPS); }
         for (int i = 0; i < NX; i++) mbar_init(bar_x_full + i * 8, 1);
         for (int i = 0; i < TC_NW; i++) { mbar_init(bar_w_full + i * 8, TC_DEC_WARPS); mbar_init(bar_step_free + i * 8, 1); }
         mbar_init(bar_acc_full, 1); mbar_init(bar_acc_empty, TC_EPI_WARPS);
@@ -311,28 +306,7 @@ k_expert_gemm_tc(const TcSeg *__restrict__ segs, const TcCtl *__restrict__ ctl, 
     const int ntask = ctl->ntask, nseg = ctl->nseg;
 
     if (warp == 0) {
-        // ---- weight producer ------------------------------------------------------------------
-        if (lane == 0) {
-            TcRing r;
-            int issued = 0;
-            bool ok = true;
-            for (int task = blockIdx.x; task < ntask && ok; task += gridDim.x) {
-                const TcSeg *sg = tc_find_seg(segs, nseg, task);
-                const int ft = task - sg->task0, nkb128 = sg->nkb64 >> 1;
-                const int ntile = min(8, sg->O / TILE_ROWS - ft * 8);       // packed 32-feature tiles of this task
-                const uint8_t *wbase = sg->w + (size_t)(ft * 8) * nkb128 * CH;
-                for (int kb = 0; kb < nkb128; kb++, issued++) {
-                    if (r.wrapped && !tc_wait(bar_raw_empty + r.s * 8, r.par ^ 1, abort_flag)) { ok = false; break; }
-                    mbar_expect_tx(bar_raw_full + r.s * 8, ntile * CH);
-                    for (int t = 0; t < ntile; t++)
-                        bulk_g2s(raw0 + r.s * RAW_STAGE + t * CH, wbase + ((size_t)t * nkb128 + kb) * CH, CH, bar_raw_full + r.s * 8);
-                    r.next(NRAW);
-                }
-            }
-            if (!ok)      // copies still in flight must land before the CTA's shared memory is given up
-                for (int k = issued > NRAW ? issued - NRAW : 0; k < issued; k++)
-                    mbar_wait_bounded(bar_raw_full + (k % NRAW) * 8, (k / NRAW) & 1);
-        }
+        // warp 0 only owns the TMEM allocation (made above, freed below)
     } else if (warp == 1) {
         // ---- activation producer --------------------------------------------------------------
         if (lane == 0) {
@@ -423,8 +397,47 @@ k_expert_gemm_tc(const TcSeg *__restrict__ segs, const TcCtl *__restrict__ ctl, 
         // free of bank conflicts.
         const int ft = lane & 3, fg = (lane & 4) ? (((lane >> 3) * 2 + 5) & 7) : (lane >> 3) * 2;
         const int fl = fg * 4 + ft;
-        TcRing rr, rw;
+        TcRing rw;
         bool ok = true;
+        // This warp's tile stream, block by block across the CTA's tasks: `ld` runs one 128-column
+        // block ahead of the decode (registers), `pf` three more ahead (L2 prefetch, no registers).
+        struct WIt { int task, kb, nkb128; const uint8_t *p; bool live; };
+        auto it_init = [&](WIt &it, int task) {
+            it.task = task; it.kb = 0; it.nkb128 = 1; it.p = nullptr; it.live = false;
+            if (task < ntask) {
+                const TcSeg *g = tc_find_seg(segs, nseg, task);
+                const int ft8 = (task - g->task0) * 8;
+                it.nkb128 = g->nkb64 >> 1;
+                it.live = t8 < g->O / TILE_ROWS - ft8;
+                it.p = g->w + ((size_t)(ft8 + t8) * it.nkb128) * CH;
+            }
+        };
+        auto it_next = [&](WIt &it) { if (++it.kb == it.nkb128) it_init(it, it.task + gridDim.x); else it.p += CH; };
+        auto ld_block = [&](const WIt &it, uint4 (&w)[4], uint2 (&sc)[4]) {
+#pragma unroll
+            for (int q = 0; q < 4; q++) { w[q] = make_uint4(0, 0, 0, 0); sc[q] = make_uint2(0, 0); }
+            if (it.task < ntask && it.live) {
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    w[q] = ldg_nc128(it.p + q * 512 + fl * 16);
+                    const int slot = (((q >> 1) * 8 + fg) * 2 + (q & 1)) * 4;
+                    if (MODE == SC_H16)
+                        asm volatile("ld.global.nc.v2.u32 {%0,%1}, [%2];" : "=r"(sc[q].x), "=r"(sc[q].y) : "l"(it.p + CODE_BYTES + slot * 2));
+                    else if (MODE == SC_MX)
+                        asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(sc[q].x) : "l"(it.p + CODE_BYTES + slot));
+                }
+            }
+        };
+        WIt ld, pf;
+        it_init(ld, blockIdx.x);
+        it_init(pf, blockIdx.x);
+        for (int i = 0; i < 4 && pf.task < ntask; i++) {
+            if (pf.live && lane == 0) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(pf.p), "r"((uint32_t)CH) : "memory");
+            it_next(pf);
+        }
+        uint4 nw[4];
+        uint2 nsc[4];
+        ld_block(ld, nw, nsc);
         for (int task = blockIdx.x; task < ntask && ok; task += gridDim.x) {
             const TcSeg *sg = tc_find_seg(segs, nseg, task);
             const int nkb128 = sg->nkb64 >> 1, shift = sg->shift;
@@ -434,25 +447,16 @@ k_expert_gemm_tc(const TcSeg *__restrict__ segs, const TcCtl *__restrict__ ctl, 
             const __half2 f_a = __half2half2(__ushort_as_half((unsigned short)((15 + sh_a) << 10)));
             const __half2 f_b = __half2half2(__ushort_as_half((unsigned short)((15 + sh_b) << 10)));
             for (int kb = 0; kb < nkb128 && ok; kb++) {
-                if (!tc_wait(bar_raw_full + rr.s * 8, rr.par, abort_flag)) { ok = false; break; }
-                const uint32_t rbase = raw0 + rr.s * RAW_STAGE + t8 * CH;
                 uint4 w[4];
                 uint2 sc[4];
 #pragma unroll
-                for (int q = 0; q < 4; q++) { w[q] = make_uint4(0, 0, 0, 0); sc[q] = make_uint2(0, 0); }
-                if (live) {
-#pragma unroll
-                    for (int q = 0; q < 4; q++) {
-                        const int j = q;
-                        w[q] = lds128(rbase + j * 512 + fl * 16);
-                        const int slot = (((j >> 1) * 8 + fg) * 2 + (j & 1)) * 4;
-                        if (MODE == SC_H16) sc[q] = lds64(rbase + CODE_BYTES + slot * 2);
-                        else if (MODE == SC_MX) { uint32_t v; asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(rbase + CODE_BYTES + slot)); sc[q] = make_uint2(v, 0); }
-                    }
+                for (int q = 0; q < 4; q++) { w[q] = nw[q]; sc[q] = nsc[q]; }
+                it_next(ld);
+                ld_block(ld, nw, nsc);               // the next block, consumed one iteration later
+                if (pf.task < ntask) {
+                    if (pf.live && lane == 0) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(pf.p), "r"((uint32_t)CH) : "memory");
+                    it_next(pf);
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_raw_empty + rr.s * 8);
-                rr.next(NRAW);
 #pragma unroll
                 for (int half = 0; half < 2; half++) {
                     if (rw.wrapped && !tc_wait(bar_step_free + rw.s * 8, rw.par ^ 1, abort_flag)) { ok = false; break; }

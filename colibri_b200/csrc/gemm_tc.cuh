@@ -72,8 +72,10 @@
 #define TC_FEAT 256         // output features per task (N of the MMA)
 #define TC_KB 64            // columns per W stage
 #define TC_XKB 32           // columns per activation stage
-#define TC_NW 2             // W ring depth = steps in flight; the activation ring holds the same two steps
-#define TC_NX 4             // activation stages (32 columns each)
+#define TC_NW_MAX 3
+// W ring depth = 64-column steps in flight (what fits beside the hi/lo tiles of grouped int4);
+// the activation ring holds the same steps, two 32-column stages each
+__host__ __device__ constexpr int tc_nw(int mode) { return mode == SC_H16 ? 2 : 3; }
 #define TC_FLUSH_KB 8        // 64-column blocks per partial sum (see "Accumulation" above)
 #define TC_DEC_WARPS 8
 #define TC_EPI_WARPS 8
@@ -86,7 +88,7 @@ __host__ __device__ constexpr int tc_chunk_bytes(int mode) {
 }
 __host__ __device__ constexpr int tc_w_stage_bytes(int mode) { return (mode == SC_H16 ? 2 : 1) * TC_FEAT * TC_KB * 2; }
 __host__ __device__ constexpr int tc_smem_total(int mode) {
-    return TC_NW * tc_w_stage_bytes(mode) + TC_NX * TC_X_STAGE + 1024;
+    return tc_nw(mode) * (tc_w_stage_bytes(mode) + 2 * TC_X_STAGE) + 1024;
 }
 
 struct TcSeg {
@@ -233,9 +235,9 @@ __global__ void __launch_bounds__(256) k_prep_umma(__half *__restrict__ bq, floa
 }
 
 struct TcBars {
-    unsigned long long x_full[TC_NX];
-    unsigned long long w_full[TC_NW];
-    unsigned long long step_free[TC_NW];     // the MMAs of a 64-column step are done: its W stage and X stages are free
+    unsigned long long x_full[2 * TC_NW_MAX];
+    unsigned long long w_full[TC_NW_MAX];
+    unsigned long long step_free[TC_NW_MAX];     // the MMAs of a 64-column step are done: its W stage and X stages are free
     unsigned long long acc_full[2], acc_empty[2];
     unsigned long long drain;
 };
@@ -273,7 +275,7 @@ k_expert_gemm_tc(const TcSeg *__restrict__ segs, const TcCtl *__restrict__ ctl, 
     constexpr bool TWO_W = (MODE == SC_H16);             // weights need a hi and a lo term
     constexpr int W_BYTES = TC_FEAT * TC_KB * 2;         // 32 KB per term
     constexpr int W_STAGE = tc_w_stage_bytes(MODE);
-    constexpr int NX = TC_NX;
+    constexpr int TC_NW = tc_nw(MODE), NX = 2 * TC_NW;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ TcBars s_bars;
     __shared__ uint32_t s_tmem;

@@ -149,6 +149,29 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
         : "memory");
 }
 
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+
 // Activation preparation for the tensor-core path.
 // Row n of pass p lives in the pass's tiles: halfs at
 //   base_p + ((kb*2 + term)*4 + kc) * npad*8 + (n/8)*64 + (n%8)*8 + (k%8),   kb = k/32, kc = (k%32)/8
@@ -535,22 +558,22 @@ k_expert_gemm_tc(const TcSeg *__restrict__ segs, const TcCtl *__restrict__ ctl, 
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 if (live) {
                     const bool last = ch == nchunk - 1;
-                    for (int c0 = cbeg; c0 < cend; c0 += 16) {
-                        uint32_t pr[16], rr[16];
+                    for (int c0 = cbeg; c0 < cend; c0 += 32) {      // the halves are 64 or 128 columns wide
+                        uint32_t pr[32], rr[32];
                         const uint32_t tp = tmem + ((uint32_t)(q4 * 32) << 16) + (uint32_t)c0;   // partial sum
                         const uint32_t tr = tp + 256u;                                              // running sum
-                        tmem_ld16(tp, pr);
-                        if (ch > 0) tmem_ld16(tr, rr);
+                        tmem_ld32(tp, pr);
+                        if (ch > 0) tmem_ld32(tr, rr);
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                         if (ch > 0) {
 #pragma unroll
-                            for (int i = 0; i < 16; i++) pr[i] = __float_as_uint(__uint_as_float(pr[i]) + __uint_as_float(rr[i]));
+                            for (int i = 0; i < 32; i++) pr[i] = __float_as_uint(__uint_as_float(pr[i]) + __uint_as_float(rr[i]));
                         }
                         if (!last) {
-                            tmem_st16(tr, pr);
+                            tmem_st32(tr, pr);
                         } else if (n < nrows) {
 #pragma unroll
-                            for (int i = 0; i < 16; i += 4) {
+                            for (int i = 0; i < 32; i += 4) {
                                 float4 o4;
                                 o4.x = __uint_as_float(pr[i]) * bi * fs; o4.y = __uint_as_float(pr[i + 1]) * bi * fs;
                                 o4.z = __uint_as_float(pr[i + 2]) * bi * fs; o4.w = __uint_as_float(pr[i + 3]) * bi * fs;

@@ -690,13 +690,103 @@ def run_ep_arm(args):
         dist.destroy_process_group()
 
 
+# ---------------------------------------------------------------------------
+# batched multi-token decode through a 4-layer stack (configuration 4)
+# ---------------------------------------------------------------------------
+def run_stack_arm(args):
+    """Configuration 4: K candidate tokens per step (K = --M, default 8) through 4 MoE layers of
+    the DeepSeek-V3-style shape with int4 g32 experts, residual resident on the device
+    (rmsnorm, device router, fused layer kernel, residual add), f32 head over a 129280-entry
+    vocabulary, greedy pick on the device; token ids uniform from seed 1. value = algorithmic
+    bytes (distinct experts of every layer call + the head + activations) / step time, the step
+    timed end to end on the host (embedding gather and upload in, K picks out)."""
+    import torch
+    from colibri_b200.backend import Backend, MoeLayer
+    from colibri_b200.stack import MoeStack
+    cfg = dict(W.CONFIGS["c4"])
+    D, I, E, Kt, vocab = cfg["D"], cfg["I"], cfg["E"], cfg["K"], 129280
+    K = args.M if args.M > 1 else 8
+    NL = 4
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    be = Backend()
+    if be.init_devices((0,)) != 1:
+        raise RuntimeError("coli_cuda_init failed: the CUDA backend is required (no CPU fallback)")
+    up = lambda t: be.upload(t.w, t.s, t.fmt, t.I, t.O, 0, t.gs)
+    rng = np.random.default_rng(9)
+    lays, handles = [], []
+    for li in range(NL):
+        g, u, d = gen_layer_host(torch, cfg, 500 + li, dev)
+        sg, su, sd = gen_layer_host(torch, cfg, 900 + li, dev, n_experts=1)
+        hg, hu, hd = [up(t) for t in g], [up(t) for t in u], [up(t) for t in d]
+        sh = (up(sg[0]), up(su[0]), up(sd[0]))
+        if not all(hg + hu + hd + list(sh)):
+            raise RuntimeError("tensor upload failed")
+        rw = (rng.standard_normal((E, D), dtype=np.float32) * np.float32(0.02)).astype(np.float32)
+        rb = (rng.standard_normal(E) * 0.01).astype(np.float32)
+        lays.append(MoeLayer(be, D, I, E, Kt, hg, hu, hd, 1, 1, ROUTED_SCALE, 0.0, router_w=rw, router_bias=rb,
+                             shared=sh, max_rows=8))
+        handles += hg + hu + hd + list(sh)
+        del g, u, d
+    gen = torch.Generator(device=dev); gen.manual_seed(77)
+    lm = (torch.randn((vocab, D), generator=gen, device=dev) * 0.02).cpu().numpy()
+    embed = (torch.randn((vocab, D), generator=gen, device=dev) * 0.5).cpu().numpy()
+    lm_h = be.upload(lm, None, 0, D, vocab, 0, 0)
+    ones = np.ones(D, np.float32)
+    st = MoeStack(be, 0, D, vocab, embed, lays, [ones] * NL, ones, lm_h, 1e-5, max_rows=8)
+    ids_rng = np.random.default_rng(1)
+    ids = [ids_rng.integers(0, vocab, size=K) for _ in range(args.steps + max(args.warmup, 3))]
+    for i in range(max(args.warmup, 3)):
+        st.step(ids[i], want_logits=False)
+    sampler = ClockSampler(0)
+    sampler.start()
+    n0 = be.launch_total(0)
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        st.step(ids[max(args.warmup, 3) + i], want_logits=False)
+    dt = time.perf_counter() - t0
+    launches = int(be.launch_total(0) - n0)
+    clocks = sampler.stop()
+    if be.kernel_status(0) != 0:
+        raise RuntimeError("a kernel wait guard expired")
+    # distinct experts per layer call: about E*(1-(1-K/E)^rows) routed + 1 shared (uniform routing)
+    nu = E * (1.0 - (1.0 - Kt / E) ** K) + 1
+    eb = expert_bytes_device(cfg)
+    step_bytes = NL * nu * eb + vocab * D * 4 + 2 * K * D * 4
+    peak, which = measured_peaks()
+    value = step_bytes * args.steps / dt / 1e9
+    line = {
+        "metric": "moe_expert_ffn_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"c4_stack: {K} candidate tokens per step through {NL} MoE layers (D={D}, I={I}, E={E}+1 "
+                               f"shared, top-{Kt} sigmoid, int4 g32) + f32 head over {vocab} entries, residual on the device",
+                   "l2": "every step touches > 126 MB of weights", "bytes_per_step": step_bytes,
+                   "distinct_experts_per_layer_expected": nu, "tokens_per_s": K * args.steps / dt},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": K * D * 4, "d2h_bytes_per_step": K * 4,
+                "ms_per_step": dt / args.steps * 1e3},
+        "gpu_launches": launches, "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": value, "peak": peak, "unit": "GB/s", "frac": value / peak,
+                     "traffic": None, "kernel": "whole step (k_moe_decode x4, k_generic_matmul head)", "peak_source": which},
+        "cpu_baseline": None,
+    }
+    print(json.dumps(line), flush=True)
+    st.free()
+    for l in lays:
+        l.free()
+    for h in handles:
+        be.tensor_free(h)
+    be.tensor_free(lm_h)
+    be.shutdown()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2_decode", choices=["c2_decode", "c3_decode", "c4_decode", "c5_ep"],
+    ap.add_argument("--workload", default="c2_decode", choices=["c2_decode", "c3_decode", "c4_decode", "c5_ep", "c4_stack"],
                     help="layer shape and weight format (configuration 2, 3 or 4 of the benchmark)")
     ap.add_argument("--M", type=int, default=1, help="rows per layer call")
     ap.add_argument("--experts", type=int, default=0, help="override the expert count (profiling subsets)")
@@ -707,7 +797,13 @@ def main():
     ap.add_argument("--tc", type=int, default=1, choices=[0, 1, 2],
                     help="tensor-core path: 0 never, 1 when it pays (default), 2 whenever possible")
     args = ap.parse_args()
-    if args.workload == "c5_ep":
+    if args.workload == "c4_stack":
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the CPU run of this stack needs 25 GB of expert "
+                              "weights on the host; the reference CPU arm is timed on the default workload"}))
+        else:
+            run_stack_arm(args)
+    elif args.workload == "c5_ep":
         if args.impl == "reference":
             print(json.dumps({"impl": "reference", "unavailable": "the reference has no expert-parallel path "
                               "(no collective library); its CPU arm is timed on the default workload"}))

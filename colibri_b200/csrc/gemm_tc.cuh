@@ -56,7 +56,7 @@
 //                into registers (128-bit loads one 128-column block ahead, an L2 bulk
 //                prefetch four more blocks ahead: staging the raw chunks in shared memory
 //                cost a sixth of the shared-memory bandwidth, which bounds this kernel) ->
-//                fp16 W tile(s) of a 2-stage ring (one 16-byte shared store per 8 weights),
+//                fp16 W tile(s) of a 2- or 3-stage ring (one 16-byte shared store per 8 weights),
 //                fence to the async proxy, one arrival per warp
 //   warps 11-18  read back a finished partial sum (tcgen05.ld, lane = row; two warps per
 //                TMEM lane quarter, half of the feature columns each) and add it to the

@@ -107,7 +107,6 @@ ADDITIVE_ABI = [
     ("coli_cuda_set_fused_decode", None, [C.c_int]),
     ("coli_cuda_set_tensor_core", None, [C.c_int]),
     ("coli_cuda_launch_total", C.c_ulonglong, [C.c_int]),
-    ("coli_cuda_set_decode_probe", None, [_vp]),
     ("coli_cuda_set_kernel_events", None, [C.c_int]),
     ("coli_cuda_kernel_events", C.c_int, [C.c_int, _f32p, _i32p]),
     ("coli_cuda_stream", _vp, [C.c_int]),

@@ -11,6 +11,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <cmath>
+#include <atomic>
 #include <mutex>
 #include <vector>
 
@@ -43,8 +44,9 @@ struct DeviceCtx {
     size_t host_x_cap = 0, host_y_cap = 0;
     int group_pending = 0;
     int *status = nullptr;                    // pinned host int the kernels store into (kstat_set): sticky kernel status
-    unsigned long long *gridbar = nullptr;    // arrival counter of the fused decode kernel's grid barrier
-    unsigned long long epoch = 0;             // arrivals expected at that counter so far
+    unsigned int *dec_sync = nullptr;         // fused decode kernel: barrier arrivals, generation, output-slice tickets
+    unsigned long long *exp_tab_dev = nullptr; // global-memory copy of the 2^(i/32) table
+    const float *e4m3_lut_dev = nullptr;       // device address of the fmt 8 decode table
     int sticky_status = 0;                    // last non-zero kernel status seen by the host
     float last_ms = 0.f;
     int last_launches = 0;
@@ -60,7 +62,7 @@ static DeviceCtx g_ctx[COLI_CUDA_MAX_DEVICES];
 static int g_nctx = 0;
 static std::mutex g_mu;
 static int g_timing = 0;
-static long g_gpu_calls = 0;
+static std::atomic<long> g_gpu_calls{0};
 static thread_local int g_cur_dev = -1;
 
 static int cuda_ok(cudaError_t e, const char *what) {
@@ -111,7 +113,7 @@ static int fault_injected() {
 static size_t row_bytes(int fmt, int I) {
     switch (fmt) {
     case 0: return (size_t)I * 4;
-    case 1: return (size_t)I;
+    case 1: case 8: return (size_t)I;
     case 2: case 4: case 7: return ((size_t)I + 1) / 2;
     case 3: return ((size_t)I + 3) / 4;
     }
@@ -145,9 +147,8 @@ static int tc_smem_bytes() { return tc_smem_total(MODE); }
 extern "C" void coli_cuda_shutdown(void);
 
 static int decode_smem_bytes(int mode) {
-    const int nst = mode == SC_F32 ? 3 : 4;
-    return DEC_WARPS * nst * (chunk_bytes_of(mode) + 8) + (int)((sizeof(DecShared) + 127) & ~127) +
-           DEC_ACT_BYTES + 2048;
+    return DEC_WARPS * DEC_NST * chunk_bytes_of(mode) + 512 + (int)((sizeof(DecShared) + 127) & ~127) +
+           2 * DEC_PART_BYTES + DEC_ACT_BYTES;
 }
 
 extern "C" int coli_cuda_init(const int *devices, int count) {
@@ -179,8 +180,10 @@ extern "C" int coli_cuda_init(const int *devices, int count) {
             !cuda_ok(cudaEventCreate(&c->ev0), "event") || !cuda_ok(cudaEventCreate(&c->ev1), "event") ||
             !cuda_ok(cudaEventCreateWithFlags(&c->ev_done, cudaEventDisableTiming), "event") ||
             !cuda_ok(cudaHostAlloc((void **)&c->status, sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable), "status") ||
-            !cuda_ok(cudaMalloc((void **)&c->gridbar, sizeof(unsigned long long)), "grid barrier") ||
-            !cuda_ok(cudaMemset(c->gridbar, 0, sizeof(unsigned long long)), "grid barrier") ||
+            !cuda_ok(cudaMalloc((void **)&c->dec_sync, DEC_SYNC_WORDS * sizeof(unsigned int)), "grid barrier") ||
+            !cuda_ok(cudaMemset(c->dec_sync, 0, DEC_SYNC_WORDS * sizeof(unsigned int)), "grid barrier") ||
+            !cuda_ok(cudaMalloc((void **)&c->exp_tab_dev, sizeof(tab)), "exp table") ||
+            !cuda_ok(cudaMemcpy(c->exp_tab_dev, tab, sizeof(tab), cudaMemcpyHostToDevice), "exp table") ||
             !cuda_ok(cudaMemcpyToSymbol(c_exp2_tab, tab, sizeof(tab)), "exp table")) {
             g_nctx = i + 1; coli_cuda_shutdown(); return 0;
         }
@@ -211,7 +214,8 @@ extern "C" void coli_cuda_shutdown(void) {
         if (c->host_x) cudaFreeHost(c->host_x);
         if (c->host_y) cudaFreeHost(c->host_y);
         if (c->status) cudaFreeHost(c->status);
-        if (c->gridbar) cudaFree(c->gridbar);
+        if (c->dec_sync) cudaFree(c->dec_sync);
+        if (c->exp_tab_dev) cudaFree(c->exp_tab_dev);
         if (c->ev0) cudaEventDestroy(c->ev0);
         if (c->ev1) cudaEventDestroy(c->ev1);
         if (c->ev_done) cudaEventDestroy(c->ev_done);
@@ -223,6 +227,7 @@ extern "C" void coli_cuda_shutdown(void) {
     g_nctx = 0;
     g_cur_dev = -1;
     g_gpu_calls = 0;
+    g_fp8_lut_ready = 0;
 }
 
 extern "C" int coli_cuda_device_count(void) { return g_nctx; }
@@ -238,6 +243,7 @@ extern "C" int coli_cuda_device_integrated(int device) {
     return prop.integrated ? 1 : 0;
 }
 extern "C" void coli_cuda_stats(int device, size_t *tensor_count, size_t *tensor_bytes) {
+    std::lock_guard<std::mutex> lock(g_mu);
     size_t n = 0, b = 0;
     for (int i = 0; i < g_nctx; i++)
         if (device < 0 || g_ctx[i].device == device) { n += g_ctx[i].tensor_count; b += g_ctx[i].tensor_bytes; }
@@ -270,7 +276,22 @@ extern "C" void coli_cuda_group_stats_device(int device, uint64_t *calls, uint64
     if (kernel_ms) *kernel_ms = c ? c->g_kern : 0; if (d2h_ms) *d2h_ms = c ? c->g_d2h : 0;
 }
 extern "C" int coli_cuda_e8_set_grid(const void *) { return 0; }
-extern "C" int coli_cuda_fp8_set_lut(const float *) { return 0; }
+// fmt 8 (FP8 E4M3 bytes, one f32 scale per 128x128 block; c/quant.h:430-536): the engine
+// hands over its 256-entry decode table once after init (c/backend_cuda.cu:918-927); uploads
+// of fmt 8 are refused until it has (the kernels would read a zero table).
+static int g_fp8_lut_ready = 0;
+extern "C" int coli_cuda_fp8_set_lut(const float *lut) {
+    if (!lut || g_nctx < 1) return 0;
+    for (int i = 0; i < g_nctx; i++) {
+        if (!select_ctx(&g_ctx[i])) return 0;
+        if (!cuda_ok(cudaMemcpyToSymbol(d_e4m3_lut, lut, 256 * sizeof(float)), "e4m3 table upload")) return 0;
+        void *p = nullptr;
+        if (!cuda_ok(cudaGetSymbolAddress(&p, d_e4m3_lut), "e4m3 table address")) return 0;
+        g_ctx[i].e4m3_lut_dev = static_cast<const float *>(p);
+    }
+    g_fp8_lut_ready = 1;
+    return 1;
+}
 extern "C" void coli_cuda_set_timing(int enabled) { g_timing = enabled ? 1 : 0; }
 extern "C" int coli_cuda_last_timing(int device, float *kernel_ms, int *launches) {
     DeviceCtx *c = find_ctx(device);
@@ -365,7 +386,8 @@ static void tensor_release(ColiCudaTensor *t) {
 static int tensor_fill(DeviceCtx *c, ColiCudaTensor *t, const void *weights, const void *scales,
                        int allocate) {
     const size_t wbytes = row_bytes(t->fmt, t->I) * (size_t)t->O;
-    const size_t scount = t->fmt == 0 ? 0 : (size_t)t->O * (size_t)t->ng;
+    const size_t scount = t->fmt == 0 ? 0 : t->fmt == 8 ? (size_t)((t->O + 127) / 128) * (size_t)t->ng
+                                                        : (size_t)t->O * (size_t)t->ng;
     const size_t sbytes = t->fmt == 7 ? scount : scount * sizeof(float);
     if (!t->packed) {
         if (allocate) {
@@ -427,14 +449,17 @@ extern "C" int coli_cuda_tensor_upload(ColiCudaTensor **tensor, const void *weig
     }
     DeviceCtx *c = find_ctx(device);
     if (!weights || I < 1 || O < 1 || !select_ctx(c)) return 0;
-    if (!(fmt == 0 || fmt == 1 || fmt == 2 || fmt == 3 || fmt == 4 || fmt == 7)) return 0;
+    if (!(fmt == 0 || fmt == 1 || fmt == 2 || fmt == 3 || fmt == 4 || fmt == 7 || fmt == 8)) return 0;
     if (fmt && !scales) return 0;
+    if (fmt == 8 && !g_fp8_lut_ready) return 0;
     ColiCudaTensor *t = static_cast<ColiCudaTensor *>(std::calloc(1, sizeof(*t)));
     if (!t) return 0;
     t->fmt = fmt; t->I = I; t->O = O; t->device = device; t->gs = want_gs;
-    t->ng = fmt == 7 ? (I + 31) / 32 : (want_gs ? (I + want_gs - 1) / want_gs : 1);
+    t->ng = fmt == 7 ? (I + 31) / 32 : fmt == 8 ? (I + 127) / 128 : (want_gs ? (I + want_gs - 1) / want_gs : 1);
     const size_t wbytes = row_bytes(fmt, I) * (size_t)O;
-    t->logical_bytes = wbytes + (fmt == 0 ? 0 : fmt == 7 ? (size_t)O * t->ng : (size_t)O * t->ng * sizeof(float));
+    t->logical_bytes = wbytes + (fmt == 0 ? 0 : fmt == 7 ? (size_t)O * t->ng
+                                : fmt == 8 ? (size_t)((O + 127) / 128) * t->ng * sizeof(float)
+                                           : (size_t)O * t->ng * sizeof(float));
     t->packed = (fmt == 2 || fmt == 7 || (fmt == 4 && (want_gs == 32 || want_gs == 64 || want_gs == 128))) &&
                 I % BLOCK_K == 0 && O % TILE_ROWS == 0;
     if (!tensor_fill(c, t, weights, scales, 1)) {
@@ -442,9 +467,12 @@ extern "C" int coli_cuda_tensor_upload(ColiCudaTensor **tensor, const void *weig
         std::free(t);
         return 0;
     }
-    c->tensor_count++;
-    c->tensor_bytes += t->logical_bytes;
-    c->physical_bytes += t->physical_bytes;
+    {
+        std::lock_guard<std::mutex> lock(g_mu);     // uploads may come from one host thread per device
+        c->tensor_count++;
+        c->tensor_bytes += t->logical_bytes;
+        c->physical_bytes += t->physical_bytes;
+    }
     *tensor = t;
     return 1;
 }
@@ -456,15 +484,22 @@ extern "C" int coli_cuda_tensor_upload_g(ColiCudaTensor **tensor, const void *we
     g_upload_gs = 0;
     return r;
 }
+// The entropy-coded upload of builds with -DCOLI_ANS (c/backend_cuda.h:60-67): this backend
+// holds no decoder for it and refuses, which the engine answers by uploading the plain bytes.
+extern "C" int coli_cuda_tensor_upload_compressed(ColiCudaTensor **, const void *, size_t, const void *, size_t,
+                                                  int, int, int, int) { return 0; }
 extern "C" void coli_cuda_tensor_free(ColiCudaTensor *t) {
     if (!t) return;
     DeviceCtx *c = find_ctx(t->device);
     if (c) {
         select_ctx(c);
         cudaStreamSynchronize(c->stream);
-        if (c->tensor_count) c->tensor_count--;
-        if (c->tensor_bytes >= t->logical_bytes) c->tensor_bytes -= t->logical_bytes;
-        if (c->physical_bytes >= t->physical_bytes) c->physical_bytes -= t->physical_bytes;
+        {
+            std::lock_guard<std::mutex> lock(g_mu);
+            if (c->tensor_count) c->tensor_count--;
+            if (c->tensor_bytes >= t->logical_bytes) c->tensor_bytes -= t->logical_bytes;
+            if (c->physical_bytes >= t->physical_bytes) c->physical_bytes -= t->physical_bytes;
+        }
         tensor_release(t);
         (void)cudaGetLastError();
     }
@@ -667,6 +702,17 @@ static int linear_packed(DeviceCtx *c, const ColiCudaTensor *t, float *y_dev, co
 }
 
 static int linear_raw(DeviceCtx *c, const ColiCudaTensor *t, float *y_dev, const float *x_dev, int S) {
+    // rows that start 16-byte aligned take the streaming kernel (128-bit loads)
+    const bool dense = (t->fmt == 0 && t->I % 4 == 0) || ((t->fmt == 1 || t->fmt == 8) && t->I % 16 == 0);
+    if (dense && (reinterpret_cast<uintptr_t>(x_dev) & 15) == 0 && (reinterpret_cast<uintptr_t>(t->raw_w) & 15) == 0) {
+        dim3 grid((unsigned)((t->O + 31) / 32), (unsigned)((S + 7) / 8));
+        const float *sc = static_cast<const float *>(t->raw_s);
+        if (t->fmt == 0) k_dense_gemv<0><<<grid, 256, 0, c->stream>>>(y_dev, x_dev, t->raw_w, sc, nullptr, S, t->I, t->O);
+        else if (t->fmt == 1) k_dense_gemv<1><<<grid, 256, 0, c->stream>>>(y_dev, x_dev, t->raw_w, sc, nullptr, S, t->I, t->O);
+        else k_dense_gemv<8><<<grid, 256, 0, c->stream>>>(y_dev, x_dev, t->raw_w, sc, c->e4m3_lut_dev, S, t->I, t->O);
+        c->last_launches++;
+        return cuda_ok(cudaGetLastError(), "matmul launch");
+    }
     dim3 grid((unsigned)((t->O + 7) / 8), (unsigned)((S + 7) / 8));
     k_generic_matmul<<<grid, 256, 0, c->stream>>>(y_dev, x_dev, t->raw_w, t->raw_s, t->fmt, S, t->I, t->O,
                                                   t->gs > 0 ? t->gs : t->I, t->ng);
@@ -682,10 +728,9 @@ static int check_status(DeviceCtx *c) {
     const int v = *reinterpret_cast<volatile int *>(c->status);
     if (v) {
         std::fprintf(stderr, "[CUDA] kernel wait guard expired (status %d)\n", v);
-        // the grid barrier's arrival count is no longer a multiple of the grid: start over
-        cudaMemsetAsync(c->gridbar, 0, sizeof(unsigned long long), c->stream);
+        // the grid barrier's arrival count and the tickets may be mid-way: start over
+        cudaMemsetAsync(c->dec_sync, 0, DEC_SYNC_WORDS * sizeof(unsigned int), c->stream);
         *reinterpret_cast<volatile int *>(c->status) = 0;
-        c->epoch = 0;
         c->sticky_status = v;
         return 0;
     }
@@ -1093,8 +1138,6 @@ extern "C" int coli_cuda_attention_project_batch_dev(ColiCudaTensor *, ColiCudaT
 extern "C" int coli_cuda_attention_absorb_batch_dev(ColiCudaTensor *, float *, const float *, const float *, const float *, int, int, int, int, int, int, int, float) { return 0; }
 extern "C" int coli_cuda_attention_absorb_kvdev(ColiCudaTensor *, float *, const float *, const float *, const float *, int, int, int, int, int, int, float) { return 0; }
 extern "C" int coli_cuda_attention_project_batch_dev_out(ColiCudaTensor *, ColiCudaTensor *, float *, const float *, const float *, const float *, int, int, int, int, int, int, int, float) { return 0; }
-extern "C" int coli_cuda_pipe_rope(int, float *, const int *, int, int, int, int, int, float) { return 0; }
-extern "C" int coli_cuda_pipe_rope_base(int, float *, int, int, int, int, int, int, float) { return 0; }
 
 // ---------------------------------------------------------------------------
 // Resident-pipeline primitives
@@ -1146,6 +1189,24 @@ extern "C" int coli_cuda_pipe_silu_mul(int device, float *gate_dev, const float 
     if (!n || !select_ctx(c)) return 0;
     k_silu_mul<<<(unsigned)((n + 255) / 256), 256, 0, c->stream>>>(gate_dev, up_dev, n);
     return cuda_ok(cudaGetLastError(), "pipe silu mul");
+}
+extern "C" int coli_cuda_pipe_rope(int device, float *v_dev, const int *pos_dev, int rows, int stride, int offset,
+                                   int R, int heads, float theta) {
+    if (fault_injected()) return 0;
+    DeviceCtx *c = find_ctx(device);
+    if (!v_dev || !pos_dev || rows < 1 || R < 2 || R > 256 || heads < 1 || !select_ctx(c)) return 0;
+    k_rope_rows<<<rows, 128, 0, c->stream>>>(v_dev, pos_dev, 0, stride, offset, R, heads, theta);
+    c->last_launches++;
+    return cuda_ok(cudaGetLastError(), "pipe rope");
+}
+extern "C" int coli_cuda_pipe_rope_base(int device, float *v_dev, int pos_base, int rows, int stride, int offset,
+                                        int R, int heads, float theta) {
+    if (fault_injected()) return 0;
+    DeviceCtx *c = find_ctx(device);
+    if (!v_dev || rows < 1 || R < 2 || R > 256 || heads < 1 || !select_ctx(c)) return 0;
+    k_rope_rows<<<rows, 128, 0, c->stream>>>(v_dev, nullptr, pos_base, stride, offset, R, heads, theta);
+    c->last_launches++;
+    return cuda_ok(cudaGetLastError(), "pipe rope");
 }
 extern "C" int coli_cuda_pipe_add(int device, float *x_dev, const float *t_dev, size_t n) {
     if (fault_injected()) return 0;
@@ -1343,6 +1404,7 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH
 static unsigned char *g_noalloc_dev[64];   // device address of the array, per CUDA ordinal
 
 extern "C" int coli_cuda_pipe_gemm_noalloc(ColiCudaTensor *t, float *y_dev, const float *x_dev, int S) {
+    if (fault_injected()) return 0;
     if (!t || !y_dev || !x_dev || S < 1) return 0;
     DeviceCtx *c = find_ctx(t->device);
     if (!select_ctx(c)) return 0;
@@ -1402,5 +1464,6 @@ extern "C" int coli_cuda_pipe_gemm_noalloc(ColiCudaTensor *t, float *y_dev, cons
     }
     const size_t n4 = (size_t)S * t->O / 4;
     k_reduce_parts<<<(unsigned)((n4 + 255) / 256), 256, 0, c->stream>>>(y_dev, pd_dev, S, t->O, nkpart);
+    c->last_launches += 3;
     return cuda_ok(cudaGetLastError(), "pipe_gemm_noalloc launch");
 }

@@ -126,8 +126,11 @@ __device__ __forceinline__ uint32_t word_of(const uint4 &v, int i) {
 // four 128-bit loads give every A fragment of the lane, then per 32-column group
 // decode, two MMAs per 16-row half and column set, and the flush into `bacc` with
 // the group's scales. loadB(grp, cs) returns the B fragments of a group.
-template <int MODE, int NC, class LoadB>
-__device__ __forceinline__ void block_mma(uint32_t st, int lane, int g, LoadB loadB, float (&bacc)[NC][2][4]) {
+// GS: the activations carry one scale per 32-column group instead of one per block
+// (ixg[grp], the same for every column set); it is folded into the group flush.
+template <int MODE, int NC, bool GS = false, class LoadB>
+__device__ __forceinline__ void block_mma(uint32_t st, int lane, int g, LoadB loadB, float (&bacc)[NC][2][4],
+                                          const float *ixg = nullptr) {
     uint4 w[4];
 #pragma unroll
     for (int j = 0; j < 4; j++) w[j] = lds128(st + j * 512 + lane * 16);
@@ -178,12 +181,13 @@ __device__ __forceinline__ void block_mma(uint32_t st, int lane, int g, LoadB lo
                 s0 = __uint_as_float(((sc8[s].x >> (8 * grp)) & 0xFFu) << 23);
                 s1 = __uint_as_float(((sc8[s].y >> (8 * grp)) & 0xFFu) << 23);
             }
+            if (GS) { s0 *= ixg[grp]; s1 *= ixg[grp]; }
 #pragma unroll
             for (int cs = 0; cs < NC; cs++) {
                 float c[4] = {0.f, 0.f, 0.f, 0.f};
                 mma_f16(c, a_lo[0], a_hi[0], a_lo[1], a_hi[1], b[cs].x, b[cs].y);
                 mma_f16(c, a_lo[2], a_hi[2], a_lo[3], a_hi[3], b[cs].z, b[cs].w);
-                if (MODE == SC_ROW) {
+                if (MODE == SC_ROW && !GS) {
                     bacc[cs][s][0] += c[0]; bacc[cs][s][1] += c[1];
                     bacc[cs][s][2] += c[2]; bacc[cs][s][3] += c[3];
                 } else {

@@ -248,9 +248,14 @@ __global__ void k_combine_rows(float *__restrict__ out, const float *__restrict_
 // output row o and chunk of up to 8 input rows; lanes stride over columns,
 // products in f32, shuffle reduction. y[s*O+o].
 // ---------------------------------------------------------------------------
+__device__ float d_e4m3_lut[256];     // decode table of fmt 8, set by coli_cuda_fp8_set_lut
+
 __device__ __forceinline__ float raw_weight(const void *w, const void *sc, int fmt, int I, int gs,
                                             int ng, int o, int i) {
     if (fmt == 0) return static_cast<const float *>(w)[(size_t)o * I + i];
+    if (fmt == 8)      // ng = 128-column blocks per row; one scale per 128x128 block
+        return d_e4m3_lut[static_cast<const uint8_t *>(w)[(size_t)o * I + i]] *
+               static_cast<const float *>(sc)[(size_t)(o >> 7) * ng + (i >> 7)];
     if (fmt == 1)
         return (float)static_cast<const int8_t *>(w)[(size_t)o * I + i] * static_cast<const float *>(sc)[o];
     if (fmt == 3) {
@@ -291,6 +296,136 @@ __global__ void k_generic_matmul(float *__restrict__ y, const float *__restrict_
 #pragma unroll
         for (int off = 16; off; off >>= 1) a += __shfl_xor_sync(0xffffffffu, a, off);
         if (lane == 0 && r < ns) y[(size_t)(s0 + r) * O + o] = a;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Streaming GEMV for row-major tensors that the packed layout does not cover and whose
+// rows are 16-byte aligned: fmt 0 (f32, e.g. a vocabulary head), fmt 1 (int8 with a scale
+// per row) and fmt 8 (FP8 E4M3 bytes with one f32 scale per 128x128 block, the decode
+// table in `lut`). Bound by HBM: every weight byte is read once with 128-bit loads.
+//   y[s*O + o] = sum_i x[s,i] * w[o,i]
+// One warp owns 4 output rows and up to 8 rows of x (blockIdx.y selects the group of 8);
+// the CTA stages 1024 columns of those x rows in shared memory per round, a lane takes
+// 16-byte pieces of its 4 weight rows and multiplies them with the staged columns, so x
+// costs one shared-memory read per 4 output rows. Requires I % 16 == 0 (fmt 0: I % 4 == 0).
+// ---------------------------------------------------------------------------
+template <int FMT>
+__global__ void __launch_bounds__(256) k_dense_gemv(float *__restrict__ y, const float *__restrict__ x,
+                                                    const void *__restrict__ w, const float *__restrict__ sc,
+                                                    const float *__restrict__ lut, int S, int I, int O) {
+    constexpr int VPL = FMT == 0 ? 4 : 16;          // values in one 16-byte piece
+    constexpr int CK = 1024;                        // columns of x staged per round
+    constexpr int PIECES = CK / (32 * VPL);
+    __shared__ __align__(16) float xs[8 * CK];
+    __shared__ float s_lut[256];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int s0 = blockIdx.y * 8, ns = min(8, S - s0);
+    const int o0 = (blockIdx.x * 8 + warp) * 4;
+    if (FMT == 8) s_lut[tid] = lut[tid];
+    float acc[4][8];
+#pragma unroll
+    for (int r = 0; r < 4; r++)
+#pragma unroll
+        for (int q = 0; q < 8; q++) acc[r][q] = 0.f;
+    const size_t rowb = FMT == 0 ? (size_t)I * 4 : (size_t)I;       // bytes per weight row
+    const uint8_t *wb = static_cast<const uint8_t *>(w);
+    const int nblk = (I + 127) >> 7;
+    for (int c0 = 0; c0 < I; c0 += CK) {
+        __syncthreads();
+        for (int idx = tid; idx < 8 * CK / 4; idx += 256) {
+            const int q = idx / (CK / 4), j = idx - q * (CK / 4), col = c0 + j * 4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (q < ns && col < I) v = *reinterpret_cast<const float4 *>(x + (size_t)(s0 + q) * I + col);
+            reinterpret_cast<float4 *>(xs)[idx] = v;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int p = 0; p < PIECES; p++) {
+            const int col = c0 + (p * 32 + lane) * VPL;
+            if (col >= I) continue;
+            if (FMT == 0) {
+                float4 wv[4];
+#pragma unroll
+                for (int r = 0; r < 4; r++)
+                    wv[r] = o0 + r < O ? __ldcs(reinterpret_cast<const float4 *>(wb + (size_t)(o0 + r) * rowb) + (col >> 2))
+                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int q = 0; q < 8; q++) {
+                    const float4 xv = reinterpret_cast<const float4 *>(xs)[q * (CK / 4) + ((col - c0) >> 2)];
+#pragma unroll
+                    for (int r = 0; r < 4; r++)
+                        acc[r][q] = fmaf(wv[r].w, xv.w, fmaf(wv[r].z, xv.z, fmaf(wv[r].y, xv.y, fmaf(wv[r].x, xv.x, acc[r][q]))));
+                }
+            } else {
+                float wd[4][16];
+#pragma unroll
+                for (int r = 0; r < 4; r++) {
+                    uint4 raw = make_uint4(0, 0, 0, 0);
+                    float bs = 0.f;
+                    if (o0 + r < O) {
+                        raw = __ldcs(reinterpret_cast<const uint4 *>(wb + (size_t)(o0 + r) * rowb + col));
+                        bs = FMT == 8 ? sc[(size_t)((o0 + r) >> 7) * nblk + (col >> 7)] : 1.f;
+                    }
+                    const uint32_t wds[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                    for (int b = 0; b < 16; b++) {
+                        const uint32_t byte = (wds[b >> 2] >> (8 * (b & 3))) & 0xFFu;
+                        wd[r][b] = FMT == 8 ? s_lut[byte] * bs : (float)(int)(int8_t)byte;
+                    }
+                }
+#pragma unroll
+                for (int q = 0; q < 8; q++) {
+                    float4 xv[4];
+#pragma unroll
+                    for (int k = 0; k < 4; k++)
+                        xv[k] = reinterpret_cast<const float4 *>(xs)[q * (CK / 4) + ((col - c0) >> 2) + k];
+#pragma unroll
+                    for (int r = 0; r < 4; r++) {
+                        float a = acc[r][q];
+#pragma unroll
+                        for (int k = 0; k < 4; k++) {
+                            a = fmaf(wd[r][4 * k + 0], xv[k].x, a); a = fmaf(wd[r][4 * k + 1], xv[k].y, a);
+                            a = fmaf(wd[r][4 * k + 2], xv[k].z, a); a = fmaf(wd[r][4 * k + 3], xv[k].w, a);
+                        }
+                        acc[r][q] = a;
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < 4; r++)
+#pragma unroll
+        for (int q = 0; q < 8; q++) {
+            float a = acc[r][q];
+#pragma unroll
+            for (int off = 16; off; off >>= 1) a += __shfl_xor_sync(0xffffffffu, a, off);
+            if (lane == 0 && q < ns && o0 + r < O)
+                y[(size_t)(s0 + q) * O + o0 + r] = FMT == 1 ? a * sc[o0 + r] : a;
+        }
+}
+
+// Interleaved rotary embedding of the resident pipeline (the arithmetic of
+// c/backend_cuda.cu:2049-2063): block b rotates the R floats at v + b*stride + offset by
+// the angle of position pos[b / heads] (or pos_base + b / heads): pair (2j, 2j+1) of the
+// input lands at (j, R/2 + j).
+__global__ void k_rope_rows(float *v, const int *pos, int pos_base, int stride, int offset, int R, int heads,
+                            float theta) {
+    float *p = v + (size_t)blockIdx.x * stride + offset;
+    const int half = R / 2;
+    const int ps = pos ? pos[blockIdx.x / heads] : pos_base + (int)(blockIdx.x / heads);
+    __shared__ float in[256];
+    for (int j = threadIdx.x; j < R; j += blockDim.x) in[j] = p[j];
+    __syncthreads();
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+        const float inv = powf(theta, -2.0f * (float)j / (float)R);
+        const float ang = (float)ps * inv;
+        float sn, cs;
+        sincosf(ang, &sn, &cs);
+        const float a = in[2 * j], b = in[2 * j + 1];
+        p[j] = a * cs - b * sn;
+        p[half + j] = b * cs + a * sn;
     }
 }
 

@@ -1,39 +1,46 @@
-// One MoE layer for a decode-sized batch (M <= 8 rows) as ONE persistent
-// cooperative kernel: route -> union -> activation prep -> gate/up GEMV ->
-// SwiGLU -> down GEMV -> weighted combine (+ shared expert).
+// One MoE layer for a decode-sized batch (M <= 8 rows) as ONE persistent kernel:
+// route -> union -> activation split -> gate/up GEMV -> SwiGLU -> down GEMV ->
+// weighted combine (+ shared expert).
 //
-// Why one kernel: at decode sizes a layer moves only tens of MB (28 MB for the
-// OLMoE shape at M=1, about 4 us of HBM time), so the drain/fill of every
-// kernel boundary costs as much as the work itself. Here the phases are
-// separated by grid-wide barriers instead, and the weight stream never stops:
-// before a CTA waits at a barrier its warps have already issued the bulk copies
-// of their first blocks of the NEXT phase (weights do not depend on the
-// activations), so HBM stays busy while the barrier and the small distributed
-// steps (activation split, SwiGLU, combine) run.
+// Why one kernel: at decode sizes a layer moves only tens of MB (28 MB for the OLMoE
+// shape at M=1, about 4 us of HBM time), so every kernel boundary, grid-wide barrier
+// and round trip through global memory costs as much as the work itself. The layer
+// therefore has exactly one grid-wide exchange (the SwiGLU activations, which every
+// output row of the down projection needs) and one last-arriver hand-over at the end:
 //
-// Routing is computed redundantly by every CTA (top-8 of a few hundred scores
-// is a microsecond of work and saves a barrier plus a round trip through
-// global memory); its tables live in shared memory. CTA 0 writes idx/w/keff.
+//  * Routing is computed redundantly by every CTA (top-8 of a few hundred scores is a
+//    microsecond of work and saves a barrier plus a round trip through global memory).
+//    CTA 0 writes idx/w/keff.
+//  * Work is cut so that a result never leaves its CTA before it is final. A unit of
+//    the gate/up phase is (expert pass, 32 rows of the intermediate dimension, gate and
+//    up): a group of WPK warps splits the contraction by 128-column blocks, adds the
+//    per-warp sums in shared memory in a fixed order, applies the SwiGLU and writes the
+//    32 activations straight in the fp16 hi/lo fragment form the down phase multiplies
+//    with (one power-of-two scale per 32 activations). A unit of the down phase is
+//    (expert pass, 32 output rows) over the whole intermediate dimension, reduced the
+//    same way into Y[pass row, 32 columns].
+//  * Between the phases the CTAs meet at one grid barrier; the weight stream does not
+//    stop for it, because a warp's ring of bulk copies runs ahead into the down phase's
+//    first blocks (weights do not depend on the activations).
+//  * The weighted combine needs no barrier: the group that completes the last pass of a
+//    32-column slice of the output (a ticket per slice) adds the slice's terms, for
+//    every token in that token's selection order, shared expert last, and resets the ticket.
 //
-// The GEMV inner loop is the one of gemv_stream.cuh with one 8-column set
-// (4 rows per pass; an expert with more rows takes two passes).
+// Activations: x is split into fp16 hi/lo fragments by every CTA in its own shared
+// memory while the first weight blocks are in flight (or read from global memory, split
+// by a preceding kernel, when M*D*4 bytes do not fit). After the barrier a CTA copies
+// the activations of the one or two expert passes its down units belong to into the
+// same region.
 //
-// Activations: when they are small enough (M*D*4 bytes <= 64 KB and the h slices
-// of a CTA's down tasks fit the same region) they never touch global memory:
-// every CTA splits x into fp16 hi/lo fragments in its own shared memory while the
-// first gate/up chunks are in flight, and after the gate/up barrier the warps of a
-// CTA compute, once, the SwiGLU slices their down tasks need (tasks are dealt to
-// CTAs in contiguous ranges, so a CTA touches one or two (expert, slice) groups).
-// That removes two grid barriers and takes the B-operand loads of the inner loop
-// from L2 latency to shared-memory latency. Otherwise the split activations go
-// through global memory with a barrier after each producer step.
+// Sums are formed in an order that depends only on the shapes (which warp owns which
+// block is a function of the block index), so a token's result is bit-identical
+// whatever else is in the batch.
 //
-// Grid barrier: an arrival counter in global memory that only grows; the host
-// passes the number of arrivals expected before the launch, and the k-th barrier
-// of the launch waits for that plus (k+1) * gridDim.x. Every spin is bounded
-// (about 20 ms); on expiry the CTA records
-// KSTAT_GRID_TIMEOUT, drains its copies and returns. The kernel is launched
-// cooperatively so that all CTAs are co-resident.
+// Waits: the grid barrier (an arrival counter plus a generation word, so it needs no
+// per-launch value from the host and a launch can be replayed from a CUDA graph) and
+// every mbarrier wait are bounded; on expiry a CTA records a status code, keeps walking
+// its loops without waiting (so that no CTA-level barrier is abandoned), drains its
+// copies and returns. The grid is one CTA per SM, so all CTAs are co-resident.
 #pragma once
 #include "common.cuh"
 #include "gemv_stream.cuh"
@@ -43,11 +50,15 @@
 #define KSTAT_GRID_TIMEOUT 2
 #define DEC_MAX_M 8
 #define DEC_MAX_E 256
-#define DEC_MAX_PASS 80          // <= 64 distinct experts + second passes + shared passes
-#define DEC_NBAR 4
+#define DEC_MAX_K 16
+#define DEC_MAX_PASS 136         // distinct experts + second passes + shared passes (host checks M*K + 2 <= 136 <= SMs)
 #define DEC_WARPS 16
-#define DEC_ACT_BYTES 65536       // shared-memory activation region (x fragments, then h slots)
-#define DEC_NPROBE 12
+#define DEC_NST 3                // ring stages per warp
+#define DEC_ACT_BYTES (65536 + 2048)   // x fragments + scales, later the h slices of two passes + scales
+#define DEC_PART_BYTES 16384     // one buffer of per-warp partial sums: 16 warps x 32 lanes x 2 float4
+#define DEC_MAX_I 2048           // two passes x 4 rows x I x 4 bytes must fit the activation region
+#define DEC_MAX_TILES 1024       // tickets: D / 32
+#define DEC_SYNC_WORDS (16 + DEC_MAX_TILES)
 
 struct DecPass {
     int e;            // expert id, or -1 for the shared expert
@@ -62,25 +73,24 @@ struct DecodeArgs {
     const float *x, *logits, *router_bias;
     float *out;
     int *idx_out; float *w_out; int *keff_out;
-    __half *xq; float *xs;            // [M][nkb1][256], [M][nkb1]
-    float *partG, *partU;             // [nkp1][npos][I]
-    __half *hq; float *hs;            // [npos][nkb2][256], [npos][nkb2]
-    float *partD;                     // [nkp2][npos][D]
-    unsigned long long *bar;
-    unsigned long long bar_base;      // arrivals expected before this launch (host-side running total)
+    const __half *xq; const float *xs;   // x already split by k_prep_rows (only read when act_smem == 0)
+    __half *hq; float *hs;               // SwiGLU activations: [npos][I/128][256] halfs, [npos][I/32] inverse scales
+    float *Y;                            // down-projection results per pass row: [npos][D]
+    unsigned int *sync;                  // [0] barrier arrivals, [1] barrier generation, [16 + tile] tickets
+    const unsigned long long *exp_tab;   // global copy of the 2^(i/32) table
     int *status;
-    int M, nkp1, nkp2;
-    int act_smem;                     // 1: activations stay in shared memory (see above)
-    unsigned long long *probe;        // optional [gridDim.x][DEC_NPROBE] phase timestamps (ns), or NULL
+    int M, act_smem;
+    int wpk1, wpk2;                      // warps per unit in the gate/up and the down phase (4, 8 or 16)
+#ifdef COLI_DECODE_PROBE
+    unsigned long long *probe;           // optional [gridDim.x][DEC_NPROBE] phase timestamps (ns)
+#endif
 };
 
 struct DecShared {
-    int idx[DEC_MAX_M * ROUTE_MAX_K];
-    float w[DEC_MAX_M * ROUTE_MAX_K];
+    int idx[DEC_MAX_M * DEC_MAX_K];
+    float w[DEC_MAX_M * DEC_MAX_K];
+    int pos_of[DEC_MAX_M * DEC_MAX_K];
     int keff[DEC_MAX_M];
-    int pos_of[DEC_MAX_M * ROUTE_MAX_K];
-    int first[DEC_MAX_E], cnt[DEC_MAX_E], base[DEC_MAX_E], passbase[DEC_MAX_E];
-    int uniq[DEC_MAX_E];
     DecPass pass[DEC_MAX_PASS];
     int nu, npass, npos, shared_pos0, failed;
     float rowtmp[2 * DEC_MAX_M];
@@ -88,42 +98,46 @@ struct DecShared {
     unsigned long long exp_tab[32];
 };
 
-__device__ __forceinline__ void dec_probe(const DecodeArgs &a, int slot) {
-    if (a.probe && threadIdx.x == 0) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-        a.probe[(size_t)blockIdx.x * DEC_NPROBE + slot] = t;
-    }
+#ifdef COLI_DECODE_PROBE
+#define DEC_NPROBE 12
+#define DEC_PROBE(a, slot)                                                             \
+    do {                                                                               \
+        if ((a).probe && threadIdx.x == 0) {                                           \
+            unsigned long long t_;                                                     \
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_));                      \
+            (a).probe[(size_t)blockIdx.x * DEC_NPROBE + (slot)] = t_;                  \
+        }                                                                              \
+    } while (0)
+#else
+#define DEC_PROBE(a, slot) do { } while (0)
+#endif
+
+__device__ __forceinline__ void bar_sync_named(int id, int nthreads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
-__device__ __forceinline__ void dec_probe_lane(const DecodeArgs &a, int slot) {   // any one lane
-    if (a.probe) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-        a.probe[(size_t)blockIdx.x * DEC_NPROBE + slot] = t;
-    }
-}
-
-__device__ __forceinline__ uint4 ldg128(const void *p) {
-    uint4 v;
-    asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
-
-// All threads of the CTA call this. Returns false on timeout.
-__device__ __forceinline__ bool grid_barrier(unsigned long long *counter, unsigned long long target,
-                                             int *s_failed) {
+// All threads of the CTA call this. One arrival counter and one generation word: the last
+// CTA to arrive clears the counter and advances the generation, the others poll the
+// generation they read before arriving. Returns false on timeout (about 20 ms).
+__device__ __forceinline__ bool grid_barrier(unsigned int *sync, int *s_failed) {
     __syncthreads();
     if (threadIdx.x == 0) {
-        // release-add (orders this CTA's earlier writes, made visible to thread 0 by
-        // the CTA barrier above), then acquire-poll
-        asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(counter), "l"(1ULL) : "memory");
-        long long t0 = clock64();
-        for (;;) {
-            unsigned long long v;
-            asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(counter) : "memory");
-            if (v >= target) break;
-            if (clock64() - t0 > 40000000LL) { *s_failed = 1; break; }   // ~20 ms: a barrier takes microseconds
+        unsigned int gen0, old;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(gen0) : "l"(sync + 1) : "memory");
+        // acq_rel add: orders this CTA's earlier writes (made visible to thread 0 by the CTA
+        // barrier above) before the arrival, and the arrival before what follows
+        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(sync) : "memory");
+        if (old == gridDim.x - 1) {
+            asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(sync), "r"(0u) : "memory");
+            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(sync + 1), "r"(gen0 + 1u) : "memory");
+        } else {
+            long long t0 = clock64();
+            for (;;) {
+                unsigned int v;
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(sync + 1) : "memory");
+                if (v != gen0) break;
+                if (clock64() - t0 > 40000000LL) { *s_failed = 1; break; }   // a barrier takes microseconds
+            }
         }
     }
     __syncthreads();
@@ -155,7 +169,8 @@ __device__ __forceinline__ void route_row_warp(const float *z, const float *bias
         float tot = 0.f;
         if (lane == 0) {     // the engine's serial ascending sum; loads batched four at a time
             int e = 0;
-            for (; e + 4 <= E; e += 4) {
+            const bool al = (reinterpret_cast<uintptr_t>(score) & 15) == 0;   // else scalar adds, same order
+            for (; al && e + 4 <= E; e += 4) {
                 float4 v = *reinterpret_cast<const float4 *>(score + e);
                 tot = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(tot, v.x), v.y), v.z), v.w);
             }
@@ -251,7 +266,8 @@ __device__ __forceinline__ void route_rows_cta(const float *logits, const float 
             const float *sc = score + (size_t)tid * E;
             float tot = 0.f;
             int e = 0;
-            for (; e + 4 <= E; e += 4) {
+            const bool al = (reinterpret_cast<uintptr_t>(sc) & 15) == 0;      // else scalar adds, same order
+            for (; al && e + 4 <= E; e += 4) {
                 float4 v = *reinterpret_cast<const float4 *>(sc + e);
                 tot = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(tot, v.x), v.y), v.z), v.w);
             }
@@ -344,221 +360,130 @@ __device__ __forceinline__ void route_rows_cta(const float *logits, const float 
     __syncthreads();
 }
 
-// Description of one GEMV phase of the fused kernel. Tasks are numbered
-// ((segment * nkpart + kpart) * ntiles + tile); this CTA owns [t0, t1) and its warp w
-// takes t0 + w, t0 + w + 16, ...
+
+// One GEMV phase as seen by one warp. Units [u0, u1) belong to this CTA; group gidx of
+// wpk warps takes units first_u, first_u + ng, ...; inside a unit warp wl of the group
+// takes blocks wl, wl + wpk, ... of the contraction (gate first, then up, in phase 1).
 struct DecPhase {
-    int which;        // 1: gate/up (segments alternate gate, up), 2: down
-    int ntask, tps, ntiles, nkb, nkpart, kb_per_part, O, npos;
-    int t0, t1;
+    int which;        // 1: gate/up, 2: down
+    int nt, nkb;      // 32-row tiles of the output, 128-column blocks of the contraction
+    int wpk, ng;
+    int u0, u1, first_u, wl, gidx;
 };
 
-struct DecIter {
-    int task, kb, kb_end;
-    const uint8_t *ptr;
+// Position of a warp's copy stream: it runs through phase 1 and on into phase 2.
+struct DecIt {
+    int ph, u, kb, mat;              // ph 3: nothing left
+    const uint8_t *base0, *base1;    // block 0 of the current tile: gate / up, or down / unused
 };
 
 template <int CH>
-__device__ __forceinline__ void dec_task_setup(DecIter &p, const DecPhase &ph, const DecodeArgs &a,
-                                               const DecShared *sh, int &seg_i, int &tile, int &kpart) {
-    seg_i = p.task / ph.tps;
-    int local = p.task - seg_i * ph.tps;
-    kpart = local / ph.ntiles;
-    tile = local - kpart * ph.ntiles;
-    const DecPass &ps = sh->pass[ph.which == 1 ? (seg_i >> 1) : seg_i];
-    const uint8_t *w = ph.which == 1 ? ((seg_i & 1) ? ps.wu : ps.wg) : ps.wd;
-    p.kb = kpart * ph.kb_per_part;
-    p.kb_end = p.kb + ph.kb_per_part;
-    p.ptr = w + ((size_t)tile * ph.nkb + p.kb) * CH;
+__device__ __forceinline__ void dec_it_unit(DecIt &it, const DecPhase &ph, const DecShared *sh) {
+    const int pass = it.u / ph.nt, tile = it.u - pass * ph.nt;
+    const DecPass &ps = sh->pass[pass];
+    const size_t off = (size_t)tile * ph.nkb * CH;
+    if (ph.which == 1) { it.base0 = ps.wg + off; it.base1 = ps.wu + off; }
+    else { it.base0 = ps.wd + off; it.base1 = nullptr; }
+}
+template <int CH>
+__device__ __forceinline__ void dec_it_start(DecIt &it, int which, const DecPhase &ph1, const DecPhase &ph2,
+                                             const DecShared *sh) {
+    for (int w = which; w <= 2; w++) {
+        const DecPhase &ph = w == 1 ? ph1 : ph2;
+        if (ph.first_u < ph.u1 && ph.wl < ph.nkb) {
+            it.ph = w; it.u = ph.first_u; it.kb = ph.wl; it.mat = 0;
+            dec_it_unit<CH>(it, ph, sh);
+            return;
+        }
+    }
+    it.ph = 3;
+}
+template <int CH>
+__device__ __forceinline__ void dec_it_next(DecIt &it, const DecPhase &ph1, const DecPhase &ph2,
+                                            const DecShared *sh) {
+    const DecPhase &ph = it.ph == 1 ? ph1 : ph2;
+    it.kb += ph.wpk;
+    if (it.kb < ph.nkb) return;
+    it.kb = ph.wl;
+    if (ph.which == 1 && it.mat == 0) { it.mat = 1; return; }
+    it.mat = 0;
+    it.u += ph.ng;
+    if (it.u < ph.u1) { dec_it_unit<CH>(it, ph, sh); return; }
+    if (it.ph == 1) dec_it_start<CH>(it, 2, ph1, ph2, sh); else it.ph = 3;
 }
 
 // Ring state of one warp across the phases of the kernel.
 struct WarpRing {
     uint32_t ring, bars;
     int issued, consumed;
+    bool ok;          // false once a wait has expired: later waits are skipped
 };
 
 template <int CH, int NST>
-__device__ __forceinline__ void dec_issue_one(WarpRing &wr, DecIter &prod, const DecPhase &ph,
-                                              const DecodeArgs &a, const DecShared *sh, int lane) {
-    if (prod.task >= ph.t1) return;
+__device__ __forceinline__ void dec_issue_one(WarpRing &wr, DecIt &it, const DecPhase &ph1, const DecPhase &ph2,
+                                              const DecShared *sh, int lane) {
+    if (it.ph > 2) return;
     if (wr.issued - wr.consumed >= NST) return;
     if (lane == 0) {
-        uint32_t bar = wr.bars + (wr.issued % NST) * 8;
+        const uint32_t bar = wr.bars + (wr.issued % NST) * 8;
         mbar_expect_tx(bar, CH);
-        bulk_g2s(wr.ring + (wr.issued % NST) * CH, prod.ptr, CH, bar);
+        bulk_g2s(wr.ring + (wr.issued % NST) * CH, (it.mat ? it.base1 : it.base0) + (size_t)it.kb * CH, CH, bar);
     }
     wr.issued++;
-    prod.kb++;
-    prod.ptr += CH;
-    if (prod.kb == prod.kb_end) {
-        prod.task += DEC_WARPS;
-        int d0, d1, d2;
-        if (prod.task < ph.t1) dec_task_setup<CH>(prod, ph, a, sh, d0, d1, d2);
-    }
+    dec_it_next<CH>(it, ph1, ph2, sh);
 }
 
-// SwiGLU of one 128-wide block of one packed row from the gate/up partial sums,
-// split into fp16 hi/lo fragments at `dst` (256 halfs); returns the inverse scale.
-__device__ __forceinline__ float dec_swiglu_block(const DecodeArgs &a, int npos, int pos, int kb, int lane,
-                                                  __half *dst) {
-    const int I = a.rule.I;
-    float4 gs = make_float4(0, 0, 0, 0), us = gs;
-    // all loads of up to 8 partial sums are issued before the first add (one memory
-    // round trip instead of one per slice); the sum stays in ascending slice order
-    for (int k0 = 0; k0 < a.nkp1; k0 += 8) {
-        float4 ga[8], ua[8];
-#pragma unroll
-        for (int j = 0; j < 8; j++) {
-            if (k0 + j < a.nkp1) {
-                size_t off = ((size_t)(k0 + j) * npos + pos) * I + kb * BLOCK_K + lane * 4;
-                ga[j] = *reinterpret_cast<const float4 *>(a.partG + off);
-                ua[j] = *reinterpret_cast<const float4 *>(a.partU + off);
-            } else {
-                ga[j] = make_float4(0, 0, 0, 0); ua[j] = ga[j];
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < 8; j++) {
-            gs.x += ga[j].x; gs.y += ga[j].y; gs.z += ga[j].z; gs.w += ga[j].w;
-            us.x += ua[j].x; us.y += ua[j].y; us.z += ua[j].z; us.w += ua[j].w;
-        }
-    }
-    float4 h;
-    h.x = (gs.x / (1.0f + expf(-gs.x))) * us.x;
-    h.y = (gs.y / (1.0f + expf(-gs.y))) * us.y;
-    h.z = (gs.z / (1.0f + expf(-gs.z))) * us.z;
-    h.w = (gs.w / (1.0f + expf(-gs.w))) * us.w;
-    float m = warp_max(fmaxf(fmaxf(fabsf(h.x), fabsf(h.y)), fmaxf(fabsf(h.z), fabsf(h.w))));
-    float s = block_scale_from_max(m);
-    store_split4(dst, lane, h, s);
-    return 1.f / s;
+// Waits for the oldest outstanding chunk of the ring; returns its shared-memory address.
+template <int CH, int NST>
+__device__ __forceinline__ uint32_t dec_wait_chunk(WarpRing &wr) {
+    const int stage = wr.consumed % NST;
+    if (wr.ok && !mbar_wait_bounded(wr.bars + stage * 8, (wr.consumed / NST) & 1)) wr.ok = false;
+    return wr.ring + stage * CH;
 }
 
-// Bytes of one (expert pass, contraction slice) group of h in shared memory:
-// up to 4 rows x kb_per_part blocks of fragments, then their inverse scales.
-__device__ __host__ inline int dec_slice_bytes(int kbpp) { return 4 * kbpp * 512 + ((4 * kbpp * 4 + 15) & ~15); }
-
-// Consumes every task of the phase that belongs to this warp. `prod` must have
-// been initialised (and possibly primed) by the caller.
-//   bq / bscale : B operand fragments and inverse block scales in global memory, or
-//                 (phase 1, activations in shared memory) this CTA's copy of x
-//   slices      : when non-null (phase 2, activations in shared memory) the h slices of
-//                 this CTA's groups, group (task / ntiles) at index gidx - first group
-template <int MODE, int NST>
-__device__ __forceinline__ bool dec_consume_phase(WarpRing &wr, DecIter &prod, const DecPhase &ph,
-                                                  const DecodeArgs &a, const DecShared *sh, int warp,
-                                                  int lane, const __half *bq, const float *bscale,
-                                                  const uint8_t *slices) {
-    constexpr int CH = CODE_BYTES + (MODE == SC_H16 ? 256 : MODE == SC_F32 ? 512 : MODE == SC_MX ? 128 : 0);
-    const int g = lane >> 2, t = lane & 3;
-    DecIter cons;
-    cons.task = ph.t0 + warp;
-    while (cons.task < ph.t1) {
-        int seg_i, tile, kpart;
-        dec_task_setup<CH>(cons, ph, a, sh, seg_i, tile, kpart);
-        const DecPass &ps = sh->pass[ph.which == 1 ? (seg_i >> 1) : seg_i];
-        const int nrows = ps.nrows;
-        int b_nkb = ph.nkb, b_kb0 = 0;     // B operand addressing: row stride in blocks, first block
-        const int rb = g >> 1;
-        const bool bvalid = rb < nrows;
-        const bool svalid = t < nrows;
-        int rid_b = bvalid ? (ph.which == 1 ? ps.rowid[rb] : ps.pos0 + rb) : 0;
-        int rid_s = svalid ? (ph.which == 1 ? ps.rowid[t] : ps.pos0 + t) : 0;
-        const __half *bbase = bq;
-        const float *sbase = bscale;
-        if (slices) {
-            const int kbpp = ph.kb_per_part;
-            const uint8_t *sl = slices + (size_t)(cons.task / ph.ntiles - ph.t0 / ph.ntiles) * dec_slice_bytes(kbpp);
-            bbase = reinterpret_cast<const __half *>(sl);
-            sbase = reinterpret_cast<const float *>(sl + 4 * kbpp * 512);
-            b_nkb = kbpp; b_kb0 = cons.kb;
-            rid_b = rb; rid_s = t;
-        }
-        const __half *bptr = bbase + ((size_t)rid_b * b_nkb - b_kb0) * 256 + (g & 1) * 32 + t * 8;
-        const float *sptr = sbase + (size_t)rid_s * b_nkb - b_kb0;
-        float R[2][4];
-#pragma unroll
-        for (int s = 0; s < 2; s++)
-#pragma unroll
-            for (int i = 0; i < 4; i++) R[s][i] = 0.f;
-        for (int kb = cons.kb; kb < cons.kb_end; kb++) {
-            const int stage = wr.consumed % NST;
-            const uint32_t st = wr.ring + stage * CH;
-            float ixs = svalid ? sptr[kb] : 0.f;
-            // the B fragments do not depend on the chunk: fetch them before waiting for it
-            uint4 bpre[4];
-#pragma unroll
-            for (int grp = 0; grp < 4; grp++)
-                bpre[grp] = bvalid ? *reinterpret_cast<const uint4 *>(bptr + (size_t)kb * 256 + grp * 64)
-                                   : make_uint4(0, 0, 0, 0);
-            if (!mbar_wait_bounded(wr.bars + stage * 8, (wr.consumed / NST) & 1)) return false;
-            float bacc[1][2][4];
-            block_mma<MODE, 1>(st, lane, g, [&](int grp, int) { return bpre[grp]; }, bacc);
-#pragma unroll
-            for (int s = 0; s < 2; s++)
-#pragma unroll
-                for (int i = 0; i < 4; i++) R[s][i] = fmaf(bacc[0][s][i], ixs, R[s][i]);
-            wr.consumed++;
-            __syncwarp();
-            dec_issue_one<CH, NST>(wr, prod, ph, a, sh, lane);
-        }
-        const float mx_fix = (MODE == SC_MX) ? 16384.f : 1.f;
-        if (t < nrows) {
-            const float *rowscale = nullptr;
-            float *outp;
-            if (ph.which == 1) {
-                outp = (seg_i & 1) ? a.partU : a.partG;
-                if (MODE == SC_ROW) rowscale = ps.e >= 0 ? ((seg_i & 1) ? a.tab.up_rs[ps.e] : a.tab.gate_rs[ps.e])
-                                                         : ((seg_i & 1) ? a.tab.sh_up_rs : a.tab.sh_gate_rs);
-            } else {
-                outp = a.partD;
-                if (MODE == SC_ROW) rowscale = ps.e >= 0 ? a.tab.down_rs[ps.e] : a.tab.sh_down_rs;
-            }
-#pragma unroll
-            for (int s = 0; s < 2; s++) {
-                int o = tile * TILE_ROWS + s * 16 + g;
-                float v0 = (R[s][0] + R[s][1]) * mx_fix;
-                float v1 = (R[s][2] + R[s][3]) * mx_fix;
-                if (MODE == SC_ROW) { v0 *= rowscale[o]; v1 *= rowscale[o + 8]; }
-                float *dst = outp + ((size_t)kpart * ph.npos + ps.pos0 + t) * ph.O + o;
-                dst[0] = v0;
-                dst[8] = v1;
-            }
-        }
-        cons.task += DEC_WARPS;
-    }
-    return true;
-}
-
-template <int MODE> struct DecCfg { static constexpr int NST = MODE == SC_F32 ? 3 : 4; };
-
-// This CTA's contiguous share [t0, t1) of ntask tasks: sizes differ by at most one.
-__device__ __forceinline__ void dec_cta_range(int ntask, int &t0, int &t1) {
+// This CTA's contiguous share [t0, t1) of n units: sizes differ by at most one.
+__device__ __forceinline__ void dec_cta_range(int n, int &t0, int &t1) {
     const int G = gridDim.x, b = blockIdx.x;
-    const int q = ntask / G, r = ntask - q * G;
+    const int q = n / G, r = n - q * G;
     t0 = b * q + (b < r ? b : r);
     t1 = t0 + q + (b < r ? 1 : 0);
+}
+
+// Source of output row r (0..31) of a tile in the per-warp partial sums: the lane that
+// holds it for token row `mrow` and the element of that lane's float4.
+__device__ __forceinline__ void dec_part_src(int r, int mrow, int &src_lane, int &el) {
+    src_lane = (r & 7) * 4 + mrow;
+    el = (r >> 4) * 2 + ((r >> 3) & 1);
 }
 
 template <int MODE>
 __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) {
     constexpr int CH = CODE_BYTES + (MODE == SC_H16 ? 256 : MODE == SC_F32 ? 512 : MODE == SC_MX ? 128 : 0);
-    constexpr int NST = DecCfg<MODE>::NST;
+    constexpr int NST = DEC_NST;
     extern __shared__ __align__(128) uint8_t smem[];
-    // layout: rings | mbarriers | DecShared | activation region
-    // The activation region holds, in turn: the routing scratch (2*M*E floats), the
-    // fp16 fragments of x (act_smem), the h slices of this CTA's down tasks (act_smem).
-    DecShared *sh = reinterpret_cast<DecShared *>(smem + DEC_WARPS * NST * (CH + 8));
-    uint8_t *act = reinterpret_cast<uint8_t *>(sh) + ((sizeof(DecShared) + 127) & ~127);
+    // layout: rings | mbarriers (512 B) | DecShared | partial sums (2 buffers; the routing
+    // scratch and tables live here first) | activation region
+    DecShared *sh = reinterpret_cast<DecShared *>(smem + DEC_WARPS * NST * CH + 512);
+    uint8_t *part = reinterpret_cast<uint8_t *>(sh) + ((sizeof(DecShared) + 127) & ~127);
+    uint8_t *act = part + 2 * DEC_PART_BYTES;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+    const int g = lane >> 2, t = lane & 3;
     const RouteRule &r = a.rule;
     const int E = r.E, K = r.K, M = a.M, D = r.D, I = r.I;
-    const int nkb1 = D / BLOCK_K, nkb2 = I / BLOCK_K;
+    const int nkb1 = D / BLOCK_K, nkb2 = I / BLOCK_K, nt1 = I / TILE_ROWS, nt2 = D / TILE_ROWS;
     WarpRing wr;
     wr.ring = smem_u32(smem) + warp * (NST * CH);
     wr.bars = smem_u32(smem) + DEC_WARPS * NST * CH + warp * NST * 8;
-    wr.issued = 0; wr.consumed = 0;
+    wr.issued = 0; wr.consumed = 0; wr.ok = true;
+    // routing scratch inside the partial-sum buffers (dead before the first partial sum is written)
+    float *score = reinterpret_cast<float *>(part);                     // [M*E]  (<= 8 KB)
+    float *choice = reinterpret_cast<float *>(part + 8192);             // [M*E]
+    int *t_first = reinterpret_cast<int *>(part + 16384);               // [E] each
+    int *t_cnt = t_first + DEC_MAX_E, *t_base = t_cnt + DEC_MAX_E, *t_passbase = t_base + DEC_MAX_E;
+    int *t_uniq = t_passbase + DEC_MAX_E;
+    const uint8_t **ptab = reinterpret_cast<const uint8_t **>(part + 16384 + 5 * DEC_MAX_E * 4);   // [3*E]
+    unsigned long long *wtab = reinterpret_cast<unsigned long long *>(part + 16384 + 5 * DEC_MAX_E * 4 + 3 * DEC_MAX_E * 8) + warp * 32;
+
     // Programmatic dependent launch (when the host asked for it): let the next kernel of the
     // stream be scheduled onto SMs as this grid's CTAs leave them, and wait here until the
     // previous kernel has completed and its writes are visible. Both are no-ops in an
@@ -566,8 +491,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // While the previous kernel drains: warm the TLB and L2 for the first addresses this CTA
     // will read (prefetches carry no values, so it does not matter that the previous kernel
-    // may still be writing some of them; the first global access of a kernel otherwise costs
-    // about 2 us).
+    // may still be writing some of them).
     if (warp == 0) {
         const char *pf = nullptr;
         if (lane == 0) pf = reinterpret_cast<const char *>(a.logits);
@@ -576,24 +500,26 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
         else if (lane == 3) pf = reinterpret_cast<const char *>(a.tab.up_pk);
         else if (lane == 4) pf = reinterpret_cast<const char *>(a.tab.down_pk);
         else if (lane == 5) pf = reinterpret_cast<const char *>(a.router_bias);
-        else if (lane == 6) pf = reinterpret_cast<const char *>(a.bar);
+        else if (lane == 6) pf = reinterpret_cast<const char *>(a.sync);
+        else if (lane == 7) pf = reinterpret_cast<const char *>(a.exp_tab);
         if (pf) asm volatile("prefetch.global.L2 [%0];" ::"l"(pf));
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    dec_probe(a, 0);
+    DEC_PROBE(a, 0);
     // Loads whose addresses do not depend on the routing are issued first and consumed after
-    // it, so their latency hides behind the routing: this thread's expert's tensor pointers
-    // (E <= 256 <= threads) and, when the activations live in shared memory, this warp's
-    // blocks of x (at most 8 per warp: M*D*4 B fit the 64 KB region).
+    // it, so their latency hides behind the routing: the exponential table, this thread's
+    // expert's tensor pointers (E <= 256 <= threads) and, when the activations live in shared
+    // memory, this warp's blocks of x (at most 8 per warp: M*D*4 B fit the 64 KB region).
+    const unsigned long long tab_v = a.exp_tab[lane];
     const uint8_t *pre_g = nullptr, *pre_u = nullptr, *pre_d = nullptr;
     if (tid < E) { pre_g = a.tab.gate_pk[tid]; pre_u = a.tab.up_pk[tid]; pre_d = a.tab.down_pk[tid]; }
     float4 xpre[8];
     if (a.act_smem) {
 #pragma unroll
         for (int u = 0; u < 8; u++) {
-            int wid = warp + u * DEC_WARPS;
+            const int wid = warp + u * DEC_WARPS;
             if (wid < M * nkb1) {
-                int row = wid / nkb1, kb = wid - row * nkb1;
+                const int row = wid / nkb1, kb = wid - row * nkb1;
                 xpre[u] = *reinterpret_cast<const float4 *>(a.x + (size_t)row * D + kb * BLOCK_K + lane * 4);
             }
         }
@@ -603,21 +529,126 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (tid == 0) { sh->failed = 0; sh->nu = 0; }
-    if (warp == DEC_WARPS - 1) sh->exp_tab[lane] = c_exp2_tab[lane];
-    for (int e = tid; e < E; e += blockDim.x) { sh->first[e] = 0x7fffffff; sh->cnt[e] = 0; }
-    __syncthreads();
+    for (int e = tid; e < E; e += blockDim.x) { t_first[e] = 0x7fffffff; t_cnt[e] = 0; }
+    wtab[lane] = tab_v;          // this warp's own copy of the table (no CTA-wide wait before the routing)
+    __syncwarp();
 
-    // ---- routing, redundantly in every CTA, all threads -----------------------------
-    {
-        float *score = reinterpret_cast<float *>(act);
-        float *choice = score + (size_t)M * E;
+    // ---- routing, redundantly in every CTA -------------------------------------------
+    // Scores: softmax rows by one warp each (the serial denominator is the long pole),
+    // sigmoid scores by all threads. Same arithmetic, element for element, as route_row_warp.
+    bool bad = false;
+    if (r.gating == 0) {
+        if (warp < M) {
+            const float *z = a.logits + (size_t)warp * E;
+            float *sc = score + (size_t)warp * E, *chc = choice + (size_t)warp * E;
+            float m = -1e30f;
+            for (int e = lane; e < E; e += 32) { float v = z[e]; if (v > m) m = v; }
+#pragma unroll
+            for (int off = 16; off; off >>= 1) { float o = __shfl_xor_sync(0xffffffffu, m, off); if (o > m) m = o; }
+            for (int e = lane; e < E; e += 32)
+                sc[e] = coli_expf_exact(__fsub_rn(z[e], m), reinterpret_cast<const uint64_t *>(wtab));
+            __syncwarp();
+            float tot = 0.f;     // the engine's serial ascending sum, by every lane (broadcast reads)
+            int e = 0;
+            if ((E & 3) == 0)
+                for (; e < E; e += 4) {
+                    const float4 v = *reinterpret_cast<const float4 *>(sc + e);
+                    tot = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(tot, v.x), v.y), v.z), v.w);
+                }
+            for (; e < E; e++) tot = __fadd_rn(tot, sc[e]);
+            __syncwarp();
+            for (int e2 = lane; e2 < E; e2 += 32) {
+                const float p = __fdiv_rn(sc[e2], tot);
+                sc[e2] = p; chc[e2] = p;
+                bad |= !(p > -1e30f);
+            }
+        }
+    } else {
+        for (int i = tid; i < M * E; i += blockDim.x) {
+            const float sg = __fdiv_rn(1.f, __fadd_rn(1.f, coli_expf_exact(-a.logits[i], reinterpret_cast<const uint64_t *>(wtab))));
+            const float c = a.router_bias ? __fadd_rn(sg, a.router_bias[i % E]) : sg;
+            score[i] = sg; choice[i] = c;
+            bad |= !(c > -1e30f);
+        }
+    }
+    // x -> fp16 hi/lo fragments in this CTA's activation region (independent of the routing)
+    __half *xq_s = reinterpret_cast<__half *>(act);
+    float *xs_s = reinterpret_cast<float *>(act + (size_t)M * nkb1 * 512);
+    if (a.act_smem) {
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const int wid = warp + u * DEC_WARPS;
+            if (wid < M * nkb1) {
+                const int row = wid / nkb1, kb = wid - row * nkb1;
+                const float m = warp_max(fmaxf(fmaxf(fabsf(xpre[u].x), fabsf(xpre[u].y)), fmaxf(fabsf(xpre[u].z), fabsf(xpre[u].w))));
+                const float sc = block_scale_from_max(m);
+                store_split4(xq_s + ((size_t)row * nkb1 + kb) * 256, lane, xpre[u], sc);
+                if (lane == 0) xs_s[(size_t)row * nkb1 + kb] = 1.f / sc;
+            }
+        }
+    }
+    if (tid < E) { ptab[tid] = pre_g; ptab[E + tid] = pre_u; ptab[2 * E + tid] = pre_d; }
+    const int any_bad = __syncthreads_or(bad ? 1 : 0);
+    if (any_bad) {
+        // a NaN or a value <= -1e30 among the candidates: the general form, which also
+        // reproduces the engine's "nothing found -> expert kk" degradation row by row
+        if (warp == 0) sh->exp_tab[lane] = tab_v;
+        __syncthreads();
         route_rows_cta(a.logits, a.router_bias, r, M, score, choice, sh->rowtmp, sh->rowflag, sh->idx, sh->w,
                        sh->keff, reinterpret_cast<const uint64_t *>(sh->exp_tab));
+    } else {
+        // Selection by ranking (see route_row_warp): slot kk holds the element of rank kk.
+        for (int i = tid; i < M * E; i += blockDim.x) {
+            const int s = i / E, e = i - s * E;
+            const float c = choice[i];
+            const float *row = choice + (size_t)s * E;
+            int rank = 0, o = 0;
+            if ((E & 3) == 0) {
+#pragma unroll 4
+                for (; o < E; o += 4) {
+                    const float4 v = *reinterpret_cast<const float4 *>(row + o);
+                    rank += (v.x > c) || (v.x == c && o < e);
+                    rank += (v.y > c) || (v.y == c && o + 1 < e);
+                    rank += (v.z > c) || (v.z == c && o + 2 < e);
+                    rank += (v.w > c) || (v.w == c && o + 3 < e);
+                }
+            }
+            for (; o < E; o++) { const float v = row[o]; rank += (v > c) || (v == c && o < e); }
+            if (rank < K) { sh->idx[s * K + rank] = e; sh->w[s * K + rank] = score[i]; }
+        }
+        __syncthreads();
+        if (tid < M) {      // the engine's tail on the K selected weights, one thread per row
+            sh->rowflag[tid] = 0;
+            int *ix = sh->idx + tid * K;
+            float *w = sh->w + tid * K;
+            int Ke = K;
+            if (r.gating == 1 && r.topp > 0.f && r.topp < 1.f) {
+                for (int p = 1; p < K; p++) {
+                    int ii = ix[p]; float ww = w[p]; int b = p - 1;
+                    while (b >= 0 && w[b] < ww) { w[b + 1] = w[b]; ix[b + 1] = ix[b]; b--; }
+                    w[b + 1] = ww; ix[b + 1] = ii;
+                }
+                float tot = 1e-20f;
+                for (int kk = 0; kk < K; kk++) tot = __fadd_rn(tot, w[kk]);
+                float cum = 0.f;
+                for (int kk = 0; kk < K; kk++) {
+                    cum = __fadd_rn(cum, w[kk]);
+                    if (cum >= __fmul_rn(r.topp, tot)) { Ke = kk + 1; break; }
+                }
+            }
+            if (r.norm_topk) {
+                float sm = 0.f;
+                for (int kk = 0; kk < Ke; kk++) sm = __fadd_rn(sm, w[kk]);
+                if (r.gating == 1) sm = __fadd_rn(sm, 1e-20f);
+                for (int kk = 0; kk < Ke; kk++) w[kk] = __fdiv_rn(w[kk], sm);
+            }
+            if (r.gating == 1) for (int kk = 0; kk < Ke; kk++) w[kk] = __fmul_rn(w[kk], r.routed_scale);
+            sh->keff[tid] = Ke;
+        }
+        __syncthreads();
     }
-    dec_probe(a, 10);
-    // the routing scratch is dead: park the preloaded tensor pointers there until the passes exist
-    const uint8_t **ptab = reinterpret_cast<const uint8_t **>(act);
-    if (tid < E) { ptab[tid] = pre_g; ptab[E + tid] = pre_u; ptab[2 * E + tid] = pre_d; }
+    DEC_PROBE(a, 10);
+    // ---- union, packed row order and pass list -----------------------------------------
     if (M == 1 && sh->rowflag[0] == 0) {
         // one row without NaN candidates: its selections are distinct experts, so entry kk is
         // expert number kk of the union, pass kk, position kk
@@ -641,21 +672,21 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
     } else {
         for (int i = tid; i < M * K; i += blockDim.x) {
             int s = i / K, kk = i - s * K;
-            if (kk < sh->keff[s]) { int e = sh->idx[i]; atomicMin(&sh->first[e], i); atomicAdd(&sh->cnt[e], 1); }
+            if (kk < sh->keff[s]) { int e = sh->idx[i]; atomicMin(&t_first[e], i); atomicAdd(&t_cnt[e], 1); }
         }
         __syncthreads();
         // union in first-appearance order: entry i opens a new expert iff it is that
         // expert's first entry; its rank is the number of such entries before it
         for (int i = tid; i < M * K; i += blockDim.x) {
             int s = i / K, kk = i - s * K;
-            sh->pos_of[i] = (kk < sh->keff[s] && sh->first[sh->idx[i]] == i) ? 1 : 0;
+            sh->pos_of[i] = (kk < sh->keff[s] && t_first[sh->idx[i]] == i) ? 1 : 0;
         }
         __syncthreads();
         for (int i = tid; i < M * K; i += blockDim.x) {
             if (sh->pos_of[i]) {
                 int rank = 0;
                 for (int q = 0; q < i; q++) rank += sh->pos_of[q];
-                sh->uniq[rank] = sh->idx[i];
+                t_uniq[rank] = sh->idx[i];
                 atomicAdd(&sh->nu, 1);
             }
         }
@@ -663,11 +694,11 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
         const int nu = sh->nu;
         for (int j = tid; j < nu; j += blockDim.x) {
             int pos = 0, np = 0;
-            for (int q = 0; q < j; q++) { int c = sh->cnt[sh->uniq[q]]; pos += c; np += (c + 3) >> 2; }
-            int e = sh->uniq[j];
-            sh->base[e] = pos; sh->passbase[e] = np;
+            for (int q = 0; q < j; q++) { int c = t_cnt[t_uniq[q]]; pos += c; np += (c + 3) >> 2; }
+            int e = t_uniq[j];
+            t_base[e] = pos; t_passbase[e] = np;
             if (j == nu - 1) {
-                int c = sh->cnt[e];
+                int c = t_cnt[e];
                 int spos = pos + c, npass = np + ((c + 3) >> 2);
                 sh->shared_pos0 = spos;
                 if (a.tab.sh_gate_pk) {
@@ -688,11 +719,12 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
                 int e = sh->idx[i], rr = 0;
                 for (int s2 = 0; s2 < s; s2++)
                     for (int k2 = 0; k2 < sh->keff[s2]; k2++) rr += (sh->idx[s2 * K + k2] == e);
-                int pos = sh->base[e] + rr;
+                for (int k2 = 0; k2 < kk; k2++) rr += (sh->idx[s * K + k2] == e);
+                int pos = t_base[e] + rr;
                 sh->pos_of[i] = pos;
-                DecPass &ps = sh->pass[sh->passbase[e] + (rr >> 2)];
+                DecPass &ps = sh->pass[t_passbase[e] + (rr >> 2)];
                 ps.rowid[rr & 3] = s;
-                if ((rr & 3) == 0) { ps.e = e; ps.pos0 = pos; ps.nrows = min(4, sh->cnt[e] - (rr & ~3)); }
+                if ((rr & 3) == 0) { ps.e = e; ps.pos0 = pos; ps.nrows = min(4, t_cnt[e] - (rr & ~3)); }
             }
         }
         __syncthreads();
@@ -710,146 +742,212 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
         }
         if (a.keff_out) for (int s = tid; s < M; s += blockDim.x) a.keff_out[s] = sh->keff[s];
     }
-    dec_probe(a, 1);   // routing and tables done
-    const int npass = sh->npass, npos = sh->npos;
-    const int P = gridDim.x * DEC_WARPS;
-    unsigned long long bar_target = a.bar_base;
+    DEC_PROBE(a, 1);   // routing and tables done
+    const int npass = sh->npass;
 
     DecPhase ph1, ph2;
-    ph1.which = 1; ph1.ntiles = I / TILE_ROWS; ph1.nkb = nkb1; ph1.nkpart = a.nkp1;
-    ph1.kb_per_part = nkb1 / a.nkp1; ph1.tps = ph1.ntiles * a.nkp1; ph1.ntask = 2 * npass * ph1.tps;
-    ph1.O = I; ph1.npos = npos;
-    dec_cta_range(ph1.ntask, ph1.t0, ph1.t1);
-    ph2.which = 2; ph2.ntiles = D / TILE_ROWS; ph2.nkb = nkb2; ph2.nkpart = a.nkp2;
-    ph2.kb_per_part = nkb2 / a.nkp2; ph2.tps = ph2.ntiles * a.nkp2; ph2.ntask = npass * ph2.tps;
-    ph2.O = D; ph2.npos = npos;
-    dec_cta_range(ph2.ntask, ph2.t0, ph2.t1);
+    ph1.which = 1; ph1.nt = nt1; ph1.nkb = nkb1; ph1.wpk = a.wpk1; ph1.ng = DEC_WARPS / a.wpk1;
+    dec_cta_range(npass * nt1, ph1.u0, ph1.u1);
+    ph1.gidx = warp / a.wpk1; ph1.wl = warp - ph1.gidx * a.wpk1; ph1.first_u = ph1.u0 + ph1.gidx;
+    ph2.which = 2; ph2.nt = nt2; ph2.nkb = nkb2; ph2.wpk = a.wpk2; ph2.ng = DEC_WARPS / a.wpk2;
+    dec_cta_range(npass * nt2, ph2.u0, ph2.u1);
+    ph2.gidx = warp / a.wpk2; ph2.wl = warp - ph2.gidx * a.wpk2; ph2.first_u = ph2.u0 + ph2.gidx;
 
-    // ---- start the gate/up weight stream, then split x while it is in flight ----------
-    DecIter prod;
-    prod.task = ph1.t0 + warp;
-    int d0, d1, d2;
-    if (prod.task < ph1.t1) dec_task_setup<CH>(prod, ph1, a, sh, d0, d1, d2);
-    for (int s = 0; s < NST; s++) dec_issue_one<CH, NST>(wr, prod, ph1, a, sh, lane);
-    bool ok = true;
-    __half *xq_s = reinterpret_cast<__half *>(act);
-    float *xs_s = reinterpret_cast<float *>(act + (size_t)M * nkb1 * 512);
-    if (a.act_smem) {
-        // the blocks were loaded before the routing
+    // ---- start this warp's weight stream ------------------------------------------------
+    DecIt it;
+    dec_it_start<CH>(it, 1, ph1, ph2, sh);
+    for (int s = 0; s < NST; s++) dec_issue_one<CH, NST>(wr, it, ph1, ph2, sh, lane);
+    DEC_PROBE(a, 2);
+    const float mx_fix = (MODE == SC_MX) ? 16384.f : 1.f;   // fp16 fields carry e2m1 * 2^-14
+
+    // ---- gate / up -> SwiGLU activations ------------------------------------------------
+    {
+        const __half *xq = a.act_smem ? xq_s : a.xq;
+        const float *xs = a.act_smem ? xs_s : a.xs;
+        const int nrot = ph1.wpk >> 2;
+        int ucount = 0;
+        for (int u = ph1.first_u; u < ph1.u1; u += ph1.ng, ucount++) {
+            const int pass = u / nt1, tile = u - pass * nt1;
+            const DecPass &ps = sh->pass[pass];
+            const int nrows = ps.nrows;
+            const int rb = g >> 1;
+            const bool bvalid = rb < nrows, svalid = t < nrows;
+            const __half *bptr = xq + (size_t)(bvalid ? ps.rowid[rb] : 0) * nkb1 * 256 + (g & 1) * 32 + t * 8;
+            const float *sptr = xs + (size_t)(svalid ? ps.rowid[t] : 0) * nkb1;
+            // this lane's slot of the partial sums: rows g, g+8, 16+g, 24+g of the tile for token
+            // row t, gate in the first float4, up in the second
+            float4 *pb = reinterpret_cast<float4 *>(part + (ucount & 1) * DEC_PART_BYTES) + (warp * 32 + lane) * 2;
+#pragma unroll 1
+            for (int mat = 0; mat < 2; mat++) {
+                float R[2][4];
 #pragma unroll
-        for (int u = 0; u < 8; u++) {
-            int wid = warp + u * DEC_WARPS;
-            if (wid < M * nkb1) {
-                int row = wid / nkb1, kb = wid - row * nkb1;
-                float m = warp_max(fmaxf(fmaxf(fabsf(xpre[u].x), fabsf(xpre[u].y)), fmaxf(fabsf(xpre[u].z), fabsf(xpre[u].w))));
-                float sc = block_scale_from_max(m);
-                store_split4(xq_s + ((size_t)row * nkb1 + kb) * 256, lane, xpre[u], sc);
-                if (lane == 0) xs_s[(size_t)row * nkb1 + kb] = 1.f / sc;
+                for (int s = 0; s < 2; s++)
+#pragma unroll
+                    for (int i = 0; i < 4; i++) R[s][i] = 0.f;
+                for (int kb = ph1.wl; kb < nkb1; kb += ph1.wpk) {
+                    const float ixs = svalid ? sptr[kb] : 0.f;
+                    // the B fragments do not depend on the chunk: fetch them before waiting for it
+                    uint4 bpre[4];
+#pragma unroll
+                    for (int grp = 0; grp < 4; grp++)
+                        bpre[grp] = bvalid ? *reinterpret_cast<const uint4 *>(bptr + (size_t)kb * 256 + grp * 64)
+                                           : make_uint4(0, 0, 0, 0);
+                    const uint32_t st = dec_wait_chunk<CH, NST>(wr);
+                    float bacc[1][2][4];
+                    block_mma<MODE, 1>(st, lane, g, [&](int grp, int) { return bpre[grp]; }, bacc);
+#pragma unroll
+                    for (int s = 0; s < 2; s++)
+#pragma unroll
+                        for (int i = 0; i < 4; i++) R[s][i] = fmaf(bacc[0][s][i], ixs, R[s][i]);
+                    wr.consumed++;
+                    __syncwarp();
+                    dec_issue_one<CH, NST>(wr, it, ph1, ph2, sh, lane);
+                }
+                pb[mat] = make_float4((R[0][0] + R[0][1]) * mx_fix, (R[0][2] + R[0][3]) * mx_fix,
+                                      (R[1][0] + R[1][1]) * mx_fix, (R[1][2] + R[1][3]) * mx_fix);
             }
-        }
-        __syncthreads();
-        dec_probe(a, 2);
-    } else {
-        // activations through global memory: distributed split, then a barrier
-        for (int wid = blockIdx.x * DEC_WARPS + warp; wid < M * nkb1; wid += P) {
-            int row = wid / nkb1, kb = wid - row * nkb1;
-            float4 v = *reinterpret_cast<const float4 *>(a.x + (size_t)row * D + kb * BLOCK_K + lane * 4);
-            float m = warp_max(fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
-            float s = block_scale_from_max(m);
-            store_split4(a.xq + ((size_t)row * nkb1 + kb) * 256, lane, v, s);
-            if (lane == 0) a.xs[(size_t)row * nkb1 + kb] = 1.f / s;
-        }
-        dec_probe(a, 2);
-        bar_target += gridDim.x;
-        ok = grid_barrier(a.bar, bar_target, &sh->failed);
-    }
-    dec_probe(a, 3);
-    // ---- gate / up ------------------------------------------------------------------
-    if (ok) ok = dec_consume_phase<MODE, NST>(wr, prod, ph1, a, sh, warp, lane, a.act_smem ? xq_s : a.xq,
-                                              a.act_smem ? xs_s : a.xs, nullptr);
-    if (!ok) sh->failed = 1;
-    // start the down weight stream before waiting for the other CTAs
-    prod.task = ph2.t0 + warp;
-    if (ok && prod.task < ph2.t1) dec_task_setup<CH>(prod, ph2, a, sh, d0, d1, d2);
-    if (ok) for (int s = 0; s < NST; s++) dec_issue_one<CH, NST>(wr, prod, ph2, a, sh, lane);
-    dec_probe(a, 4);   // gate/up consumed, down stream primed
-    bar_target += gridDim.x;
-    ok = grid_barrier(a.bar, bar_target, &sh->failed) && ok;
-    dec_probe(a, 5);
-    if (a.act_smem) {
-        // SwiGLU slices of this CTA's groups, one block per warp at a time, into the
-        // activation region (x is no longer needed: every warp passed the barrier)
-        if (ok && ph2.t1 > ph2.t0) {
-            const int kbpp = ph2.kb_per_part, slb = dec_slice_bytes(kbpp);
-            const int g0 = ph2.t0 / ph2.ntiles, g1 = (ph2.t1 - 1) / ph2.ntiles;
-            const int per = 4 * kbpp;                          // block slots per group
-            for (int w = warp; w < (g1 - g0 + 1) * per; w += DEC_WARPS) {
-                int gi = w / per, rem = w - gi * per, rr = rem / kbpp, j = rem - rr * kbpp;
-                int grp_id = g0 + gi, seg = grp_id / a.nkp2, kp = grp_id - seg * a.nkp2;
-                const DecPass &ps = sh->pass[seg];
-                if (rr < ps.nrows) {
-                    uint8_t *sl = act + (size_t)gi * slb;
-                    float inv = dec_swiglu_block(a, npos, ps.pos0 + rr, kp * kbpp + j, lane,
-                                                 reinterpret_cast<__half *>(sl) + (size_t)(rr * kbpp + j) * 256);
-                    if (lane == 0) reinterpret_cast<float *>(sl + 4 * kbpp * 512)[rr * kbpp + j] = inv;
+            bar_sync_named(1 + ph1.gidx, ph1.wpk * 32);
+            // Four warps of the group (a different four every unit) add the per-warp sums in
+            // warp order, apply the SwiGLU and write the 32 activations of one token row each.
+            const int lw = (ph1.wl + 4 * (nrot - ucount % nrot)) % ph1.wpk;
+            if (lw < 4) {
+                const int mrow = lw;
+                int src, el;
+                dec_part_src(lane, mrow, src, el);
+                const float *pbase = reinterpret_cast<const float *>(part + (ucount & 1) * DEC_PART_BYTES) +
+                                     ((size_t)(ph1.gidx * ph1.wpk) * 32 + src) * 8 + el;
+                float gs = 0.f, us = 0.f;
+                for (int w = 0; w < ph1.wpk; w++) { gs += pbase[w * 256]; us += pbase[w * 256 + 4]; }
+                if (MODE == SC_ROW) {
+                    const int o = tile * TILE_ROWS + lane;
+                    gs *= (ps.e >= 0 ? a.tab.gate_rs[ps.e] : a.tab.sh_gate_rs)[o];
+                    us *= (ps.e >= 0 ? a.tab.up_rs[ps.e] : a.tab.sh_up_rs)[o];
+                }
+                const float h = mrow < nrows ? (gs / (1.0f + expf(-gs))) * us : 0.f;
+                const float m = warp_max(fabsf(h));
+                const float s = block_scale_from_max(m);
+                const float hx = h * s;
+                const __half hi = __float2half_rn(hx);
+                const __half lo = __float2half_rn(hx - __half2float(hi));
+                if (mrow < nrows) {
+                    const int pos = ps.pos0 + mrow;
+                    __half *dst = a.hq + ((size_t)pos * nkb2 + (tile >> 2)) * 256 + (tile & 3) * 64;
+                    dst[lane] = hi;
+                    dst[32 + lane] = lo;
+                    if (lane == 0) a.hs[(size_t)pos * nkb2 * 4 + tile] = 1.f / s;
                 }
             }
         }
-        __syncthreads();
-        dec_probe(a, 6);
-    } else {
-        // SwiGLU + split of h, distributed, then a barrier
-        if (ok)
-            for (int wid = blockIdx.x * DEC_WARPS + warp; wid < npos * nkb2; wid += P) {
-                int pos = wid / nkb2, kb = wid - pos * nkb2;
-                float inv = dec_swiglu_block(a, npos, pos, kb, lane, a.hq + ((size_t)pos * nkb2 + kb) * 256);
-                if (lane == 0) a.hs[(size_t)pos * nkb2 + kb] = inv;
-            }
-        dec_probe(a, 6);
-        bar_target += gridDim.x;
-        ok = grid_barrier(a.bar, bar_target, &sh->failed) && ok;
     }
-    dec_probe(a, 7);
-    // ---- down -------------------------------------------------------------------------
-    if (ok) ok = dec_consume_phase<MODE, NST>(wr, prod, ph2, a, sh, warp, lane, a.hq, a.hs,
-                                              a.act_smem ? act : nullptr);
-    if (!ok) sh->failed = 1;
-    dec_probe(a, 8);   // down consumed
-    bar_target += gridDim.x;
-    ok = grid_barrier(a.bar, bar_target, &sh->failed) && ok;
-    // One warp per float4 of the output; its lanes take the (selected expert, slice)
-    // terms w*partial round-robin (the shared expert's slices last, weight 1) and a
-    // fixed shuffle tree adds the lanes: deterministic, and every load is in flight at once.
-    if (ok) {
-        const int dq = D / 4;
-        const int gw = blockIdx.x * DEC_WARPS + warp;
-        for (int i = gw; i < M * dq; i += P) {
-            int s = i / dq, d4 = i - s * dq;
-            const int ke = sh->keff[s];
-            const int nterm = (ke + (a.tab.sh_gate_pk ? 1 : 0)) * a.nkp2;
-            float4 acc = make_float4(0, 0, 0, 0);
-            for (int term = lane; term < nterm; term += 32) {
-                int kk = term / a.nkp2, kp = term - kk * a.nkp2;
-                int pos; float wgt;
-                if (kk < ke) { pos = sh->pos_of[s * K + kk]; wgt = sh->w[s * K + kk]; }
-                else { pos = sh->shared_pos0 + s; wgt = 1.f; }
-                float4 v = reinterpret_cast<const float4 *>(a.partD + ((size_t)kp * npos + pos) * D)[d4];
-                acc.x = fmaf(wgt, v.x, acc.x); acc.y = fmaf(wgt, v.y, acc.y);
-                acc.z = fmaf(wgt, v.z, acc.z); acc.w = fmaf(wgt, v.w, acc.w);
-            }
-#pragma unroll
-            for (int off = 16; off; off >>= 1) {
-                acc.x += __shfl_xor_sync(0xffffffffu, acc.x, off);
-                acc.y += __shfl_xor_sync(0xffffffffu, acc.y, off);
-                acc.z += __shfl_xor_sync(0xffffffffu, acc.z, off);
-                acc.w += __shfl_xor_sync(0xffffffffu, acc.w, off);
-            }
-            if (lane == 0) reinterpret_cast<float4 *>(a.out)[i] = acc;
+    DEC_PROBE(a, 4);   // gate/up consumed (the ring already holds the first down blocks)
+    bool ok = grid_barrier(a.sync, &sh->failed);
+    DEC_PROBE(a, 5);
+    // ---- the SwiGLU activations of this CTA's one or two passes -> shared memory ---------
+    const int pA = ph2.u1 > ph2.u0 ? ph2.u0 / nt2 : 0;
+    const int pB = ph2.u1 > ph2.u0 ? (ph2.u1 - 1) / nt2 : -1;
+    float *hs_s = reinterpret_cast<float *>(act + (size_t)2 * 4 * I * 4);
+    {
+        const int row16 = I / 4;                    // 16-byte pieces of one row of fragments
+        const int sc16 = nkb2;                      // 16-byte pieces of one row of scales
+        const int per = row16 + sc16;
+        const int nslot = (pB - pA + 1) * 4;
+        for (int i = tid; i < nslot * per; i += blockDim.x) {
+            const int slot = i / per, j = i - slot * per;
+            const DecPass &ps = sh->pass[pA + (slot >> 2)];
+            const int mrow = slot & 3;
+            if (mrow >= ps.nrows) continue;
+            const int pos = ps.pos0 + mrow;
+            if (j < row16)
+                reinterpret_cast<uint4 *>(act + (size_t)slot * I * 4)[j] =
+                    __ldcg(reinterpret_cast<const uint4 *>(a.hq + (size_t)pos * I * 2) + j);
+            else
+                reinterpret_cast<float4 *>(hs_s + (size_t)slot * nkb2 * 4)[j - row16] =
+                    __ldcg(reinterpret_cast<const float4 *>(a.hs + (size_t)pos * nkb2 * 4) + (j - row16));
         }
     }
-    dec_probe(a, 9);
-    if (!ok) {
-        if (tid == 0) kstat_set(a.status, sh->failed ? KSTAT_GRID_TIMEOUT : KSTAT_MBAR_TIMEOUT);
+    __syncthreads();
+    DEC_PROBE(a, 6);
+    // ---- down -> Y, and the weighted combine by whoever completes a slice -----------------
+    {
+        const int nrot = ph2.wpk >> 2;
+        unsigned int *tickets = a.sync + 16;
+        int ucount = 0;
+        for (int u = ph2.first_u; u < ph2.u1; u += ph2.ng, ucount++) {
+            const int pass = u / nt2, tile = u - pass * nt2;
+            const DecPass &ps = sh->pass[pass];
+            const int nrows = ps.nrows, si = pass - pA;
+            const int rb = g >> 1;
+            const bool bvalid = rb < nrows, svalid = t < nrows;
+            const __half *bptr = reinterpret_cast<const __half *>(act + (size_t)(si * 4 + rb) * I * 4) + (g & 1) * 32 + t * 8;
+            const float *sptr = hs_s + (size_t)(si * 4 + t) * nkb2 * 4;
+            float R[2][4];
+#pragma unroll
+            for (int s = 0; s < 2; s++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) R[s][i] = 0.f;
+            for (int kb = ph2.wl; kb < nkb2; kb += ph2.wpk) {
+                const float4 ix4 = svalid ? *reinterpret_cast<const float4 *>(sptr + kb * 4) : make_float4(0, 0, 0, 0);
+                const float ixg[4] = {ix4.x, ix4.y, ix4.z, ix4.w};
+                uint4 bpre[4];
+#pragma unroll
+                for (int grp = 0; grp < 4; grp++)
+                    bpre[grp] = bvalid ? *reinterpret_cast<const uint4 *>(bptr + (size_t)kb * 256 + grp * 64)
+                                       : make_uint4(0, 0, 0, 0);
+                const uint32_t st = dec_wait_chunk<CH, NST>(wr);
+                float bacc[1][2][4];
+                block_mma<MODE, 1, true>(st, lane, g, [&](int grp, int) { return bpre[grp]; }, bacc, ixg);
+#pragma unroll
+                for (int s = 0; s < 2; s++)
+#pragma unroll
+                    for (int i = 0; i < 4; i++) R[s][i] += bacc[0][s][i];
+                wr.consumed++;
+                __syncwarp();
+                dec_issue_one<CH, NST>(wr, it, ph1, ph2, sh, lane);
+            }
+            float4 *pb = reinterpret_cast<float4 *>(part + (ucount & 1) * DEC_PART_BYTES) + (warp * 32 + lane) * 2;
+            pb[0] = make_float4((R[0][0] + R[0][1]) * mx_fix, (R[0][2] + R[0][3]) * mx_fix,
+                                (R[1][0] + R[1][1]) * mx_fix, (R[1][2] + R[1][3]) * mx_fix);
+            bar_sync_named(1 + ph2.gidx, ph2.wpk * 32);
+            const int lw = (ph2.wl + 4 * (nrot - ucount % nrot)) % ph2.wpk;
+            if (lw < 4) {
+                const int mrow = lw;
+                int src, el;
+                dec_part_src(lane, mrow, src, el);
+                const float *pbase = reinterpret_cast<const float *>(part + (ucount & 1) * DEC_PART_BYTES) +
+                                     ((size_t)(ph2.gidx * ph2.wpk) * 32 + src) * 8 + el;
+                float y = 0.f;
+                for (int w = 0; w < ph2.wpk; w++) y += pbase[w * 256];
+                const int o = tile * TILE_ROWS + lane;
+                if (MODE == SC_ROW) y *= (ps.e >= 0 ? a.tab.down_rs[ps.e] : a.tab.sh_down_rs)[o];
+                if (mrow < nrows) a.Y[(size_t)(ps.pos0 + mrow) * D + o] = y;
+                // ticket of this 32-column slice of the output: 4 arrivals per pass
+                __threadfence();
+                __syncwarp();
+                int last = 0;
+                if (lane == 0) last = atomicAdd(&tickets[tile], 1u) == (unsigned int)(4 * npass - 1);
+                last = __shfl_sync(0xffffffffu, last, 0);
+                if (last) {
+                    __threadfence();
+                    const bool has_shared = a.tab.sh_gate_pk != nullptr;
+                    for (int s = 0; s < M; s++) {
+                        const int ke = sh->keff[s];
+                        float acc = 0.f;
+#pragma unroll 4
+                        for (int kk = 0; kk < ke; kk++)
+                            acc = fmaf(sh->w[s * K + kk], __ldcg(a.Y + (size_t)sh->pos_of[s * K + kk] * D + o), acc);
+                        if (has_shared) acc += __ldcg(a.Y + (size_t)(sh->shared_pos0 + s) * D + o);
+                        a.out[(size_t)s * D + o] = acc;
+                    }
+                    if (lane == 0) tickets[tile] = 0u;       // ready for the next launch
+                }
+            }
+        }
+    }
+    DEC_PROBE(a, 9);
+    if (!wr.ok) sh->failed = 2;
+    __syncthreads();
+    if (!ok || sh->failed) {
+        if (tid == 0) kstat_set(a.status, sh->failed == 2 ? KSTAT_MBAR_TIMEOUT : KSTAT_GRID_TIMEOUT);
         // drain copies still in flight before the shared memory goes away (bounded)
         for (int i = wr.consumed; i < wr.issued; i++)
             if (!mbar_wait_bounded(wr.bars + (i % NST) * 8, (i / NST) & 1)) break;

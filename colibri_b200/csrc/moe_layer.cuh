@@ -115,9 +115,27 @@ extern "C" void coli_cuda_moe_layer_free(ColiCudaMoeLayer *L) {
 }
 
 static int g_fused_decode = 3;
+extern "C" void coli_cuda_set_fused_decode(int enabled) { g_fused_decode = enabled; }
+#ifdef COLI_DECODE_PROBE
+// Development builds only (-DCOLI_DECODE_PROBE): phase timestamps of the fused kernel.
 static unsigned long long *g_decode_probe = nullptr;
 extern "C" void coli_cuda_set_decode_probe(void *dev_buffer) { g_decode_probe = static_cast<unsigned long long *>(dev_buffer); }
-extern "C" void coli_cuda_set_fused_decode(int enabled) { g_fused_decode = enabled; }
+#endif
+
+// Warps that share one unit of a phase of the fused decode kernel (4, 8 or 16): the count
+// that wastes the fewest warp slots on the phase's nkb blocks, ties going to 8 for the
+// gate/up phase (few units per CTA) and to 4 for the down phase (many). A function of the
+// shape only: the order of every sum in the kernel follows from it.
+static int dec_pick_wpk(int nkb, int phase) {
+    const int pref[2][3] = {{8, 16, 4}, {4, 8, 16}};
+    int best = 0, bw = 1 << 30;
+    for (int i = 0; i < 3; i++) {
+        const int w = pref[phase - 1][i];
+        const int waste = (nkb + w - 1) / w * w - nkb;
+        if (waste < bw) { bw = waste; best = w; }
+    }
+    return best;
+}
 
 struct LayerPlan {
     int nc, rpp, nkp1, nkp2, seg_cap, npos_cap;
@@ -190,8 +208,15 @@ static int layer_run(ColiCudaMoeLayer *L, DeviceCtx *c, float *out_dev, const fl
     const LayerPlan p = layer_plan(L, c, M);
     const int nkb1 = r.D / BLOCK_K, nkb2 = r.I / BLOCK_K;
     // worth it from a mean of TC_MEAN_ROWS rows per routed expert (see group_tc_ok)
-    const bool use_tc = !route_only && !uniq_dev && L->tc_ok && M >= TC_LAYER_MIN_ROWS &&
-                        (g_tc_enabled == 2 || (g_tc_enabled == 1 && (long)M * r.K >= (long)TC_MEAN_ROWS * r.E));
+    bool use_tc = !route_only && !uniq_dev && L->tc_ok && M >= TC_LAYER_MIN_ROWS &&
+                  (g_tc_enabled == 2 || (g_tc_enabled == 1 && (long)M * r.K >= (long)TC_MEAN_ROWS * r.E));
+    if (use_tc) {
+        // coli_cuda_tensor_update may have refreshed a tensor with scales the tensor-core
+        // path cannot carry exactly since the layer was created: look again (E flags)
+        for (int e = 0; e < r.E && use_tc; e++)
+            use_tc = L->h_gates[e]->tc_ok && L->h_ups[e]->tc_ok && L->h_downs[e]->tc_ok;
+        if (use_tc && L->has_shared) use_tc = L->h_shared[0]->tc_ok && L->h_shared[1]->tc_ok && L->h_shared[2]->tc_ok;
+    }
     if (!reserve(c, &L->logits, (size_t)M * r.E * sizeof(float)) ||
         !reserve(c, &L->pos_of, (size_t)M * r.K * sizeof(int)) ||
         !reserve(c, &L->uniq, (size_t)r.E * sizeof(int)) || !reserve(c, &L->scal, 64) ||
@@ -214,36 +239,32 @@ static int layer_run(ColiCudaMoeLayer *L, DeviceCtx *c, float *out_dev, const fl
         c->last_launches++;
         lg = (const float *)L->logits.p;
     }
-    if (!route_only && g_fused_decode && M <= DEC_MAX_M && r.E <= DEC_MAX_E && L->mode_gu == L->mode_d) {
-        // one cooperative kernel for the whole layer
-        LayerPlan q = p;
-        long passes = (long)(M * r.K < r.E ? M * r.K : r.E) + (L->has_shared ? (M + 3) / 4 : 0);
-        q.nkp1 = pick_nkpart(nkb1, 2 * passes * (r.I / TILE_ROWS), c->sms);
-        q.nkp2 = pick_nkpart(nkb2, passes * (r.D / TILE_ROWS), c->sms);
-        // activations in shared memory: the routing scratch (2*M*E floats), the x fragments
-        // (M*D*4 B + scales) and the h slices of one CTA's down tasks must each fit the region
-        const size_t act_cap = DEC_ACT_BYTES + 2048;
-        int act_smem = (size_t)M * r.D * 4 + (size_t)M * nkb1 * 4 <= act_cap;
-        if (act_smem) {
-            long t2 = passes * (r.D / TILE_ROWS) * q.nkp2;
-            long chunk = (t2 + c->sms - 1) / c->sms;
-            long groups = chunk / (r.D / TILE_ROWS) + 2;
-            if ((size_t)groups * dec_slice_bytes(nkb2 / q.nkp2) > act_cap) act_smem = 0;
+    if (!route_only && g_fused_decode && M <= DEC_MAX_M && r.E <= DEC_MAX_E && r.K <= DEC_MAX_K &&
+        L->mode_gu == L->mode_d && r.I <= DEC_MAX_I && r.D / TILE_ROWS <= DEC_MAX_TILES &&
+        M * r.K + 2 <= DEC_MAX_PASS && c->sms >= DEC_MAX_PASS) {
+        // one kernel for the whole layer (moe_decode.cuh)
+        const int act_smem = (size_t)M * nkb1 * 516 <= (size_t)DEC_ACT_BYTES;
+        if (!reserve(c, &L->hq, (size_t)p.npos_cap * r.I * 2 * sizeof(__half)) ||
+            !reserve(c, &L->hs, (size_t)p.npos_cap * (r.I / 32) * sizeof(float)) ||
+            !reserve(c, &L->pd, (size_t)p.npos_cap * r.D * sizeof(float))) return 0;
+        if (!act_smem) {
+            // x does not fit the kernel's shared memory: split it once here, the kernel reads the fragments
+            k_prep_rows<<<(M * nkb1 * 32 + 255) / 256, 256, 0, c->stream>>>((__half *)L->xq.p, (float *)L->xs.p, x_dev, nullptr, M, r.D);
+            c->last_launches++;
         }
-        if ((size_t)2 * M * r.E * sizeof(float) > act_cap) return 0;
-        if (!reserve(c, &L->pg, (size_t)q.nkp1 * p.npos_cap * r.I * sizeof(float)) ||
-            !reserve(c, &L->pu, (size_t)q.nkp1 * p.npos_cap * r.I * sizeof(float)) ||
-            !reserve(c, &L->pd, (size_t)q.nkp2 * p.npos_cap * r.D * sizeof(float))) return 0;
         DecodeArgs a;
+        std::memset(&a, 0, sizeof(a));
         a.rule = r; a.tab = L->tab;
         a.x = x_dev; a.logits = lg; a.router_bias = L->router_bias;
         a.out = out_dev; a.idx_out = idx_dev; a.w_out = w_dev; a.keff_out = keff_dev;
-        a.xq = (__half *)L->xq.p; a.xs = (float *)L->xs.p;
-        a.partG = (float *)L->pg.p; a.partU = (float *)L->pu.p;
-        a.hq = (__half *)L->hq.p; a.hs = (float *)L->hs.p; a.partD = (float *)L->pd.p;
-        a.bar = c->gridbar; a.bar_base = c->epoch; a.status = c->status;
-        c->epoch += (unsigned long long)(act_smem ? 2 : 4) * (unsigned long long)c->sms;
-        a.M = M; a.nkp1 = q.nkp1; a.nkp2 = q.nkp2; a.act_smem = act_smem; a.probe = g_decode_probe;
+        a.xq = (const __half *)L->xq.p; a.xs = (const float *)L->xs.p;
+        a.hq = (__half *)L->hq.p; a.hs = (float *)L->hs.p; a.Y = (float *)L->pd.p;
+        a.sync = c->dec_sync; a.exp_tab = c->exp_tab_dev; a.status = c->status;
+        a.M = M; a.act_smem = act_smem;
+        a.wpk1 = dec_pick_wpk(nkb1, 1); a.wpk2 = dec_pick_wpk(nkb2, 2);
+#ifdef COLI_DECODE_PROBE
+        a.probe = g_decode_probe;
+#endif
         void *args[] = {&a};
         const void *fn = L->mode_gu == SC_ROW ? (const void *)k_moe_decode<SC_ROW>
                        : L->mode_gu == SC_H16 ? (const void *)k_moe_decode<SC_H16>

@@ -10,9 +10,10 @@ structure of c/olmoe.c step() (:702-750), attention() (:596-643) and generate() 
 
 Everything but `moe` is host code (numpy, f32) and is the same object on both sides of a
 comparison, so two runs differ only through their MoE callback: the CPU oracle or the CUDA
-backend. The dense products use numpy's summation order, not olmoe.c's (whose `omp simd
-reduction` leaves the order to the compiler), so the dense glue is a restatement that is not
-pinned against the olmoe binary; the MoE part is (tests/test_oracle.py)."""
+backend. The dense products use numpy's summation order, not olmoe.c's serial loops, so
+logits agree to f32 rounding, not bit for bit. The glue is pinned against the engine itself
+through its tokens: on a synthetic int8 snapshot the unmodified olmoe binary's `C engine :`
+line equals this decoder's tokens (tests/golden/make_olmoe_golden.py, tests/test_olmoe_pin.py)."""
 from __future__ import annotations
 
 import numpy as np
@@ -42,19 +43,19 @@ def rope_rows(v, pos, n_heads, head_dim, theta):
 class OlmoeModel:
     """Dense weights (f32) of the model; expert weights live with the MoE callback."""
 
-    def __init__(self, D, n_heads, head_dim, n_layers, vocab, theta, eps, seed):
+    def __init__(self, D, n_heads, head_dim, n_layers, vocab, theta, eps, seed, norm_jitter=0.0):
         rng = np.random.default_rng(seed)
         n = lambda *s: (rng.standard_normal(s, dtype=np.float32) * np.float32(0.02)).astype(np.float32)
+        ln = lambda: (np.float32(1.0) + np.float32(norm_jitter) * rng.standard_normal(D, dtype=np.float32)).astype(np.float32)
         self.D, self.H, self.hd, self.n_layers, self.vocab = D, n_heads, head_dim, n_layers, vocab
         self.theta, self.eps = theta, eps
         self.embed = n(vocab, D)
         self.lm_head = n(vocab, D)
-        self.final_norm = np.ones(D, np.float32)
+        self.final_norm = ln()
         self.layers = []
         for _ in range(n_layers):
             self.layers.append(dict(q=n(D, D), k=n(D, D), v=n(D, D), o=n(D, D),
-                                    qn=np.ones(D, np.float32), kn=np.ones(D, np.float32),
-                                    in_ln=np.ones(D, np.float32), post_ln=np.ones(D, np.float32)))
+                                    qn=ln(), kn=ln(), in_ln=ln(), post_ln=ln()))
 
 
 class Decoder:

@@ -267,7 +267,7 @@ int coli_cuda_last_timing(int device, float *kernel_ms, int *launches);
 void coli_cuda_set_timing(int enabled);
 
 /* Decode-sized layer calls (M <= 8) normally run as one fused kernel of one CTA per SM
- * with grid barriers inside:
+ * with one grid barrier inside:
  *   3 (default)  plain launch with programmatic stream serialisation: the next layer
  *                call's CTAs are scheduled as this call's CTAs exit and wait (before
  *                touching global memory) until it has completed, which hides most of
@@ -275,8 +275,9 @@ void coli_cuda_set_timing(int enabled);
  *   2            plain launch
  *   1            cooperative launch (the driver guarantees the grid is co-resident)
  *   0            the multi-kernel path instead (A/B testing)
- * Every grid-barrier wait is bounded; a launch whose CTAs were not co-resident would end
- * with the call returning 0, not with a hang. */
+ * The grid-barrier wait is bounded; a launch whose CTAs were not co-resident would end
+ * with the call returning 0, not with a hang. The barrier keeps its state on the device
+ * (arrival count + generation), so a captured launch can be replayed from a CUDA graph. */
 void coli_cuda_set_fused_decode(int enabled);
 
 /* Expert groups and layer calls with many rows per expert run on the tcgen05
@@ -293,13 +294,6 @@ void coli_cuda_set_tensor_core(int enabled);
 /* Kernels this backend has launched on `device` since coli_cuda_init (every compute
  * entry point counts its own launches). No counterpart in the reference. */
 unsigned long long coli_cuda_launch_total(int device);
-
-/* Phase probe of the fused decode kernel: with a device buffer of
- * (#SMs x 12) 64-bit words set, thread 0 of every CTA stores the global
- * nanosecond timer at each phase boundary of the next launches (start, routed,
- * split written, barrier, gate/up done, barrier, SwiGLU written, barrier, down
- * done, end, routing warp done, first helper warp's split done). NULL (the default) turns it off. */
-void coli_cuda_set_decode_probe(void *dev_buffer);
 
 /* Per-kernel timing of the dominant kernel: while enabled, every launch of the
  * streaming GEMV and of the fused decode kernel is bracketed by a CUDA event pair on the backend's stream.

@@ -5,6 +5,12 @@ Run in a container that has the reference checkout (so that oracle/_ref builds):
 It feeds seeded inputs through oracle/_ref/libcoli_ref_cpu.so (the reference's
 c/quant.h compiled unchanged) and stores inputs and outputs. The CPU tests then
 hold the restated oracle to these vectors on machines without the reference.
+
+It also imports the reference's offline quantisers (c/tools/convert_fp8_to_int4.py
+`quant_int4_grouped`, `quant_int4`; c/tools/make_deepseek_v4_tiny.py `quantize_fp4`)
+from the checkout and stores their outputs on seeded weights (quant_vectors.npz), so
+that colibri_b200/quant.py and the benchmark's torch generators can be held to them
+bit for bit.
 """
 import os
 import sys
@@ -27,8 +33,51 @@ CASES = [  # name, fmt, gs, S, I, O  (shapes of c/tests/test_i4_grouped.c and te
 ]
 
 
+REFERENCE = os.environ.get("COLI_REFERENCE", "/root/reference")
+
+
+def quantiser_vectors():
+    """Outputs of the reference's own Python quantisers on seeded N(0, 0.02) weights."""
+    import importlib.util
+    import torch
+
+    def load(name, rel):
+        spec = importlib.util.spec_from_file_location(name, os.path.join(REFERENCE, rel))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        return mod
+
+    conv = load("ref_convert_fp8_to_int4", "c/tools/convert_fp8_to_int4.py")
+    tiny = load("ref_make_deepseek_v4_tiny", "c/tools/make_deepseek_v4_tiny.py")
+    out = {}
+    rng = np.random.default_rng(4242)
+    shapes = {"a": (24, 256), "b": (7, 200), "c": (16, 1024)}
+    for nm, (O, I) in shapes.items():
+        w = (rng.standard_normal((O, I)) * 0.02).astype(np.float32)
+        if nm == "a":
+            w[3, 32:64] = 0.0                  # an all-zero group
+            w[5, 0] = 0.07                     # an outlier
+        out[f"w.{nm}"] = w
+        for gs in (32, 64, 128):
+            q, s = conv.quant_int4_grouped(w, 4, gs)
+            out[f"i4g{gs}.{nm}.q"] = q.reshape(O, -1)
+            out[f"i4g{gs}.{nm}.s"] = s
+        q, s = conv.quant_int4(w, 4)
+        out[f"i4row.{nm}.q"] = q.reshape(O, -1)
+        out[f"i4row.{nm}.s"] = s
+        if I % 128 == 0:
+            packed, scales, deq = tiny.quantize_fp4(torch, torch.from_numpy(w))
+            out[f"fp4.{nm}.q"] = packed.view(torch.uint8).numpy()
+            out[f"fp4.{nm}.e"] = scales.view(torch.uint8).numpy()
+            out[f"fp4.{nm}.deq"] = deq.numpy()
+    return out
+
+
 def main():
     build()
+    qv = quantiser_vectors()
+    np.savez_compressed(os.path.join(os.path.dirname(os.path.abspath(__file__)), "quant_vectors.npz"), **qv)
+    print("wrote", len(qv), "quantiser arrays")
     ref = RefCpu()
     out = {}
     for i, (name, fmt, gs, S, I, O) in enumerate(CASES):

@@ -62,3 +62,53 @@ def test_bf16_round():
     assert r[0] == 1.0 and r[2] == 1.0078125
     assert r[1] == 1.0               # exact tie rounds to even mantissa
     assert (r.view(np.uint32) & 0xFFFF == 0).all()
+
+
+# ---- the reference's own offline quantisers, bit for bit ------------------------------
+# tests/golden/quant_vectors.npz holds outputs of c/tools/convert_fp8_to_int4.py
+# (quant_int4_grouped :79-109, quant_int4 :64-77) and c/tools/make_deepseek_v4_tiny.py
+# (quantize_fp4 :97-121) on seeded weights, written by tests/golden/make_golden.py.
+import os
+
+import pytest
+
+QV = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "quant_vectors.npz"))
+
+
+@pytest.mark.parametrize("nm", ["a", "b", "c"])
+@pytest.mark.parametrize("gs", [32, 64, 128])
+def test_int4_grouped_matches_reference_converter(nm, gs):
+    w = QV[f"w.{nm}"]
+    q, s = quant_int4_grouped(w, gs)
+    assert np.array_equal(s.view(np.uint32), QV[f"i4g{gs}.{nm}.s"].view(np.uint32))
+    assert np.array_equal(q, QV[f"i4g{gs}.{nm}.q"])
+
+
+@pytest.mark.parametrize("nm", ["a", "b", "c"])
+def test_int4_rows_matches_reference_converter(nm):
+    w = QV[f"w.{nm}"]
+    q, s = quant_int4_rows(w)
+    assert np.array_equal(s.view(np.uint32), QV[f"i4row.{nm}.s"].view(np.uint32))
+    assert np.array_equal(q, QV[f"i4row.{nm}.q"])
+
+
+@pytest.mark.parametrize("nm", ["a", "c"])
+def test_mxfp4_matches_reference_converter(nm):
+    w = QV[f"w.{nm}"]
+    q, e = quant_mxfp4(w)
+    assert np.array_equal(e, QV[f"fp4.{nm}.e"])
+    assert np.array_equal(q, QV[f"fp4.{nm}.q"])
+    assert np.array_equal(dequant(q, e.reshape(-1), 7, w.shape[1]), QV[f"fp4.{nm}.deq"])
+
+
+def test_fp16_scale_variant_only_rounds_the_scale():
+    # "group 32, fp16 scale": the reference rule with the scale rounded to fp16 before the
+    # division; codes follow from that scale by the same rint/clip
+    w = QV["w.c"]
+    q, s = quant_int4_grouped(w, 32, np.float16)
+    s_ref = QV["i4g32.c.s"].astype(np.float16).astype(np.float32)
+    assert np.array_equal(s, np.maximum(s_ref, np.float32(6e-8)))
+    O, I = w.shape
+    wr = w.reshape(O, I // 32, 32)
+    want = np.clip(np.rint(wr / s.reshape(O, I // 32, 1)), -8, 7).astype(np.int32).reshape(O, I) + 8
+    assert np.array_equal(unpack_nibbles(q, I), want.astype(np.uint8))

@@ -64,6 +64,7 @@ static std::mutex g_mu;
 static int g_timing = 0;
 static std::atomic<long> g_gpu_calls{0};
 static thread_local int g_cur_dev = -1;
+static int g_fp8_lut_ready = 0;           // the fmt 8 decode table has been handed over (coli_cuda_fp8_set_lut)
 
 static int cuda_ok(cudaError_t e, const char *what) {
     if (e == cudaSuccess) return 1;
@@ -148,7 +149,7 @@ extern "C" void coli_cuda_shutdown(void);
 
 static int decode_smem_bytes(int mode) {
     return DEC_WARPS * DEC_NST * chunk_bytes_of(mode) + 512 + (int)((sizeof(DecShared) + 127) & ~127) +
-           2 * DEC_PART_BYTES + DEC_ACT_BYTES;
+           2 * DEC_PART_BYTES + dec_act_bytes(mode);
 }
 
 extern "C" int coli_cuda_init(const int *devices, int count) {
@@ -279,7 +280,6 @@ extern "C" int coli_cuda_e8_set_grid(const void *) { return 0; }
 // fmt 8 (FP8 E4M3 bytes, one f32 scale per 128x128 block; c/quant.h:430-536): the engine
 // hands over its 256-entry decode table once after init (c/backend_cuda.cu:918-927); uploads
 // of fmt 8 are refused until it has (the kernels would read a zero table).
-static int g_fp8_lut_ready = 0;
 extern "C" int coli_cuda_fp8_set_lut(const float *lut) {
     if (!lut || g_nctx < 1) return 0;
     for (int i = 0; i < g_nctx; i++) {

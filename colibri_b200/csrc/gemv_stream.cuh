@@ -128,33 +128,36 @@ __device__ __forceinline__ uint32_t word_of(const uint4 &v, int i) {
 // the group's scales. loadB(grp, cs) returns the B fragments of a group.
 // GS: the activations carry one scale per 32-column group instead of one per block
 // (ixg[grp], the same for every column set); it is folded into the group flush.
-template <int MODE, int NC, bool GS = false, class LoadB>
+// NS: 16-row halves present at `st` (2: a whole chunk; 1: one half, its 1024 bytes of
+// codes followed by its half of the scales; bacc[.][1] is then left untouched).
+template <int MODE, int NC, bool GS = false, int NS = 2, class LoadB>
 __device__ __forceinline__ void block_mma(uint32_t st, int lane, int g, LoadB loadB, float (&bacc)[NC][2][4],
                                           const float *ixg = nullptr) {
+    constexpr int SC0 = NS * 1024;      // offset of the scale part
     uint4 w[4];
 #pragma unroll
-    for (int j = 0; j < 4; j++) w[j] = lds128(st + j * 512 + lane * 16);
+    for (int j = 0; j < 2 * NS; j++) w[j] = lds128(st + j * 512 + lane * 16);
     // scales of rows g (h=0) and g+8 (h=1) of both 16-row halves
     uint4 sc16[2];
     uint4 sc32[2][2];
     uint2 sc8[2];
     if (MODE == SC_H16) {
 #pragma unroll
-        for (int s = 0; s < 2; s++) sc16[s] = lds128(st + CODE_BYTES + (s * 8 + g) * 16);
+        for (int s = 0; s < NS; s++) sc16[s] = lds128(st + SC0 + (s * 8 + g) * 16);
     } else if (MODE == SC_F32) {
 #pragma unroll
-        for (int s = 0; s < 2; s++) {
-            sc32[s][0] = lds128(st + CODE_BYTES + (s * 8 + g) * 32);
-            sc32[s][1] = lds128(st + CODE_BYTES + (s * 8 + g) * 32 + 16);
+        for (int s = 0; s < NS; s++) {
+            sc32[s][0] = lds128(st + SC0 + (s * 8 + g) * 32);
+            sc32[s][1] = lds128(st + SC0 + (s * 8 + g) * 32 + 16);
         }
     } else if (MODE == SC_MX) {
 #pragma unroll
-        for (int s = 0; s < 2; s++) sc8[s] = lds64(st + CODE_BYTES + (s * 8 + g) * 8);
+        for (int s = 0; s < NS; s++) sc8[s] = lds64(st + SC0 + (s * 8 + g) * 8);
     }
 #pragma unroll
     for (int cs = 0; cs < NC; cs++)
 #pragma unroll
-        for (int s = 0; s < 2; s++)
+        for (int s = 0; s < NS; s++)
 #pragma unroll
             for (int i = 0; i < 4; i++) bacc[cs][s][i] = 0.f;
 #pragma unroll
@@ -163,7 +166,7 @@ __device__ __forceinline__ void block_mma(uint32_t st, int lane, int g, LoadB lo
 #pragma unroll
         for (int cs = 0; cs < NC; cs++) b[cs] = loadB(grp, cs);
 #pragma unroll
-        for (int s = 0; s < 2; s++) {
+        for (int s = 0; s < NS; s++) {
             uint32_t a_lo[4], a_hi[4];
             decode_word<MODE>(word_of(w[s * 2 + 0], grp), a_lo);   // row g
             decode_word<MODE>(word_of(w[s * 2 + 1], grp), a_hi);   // row g+8

@@ -25,6 +25,10 @@
 //  * The weighted combine needs no barrier: the group that completes the last pass of a
 //    32-column slice of the output (a ticket per slice) adds the slice's terms, for
 //    every token in that token's selection order, shared expert last, and resets the ticket.
+//  * When the call is small enough that every pass row's activations fit one CTA's shared
+//    memory (the OLMoE shape at M=1), the down phase is cut the other way: a CTA owns 16
+//    output rows over ALL passes (half-chunks of the weight stream), so the combine is
+//    local and the results leave the CTA once, as the final output.
 //
 // Activations: x is split into fp16 hi/lo fragments by every CTA in its own shared
 // memory while the first weight blocks are in flight (or read from global memory, split
@@ -51,10 +55,12 @@
 #define DEC_MAX_M 8
 #define DEC_MAX_E 256
 #define DEC_MAX_K 16
-#define DEC_MAX_PASS 136         // distinct experts + second passes + shared passes (host checks M*K + 2 <= 136 <= SMs)
+#define DEC_MAX_PASS 96          // distinct experts + second passes + shared passes (host checks M*K + 2 <= 96 <= SMs)
 #define DEC_WARPS 16
 #define DEC_NST 3                // ring stages per warp
-#define DEC_ACT_BYTES (65536 + 2048)   // x fragments + scales, later the h slices of two passes + scales
+// activation region: x fragments + scales, later the SwiGLU activations of the down phase
+// (two passes x 4 rows, or every pass row when the combine is local) + scales
+__host__ __device__ constexpr int dec_act_bytes(int mode) { return mode == SC_F32 ? 65536 + 2048 : 78 * 1024; }
 #define DEC_PART_BYTES 16384     // one buffer of per-warp partial sums: 16 warps x 32 lanes x 2 float4
 #define DEC_MAX_I 2048           // two passes x 4 rows x I x 4 bytes must fit the activation region
 #define DEC_MAX_TILES 1024       // tickets: D / 32
@@ -81,6 +87,7 @@ struct DecodeArgs {
     int *status;
     int M, act_smem;
     int wpk1, wpk2;                      // warps per unit in the gate/up and the down phase (4, 8 or 16)
+    int local2;                          // down phase: 1 = a CTA owns 16 output rows over every pass and combines them itself
 #ifdef COLI_DECODE_PROBE
     unsigned long long *probe;           // optional [gridDim.x][DEC_NPROBE] phase timestamps (ns)
 #endif
@@ -369,16 +376,24 @@ struct DecPhase {
     int nt, nkb;      // 32-row tiles of the output, 128-column blocks of the contraction
     int wpk, ng;
     int u0, u1, first_u, wl, gidx;
+    int local, npass; // local: units are 16-row halves of the output, every group walks passes gidx, gidx + ng, ...
 };
 
 // Position of a warp's copy stream: it runs through phase 1 and on into phase 2.
 struct DecIt {
-    int ph, u, kb, mat;              // ph 3: nothing left
+    int ph, u, kb, mat, p;           // ph 3: nothing left; p: pass (local down phase only)
     const uint8_t *base0, *base1;    // block 0 of the current tile: gate / up, or down / unused
+                                     // (local down phase: codes / scales of the 16-row half)
 };
 
 template <int CH>
 __device__ __forceinline__ void dec_it_unit(DecIt &it, const DecPhase &ph, const DecShared *sh) {
+    if (ph.local) {
+        const uint8_t *tile0 = sh->pass[it.p].wd + (size_t)(it.u >> 1) * ph.nkb * CH;
+        it.base0 = tile0 + (it.u & 1) * 1024;
+        it.base1 = tile0 + CODE_BYTES + (it.u & 1) * ((CH - CODE_BYTES) / 2);
+        return;
+    }
     const int pass = it.u / ph.nt, tile = it.u - pass * ph.nt;
     const DecPass &ps = sh->pass[pass];
     const size_t off = (size_t)tile * ph.nkb * CH;
@@ -390,8 +405,8 @@ __device__ __forceinline__ void dec_it_start(DecIt &it, int which, const DecPhas
                                              const DecShared *sh) {
     for (int w = which; w <= 2; w++) {
         const DecPhase &ph = w == 1 ? ph1 : ph2;
-        if (ph.first_u < ph.u1 && ph.wl < ph.nkb) {
-            it.ph = w; it.u = ph.first_u; it.kb = ph.wl; it.mat = 0;
+        if (ph.first_u < ph.u1 && ph.wl < ph.nkb && (!ph.local || ph.gidx < ph.npass)) {
+            it.ph = w; it.u = ph.first_u; it.kb = ph.wl; it.mat = 0; it.p = ph.gidx;
             dec_it_unit<CH>(it, ph, sh);
             return;
         }
@@ -405,6 +420,12 @@ __device__ __forceinline__ void dec_it_next(DecIt &it, const DecPhase &ph1, cons
     it.kb += ph.wpk;
     if (it.kb < ph.nkb) return;
     it.kb = ph.wl;
+    if (ph.local) {
+        it.p += ph.ng;
+        if (it.p >= ph.npass) { it.p = ph.gidx; it.u += 1; }
+        if (it.u < ph.u1) dec_it_unit<CH>(it, ph, sh); else it.ph = 3;
+        return;
+    }
     if (ph.which == 1 && it.mat == 0) { it.mat = 1; return; }
     it.mat = 0;
     it.u += ph.ng;
@@ -425,9 +446,17 @@ __device__ __forceinline__ void dec_issue_one(WarpRing &wr, DecIt &it, const Dec
     if (it.ph > 2) return;
     if (wr.issued - wr.consumed >= NST) return;
     if (lane == 0) {
-        const uint32_t bar = wr.bars + (wr.issued % NST) * 8;
-        mbar_expect_tx(bar, CH);
-        bulk_g2s(wr.ring + (wr.issued % NST) * CH, (it.mat ? it.base1 : it.base0) + (size_t)it.kb * CH, CH, bar);
+        const uint32_t bar = wr.bars + (wr.issued % NST) * 8, dst = wr.ring + (wr.issued % NST) * CH;
+        if (it.ph == 2 && ph2.local) {
+            // one 16-row half: 1024 bytes of codes, then its half of the scales
+            constexpr int SCH = (CH - CODE_BYTES) / 2;
+            mbar_expect_tx(bar, 1024 + SCH);
+            bulk_g2s(dst, it.base0 + (size_t)it.kb * CH, 1024, bar);
+            if (SCH) bulk_g2s(dst + 1024, it.base1 + (size_t)it.kb * CH, SCH, bar);
+        } else {
+            mbar_expect_tx(bar, CH);
+            bulk_g2s(dst, (it.mat ? it.base1 : it.base0) + (size_t)it.kb * CH, CH, bar);
+        }
     }
     wr.issued++;
     dec_it_next<CH>(it, ph1, ph2, sh);
@@ -511,6 +540,23 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
     // expert's tensor pointers (E <= 256 <= threads) and, when the activations live in shared
     // memory, this warp's blocks of x (at most 8 per warp: M*D*4 B fit the 64 KB region).
     const unsigned long long tab_v = a.exp_tab[lane];
+    float zpre[8];            // softmax: this lane's logits of row `warp`; sigmoid: this thread's elements
+    float bpre_r[4];
+#pragma unroll
+    for (int j = 0; j < 8; j++) zpre[j] = 0.f;
+    if (r.gating == 0) {
+        if (warp < M) {
+#pragma unroll
+            for (int j = 0; j < 8; j++) { const int e = j * 32 + lane; if (e < E) zpre[j] = a.logits[(size_t)warp * E + e]; }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int i = tid + j * DEC_WARPS * 32;
+            bpre_r[j] = 0.f;
+            if (i < M * E) { zpre[j] = a.logits[i]; if (a.router_bias) bpre_r[j] = a.router_bias[i % E]; }
+        }
+    }
     const uint8_t *pre_g = nullptr, *pre_u = nullptr, *pre_d = nullptr;
     if (tid < E) { pre_g = a.tab.gate_pk[tid]; pre_u = a.tab.up_pk[tid]; pre_d = a.tab.down_pk[tid]; }
     float4 xpre[8];
@@ -539,14 +585,16 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
     bool bad = false;
     if (r.gating == 0) {
         if (warp < M) {
-            const float *z = a.logits + (size_t)warp * E;
             float *sc = score + (size_t)warp * E, *chc = choice + (size_t)warp * E;
             float m = -1e30f;
-            for (int e = lane; e < E; e += 32) { float v = z[e]; if (v > m) m = v; }
+#pragma unroll
+            for (int j = 0; j < 8; j++) if (j * 32 + lane < E && zpre[j] > m) m = zpre[j];
 #pragma unroll
             for (int off = 16; off; off >>= 1) { float o = __shfl_xor_sync(0xffffffffu, m, off); if (o > m) m = o; }
-            for (int e = lane; e < E; e += 32)
-                sc[e] = coli_expf_exact(__fsub_rn(z[e], m), reinterpret_cast<const uint64_t *>(wtab));
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                if (j * 32 + lane < E)
+                    sc[j * 32 + lane] = coli_expf_exact(__fsub_rn(zpre[j], m), reinterpret_cast<const uint64_t *>(wtab));
             __syncwarp();
             float tot = 0.f;     // the engine's serial ascending sum, by every lane (broadcast reads)
             int e = 0;
@@ -564,11 +612,15 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
             }
         }
     } else {
-        for (int i = tid; i < M * E; i += blockDim.x) {
-            const float sg = __fdiv_rn(1.f, __fadd_rn(1.f, coli_expf_exact(-a.logits[i], reinterpret_cast<const uint64_t *>(wtab))));
-            const float c = a.router_bias ? __fadd_rn(sg, a.router_bias[i % E]) : sg;
-            score[i] = sg; choice[i] = c;
-            bad |= !(c > -1e30f);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int i = tid + j * DEC_WARPS * 32;
+            if (i < M * E) {
+                const float sg = __fdiv_rn(1.f, __fadd_rn(1.f, coli_expf_exact(-zpre[j], reinterpret_cast<const uint64_t *>(wtab))));
+                const float c = a.router_bias ? __fadd_rn(sg, bpre_r[j]) : sg;
+                score[i] = sg; choice[i] = c;
+                bad |= !(c > -1e30f);
+            }
         }
     }
     // x -> fp16 hi/lo fragments in this CTA's activation region (independent of the routing)
@@ -749,9 +801,12 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
     ph1.which = 1; ph1.nt = nt1; ph1.nkb = nkb1; ph1.wpk = a.wpk1; ph1.ng = DEC_WARPS / a.wpk1;
     dec_cta_range(npass * nt1, ph1.u0, ph1.u1);
     ph1.gidx = warp / a.wpk1; ph1.wl = warp - ph1.gidx * a.wpk1; ph1.first_u = ph1.u0 + ph1.gidx;
+    ph1.local = 0; ph1.npass = npass;
     ph2.which = 2; ph2.nt = nt2; ph2.nkb = nkb2; ph2.wpk = a.wpk2; ph2.ng = DEC_WARPS / a.wpk2;
-    dec_cta_range(npass * nt2, ph2.u0, ph2.u1);
-    ph2.gidx = warp / a.wpk2; ph2.wl = warp - ph2.gidx * a.wpk2; ph2.first_u = ph2.u0 + ph2.gidx;
+    ph2.local = a.local2; ph2.npass = npass;
+    ph2.gidx = warp / a.wpk2; ph2.wl = warp - ph2.gidx * a.wpk2;
+    if (a.local2) { dec_cta_range(2 * nt2, ph2.u0, ph2.u1); ph2.first_u = ph2.u0; }
+    else { dec_cta_range(npass * nt2, ph2.u0, ph2.u1); ph2.first_u = ph2.u0 + ph2.gidx; }
 
     // ---- start this warp's weight stream ------------------------------------------------
     DecIt it;
@@ -845,8 +900,24 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
     // ---- the SwiGLU activations of this CTA's one or two passes -> shared memory ---------
     const int pA = ph2.u1 > ph2.u0 ? ph2.u0 / nt2 : 0;
     const int pB = ph2.u1 > ph2.u0 ? (ph2.u1 - 1) / nt2 : -1;
-    float *hs_s = reinterpret_cast<float *>(act + (size_t)2 * 4 * I * 4);
-    {
+    const int npos = sh->npos;
+    // local combine: one slot per pass row (slot = packed row), then the scales, then Y[pos][16]
+    float *hs_s = reinterpret_cast<float *>(act + (a.local2 ? (size_t)npos : (size_t)8) * I * 4);
+    float *ybuf = hs_s + (size_t)npos * nkb2 * 4;
+    if (a.local2) {
+        if (ph2.u1 > ph2.u0) {
+            const int row16 = I / 4, per = row16 + nkb2;
+            for (int i = tid; i < npos * per; i += blockDim.x) {
+                const int pos = i / per, j = i - pos * per;
+                if (j < row16)
+                    reinterpret_cast<uint4 *>(act + (size_t)pos * I * 4)[j] =
+                        __ldcg(reinterpret_cast<const uint4 *>(a.hq + (size_t)pos * I * 2) + j);
+                else
+                    reinterpret_cast<float4 *>(hs_s + (size_t)pos * nkb2 * 4)[j - row16] =
+                        __ldcg(reinterpret_cast<const float4 *>(a.hs + (size_t)pos * nkb2 * 4) + (j - row16));
+            }
+        }
+    } else {
         const int row16 = I / 4;                    // 16-byte pieces of one row of fragments
         const int sc16 = nkb2;                      // 16-byte pieces of one row of scales
         const int per = row16 + sc16;
@@ -867,8 +938,66 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
     }
     __syncthreads();
     DEC_PROBE(a, 6);
+    if (a.local2) {
+        // ---- down with a local combine: this CTA's 16 output rows over every pass ------------
+        const int nrot = ph2.wpk >> 2;
+        const bool has_shared = a.tab.sh_gate_pk != nullptr;
+        int pcount = 0;
+        for (int u = ph2.u0; u < ph2.u1; u++) {
+            for (int p = ph2.gidx; p < npass; p += ph2.ng, pcount++) {
+                const DecPass &ps = sh->pass[p];
+                const int nrows = ps.nrows;
+                const int rb = g >> 1;
+                const bool bvalid = rb < nrows, svalid = t < nrows;
+                const __half *bptr = reinterpret_cast<const __half *>(act + (size_t)(ps.pos0 + (bvalid ? rb : 0)) * I * 4) + (g & 1) * 32 + t * 8;
+                const float *sptr = hs_s + (size_t)(ps.pos0 + (svalid ? t : 0)) * nkb2 * 4;
+                float R[4] = {0.f, 0.f, 0.f, 0.f};
+                for (int kb = ph2.wl; kb < nkb2; kb += ph2.wpk) {
+                    const float4 ix4 = svalid ? *reinterpret_cast<const float4 *>(sptr + kb * 4) : make_float4(0, 0, 0, 0);
+                    const float ixg[4] = {ix4.x, ix4.y, ix4.z, ix4.w};
+                    uint4 bpre[4];
+#pragma unroll
+                    for (int grp = 0; grp < 4; grp++)
+                        bpre[grp] = bvalid ? *reinterpret_cast<const uint4 *>(bptr + (size_t)kb * 256 + grp * 64)
+                                           : make_uint4(0, 0, 0, 0);
+                    const uint32_t st = dec_wait_chunk<CH, NST>(wr);
+                    float bacc[1][2][4];
+                    block_mma<MODE, 1, true, 1>(st, lane, g, [&](int grp, int) { return bpre[grp]; }, bacc, ixg);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) R[i] += bacc[0][0][i];
+                    wr.consumed++;
+                    __syncwarp();
+                    dec_issue_one<CH, NST>(wr, it, ph1, ph2, sh, lane);
+                }
+                // rows g and g+8 of the 16-row half for token row t
+                float4 *pb = reinterpret_cast<float4 *>(part + (pcount & 1) * DEC_PART_BYTES) + (warp * 32 + lane) * 2;
+                pb[0] = make_float4((R[0] + R[1]) * mx_fix, (R[2] + R[3]) * mx_fix, 0.f, 0.f);
+                bar_sync_named(1 + ph2.gidx, ph2.wpk * 32);
+                const int lw = (ph2.wl + 4 * (nrot - pcount % nrot)) % ph2.wpk;
+                if (lw < 4 && lane < 16) {
+                    const int mrow = lw;
+                    const float *pbase = reinterpret_cast<const float *>(part + (pcount & 1) * DEC_PART_BYTES) +
+                                         ((size_t)(ph2.gidx * ph2.wpk) * 32 + (lane & 7) * 4 + mrow) * 8 + (lane >> 3);
+                    float y = 0.f;
+                    for (int w = 0; w < ph2.wpk; w++) y += pbase[w * 256];
+                    const int o = u * 16 + lane;
+                    if (MODE == SC_ROW) y *= (ps.e >= 0 ? a.tab.down_rs[ps.e] : a.tab.sh_down_rs)[o];
+                    if (mrow < nrows) ybuf[(ps.pos0 + mrow) * 16 + lane] = y;
+                }
+            }
+            __syncthreads();      // every pass of this slice is in ybuf
+            for (int i = tid; i < M * 16; i += blockDim.x) {
+                const int s = i >> 4, rr = i & 15;
+                const int ke = sh->keff[s];
+                float acc = 0.f;
+                for (int kk = 0; kk < ke; kk++) acc = fmaf(sh->w[s * K + kk], ybuf[sh->pos_of[s * K + kk] * 16 + rr], acc);
+                if (has_shared) acc += ybuf[(sh->shared_pos0 + s) * 16 + rr];
+                a.out[(size_t)s * D + u * 16 + rr] = acc;
+            }
+            __syncthreads();      // ybuf is reused by the next slice
+        }
+    } else {
     // ---- down -> Y, and the weighted combine by whoever completes a slice -----------------
-    {
         const int nrot = ph2.wpk >> 2;
         unsigned int *tickets = a.sync + 16;
         int ucount = 0;

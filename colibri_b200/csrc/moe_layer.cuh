@@ -243,7 +243,13 @@ static int layer_run(ColiCudaMoeLayer *L, DeviceCtx *c, float *out_dev, const fl
         L->mode_gu == L->mode_d && r.I <= DEC_MAX_I && r.D / TILE_ROWS <= DEC_MAX_TILES &&
         M * r.K + 2 <= DEC_MAX_PASS && c->sms >= DEC_MAX_PASS) {
         // one kernel for the whole layer (moe_decode.cuh)
-        const int act_smem = (size_t)M * nkb1 * 516 <= (size_t)DEC_ACT_BYTES;
+        const size_t act_cap = (size_t)dec_act_bytes(L->mode_gu);
+        const int act_smem = (size_t)M * nkb1 * 516 <= act_cap;
+        // Down phase with a local combine (a CTA owns 16 output rows over every pass): when every
+        // pass row's activations fit one CTA's shared memory and D/16 slices spread well over the SMs.
+        const long units2 = r.D / 16, waves2 = (units2 + c->sms - 1) / c->sms;
+        const int local2 = (size_t)p.npos_cap * ((size_t)r.I * 4 + (size_t)nkb2 * 16 + 64) <= act_cap &&
+                           units2 * 100 >= 85 * waves2 * c->sms;
         if (!reserve(c, &L->hq, (size_t)p.npos_cap * r.I * 2 * sizeof(__half)) ||
             !reserve(c, &L->hs, (size_t)p.npos_cap * (r.I / 32) * sizeof(float)) ||
             !reserve(c, &L->pd, (size_t)p.npos_cap * r.D * sizeof(float))) return 0;
@@ -261,7 +267,7 @@ static int layer_run(ColiCudaMoeLayer *L, DeviceCtx *c, float *out_dev, const fl
         a.hq = (__half *)L->hq.p; a.hs = (float *)L->hs.p; a.Y = (float *)L->pd.p;
         a.sync = c->dec_sync; a.exp_tab = c->exp_tab_dev; a.status = c->status;
         a.M = M; a.act_smem = act_smem;
-        a.wpk1 = dec_pick_wpk(nkb1, 1); a.wpk2 = dec_pick_wpk(nkb2, 2);
+        a.wpk1 = dec_pick_wpk(nkb1, 1); a.wpk2 = dec_pick_wpk(nkb2, 2); a.local2 = local2;
 #ifdef COLI_DECODE_PROBE
         a.probe = g_decode_probe;
 #endif

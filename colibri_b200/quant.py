@@ -12,6 +12,8 @@ stored exactly as a converted checkpoint would be:
                         through the f32 `scales` parameter of the C ABI.
 * `quant_mxfp4`         E2M1 + UE8M0 per 32 (fmt=7): c/tools/make_deepseek_v4_tiny.py:64-121.
 * `quant_int8_rows`     per-row int8 (fmt=1): c/quant.h:953-962.
+* `quant_fp8_blocks`    FP8 E4M3 bytes + one f32 scale per 128x128 block (fmt=8): the layout
+                        c/quant.h:446-452 reads; rounding as a float8_e4m3fn cast.
 
 Packing: two nibbles per byte, low nibble = even column; int4 stores value+8.
 """
@@ -93,6 +95,44 @@ def quant_mxfp4(w: np.ndarray):
     return pack_nibbles(code.reshape(O, I)), (e + 127).astype(np.uint8)
 
 
+def e4m3_values() -> np.ndarray:
+    """The 256 values of FP8 E4M3 "FN" (sign 1, exponent 4 bias 7, mantissa 3; 0x7F / 0xFF NaN)."""
+    b = np.arange(256)
+    e, m = (b >> 3) & 15, b & 7
+    v = np.where(e == 0, np.ldexp(m.astype(np.float64), -9), np.ldexp((8 + m).astype(np.float64), e - 10))
+    v = np.where(b & 0x80, -v, v).astype(np.float32)
+    v[(e == 15) & (m == 7)] = np.float32(np.nan)            # both 0x7F and 0xFF: the same quiet NaN
+    return v
+
+
+def quant_fp8_blocks(w: np.ndarray):
+    """f32 [O, I] -> (E4M3 bytes [O, I], f32 scales [ceil(O/128) * ceil(I/128)]): fmt=8, the
+    layout of c/quant.h:446-452 (the GLM-5.2-FP8 checkpoints): one scale per 128x128 block,
+    scale = amax/448 (multiplied back in on decode), values rounded to the nearest E4M3
+    number with ties to the even mantissa, as a float8_e4m3fn cast does."""
+    w = np.asarray(w, np.float32)
+    O, I = w.shape
+    nbo, nbi = (O + 127) // 128, (I + 127) // 128
+    tab = e4m3_values()
+    pos = tab[:127].astype(np.float64)                      # 0 .. 448, ascending, codes 0..126
+    q = np.zeros((O, I), np.uint8)
+    sc = np.zeros((nbo, nbi), np.float32)
+    for bo in range(nbo):
+        for bi in range(nbi):
+            blk = w[bo * 128:(bo + 1) * 128, bi * 128:(bi + 1) * 128]
+            amax = float(np.abs(blk).max()) if blk.size else 0.0
+            s = np.float32(amax / 448.0) if amax > 0 else np.float32(1.0)
+            sc[bo, bi] = s
+            a = np.minimum(np.abs(blk.astype(np.float64) / np.float64(s)), 448.0)
+            hi = np.clip(np.searchsorted(pos, a, side="left"), 1, 126)
+            lo = hi - 1
+            dlo, dhi = a - pos[lo], pos[hi] - a
+            code = np.where(dlo < dhi, lo, np.where(dhi < dlo, hi, np.where(lo % 2 == 0, lo, hi)))
+            code = np.where(a <= 0, 0, code)
+            q[bo * 128:(bo + 1) * 128, bi * 128:(bi + 1) * 128] = (code | np.where(np.signbit(blk), 0x80, 0)).astype(np.uint8)
+    return q, sc.reshape(-1).copy()
+
+
 def dequant(packed, scales, fmt, I, gs=0):
     """Reference decode to f32 [O, I] (tests and documentation)."""
     if fmt == 0:
@@ -113,6 +153,13 @@ def dequant(packed, scales, fmt, I, gs=0):
     raise ValueError(fmt)
 
 
+def dequant_fp8(q, scales, I):
+    O = q.shape[0]
+    nbi = (I + 127) // 128
+    sc = np.repeat(np.repeat(scales.reshape(-1, nbi), 128, axis=0)[:O], 128, axis=1)[:, :I]
+    return e4m3_values()[q] * sc
+
+
 class QTensor:
     """One quantised matrix on the host, as the engine's QT record holds it
     (c/colibri.c:218-235): weight bytes, scales, format, shape, group size."""
@@ -128,6 +175,8 @@ class QTensor:
         return self.w.nbytes + (self.s.nbytes if self.s is not None else 0)
 
     def dequant(self):
+        if self.fmt == 8:
+            return dequant_fp8(self.w.reshape(self.O, -1), self.s, self.I)
         return dequant(self.w.reshape(self.O, -1), self.s, self.fmt, self.I, self.gs)
 
 
@@ -149,4 +198,7 @@ def quantize(w, fmt, gs=0, scale_dtype=np.float32) -> QTensor:
     if fmt == 7:
         q, s = quant_mxfp4(w)
         return QTensor(q, s, 7, I, O)
+    if fmt == 8:
+        q, s = quant_fp8_blocks(w)
+        return QTensor(q, s, 8, I, O)
     raise ValueError(f"unsupported fmt {fmt}")

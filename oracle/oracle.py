@@ -83,9 +83,16 @@ class Oracle:
         L.orc_union.restype = C.c_int
         L.orc_moe_layer.restype = C.c_int
         L.orc_num_threads.restype = C.c_int
+        L.orc_e4m3_decode.restype = C.c_float
+        L.orc_e4m3_decode.argtypes = [C.c_uint8]
 
     def threads(self) -> int:
         return self.lib.orc_num_threads()
+
+    def e4m3_table(self) -> np.ndarray:
+        """The 256 values of FP8 E4M3 (c/quant.h:468-503), as the engine hands them to the
+        backend through coli_cuda_fp8_set_lut."""
+        return np.array([self.lib.orc_e4m3_decode(b) for b in range(256)], np.float32)
 
     def matmul(self, x, t):
         x = _f32(x).reshape(-1, t.I)
@@ -253,6 +260,8 @@ class RefCpu:
         elif t.fmt == 7:
             (L.ref_matmul_mxfp4_i8 if idot else L.ref_matmul_mxfp4)(
                 *a, _ptr(t.w, _u8p), _ptr(t.s, _u8p), *dims)
+        elif t.fmt == 8:
+            L.ref_matmul_fp8(*a, _ptr(t.w, _u8p), _ptr(t.s, _f32p), *dims)
         else:
             raise ValueError("fmt")
         return y
@@ -263,6 +272,11 @@ class RefCpu:
         uu = self.matmul(x, u)
         h = (gg / (np.float32(1) + np.exp(-gg, dtype=np.float32))) * uu
         return self.matmul(h.astype(np.float32), d)
+
+    def e4m3_table(self) -> np.ndarray:
+        out = np.zeros(256, np.float32)
+        self.lib.ref_e4m3_table(_ptr(out, _f32p))
+        return out
 
     def pack_int4(self, w, bits=4):
         w = _f32(w)

@@ -156,8 +156,52 @@ ORC_API void orc_matmul_mxfp4(float *y, const float *x, const uint8_t *q4, const
     }
 }
 
+/* c/quant.h:430-546 — fmt=8: O*I raw FP8 E4M3 bytes (sign 1, exponent 4 with bias 7,
+ * mantissa 3; exponent 0 is subnormal; exponent 15 is an ordinary binade except mantissa 7,
+ * which is NaN: the OCP "FN" convention, largest finite value 448) and one f32 scale per
+ * 128x128 block of the matrix, scale[(o/128)*ceil(I/128) + i/128], multiplied in. Inside a
+ * block row the products are summed in f32; the block sums times their scales are added in
+ * double and rounded to f32 once. A NaN byte propagates. */
+ORC_API float orc_e4m3_decode(uint8_t b) {
+    int e = (b >> 3) & 15, m = b & 7;
+    float v;
+    if (e == 15 && m == 7) {
+        union { uint32_t u; float f; } n;
+        n.u = 0x7fc00000u;
+        return n.f;                               /* both 0x7F and 0xFF: the same quiet NaN */
+    } else if (e == 0) {
+        v = ldexpf((float)m, -9);                 /* m/8 * 2^-6 */
+    } else {
+        v = ldexpf((float)(8 + m), e - 10);       /* (1 + m/8) * 2^(e-7) */
+    }
+    return (b & 0x80) ? -v : v;
+}
+ORC_API void orc_matmul_fp8(float *y, const float *x, const uint8_t *q8, const float *bscale,
+                            int S, int I, int O) {
+    int nblk = (I + 127) / 128;
+    float lut[256];
+    for (int b = 0; b < 256; b++) lut[b] = orc_e4m3_decode((uint8_t)b);
+#pragma omp parallel for schedule(static)
+    for (int o = 0; o < O; o++) {
+        const uint8_t *w = q8 + (int64_t)o * I;
+        const float *scl = bscale + (int64_t)(o / 128) * nblk;
+        for (int s = 0; s < S; s++) {
+            const float *xs = x + (int64_t)s * I;
+            double a = 0;
+            for (int bi = 0; bi * 128 < I; bi++) {
+                int base = bi * 128, blen = 128;
+                if (base + blen > I) blen = I - base;
+                float acc = 0;
+                for (int i = base; i < base + blen; i++) acc += lut[w[i]] * xs[i];
+                a += (double)acc * scl[bi];
+            }
+            y[(int64_t)s * O + o] = (float)a;
+        }
+    }
+}
+
 /* One quantised tensor as the engine's QT holds it (c/colibri.c:218-235):
- * fmt 0=f32, 1=int8 row, 2=int4 row, 3=int2 row, 4=int4 grouped, 7=MXFP4. */
+ * fmt 0=f32, 1=int8 row, 2=int4 row, 3=int2 row, 4=int4 grouped, 7=MXFP4, 8=FP8 blocks. */
 typedef struct {
     const void *w;
     const void *s; /* f32 scales (fmt 1,2,3,4), ue8m0 bytes (fmt 7), NULL (fmt 0) */
@@ -176,6 +220,7 @@ ORC_API int orc_matmul_qt(float *y, const float *x, const OrcTensor *t, int S) {
         orc_matmul_i4_grouped(y, x, (const uint8_t *)t->w, (const float *)t->s, S, t->I, t->O, t->gs);
         return 1;
     case 7: orc_matmul_mxfp4(y, x, (const uint8_t *)t->w, (const uint8_t *)t->s, S, t->I, t->O); return 1;
+    case 8: orc_matmul_fp8(y, x, (const uint8_t *)t->w, (const float *)t->s, S, t->I, t->O); return 1;
     }
     return 0;
 }

@@ -33,6 +33,12 @@ REF_API void ref_matmul_mxfp4(float *y, const float *x, const uint8_t *q, const 
 REF_API void ref_matmul_mxfp4_i8(float *y, const float *x, const uint8_t *q, const uint8_t *e8, int S, int I, int O) {
     matmul_mxfp4_i8(y, x, q, e8, S, I, O);
 }
+REF_API void ref_matmul_fp8(float *y, const float *x, const uint8_t *q8, const float *bscale, int S, int I, int O) {
+    matmul_fp8(y, x, q8, bscale, S, I, O);
+}
+REF_API void ref_e4m3_table(float *out) {
+    for (int b = 0; b < 256; b++) out[b] = e4m3_decode((uint8_t)b);
+}
 REF_API void ref_pack_int4(const float *w, uint8_t *q4, float *scale, int O, int I, int bits) {
     pack_int4(w, q4, scale, O, I, bits);
 }

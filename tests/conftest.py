@@ -30,7 +30,11 @@ def refcpu():
 def be():
     """The CUDA backend, initialised on device 0. GPU tests only."""
     from colibri_b200.backend import Backend
+    from oracle.oracle import Oracle
     b = Backend()
     assert b.init_devices((0,)) == 1, "coli_cuda_init failed"
+    # the engine hands over its FP8 E4M3 decode table once after init (c/colibri.c:9366-9368)
+    lut = Oracle().e4m3_table()
+    assert b.fp8_set_lut(lut.ctypes.data) == 1
     yield b
     b.shutdown()

@@ -30,6 +30,8 @@ CASES = [  # name, fmt, gs, S, I, O  (shapes of c/tests/test_i4_grouped.c and te
     ("row_int4", 2, 0, 3, 130, 5), ("row_int8", 1, 0, 2, 96, 7), ("f32", 0, 0, 2, 64, 5),
     ("mx_64", 7, 0, 1, 64, 32), ("mx_batch", 7, 0, 4, 128, 64), ("mx_wide", 7, 0, 1, 2048, 16),
     ("mx_96", 7, 0, 1, 96, 8),
+    # fmt 8: FP8 E4M3 bytes + one f32 scale per 128x128 block (c/quant.h:526-546), ragged edges included
+    ("fp8_blocks", 8, 0, 2, 384, 200), ("fp8_ragged", 8, 0, 3, 200, 130),
 ]
 
 
@@ -96,6 +98,7 @@ def main():
         out[name + ".x"] = x
         out[name + ".y"] = y
         out[name + ".meta"] = np.array([fmt, gs, S, I, O], np.int32)
+    out["e4m3_table"] = ref.e4m3_table()          # the reference's own 256-entry decode table
     # fused expert: gate/up/down through the reference kernels + its SwiGLU expression
     rng = np.random.default_rng(77)
     D, I = 256, 128

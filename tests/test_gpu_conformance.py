@@ -134,3 +134,25 @@ def test_reference_conformance_sequence(be):
         be.tensor_free(t)
     assert be.stats_tuple(-1) == (0, 0)
     assert be.physical_bytes(-1) == 0
+
+
+# ---- the reference's own test programs, linked against this library ---------------------
+# oracle/Makefile compiles c/tests/test_mxfp4_cuda.cu (+ c/tests/mxfp4_ref.c, the reference's
+# CPU MXFP4 decoder) and c/tests/test_pipe_cuda.cu unchanged and links them against
+# libcoli_cuda_b200.so in place of c/backend_cuda.cu. They run as separate processes (each
+# calls coli_cuda_init / coli_cuda_shutdown itself).
+import os
+import subprocess
+
+_REF_DIR = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref")
+
+
+@pytest.mark.parametrize("prog,marker", [("ref_test_mxfp4_cuda", None), ("ref_test_pipe_cuda", "pipe tests: ok")])
+def test_reference_test_programs_pass_against_this_library(prog, marker):
+    path = os.path.join(_REF_DIR, prog)
+    if not os.path.exists(path):
+        pytest.skip("oracle/_ref conformance programs not built (reference checkout absent at build time)")
+    run = subprocess.run([path], capture_output=True, text=True, timeout=300)
+    assert run.returncode == 0, run.stdout[-2000:] + run.stderr[-2000:]
+    if marker:
+        assert marker in run.stdout

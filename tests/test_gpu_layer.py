@@ -81,10 +81,11 @@ def test_olmoe_accounting(be, olmoe_layer):
     assert n_all >= n and b_all >= b
 
 
-@pytest.mark.parametrize("name,M", [("c3", 1), ("c3", 8), ("c4", 4), ("c4", 8)])
+@pytest.mark.parametrize("name,M", [("c3", 1), ("c3", 8), ("c3", 64), ("c3", 512), ("c4", 4), ("c4", 8)])
 def test_deepseek_shapes(be, oracle, name, M):
     """Full D=7168 / I=2048 shapes, 256 routed experts + shared; to keep host-side
-    generation short, the 256 expert slots cycle through 6 distinct weight sets."""
+    generation short, the 256 expert slots cycle through 6 distinct weight sets. M = 64
+    runs the streaming kernels, M = 512 the tensor-core grouped GEMM (default kernel rule)."""
     cfg = W.CONFIGS[name]
     distinct = 6
     L = W.HostLayerWeights(dict(cfg, E=distinct), 5)

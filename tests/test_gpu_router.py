@@ -135,3 +135,28 @@ def test_reference_router_shape_pipe_router(be, oracle):
     assert flips == 0        # the reference's own test tolerates 4 flips in 200; here none
     for p in (rwd, rbd, xd):
         be.pipe_free(0, p)
+
+
+@pytest.mark.parametrize("E,K", [(6, 2), (10, 4), (7, 3), (33, 8)])
+@pytest.mark.parametrize("M", [1, 2, 5, 8, 9])
+@pytest.mark.parametrize("gating", [0, 1])
+def test_expert_counts_that_are_not_multiples_of_four(be, oracle, E, K, M, gating):
+    """Rows of E scores start 16-byte aligned only when E % 4 == 0: the routing must not
+    read them as float4 otherwise (decode-sized M takes the fused kernel, larger M the
+    stand-alone routing kernel)."""
+    cfg = dict(W.CONFIGS["c2_small"], E=E, K=K, gating=gating, norm_topk=gating)
+    L = W.HostLayerWeights(cfg, 90 + E)
+    g, u, d, sh = upload_layer(be, L)
+    lay = MoeLayer(be, cfg["D"], cfg["I"], E, K, g, u, d, gating, gating, 2.5 if gating else 1.0,
+                   router_bias=L.router_bias, max_rows=16)
+    x = W.activations(M, cfg["D"], 7)
+    lg = W.router_logits(M, E, 300 + M)
+    out, idx, w, keff = lay(x, lg)
+    want, oi, ow, ok_, _ = oracle.moe_layer(host_layer(cfg, L, 2.5 if gating else 1.0), x, lg)
+    assert np.array_equal(idx, oi) and np.array_equal(keff, ok_)
+    assert np.array_equal(w.view(np.uint32), ow.view(np.uint32))
+    from tests.util import max_rel_err
+    assert max_rel_err(out, want) <= 1e-3
+    assert be.kernel_status(0) == 0
+    lay.free()
+    free_layer(be, (g, u, d, sh))

@@ -102,7 +102,7 @@ def test_e8m0_edges(oracle, exp, check):
 
 
 # ---- vectors produced by the reference's kernels ---------------------------
-CASE_NAMES = sorted({k.split(".")[0] for k in GOLD.files if not k.startswith("mlp")})
+CASE_NAMES = sorted({k.split(".")[0] for k in GOLD.files if not k.startswith("mlp") and "." in k})
 
 
 @pytest.mark.parametrize("name", CASE_NAMES)
@@ -113,7 +113,7 @@ def test_golden_matmul(oracle, name):
     x, y = GOLD[name + ".x"], GOLD[name + ".y"]
     got = oracle.matmul(x, t)
     # criterion of c/tests/test_i4_grouped.c: error relative to the summed |terms|
-    wdq = np.abs(dequant(t.w.reshape(O, -1), t.s, fmt, I, gs))
+    wdq = np.abs(t.dequant())
     mag = np.abs(x) @ wdq.T
     assert np.all(np.abs(got - y) <= 2e-6 * mag + 1e-30)
 
@@ -220,3 +220,25 @@ def test_layer_vs_dense(oracle, name):
             want[s] += ffn(x[s].astype(np.float64), *L.shared)
     np.testing.assert_allclose(out1, want, rtol=2e-4, atol=1e-6)
     assert set(uniq.tolist()) == set(idx.ravel().tolist())
+
+
+def test_e4m3_table_is_the_references(oracle):
+    # c/quant.h:468-503: the 256-entry table the engine hands to coli_cuda_fp8_set_lut
+    from colibri_b200.quant import e4m3_values
+    want = GOLD["e4m3_table"].view(np.uint32)
+    assert np.array_equal(oracle.e4m3_table().view(np.uint32), want)
+    assert np.array_equal(e4m3_values().view(np.uint32), want)
+
+
+def test_fp8_quantiser_rounds_like_a_float8_cast():
+    import torch
+    from colibri_b200.quant import quant_fp8_blocks
+    rng = np.random.default_rng(3)
+    w = (rng.standard_normal((200, 384)) * 0.02).astype(np.float32)
+    w[0, :5] = [0.0, -0.0, 1e-9, -1e-9, 0.5]
+    q, s = quant_fp8_blocks(w)
+    sc = np.repeat(np.repeat(s.reshape(-1, 3), 128, axis=0)[:200], 128, axis=1)[:, :384]
+    want = torch.from_numpy(w / sc).to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+    assert np.array_equal(q & 0x7F, want & 0x7F)            # magnitudes: nearest, ties to even
+    nz = (q & 0x7F) != 0
+    assert np.array_equal(q[nz], want[nz])

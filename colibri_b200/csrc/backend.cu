@@ -21,6 +21,7 @@
 #include "router.cuh"
 #include "moe_decode.cuh"
 #include "gemm_tc.cuh"
+#include "ep_kernels.cuh"
 
 // ---------------------------------------------------------------------------
 // Context
@@ -40,6 +41,7 @@ struct DeviceCtx {
     Buf stage_w, stage_s;                     // upload staging
     Buf x, y, bq, bs, pg, pu, hq, hs, pd, segs1, segs2, ctl, gbuf, ubuf, misc;
     Buf pipe[27];
+    Buf ep_ws, ep_x, ep_y;                    // expert-parallel layer: plan tables, permuted rows (streaming-kernel path)
     float *host_x = nullptr, *host_y = nullptr;
     size_t host_x_cap = 0, host_y_cap = 0;
     int group_pending = 0;
@@ -209,7 +211,8 @@ extern "C" void coli_cuda_shutdown(void) {
         if (cudaSetDevice(c->device) != cudaSuccess) { (void)cudaGetLastError(); continue; }
         cudaDeviceSynchronize();
         Buf *bufs[] = {&c->stage_w, &c->stage_s, &c->x, &c->y, &c->bq, &c->bs, &c->pg, &c->pu, &c->hq,
-                       &c->hs, &c->pd, &c->segs1, &c->segs2, &c->ctl, &c->gbuf, &c->ubuf, &c->misc};
+                       &c->hs, &c->pd, &c->segs1, &c->segs2, &c->ctl, &c->gbuf, &c->ubuf, &c->misc,
+                       &c->ep_ws, &c->ep_x, &c->ep_y};
         for (Buf *b : bufs) free_buf(b);
         for (int s = 0; s < 27; s++) free_buf(&c->pipe[s]);
         if (c->host_x) cudaFreeHost(c->host_x);
@@ -835,10 +838,11 @@ struct TcSegs {
     int ntask[4] = {0, 0, 0, 0};
 };
 static void add_tc_seg(TcSegs *ts, const ColiCudaTensor *t, float *out, const __half *bq, const float *binv,
-                       const int *lo_flag, int nrows, int npad, int pos0) {
+                       const int *lo_flag, int nrows, int npad, int pos0, const int *rowdst = nullptr) {
     TcSeg s;
     std::memset(&s, 0, sizeof(s));
     s.w = t->pk; s.rowscale = t->rowscale; s.bq = bq; s.binv = binv; s.lo_flag = lo_flag; s.out = out;
+    s.rowdst = rowdst;
     s.nrows = nrows; s.npad = npad; s.pos0 = pos0;
     s.O = t->O; s.nkb64 = t->I / TC_KB;
     s.task0 = ts->ntask[t->mode];
@@ -889,9 +893,13 @@ static int group_tc_ok(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
 // x_dev [total (or 1 when bcast), D] -> y_dev [total, D]; passes of up to 128 rows per expert.
 // y_dev must be 16-byte aligned (the accumulators are stored as float4).
 // rowsrc (host, optional): source row of x for every row of the call (a gather).
+// scatter_out: with rowsrc, the result of row r also goes to row rowsrc[r] of y_dev (the call
+// then works in place on a buffer whose rows are grouped differently: the expert-parallel layer).
+// x_bf16: x_dev holds bf16 rows.
 static int group_device_tc(DeviceCtx *c, ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
                            ColiCudaTensor *const *downs, const int *rows, int count, int D, int I,
-                           int total, float *y_dev, const float *x_dev, int bcast, const int *rowsrc = nullptr) {
+                           int total, float *y_dev, const float *x_dev, int bcast, const int *rowsrc = nullptr,
+                           int scatter_out = 0, int x_bf16 = 0) {
     // device tables: [rowsrc (total) | per pass: row0, npad, pos0, rows, lo flag of x, lo flag of h | per row group: pass, rg]
     std::vector<int> pass_row0, pass_npad, pass_rows, pass_pos0, pass_expert, grp_pass, grp_rg;
     int off = 0, padded = 0;
@@ -933,7 +941,7 @@ static int group_device_tc(DeviceCtx *c, ColiCudaTensor *const *gates, ColiCudaT
     __half *bq = (__half *)c->bq.p, *hq = (__half *)c->hq.p;
     float *binv = (float *)c->bs.p, *hinv = (float *)c->hs.p, *G = (float *)c->pg.p, *U = (float *)c->pu.p;
     k_prep_umma<<<ngrp, 256, 0, c->stream>>>(bq, binv, x_dev, nullptr, d_rowsrc, d_grp_pass, d_grp_rg, d_pass_row0,
-                                             d_pass_npad, d_pass_pos0, d_pass_rows, d_lo_x, D);
+                                             d_pass_npad, d_pass_pos0, d_pass_rows, d_lo_x, D, x_bf16);
     c->last_launches++;
     TcSegs t1, t2;
     for (int p = 0; p < npass; p++) {
@@ -942,11 +950,12 @@ static int group_device_tc(DeviceCtx *c, ColiCudaTensor *const *gates, ColiCudaT
         const __half *hp = hq + (size_t)2 * I * pass_row0[p];
         add_tc_seg(&t1, gates[e], G, bp, binv + pass_pos0[p], d_lo_x + p, pass_rows[p], pass_npad[p], pass_pos0[p]);
         add_tc_seg(&t1, ups[e], U, bp, binv + pass_pos0[p], d_lo_x + p, pass_rows[p], pass_npad[p], pass_pos0[p]);
-        add_tc_seg(&t2, downs[e], y_dev, hp, hinv + pass_pos0[p], d_lo_h + p, pass_rows[p], pass_npad[p], pass_pos0[p]);
+        add_tc_seg(&t2, downs[e], y_dev, hp, hinv + pass_pos0[p], d_lo_h + p, pass_rows[p], pass_npad[p], pass_pos0[p],
+                   scatter_out ? d_rowsrc : nullptr);
     }
     if (!run_tc_segs(c, &t1, &c->segs1)) return 0;
     k_prep_umma<<<ngrp, 256, 0, c->stream>>>(hq, hinv, G, U, nullptr, d_grp_pass, d_grp_rg, d_pass_row0, d_pass_npad,
-                                             d_pass_pos0, d_pass_rows, d_lo_h, I);
+                                             d_pass_pos0, d_pass_rows, d_lo_h, I, 0);
     c->last_launches++;
     if (!run_tc_segs(c, &t2, &c->segs2)) return 0;
     return cuda_ok(cudaGetLastError(), "expert group launch");
@@ -1374,6 +1383,122 @@ extern "C" int coli_cuda_moe_combine_dev(int device, float *out_dev, const float
                                                                      shared_dev, M, K, D);
     c->last_launches++;
     return cuda_ok(cudaGetLastError(), "combine launch");
+}
+
+// ---------------------------------------------------------------------------
+// Expert-parallel layer, device side (additive; the reference has no collective path:
+// it pins whole experts to devices and moves rows host -> device per call,
+// c/colibri.c:4819-4839, 8367-8417). One process per GPU; the host issues the NCCL
+// all-to-all exchanges between these calls. All work goes to the backend's stream.
+// ---------------------------------------------------------------------------
+// Plan + pack. From this rank's routing (idx [m,K], keff [m]) and the expert placement
+// (dest[e] = owning rank, slot[e] = index among that rank's experts; G ranks, `slots`
+// experts per rank at most) it produces, on the device:
+//   counts [G*slots]   live entries per (destination rank, local expert)
+//   entry_of [m*K]     position of every live entry in the send buffer, -1 for dead ones
+//   send [n, D]        the rows in (destination rank, local expert, row order), as bf16
+//                      (payload_bf16; *inexact is raised if a value is not exact in bf16,
+//                      which would change results: the caller must then use f32) or f32
+// The send buffer must hold m*K rows.
+extern "C" int coli_cuda_ep_plan_dev(int device, const float *x_dev, int m, int D, int K, const int *idx_dev,
+                                     const int *keff_dev, const int *dest_dev, const int *slot_dev, int E,
+                                     int G, int slots, int payload_bf16, int *counts_dev, int *entry_of_dev,
+                                     void *send_dev, int *inexact_dev) {
+    if (fault_injected()) return 0;
+    DeviceCtx *c = find_ctx(device);
+    const int nb = G * slots;
+    if (!x_dev || !idx_dev || !keff_dev || !dest_dev || !slot_dev || !counts_dev || !entry_of_dev || !send_dev ||
+        !inexact_dev || m < 1 || K < 1 || K > 31 || E < 1 || G < 1 || slots < 1 || D < 4 || D % 4 || !select_ctx(c)) return 0;
+    if (!reserve(c, &c->ep_ws, ((size_t)nb + 1 + (size_t)m * K) * sizeof(int))) return 0;
+    int *off = static_cast<int *>(c->ep_ws.p), *row_of = off + nb + 1;
+    if (!cuda_ok(cudaMemsetAsync(counts_dev, 0, (size_t)nb * sizeof(int), c->stream), "ep plan") ||
+        !cuda_ok(cudaMemsetAsync(entry_of_dev, 0xFF, (size_t)m * K * sizeof(int), c->stream), "ep plan")) return 0;
+    const int n = m * K;
+    k_ep_count<<<(n + 255) / 256, 256, 0, c->stream>>>(counts_dev, idx_dev, keff_dev, dest_dev, slot_dev, m, K, slots);
+    k_ep_offsets<<<1, 256, 0, c->stream>>>(off, counts_dev, nb);
+    k_ep_place<<<(E + 7) / 8, 256, 0, c->stream>>>(entry_of_dev, row_of, off, idx_dev, keff_dev, dest_dev, slot_dev, m, K, E, slots);
+    if (payload_bf16) k_ep_gather<true><<<n, 256, 0, c->stream>>>(send_dev, x_dev, row_of, off + nb, D, inexact_dev);
+    else k_ep_gather<false><<<n, 256, 0, c->stream>>>(send_dev, x_dev, row_of, off + nb, D, inexact_dev);
+    c->last_launches += 4;
+    return cuda_ok(cudaGetLastError(), "ep plan launch");
+}
+
+// Expert FFN over the rows this rank received. x_dev holds them in receive order (source
+// rank, local expert, row order), recv_counts (host) [nsrc][nslots] says how many; the
+// results go to y_dev [n, D] f32 in the same receive order, ready to be sent back. With the
+// tensor-core kernel the regrouping per expert is a gather in its activation preparation and
+// a scatter in its read-back, so no row is copied; the streaming kernels get permuted copies.
+extern "C" int coli_cuda_ep_expert_group_dev(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
+                                             ColiCudaTensor *const *downs, int nslots, const int *recv_counts,
+                                             int nsrc, float *y_dev, const void *x_dev, int x_bf16) {
+    if (fault_injected()) return 0;
+    if (!gates || !ups || !downs || !recv_counts || nslots < 1 || nsrc < 1 || !y_dev || !x_dev) return 0;
+    std::vector<int> seg_start((size_t)nsrc * nslots);
+    int n = 0;
+    for (int s = 0; s < nsrc; s++)
+        for (int e = 0; e < nslots; e++) {
+            if (recv_counts[s * nslots + e] < 0) return 0;
+            seg_start[(size_t)s * nslots + e] = n; n += recv_counts[s * nslots + e];
+        }
+    if (n == 0) return 1;
+    std::vector<ColiCudaTensor *> g, u, d;
+    std::vector<int> rows, rowmap;
+    rowmap.reserve(n);
+    for (int e = 0; e < nslots; e++) {
+        int re = 0;
+        for (int s = 0; s < nsrc; s++) {
+            const int cnt = recv_counts[s * nslots + e], st = seg_start[(size_t)s * nslots + e];
+            for (int r = 0; r < cnt; r++) rowmap.push_back(st + r);
+            re += cnt;
+        }
+        if (re) { g.push_back(gates[e]); u.push_back(ups[e]); d.push_back(downs[e]); rows.push_back(re); }
+    }
+    int device, D, I, total, max_rows, all_packed, any_packed;
+    if (!group_shape_ok(g.data(), u.data(), d.data(), rows.data(), (int)g.size(), &device, &D, &I, &total,
+                        &max_rows, &all_packed, &any_packed)) return 0;
+    if (!all_packed && any_packed) return 0;
+    DeviceCtx *c = find_ctx(device);
+    if (!select_ctx(c)) return 0;
+    timing_begin(c);
+    int ok;
+    if (all_packed && D % 128 == 0 && I % 128 == 0 && (reinterpret_cast<uintptr_t>(y_dev) & 15) == 0 &&
+        group_tc_ok(g.data(), u.data(), d.data(), (int)g.size(), max_rows, total)) {
+        ok = group_device_tc(c, g.data(), u.data(), d.data(), rows.data(), (int)g.size(), D, I, total, y_dev,
+                             static_cast<const float *>(x_dev), 0, rowmap.data(), 1, x_bf16);
+    } else {
+        if (!reserve(c, &c->ep_ws, ((size_t)n) * sizeof(int)) || !reserve(c, &c->ep_x, (size_t)n * D * sizeof(float)) ||
+            !reserve(c, &c->ep_y, (size_t)n * D * sizeof(float))) return 0;
+        int *map_dev = static_cast<int *>(c->ep_ws.p);
+        if (!cuda_ok(cudaMemcpyAsync(map_dev, rowmap.data(), (size_t)n * sizeof(int), cudaMemcpyHostToDevice, c->stream), "ep row map")) return 0;
+        if (x_bf16) k_ep_permute<true, false><<<n, 256, 0, c->stream>>>((float *)c->ep_x.p, x_dev, map_dev, n, D);
+        else k_ep_permute<false, false><<<n, 256, 0, c->stream>>>((float *)c->ep_x.p, x_dev, map_dev, n, D);
+        c->last_launches++;
+        ok = group_device(c, g.data(), u.data(), d.data(), rows.data(), (int)g.size(), D, I, total, max_rows, all_packed,
+                          (float *)c->ep_y.p, (const float *)c->ep_x.p, nullptr);
+        if (ok) {
+            k_ep_permute<false, true><<<n, 256, 0, c->stream>>>(y_dev, c->ep_y.p, map_dev, n, D);
+            c->last_launches++;
+            ok = cuda_ok(cudaGetLastError(), "ep permute launch");
+        }
+    }
+    timing_end(c);
+    if (ok) count_group(c, (int)g.size(), total);
+    return ok;
+}
+
+// out[s] = sum over the first keff[s] selections of w[s,kk] * y[entry_of[s,kk]] (+ shared[s]):
+// y holds the answers in send-buffer order, entry_of is the plan's table.
+extern "C" int coli_cuda_ep_combine_dev(int device, float *out_dev, const float *y_dev, const int *entry_of_dev,
+                                        const float *w_dev, const int *keff_dev, const float *shared_dev, int m,
+                                        int K, int D) {
+    DeviceCtx *c = find_ctx(device);
+    if (!out_dev || !y_dev || !entry_of_dev || !w_dev || !keff_dev || m < 1 || K < 1 || D < 4 || D % 4 || !select_ctx(c)) return 0;
+    if ((reinterpret_cast<uintptr_t>(out_dev) | reinterpret_cast<uintptr_t>(y_dev) | reinterpret_cast<uintptr_t>(shared_dev)) & 15) return 0;
+    const size_t n4 = (size_t)m * D / 4;
+    k_ep_combine<<<(unsigned)((n4 + 255) / 256), 256, 0, c->stream>>>(out_dev, y_dev, entry_of_dev, w_dev, keff_dev,
+                                                                   shared_dev, m, K, D);
+    c->last_launches++;
+    return cuda_ok(cudaGetLastError(), "ep combine launch");
 }
 
 // ---------------------------------------------------------------------------

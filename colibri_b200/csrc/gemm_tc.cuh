@@ -98,6 +98,7 @@ struct TcSeg {
     const float *binv;       // [nrows] 2^-r of the pass rows
     const int *lo_flag;      // non-zero when some lo term of the pass is non-zero (else the lo MMAs are skipped)
     float *out;              // [.. , O] row-major; row (pos0 + n) receives feature o
+    const int *rowdst;       // optional: the result of row (pos0 + n) goes to row rowdst[pos0 + n] of `out` instead
     int nrows, npad, pos0;
     int O, nkb64;            // output features, 64-column blocks along the contraction
     int task0;               // first task of this segment (tasks = ceil(O / 256))
@@ -179,8 +180,16 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
 // row scale is taken over the whole row;
 // 2^-r goes to binv. rowsrc: optional gather (row -> source row of x). u: when set, the
 // row is silu(x)*u (the SwiGLU of complete gate/up sums) instead of x.
-__device__ __forceinline__ float4 tc_row_vals(const float *xr, const float *ur, int k) {
-    float4 v = *reinterpret_cast<const float4 *>(xr + k);
+// xr points at a row of f32 values, or (x_bf16) of bf16 values
+__device__ __forceinline__ float4 tc_row_vals(const float *xr, const float *ur, int k, bool x_bf16 = false) {
+    float4 v;
+    if (x_bf16) {
+        const uint2 r = *reinterpret_cast<const uint2 *>(reinterpret_cast<const unsigned short *>(xr) + k);
+        v = make_float4(__uint_as_float(r.x << 16), __uint_as_float(r.x & 0xFFFF0000u),
+                        __uint_as_float(r.y << 16), __uint_as_float(r.y & 0xFFFF0000u));
+    } else {
+        v = *reinterpret_cast<const float4 *>(xr + k);
+    }
     if (ur) {
         float4 w = *reinterpret_cast<const float4 *>(ur + k);
         v.x = (v.x / (1.0f + expf(-v.x))) * w.x; v.y = (v.y / (1.0f + expf(-v.y))) * w.y;
@@ -198,7 +207,8 @@ __global__ void __launch_bounds__(256) k_prep_umma(__half *__restrict__ bq, floa
                             const int *__restrict__ rowsrc, const int *__restrict__ grp_pass,
                             const int *__restrict__ grp_rg, const int *__restrict__ pass_row0,
                             const int *__restrict__ pass_npad, const int *__restrict__ pass_pos0,
-                            const int *__restrict__ pass_rows, int *__restrict__ pass_lo, int K) {
+                            const int *__restrict__ pass_rows, int *__restrict__ pass_lo, int K,
+                            int x_bf16) {
     __shared__ float s_scale[8];
     __shared__ int s_src[8];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -211,11 +221,12 @@ __global__ void __launch_bounds__(256) k_prep_umma(__half *__restrict__ bq, floa
         if (n < nrows) {
             const int wid = pos0 + n;
             src = rowsrc ? rowsrc[wid] : wid;
-            const float *xr = x + (size_t)src * K;
+            const float *xr = x_bf16 ? reinterpret_cast<const float *>(reinterpret_cast<const unsigned short *>(x) + (size_t)src * K)
+                                     : x + (size_t)src * K;
             const float *ur = u ? u + (size_t)src * K : nullptr;
             float m = 0.f;
             for (int k = lane * 4; k < K; k += 128) {
-                float4 v = tc_row_vals(xr, ur, k);
+                float4 v = tc_row_vals(xr, ur, k, x_bf16);
                 m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
             }
             m = warp_max(m);
@@ -229,15 +240,16 @@ __global__ void __launch_bounds__(256) k_prep_umma(__half *__restrict__ bq, floa
     const int term = piece >> 5, kc = (piece >> 3) & 3, r = piece & 7;
     const int src = s_src[r];
     const float s = s_scale[r];
-    const float *xr = x + (size_t)(src < 0 ? 0 : src) * K;
-    const float *ur = u ? u + (size_t)(src < 0 ? 0 : src) * K : nullptr;
+    const size_t srow = (size_t)(src < 0 ? 0 : src) * K;
+    const float *xr = x_bf16 ? reinterpret_cast<const float *>(reinterpret_cast<const unsigned short *>(x) + srow) : x + srow;
+    const float *ur = u ? u + srow : nullptr;
     __half *base = bq + (size_t)2 * K * pass_row0[p] + (size_t)rg * 64 + r * 8;
     unsigned lo_bits = 0;
     for (int kb = kb_in; kb < K / 32; kb += 4) {
         uint4 outv = make_uint4(0, 0, 0, 0);
         if (src >= 0) {
             const int k0 = kb * 32 + kc * 8;
-            const float4 a = tc_row_vals(xr, ur, k0), b = tc_row_vals(xr, ur, k0 + 4);
+            const float4 a = tc_row_vals(xr, ur, k0, x_bf16), b = tc_row_vals(xr, ur, k0 + 4, x_bf16);
             const float xv[8] = {a.x * s, a.y * s, a.z * s, a.w * s, b.x * s, b.y * s, b.z * s, b.w * s};
             unsigned short h[8];
 #pragma unroll
@@ -549,7 +561,8 @@ k_expert_gemm_tc(const TcSeg *__restrict__ segs, const TcCtl *__restrict__ ctl, 
             const int n = q4 * 32 + lane;
             // two factors, applied one after the other: their product alone could underflow
             const float bi = n < nrows ? sg->binv[n] : 0.f, fs = sg->out_scale;
-            float *outp = sg->out + (size_t)(sg->pos0 + n) * O + f0;
+            const int orow = (sg->rowdst && n < nrows) ? sg->rowdst[sg->pos0 + n] : sg->pos0 + n;
+            float *outp = sg->out + (size_t)orow * O + f0;
             const float *rsc = MODE == SC_ROW ? sg->rowscale + f0 : nullptr;
             const int cbeg = chalf * (nfeat >> 1), cend = cbeg + (nfeat >> 1);
             const bool live = q4 * 32 < nrows;               // warp-uniform: some row of this quarter is live

@@ -115,8 +115,18 @@ struct DecShared {
             (a).probe[(size_t)blockIdx.x * DEC_NPROBE + (slot)] = t_;                  \
         }                                                                              \
     } while (0)
+// any single thread (the caller picks it): a stamp from inside a warp-level loop
+#define DEC_PROBE_T(a, slot)                                                           \
+    do {                                                                               \
+        if ((a).probe) {                                                               \
+            unsigned long long t_;                                                     \
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_));                      \
+            (a).probe[(size_t)blockIdx.x * DEC_NPROBE + (slot)] = t_;                  \
+        }                                                                              \
+    } while (0)
 #else
 #define DEC_PROBE(a, slot) do { } while (0)
+#define DEC_PROBE_T(a, slot) do { } while (0)
 #endif
 
 __device__ __forceinline__ void bar_sync_named(int id, int nthreads) {
@@ -856,6 +866,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
                         for (int i = 0; i < 4; i++) R[s][i] = fmaf(bacc[0][s][i], ixs, R[s][i]);
                     wr.consumed++;
                     __syncwarp();
+                    if (tid == 0 && wr.consumed == 1) DEC_PROBE_T(a, 3);      // first block of the stream consumed
                     dec_issue_one<CH, NST>(wr, it, ph1, ph2, sh, lane);
                 }
                 pb[mat] = make_float4((R[0][0] + R[0][1]) * mx_fix, (R[0][2] + R[0][3]) * mx_fix,
@@ -961,6 +972,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
                         bpre[grp] = bvalid ? *reinterpret_cast<const uint4 *>(bptr + (size_t)kb * 256 + grp * 64)
                                            : make_uint4(0, 0, 0, 0);
                     const uint32_t st = dec_wait_chunk<CH, NST>(wr);
+                    if (tid == 0 && p == ph2.gidx && kb == ph2.wl) DEC_PROBE_T(a, 11);   // first down block has landed
                     float bacc[1][2][4];
                     block_mma<MODE, 1, true, 1>(st, lane, g, [&](int grp, int) { return bpre[grp]; }, bacc, ixg);
 #pragma unroll
@@ -985,7 +997,9 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
                     if (mrow < nrows) ybuf[(ps.pos0 + mrow) * 16 + lane] = y;
                 }
             }
+            if (tid == 0) DEC_PROBE_T(a, 7);
             __syncthreads();      // every pass of this slice is in ybuf
+            if (tid == 0) DEC_PROBE_T(a, 8);
             for (int i = tid; i < M * 16; i += blockDim.x) {
                 const int s = i >> 4, rr = i & 15;
                 const int ke = sh->keff[s];

@@ -50,25 +50,52 @@ def test_engine_binary_live(name):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("name", sorted(GOLD))
-def test_harness_with_cuda_backend_reproduces_engine_tokens(be, name):
-    """int8 per-row experts (fmt=1) take the backend's generic kernels; routing runs on the
-    device from the router weights."""
-    from colibri_b200.backend import MoeLayer
+def test_harness_with_cuda_backend_reproduces_engine_tokens(be, oracle, name):
+    """The engine's int8 per-row experts (fmt=1) through the reference's own ABI, the way its
+    moe() drives a GPU backend (c/colibri.c:4819-4921): routing on the host, one
+    coli_cuda_expert_group call per layer over the batch's distinct experts (rows packed per
+    expert), weighted scatter-add on the host in each token's selection order."""
     from tests.util import upload_layer, free_layer
     c = GOLD[name]["case"]
-    handles, lays = [], []
+    handles = []
 
     def moe_of(cfg, layers):
+        hl = [host_layer(cfg, L, 1.0, 0.0, 0, True) for L in layers]
         for L in layers:
-            h = upload_layer(be, L)
-            handles.append(h)
-            lays.append(MoeLayer(be, cfg["D"], cfg["I"], cfg["E"], cfg["K"], h[0], h[1], h[2], 0,
-                                 cfg["norm_topk"], 1.0, 0.0, router_w=L.router_w, max_rows=max(c["prompt_len"], 8)))
-        return lambda li, x: lays[li](x, None, want_route=False)[0]
+            handles.append(upload_layer(be, L))
+
+        def moe(li, x):
+            lg = oracle.matmul(x, type("T", (), dict(w=layers[li].router_w, s=None, fmt=0, I=cfg["D"], O=cfg["E"], gs=0))())
+            idx, val, _ = oracle.route_softmax(lg, cfg["K"], bool(cfg["norm_topk"]))
+            g, u, d, _ = handles[li]
+            uniq = oracle.union(idx, np.full(len(x), cfg["K"], np.int32), cfg["E"])
+            rows_of = [np.nonzero((idx == e).any(axis=1))[0] for e in uniq]
+            xg = np.concatenate([x[r] for r in rows_of], axis=0)
+            out = np.zeros_like(x)
+            ys = []
+            for b0 in range(0, len(uniq), 64):           # the interface takes up to 64 experts per call
+                sel = list(range(b0, min(b0 + 64, len(uniq))))
+                off = sum(len(rows_of[j]) for j in range(b0))
+                n = sum(len(rows_of[j]) for j in sel)
+                ok, y = be.run_expert_group([g[uniq[j]] for j in sel], [u[uniq[j]] for j in sel],
+                                            [d[uniq[j]] for j in sel], [len(rows_of[j]) for j in sel],
+                                            xg[off:off + n], cfg["D"])
+                assert ok
+                ys.append(y)
+            y = np.concatenate(ys, axis=0)
+            pos = {}
+            off = 0
+            for j, e in enumerate(uniq):
+                for r in rows_of[j]:
+                    pos[(int(r), int(e))] = off
+                    off += 1
+            for s in range(len(x)):                      # selection order per token, as c/olmoe.c:688-697
+                for kk in range(cfg["K"]):
+                    out[s] += val[s, kk] * y[pos[(s, int(idx[s, kk]))]]
+            return out
+        return moe
     try:
         assert decode_with(moe_of, c) == GOLD[name]["tokens"]
     finally:
-        for l in lays:
-            l.free()
         for h in handles:
             free_layer(be, h)

@@ -1,38 +1,40 @@
 #!/usr/bin/env python
 """Benchmark of the MoE expert-FFN hot path.
 
-Workload `c2_decode` (default): the isolated MoE layer op at OLMoE shapes
-(hidden 2048, 64 experts, top-8 softmax routing, SwiGLU intermediate 1024, int4
-group-32 experts with fp16-valued scales) for M decode rows (default 1), run
-through L=16 distinct layers per step, as one decoded token passes the 16 MoE
-layers of OLMoE-1B-7B. A step touches L x (distinct experts) x 3.54 MB, well
-above the 126 MB L2, so no explicit L2 flush is needed.
+Workload `c2_decode` (default): the isolated MoE layer op at OLMoE shapes (hidden 2048,
+64 experts, top-8 softmax routing, SwiGLU intermediate 1024, int4 group-32 experts with
+fp16-valued scales) for M decode rows (default 1), run through L=16 distinct layers per
+step, as one decoded token passes the 16 MoE layers of OLMoE-1B-7B. A step touches
+L x (distinct experts) x 3.54 MB, well above the 126 MB L2, so no explicit L2 flush is
+needed.
 
-Metric: achieved HBM GB/s of the expert FFN = algorithmic bytes of a step
-(weights + scales of every distinct routed expert read once, plus activations
-in and out) / step time.
+Metric: achieved HBM GB/s of the expert FFN = algorithmic bytes of a step (weights +
+scales of every distinct routed expert read once, plus activations in and out) / step time.
 
-  value     device-resident: inputs already in HBM, coli_cuda_moe_layer_dev,
-            CUDA events on the backend's stream.
-  e2e       the same steps through coli_cuda_moe_layer with HOST buffers: every
-            layer call copies its input rows and router logits to the device
-            and its output rows back.
-  roofline  for the dominant kernel: the streaming dequant GEMV (algorithmic
-            weight bytes of its launches / their summed event-bracketed time,
-            against the measured copy bandwidth in MEASURED_PEAKS.json) or, for
-            calls with many rows per expert, the tcgen05 grouped GEMM
-            (algorithmic FLOPs / time against the measured bf16 rate).
-  cpu_baseline  the reference's own CPU kernels (oracle/_ref, c/quant.h compiled
-            unchanged) on a bounded sample of the same steps, rank 0 only.
+  value     device-resident: inputs already in HBM, coli_cuda_moe_layer_dev, CUDA events on
+            the backend's stream; the median over --repeats timed blocks of --steps steps
+            (min and max in `spread`).
+  e2e       the same steps through coli_cuda_moe_layer with HOST buffers: every layer call
+            copies its input rows and router logits to the device and its output rows back.
+  roofline  for the dominant kernel, from the same timed run as `value`: a decode-sized
+            layer call is one launch, so the kernel's share of a step is step time / launches
+            (launch gaps included: what the caller sees); larger M reports the event-bracketed
+            time of the GEMV / grouped-GEMM launches. Always in bytes / time against the
+            measured copy bandwidth (MEASURED_PEAKS.json); calls that take the tensor-core
+            kernel add its FLOP rate alongside.
+  cpu_baseline  the reference's own CPU kernels (oracle/_ref, c/quant.h compiled unchanged,
+            one C call per expert) over the same layers, all host threads, rank 0 only.
+  gpu_baseline  the reference's own CUDA backend (c/backend_cuda.cu compiled unchanged for
+            sm_100a, oracle/_ref) through coli_cuda_expert_group on the same per-layer expert
+            unions, rank 0 at N=1 only.
 
-`--impl reference` times that CPU implementation alone with the same metric.
-The distinct-expert counts of the byte accounting come from the device's own
-routing; the CPU oracle is used by the CPU legs only.
-Other workloads: `c3_decode` / `c4_decode` (DeepSeek-V3-style layer, MXFP4 /
-int4), `c5_ep` (expert-parallel layer over NCCL all-to-all, strong scaling).
-Multi-GPU (`--gpus N` under torchrun): the path has no exchange step at this
-configuration, so every rank decodes its own rows through its own replica
-(weak scaling); value = all ranks' bytes / max-over-ranks time.
+`--impl reference` times the CPU implementation alone with the same metric and workload.
+Other workloads: `c3_decode` / `c4_decode` (DeepSeek-V3-style layer, MXFP4 / int4), `c5_ep`
+(expert-parallel layer over NCCL all-to-all, strong scaling), `c4_stack`.
+Multi-GPU (`--gpus N` under torchrun): configurations 1-4 have no exchange step, so every
+rank decodes its own rows through its own replica (weak scaling; value = all ranks' bytes /
+max-over-ranks time). The sharded configuration (5) is then run on the same ranks and its
+strong-scaling result is attached to the same line as `config.c5_ep` (at N=1 too).
 """
 from __future__ import annotations
 
@@ -53,86 +55,72 @@ sys.path.insert(0, ROOT)
 from colibri_b200 import workloads as W  # noqa: E402
 from colibri_b200.quant import QTensor  # noqa: E402
 
-
-def measured_peaks():
-    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.exists(p):
-        try:
-            d = json.load(open(p))
-            return float(d["hbm_gbs"]), "measured"
-        except Exception:
-            pass
-    return 6650.0, "fallback"
-
-
-# DRAM bytes per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum of one
-# ncu capture, summarised in profiles/k_moe_decode_c2_m1.md and k_moe_decode_c4_e64_m1.md); other
-# workloads have no capture and report null.
-NCU_TRAFFIC_BYTES = {("c2_decode", 1, 64): 28.45e6}
 TC_MEAN_ROWS = 12     # the backend's rule for prefill-sized layer calls: mean rows per expert
+ROUTED_SCALE = 2.5    # sigmoid-gated configurations (GLM / DeepSeek-V3 style)
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the fused decode kernel (one ncu
+# capture of configuration 2 at M=1); other workloads have no capture and report null
+NCU_TRAFFIC_BYTES = {("c2_decode", 1, 64): 28.45e6}
 
 
-def measured_tensor_peak():
-    """Dense bf16 TFLOP/s of this pool's B200s, the sustained figure (the kernel is timed
-    inside a long step); the stated fallback when the driver's file is absent."""
+def peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.exists(p):
-        try:
-            d = json.load(open(p))
-            return float(d["bf16_tflops_sustained"]), "measured (sustained)"
-        except Exception:
-            pass
-    return 1400.0, "fallback (sustained)"
+    try:
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), float(d["bf16_tflops_sustained"]), "measured"
+    except Exception:
+        return 6650.0, 1400.0, "fallback"
 
 
-def tensor_roofline(useful_flop, kernel_ms, launches, terms, kernel="k_expert_gemm_tc"):
-    """roofline object of the tensor-core grouped GEMM: achieved = algorithmic FLOPs
-    (rows x 3 matrices x 2*D*I) / event time of its launches. The kernel issues `terms`
-    fp16 MMAs per algorithmic product (exact f32-equivalent operands), so the tensor
-    pipe does terms x this much work."""
-    peak, which = measured_tensor_peak()
-    ach = useful_flop / (kernel_ms * 1e-3) / 1e12 if kernel_ms > 0 else None
-    return {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s",
-            "frac": (ach / peak) if ach else None, "traffic": None, "kernel": kernel, "launches": launches,
-            "avg_launch_us": (kernel_ms / launches * 1e3) if launches else None, "peak_source": which,
-            "mma_terms_per_product": terms,
-            "tensor_pipe_frac": (ach * terms / peak) if ach else None}
+def workload_string(name, cfg, M, L):
+    """One description for both arms (the driver compares the strings)."""
+    return (f"{name}: MoE layer op (D={cfg['D']}, I={cfg['I']}, E={cfg['E']}"
+            f"{'+1 shared' if cfg['shared'] else ''}, top-{cfg['K']} "
+            f"{'softmax' if cfg['gating'] == 0 else 'sigmoid'}), "
+            f"{'int4 g32 fp16-valued scales' if cfg['fmt'] == 4 else 'MXFP4'}, M={M} rows, "
+            f"{L} distinct layers per step")
 
 
 # ---------------------------------------------------------------------------
-# synthetic weights, generated on the GPU with torch (fast) in the reference
-# converter's rules (colibri_b200.quant restates the same rules in numpy; the
-# two are compared in tests/test_gpu_bench_inputs.py)
+# synthetic weights, generated on the GPU with torch (fast) by the reference converters' rules;
+# held bit for bit to the reference's own quantisers by tests/test_quant.py (numpy restatement,
+# CPU) and tests/test_gpu_bench_inputs.py (these functions, on the GPU)
 # ---------------------------------------------------------------------------
-def gen_int4_g32_torch(torch, E, O, I, seed, device):
-    g = torch.Generator(device=device)
-    g.manual_seed(seed)
-    w = torch.randn((E, O, I), generator=g, device=device, dtype=torch.float32) * 0.02
-    wr = w.view(E, O, I // 32, 32)
-    amax = wr.abs().amax(dim=3, keepdim=True)
+def quant_int4_g32_torch(torch, w, fp16_scales=True):
+    """c/tools/convert_fp8_to_int4.py:79-109 with gs=32 for w [..., O, I]; fp16_scales rounds
+    every scale to fp16 before the division ("group 32, fp16 scale")."""
+    O, I = w.shape[-2], w.shape[-1]
+    wr = w.reshape(*w.shape[:-1], I // 32, 32)
+    amax = wr.abs().amax(dim=-1, keepdim=True)
     s = torch.clamp(amax / 7.0, min=1e-8)
-    s = s.to(torch.float16).to(torch.float32).clamp(min=6e-8)
+    if fp16_scales:
+        s = s.to(torch.float16).to(torch.float32).clamp(min=6e-8)
     q = torch.clamp(torch.round(wr / s), -8, 7).to(torch.int32) + 8
-    q = q.view(E, O, I)
-    packed = (q[:, :, 0::2] | (q[:, :, 1::2] << 4)).to(torch.uint8)
-    return packed.cpu().numpy(), s.view(E, O * (I // 32)).cpu().numpy()
+    q = q.reshape(*w.shape)
+    packed = (q[..., 0::2] | (q[..., 1::2] << 4)).to(torch.uint8)
+    return packed, s.reshape(*w.shape[:-2], O * (I // 32))
 
 
-def gen_mxfp4_torch(torch, E, O, I, seed, device):
-    """E2M1 + UE8M0 per 32 columns, the rule of c/tools/make_deepseek_v4_tiny.py:97-121."""
-    g = torch.Generator(device=device)
-    g.manual_seed(seed)
-    w = torch.randn((E, O, I), generator=g, device=device, dtype=torch.float32) * 0.02
-    wr = w.view(E, O, I // 32, 32)
-    amax = wr.abs().amax(dim=3, keepdim=True)
+def quant_mxfp4_torch(torch, w):
+    """E2M1 + UE8M0 per 32 columns, the rule of c/tools/make_deepseek_v4_tiny.py:64-121."""
+    O, I = w.shape[-2], w.shape[-1]
+    wr = w.reshape(*w.shape[:-1], I // 32, 32)
+    amax = wr.abs().amax(dim=-1, keepdim=True)
     e = torch.where(amax > 0, torch.ceil(torch.log2(amax.double() / 6.0)), torch.full_like(amax, -127).double())
     e = e.clamp(-127, 127)
-    scale = torch.pow(torch.tensor(2.0, device=device, dtype=torch.float64), e).float()
+    scale = torch.pow(torch.tensor(2.0, device=w.device, dtype=torch.float64), e).float()
     norm = (wr / scale).clamp(-6.0, 6.0)
-    lut = torch.tensor([0, .5, 1, 1.5, 2, 3, 4, 6, -0.0, -.5, -1, -1.5, -2, -3, -4, -6], device=device)
-    code = (norm.unsqueeze(-1) - lut).abs().argmin(dim=-1).to(torch.int32).view(E, O, I)
-    packed = (code[:, :, 0::2] | (code[:, :, 1::2] << 4)).to(torch.uint8)
-    return packed.cpu().numpy(), (e.view(E, O, I // 32) + 127).to(torch.uint8).cpu().numpy()
+    lut = torch.tensor([0, .5, 1, 1.5, 2, 3, 4, 6, -0.0, -.5, -1, -1.5, -2, -3, -4, -6], device=w.device)
+    code = (norm.unsqueeze(-1) - lut).abs().argmin(dim=-1).to(torch.int32).reshape(*w.shape)
+    packed = (code[..., 0::2] | (code[..., 1::2] << 4)).to(torch.uint8)
+    return packed, (e.reshape(*w.shape[:-1], I // 32) + 127).to(torch.uint8)
+
+
+def gen_weights(torch, fmt, E, O, I, seed, device):
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    w = torch.randn((E, O, I), generator=g, device=device, dtype=torch.float32) * 0.02
+    pk, sc = quant_mxfp4_torch(torch, w) if fmt == 7 else quant_int4_g32_torch(torch, w)
+    return pk.cpu().numpy(), sc.cpu().numpy()
 
 
 def gen_layer_host(torch, cfg, seed, device, n_experts=None):
@@ -147,31 +135,24 @@ def gen_layer_host(torch, cfg, seed, device, n_experts=None):
         ts = []
         for e0 in range(0, E, chunk):
             n = min(chunk, E - e0)
-            if fmt == 7:
-                pk, sc = gen_mxfp4_torch(torch, n, O, K, (seed * 10 + k) * 1000 + e0, device)
-                ts += [QTensor(pk[e], sc[e], 7, K, O, 0) for e in range(n)]
-            else:
-                pk, sc = gen_int4_g32_torch(torch, n, O, K, (seed * 10 + k) * 1000 + e0, device)
-                ts += [QTensor(pk[e], sc[e], 4, K, O, 32) for e in range(n)]
+            pk, sc = gen_weights(torch, fmt, n, O, K, (seed * 10 + k) * 1000 + e0, device)
+            ts += [QTensor(pk[e], sc[e], fmt, K, O, 32 if fmt == 4 else 0) for e in range(n)]
         out.append(ts)
     return out
 
 
 def expert_bytes_device(cfg):
-    """Algorithmic bytes of one expert as stored on the device: nibbles + fp16
-    scales for int4 g32 (4.5 bits per weight), nibbles + ue8m0 bytes for MXFP4."""
-    D, I = cfg["D"], cfg["I"]
-    per_w = 3 * D * I
+    """Algorithmic bytes of one expert as stored on the device: nibbles + fp16 scales for int4
+    g32 (4.5 bits per weight), nibbles + ue8m0 bytes for MXFP4."""
+    per_w = 3 * cfg["D"] * cfg["I"]
     return per_w // 2 + (per_w // 32) * (1 if cfg["fmt"] == 7 else 2)
 
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons sampled during the timed region."""
+    """nvidia-smi clocks / throttle reasons sampled during the timed region (read-only query)."""
 
     def __init__(self, index):
-        self.index = index
-        self.rows = []
-        self.proc = None
+        self.index, self.rows, self.proc = index, [], None
 
     def start(self):
         q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
@@ -185,6 +166,7 @@ class ClockSampler:
             self.t.start()
         except Exception:
             self.proc = None
+        return self
 
     def _read(self):
         for line in self.proc.stdout:
@@ -216,91 +198,144 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-ROUTED_SCALE = 2.5   # sigmoid-gated configurations (GLM / DeepSeek-V3 style)
+def host_threads():
+    return len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+
+
+def restore_omp_threads():
+    """torchrun exports OMP_NUM_THREADS=1 to every rank; the CPU legs are the CPU implementation
+    with all the host threads, so the variable is put back before the OpenMP runtime starts, and
+    the runtime is told again once it is loaded."""
+    n = host_threads()
+    os.environ["OMP_NUM_THREADS"] = str(n)
+    try:
+        C.CDLL("libgomp.so.1").omp_set_num_threads(C.c_int(n))
+    except OSError:
+        pass
+    return n
 
 
 # ---------------------------------------------------------------------------
-# CPU arm (reference kernels)
+# CPU arm: the reference's kernels (oracle/_ref), one C call per expert
 # ---------------------------------------------------------------------------
-def cpu_step(ref, oracle, cfg, layers_host, xs, logits, layer_ids, biases=None):
-    """One pass over `layer_ids` with the reference's CPU kernels in the engine's
-    per-expert order (c/colibri.c:4731-4786, shared expert last :4940-5001);
-    returns the bytes it touched."""
-    K, E, D = cfg["K"], cfg["E"], cfg["D"]
+class CpuExperts:
+    """The reference CPU expert FFN: oracle/_ref (c/quant.h compiled unchanged; the AVX-512
+    build when the host has the ISA, as the reference's -march=native would pick), else the
+    restated oracle ("port")."""
+
+    def __init__(self):
+        from oracle.oracle import Oracle, REF_CPU_SO
+        self.oracle = Oracle()
+        self.lib, self.kind, self.build = None, "port", "oracle restatement"
+        flags = ""
+        try:
+            flags = open("/proc/cpuinfo").read()
+        except OSError:
+            pass
+        v4 = os.path.join(os.path.dirname(REF_CPU_SO), "libcoli_ref_cpu_v4.so")
+        want_v4 = all(f in flags for f in ("avx512f", "avx512bw", "avx512vl", "avx512_vnni"))
+        for path, label in ((v4, "-O3 -march=x86-64-v4 -mavx512vnni -fopenmp") if want_v4 else (None, None),
+                            (REF_CPU_SO, "-O3 -march=x86-64-v3 -fopenmp")):
+            if path and os.path.exists(path):
+                self.lib, self.kind, self.build = C.CDLL(path), "reference", label
+                self.lib.ref_num_threads.restype = C.c_int
+                self.lib.ref_idot_kernel.restype = C.c_char_p
+                self.lib.ref_expert_mlp.restype = C.c_int
+                break
+        self._scratch = {}
+
+    def threads(self):
+        return self.lib.ref_num_threads() if self.lib else self.oracle.threads()
+
+    def idot_kernel(self):
+        return self.lib.ref_idot_kernel().decode() if self.lib else "n/a"
+
+    def expert_mlp(self, x, g, u, d, idot=False):
+        if self.lib is None:
+            return self.oracle.expert_mlp(x, g, u, d)
+        S, D, I = x.shape[0], g.I, g.O
+        key = (S, I)
+        if key not in self._scratch:
+            self._scratch[key] = (np.empty((S, I), np.float32), np.empty((S, I), np.float32))
+        sg, su = self._scratch[key]
+        y = np.empty((S, D), np.float32)
+        p = lambda a: C.c_void_p(a.ctypes.data)
+        ok = self.lib.ref_expert_mlp(p(y), p(x), S, g.fmt, g.gs, D, I, p(g.w), p(g.s), p(u.w), p(u.s), p(d.w), p(d.s),
+                                     p(sg), p(su), int(idot))
+        if not ok:
+            raise ValueError("fmt")
+        return y
+
+
+def cpu_route(oracle, cfg, lg, bias):
+    K = cfg["K"]
+    if cfg["gating"] == 0:
+        idx, val, _ = oracle.route_softmax(lg, K, False)
+        return idx, val, np.full(lg.shape[0], K, np.int32)
+    idx, val, keff, _ = oracle.route_sigmoid(lg, bias, K, 0.0, bool(cfg["norm_topk"]), ROUTED_SCALE)
+    return idx, val, keff
+
+
+def cpu_step(cpu, cfg, layers_host, xs, logits, layer_ids, biases, idot=False):
+    """One pass over `layer_ids` with the reference's CPU kernels in the engine's per-expert
+    order (c/colibri.c:4731-4786, shared expert last :4940-5001); returns the bytes it touched."""
+    E = cfg["E"]
     nbytes = 0
     eb = expert_bytes_device(cfg)
     for li in layer_ids:
         gate, up, down, shared = layers_host[li]
-        x, lg = xs[li], logits[li]
-        if cfg["gating"] == 0:
-            idx, val, _ = oracle.route_softmax(lg, K, False)
-            keff = np.full(x.shape[0], K, np.int32)
-        else:
-            idx, val, keff, _ = oracle.route_sigmoid(lg, biases[li] if biases else None, K, 0.0,
-                                                     bool(cfg["norm_topk"]), ROUTED_SCALE)
-        uniq = oracle.union(idx, keff, E)
+        x = xs[li]
+        idx, val, keff = cpu_route(cpu.oracle, cfg, logits[li], biases[li])
+        uniq = cpu.oracle.union(idx, keff, E)
         out = np.zeros_like(x)
         for e in uniq:
             rows, col = np.nonzero(idx == e)
-            y = ref.expert_mlp(x[rows], gate[e], up[e], down[e])
+            y = cpu.expert_mlp(np.ascontiguousarray(x[rows]), gate[e], up[e], down[e], idot)
             out[rows] += val[rows, col][:, None] * y
         if shared is not None:
-            out += ref.expert_mlp(x, *shared)
+            out += cpu.expert_mlp(x, *shared, idot)
         nbytes += (len(uniq) + (1 if shared is not None else 0)) * eb + 2 * x.nbytes
     return nbytes
 
 
-def run_reference_arm(args):
-    from oracle.oracle import Oracle, RefCpu
-    cfg = W.CONFIGS[args.workload.split("_")[0]]
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
-        return
-    # torchrun exports OMP_NUM_THREADS=1 to every rank; this arm is the CPU implementation with all
-    # the host threads, so the variable is put back before the OpenMP runtime starts, and the
-    # runtime is told again once it is loaded
-    ncpu = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
-    os.environ["OMP_NUM_THREADS"] = str(ncpu)
-    oracle = Oracle()
-    try:
-        C.CDLL("libgomp.so.1").omp_set_num_threads(C.c_int(ncpu))
-    except OSError:
-        pass
-    kind = "reference" if RefCpu.available() else "port"
-    ref = RefCpu() if RefCpu.available() else None
-    if ref is None:
-        class Port:   # the restated oracle as the CPU implementation
-            def expert_mlp(self, x, g, u, d): return oracle.expert_mlp(x, g, u, d)
-            def threads(self): return oracle.threads()
-        ref = Port()
-    L = args.layers
-    # bounded sample: only the experts a step routes to are generated (numpy, CPU)
-    M = args.M
-    xs = [W.activations(M, cfg["D"], 100 + li) for li in range(L)]
-    lgs = [W.router_logits(M, cfg["E"], 200 + li) for li in range(L)]
-    layers_host, biases = [], []
+def host_inputs(cfg, L, M, rank=0):
+    xs = [W.activations(M, cfg["D"], 100 + li + 1000 * rank) for li in range(L)]
+    lgs = [W.router_logits(M, cfg["E"], 200 + li + 1000 * rank) for li in range(L)]
+    biases = [(np.random.default_rng(31 + li).standard_normal(cfg["E"]) * 0.01).astype(np.float32)
+              if cfg["gating"] == 1 else None for li in range(L)]
+    return xs, lgs, biases
+
+
+def host_layers_for(oracle, cfg, L, lgs, biases):
+    """Only the experts a step routes to are generated (numpy, CPU)."""
+    layers = []
     for li in range(L):
-        bias = None
-        if cfg["gating"] == 0:
-            idx, _, _ = oracle.route_softmax(lgs[li], cfg["K"], False)
-        else:
-            bias = (np.random.default_rng(31 + li).standard_normal(cfg["E"]) * 0.01).astype(np.float32)
-            idx, _, _, _ = oracle.route_sigmoid(lgs[li], bias, cfg["K"], 0.0, bool(cfg["norm_topk"]), ROUTED_SCALE)
-        biases.append(bias)
-        need = set(np.unique(idx).tolist())
+        idx, _, keff = cpu_route(oracle, cfg, lgs[li], biases[li])
+        need = set(np.concatenate([idx[s, :keff[s]] for s in range(len(idx))]).tolist())
         gate, up, down = {}, {}, {}
         for e in need:
-            g, u, d = W.expert_weights(cfg["D"], cfg["I"], cfg["fmt"], cfg["gs"], 9000 + li * cfg["E"] + e)
-            gate[e], up[e], down[e] = g, u, d
+            gate[e], up[e], down[e] = W.expert_weights(cfg["D"], cfg["I"], cfg["fmt"], cfg["gs"], 9000 + li * cfg["E"] + e)
         shared = W.expert_weights(cfg["D"], cfg["I"], cfg["fmt"], cfg["gs"], 8000 + li) if cfg["shared"] else None
-        layers_host.append((gate, up, down, shared))
+        layers.append((gate, up, down, shared))
+    return layers
+
+
+def run_reference_arm(args):
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    cfg = W.CONFIGS[args.workload.split("_")[0]]
+    restore_omp_threads()
+    cpu = CpuExperts()
+    L, M = args.layers, args.M
+    xs, lgs, biases = host_inputs(cfg, L, M)
+    layers_host = host_layers_for(cpu.oracle, cfg, L, lgs, biases)
     ids = list(range(L))
     for _ in range(args.warmup):
-        cpu_step(ref, oracle, cfg, layers_host, xs, lgs, ids, biases)
+        cpu_step(cpu, cfg, layers_host, xs, lgs, ids, biases)
     t0 = time.perf_counter()
     nbytes = 0
     for _ in range(args.steps):
-        nbytes += cpu_step(ref, oracle, cfg, layers_host, xs, lgs, ids, biases)
+        nbytes += cpu_step(cpu, cfg, layers_host, xs, lgs, ids, biases)
     dt = time.perf_counter() - t0
     gbs = nbytes / dt / 1e9
     line = {
@@ -308,19 +343,259 @@ def run_reference_arm(args):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic", "impl": "reference",
-        "config": {"workload": f"{args.workload}: MoE layer op (D={cfg['D']}, I={cfg['I']}, E={cfg['E']}, "
-                               f"top-{cfg['K']}), {'int4 g32' if cfg['fmt'] == 4 else 'MXFP4'}, M={M}, "
-                               f"{L} layers per step"},
-        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": ref.threads(), "kind": kind,
-                         "sample": f"{args.steps} steps x {L} layers, routed experts only"},
+        "config": {"workload": workload_string(args.workload, cfg, M, L)},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cpu.threads(), "kind": cpu.kind,
+                         "sample": f"{args.steps} steps x {L} layers, routed experts only; {cpu.build}; "
+                                   f"exact f32 kernels (matmul_{'i4_grouped' if cfg['fmt'] == 4 else 'mxfp4'})"},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 
 
 # ---------------------------------------------------------------------------
+# expert-parallel block (configuration 5)
+# ---------------------------------------------------------------------------
+def run_ep_block(args, be, world, rank, local, L, M, n_experts=None, steps=None, balanced=True):
+    """Configuration 5 on the ranks of this job: GLM-scale layer (D 6144, I 2048, 256 routed
+    experts + 1 shared, top-8 sigmoid, MXFP4), L layers, M rows in total, Zipf(1.1)-skewed
+    logits; experts placed on the ranks by a routing histogram (or in equal blocks), dispatch
+    and combine as NCCL all-to-all. Strong scaling: the total work is fixed. Returns the
+    result dictionary on rank 0 (None elsewhere)."""
+    import torch
+    import torch.distributed as dist
+    from colibri_b200.ep import CudaEpLayer, ExpertMap
+
+    dev = torch.device("cuda", local)
+    cfg = dict(W.CONFIGS["c5"])
+    if n_experts:
+        cfg["E"] = n_experts
+    D, I, E, K = cfg["D"], cfg["I"], cfg["E"], cfg["K"]
+    steps = steps or args.ep_steps
+    assert E % world == 0 and M % world == 0
+    m = M // world
+    lg_all = [W.router_logits(M, E, 600 + li, zipf=1.1) for li in range(L)]
+    biases = [(np.random.default_rng(31 + li).standard_normal(E) * 0.01).astype(np.float32) for li in range(L)]
+    # routing histogram of the whole batch (this rank's GPU, the backend's own routing): the byte
+    # accounting and, when balancing, the placement (the reference ranks experts by heat the same
+    # way before it pins them to devices, c/colibri.c:8367-8417)
+    loads, step_bytes = [], 0
+    eb = expert_bytes_device(cfg)
+    for li in range(L):
+        lgd = torch.from_numpy(lg_all[li]).to(dev)
+        bd = torch.from_numpy(biases[li]).to(dev)
+        idx = torch.empty((M, K), dtype=torch.int32, device=dev)
+        w = torch.empty((M, K), dtype=torch.float32, device=dev)
+        keff = torch.empty((M,), dtype=torch.int32, device=dev)
+        if not be.route_topk_dev(local, lgd.data_ptr(), bd.data_ptr(), M, E, K, 1, 1, C.c_float(ROUTED_SCALE),
+                                 C.c_float(0.0), idx.data_ptr(), w.data_ptr(), keff.data_ptr()):
+            raise RuntimeError("coli_cuda_route_topk_dev failed")
+        torch.cuda.synchronize()
+        live = idx[torch.arange(K, device=dev).unsqueeze(0) < keff.unsqueeze(1)].to(torch.int64)
+        load = torch.bincount(live, minlength=E).cpu().numpy()
+        loads.append(load)
+        step_bytes += (int((load > 0).sum()) + world) * eb + 2 * M * D * 4
+    emaps = [ExpertMap.balanced(loads[li], world) if balanced else ExpertMap(E, world) for li in range(L)]
+    imb = [float(em.imbalance(loads[li])) for li, em in enumerate(emaps)]
+    imb_blocks = [float(ExpertMap(E, world).imbalance(loads[li])) for li in range(L)]
+    up = lambda t: be.upload(t.w, t.s, t.fmt, t.I, t.O, local, t.gs)
+    layers, handles = [], []
+
+    def expert_tensors(li, e):
+        hs = []
+        for k, (O, Kd) in enumerate(((I, D), (I, D), (D, I))):
+            pk, sc = gen_weights(torch, 7, 1, O, Kd, ((li * 1024 + e) * 4 + k) * 7 + 5, dev)
+            hs.append(up(QTensor(pk[0], sc[0], 7, Kd, O, 0)))
+        return hs
+    for li in range(L):
+        em = emaps[li]
+        hs = [[], [], []]
+        for e in em.local[rank]:
+            for k, h in enumerate(expert_tensors(li, e)):
+                hs[k].append(h)
+        sh = expert_tensors(li, 1000)
+        if not all(hs[0] + hs[1] + hs[2] + sh):
+            raise RuntimeError("tensor upload failed")
+        handles += hs[0] + hs[1] + hs[2] + sh
+        layers.append(CudaEpLayer(be, local, cfg, em, rank, hs[0], hs[1], hs[2], tuple(sh),
+                                  torch.from_numpy(biases[li]).to(dev), ROUTED_SCALE, max_rows=m, payload="bf16"))
+    xs = [torch.from_numpy(W.activations(M, D, 500 + li)[rank * m:(rank + 1) * m].copy()).to(dev) for li in range(L)]
+    lgs = [torch.from_numpy(l[rank * m:(rank + 1) * m].copy()).to(dev) for l in lg_all]
+    torch.cuda.synchronize()
+    bstream = layers[0].bstream
+
+    def step():
+        return [layers[li](xs[li], lgs[li]) for li in range(L)]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+    for _ in range(3):
+        step()
+    barrier()
+    for lay in layers:
+        lay.check_exact()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(bstream)
+    for _ in range(steps):
+        step()
+    e1.record(bstream)
+    barrier()
+    ms = e0.elapsed_time(e1)
+    # per-phase split of one more step (events on the two streams)
+    n0 = be.launch_total(local)
+    be.set_kernel_events(1)
+    for lay in layers:
+        lay.timing = {}
+    step()
+    torch.cuda.synchronize()
+    k_ms, k_n = C.c_float(), C.c_int()
+    be.kernel_events(local, C.byref(k_ms), C.byref(k_n))
+    be.set_kernel_events(0)
+    launches_step = int(be.launch_total(local) - n0)
+    pack = a2a = gemm = comb = 0.0
+    rows_recv = 0
+    for lay in layers:
+        mk = lay.timing["layers"][0]
+        pack += mk["t0"].elapsed_time(mk["pack"])
+        a2a += mk["pack"].elapsed_time(mk["recv"]) + mk["gemm"].elapsed_time(mk["back"])
+        gemm += mk["g0"].elapsed_time(mk["gemm"])
+        comb += mk["back"].elapsed_time(mk["t1"])
+        rows_recv += lay.last["n_recv"]
+        lay.timing = None
+    # end to end: rows and logits start in pinned host memory, the result is read back
+    x_pin = [x.cpu().pin_memory() for x in xs]
+    lg_pin = [l.cpu().pin_memory() for l in lgs]
+    out_pin = torch.empty((m, D), dtype=torch.float32).pin_memory()
+
+    def step_host():
+        for li in range(L):
+            with torch.cuda.stream(bstream):
+                xd = x_pin[li].to(dev, non_blocking=True)
+                ld = lg_pin[li].to(dev, non_blocking=True)
+                out = layers[li](xd, ld)
+                out_pin.copy_(out, non_blocking=True)
+        torch.cuda.synchronize()
+    for _ in range(2):
+        step_host()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step_host()
+    barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+    t = torch.tensor([ms, e2e_ms, k_ms.value, pack, a2a, gemm, comb, float(rows_recv)], device=dev, dtype=torch.float64)
+    tmin = t.clone()
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(tmin, op=dist.ReduceOp.MIN)
+    status = be.kernel_status(local)
+    for lay in layers:
+        del lay
+    for h in handles:
+        be.tensor_free(h)
+    if status != 0:
+        raise RuntimeError("a kernel wait guard expired")
+    if rank != 0:
+        return None
+    ms_all, e2e_all = float(t[0]), float(t[1])
+    hbm_peak, tc_peak, which = peaks()
+    flop_rank = float(t[7]) / 1.0 * 6.0 * D * I + m * 6.0 * D * I * L     # busiest rank: routed rows received + shared rows
+    return {
+        "workload": f"c5_ep: expert-parallel MoE layer (D={D}, I={I}, E={E}+1 shared, top-{K} sigmoid, MXFP4), "
+                    f"M={M} rows in total, {L} layers per step, Zipf(1.1) logit bias, experts placed on {world} rank(s) "
+                    f"{'by routing histogram' if balanced else 'in equal blocks'}, NCCL all-to-all dispatch (bf16 rows) "
+                    f"and combine (f32 rows)",
+        "scaling": "strong", "n_gpus": world, "steps": steps, "ms_per_step": ms_all / steps,
+        "value": step_bytes * steps / (ms_all * 1e-3) / 1e9, "unit": "GB/s", "bytes_per_step": step_bytes,
+        "e2e": {"value": step_bytes * steps / (e2e_all * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_all / steps,
+                "h2d_bytes_per_step": L * world * (m * D * 4 + m * E * 4), "d2h_bytes_per_step": L * world * m * D * 4},
+        # one step, busiest rank per phase (events; the phases of different layers do not overlap)
+        "phase_ms": {"route_plan_pack": float(t[3]), "a2a_dispatch_and_combine": float(t[4]),
+                     "expert_gemm": float(t[5]), "combine": float(t[6]), "gemm_kernels_bracketed": float(t[2])},
+        "a2a_bytes_per_rank_per_layer": int((M // world) * K * D * (2 + 4) * (world - 1) / max(world, 1)),
+        "imbalance_max_over_mean_rows": {"placed": max(imb), "equal_blocks": max(imb_blocks)},
+        "rows_received_per_step": {"max_rank": float(t[7]), "min_rank": float(tmin[7])},
+        "gpu_launches_per_step": launches_step,
+        "roofline": {"bound": "hbm", "achieved": step_bytes * steps / (ms_all * 1e-3) / 1e9 / world, "peak": hbm_peak,
+                     "unit": "GB/s per GPU", "frac": step_bytes * steps / (ms_all * 1e-3) / 1e9 / world / hbm_peak,
+                     "peak_source": which,
+                     "tensor": {"achieved_tflops_busiest_rank": flop_rank / (float(t[5]) * 1e-3) / 1e12 if t[5] > 0 else None,
+                                "peak": tc_peak, "mma_terms_per_product": 2}},
+    }
+
+
+# ---------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------
+def gpu_baseline_reference_cuda(cfg, L, M, steps, xs, lgs, biases, torch, dev):
+    """The reference's own CUDA backend (c/backend_cuda.cu compiled unchanged for sm_100a,
+    oracle/_ref/libcoli_ref_cuda.so) through coli_cuda_expert_group on the per-layer expert
+    unions of the same steps, the way the engine's moe() drives it (c/colibri.c:4819-4921):
+    routing and the weighted scatter-add stay on the host, x and y cross the bus per call.
+    Loaded into a namespace of its own (RTLD_LOCAL), after this repository's backend has shut
+    down. Host-timed; the kernel-only share comes from the library's own profile counters."""
+    from colibri_b200.backend import Backend
+    from oracle.oracle import Oracle
+    path = os.path.join(ROOT, "oracle", "_ref", "libcoli_ref_cuda.so")
+    if not os.path.exists(path):
+        return {"unavailable": "oracle/_ref/libcoli_ref_cuda.so is not built (reference checkout absent at build time)"}
+    orc = Oracle()
+    rb = Backend(path, additive=False)
+    if rb.init_devices((0,)) != 1:
+        return {"unavailable": "the reference backend's coli_cuda_init failed"}
+    os.environ["COLI_CUDA_PROFILE"] = "1"
+    eb = expert_bytes_device(cfg)
+    calls, step_bytes, handles = [], 0, []
+    up = lambda t: rb.upload(t.w, t.s, t.fmt, t.I, t.O, 0, t.gs)
+    for li in range(L):
+        idx, val, keff = cpu_route(orc, cfg, lgs[li], biases[li])
+        uniq = orc.union(idx, keff, cfg["E"])
+        g, u, d, rows, xg = [], [], [], [], []
+        for e in uniq:
+            r, _ = np.nonzero(idx == e)
+            gt, ut, dt = W.expert_weights(cfg["D"], cfg["I"], cfg["fmt"], cfg["gs"], 9000 + li * cfg["E"] + int(e))
+            hs = [up(gt), up(ut), up(dt)]
+            if not all(hs):
+                rb.shutdown()
+                return {"unavailable": f"the reference backend refused a tensor upload (fmt {cfg['fmt']})"}
+            handles += hs
+            g.append(hs[0]); u.append(hs[1]); d.append(hs[2]); rows.append(len(r)); xg.append(xs[li][r])
+        calls.append((g, u, d, rows, np.concatenate(xg, axis=0)))
+        step_bytes += len(uniq) * eb + 2 * xs[li].nbytes
+
+    def step():
+        for g, u, d, rows, xg in calls:
+            for b0 in range(0, len(g), 64):
+                b1 = min(b0 + 64, len(g))
+                off, n = sum(rows[:b0]), sum(rows[b0:b1])
+                ok, _ = rb.run_expert_group(g[b0:b1], u[b0:b1], d[b0:b1], rows[b0:b1], xg[off:off + n], cfg["D"])
+                if not ok:
+                    raise RuntimeError("reference coli_cuda_expert_group refused the call")
+    try:
+        for _ in range(3):
+            step()
+        k0 = rb.group_stats_tuple()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            step()
+        dt = time.perf_counter() - t0
+        k1 = rb.group_stats_tuple()
+    except RuntimeError as ex:
+        rb.shutdown()
+        return {"unavailable": str(ex)}
+    for h in handles:
+        rb.tensor_free(h)
+    rb.shutdown()
+    kern_ms = k1[4] - k0[4]
+    return {"kind": "reference c/backend_cuda.cu, compiled unchanged for sm_100a, coli_cuda_expert_group "
+                    "(routed experts only; routing and combine on the host)",
+            "value": step_bytes * steps / dt / 1e9, "unit": "GB/s", "ms_per_step": dt / steps * 1e3,
+            "kernel_only": {"value": step_bytes * steps / (kern_ms * 1e-3) / 1e9 if kern_ms > 0 else None,
+                            "ms_per_step": kern_ms / steps},
+            "steps": steps}
+
+
 def run_gpu_arm(args):
     import torch
     import torch.distributed as dist
@@ -334,44 +609,65 @@ def run_gpu_arm(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    cfg = dict(W.CONFIGS[args.workload.split("_")[0]])
+    name = args.workload
+    cfg = dict(W.CONFIGS[name.split("_")[0]])
     if args.experts:
         cfg["E"] = args.experts          # profiling subsets only; the default is the full configuration
     D, I, E, K = cfg["D"], cfg["I"], cfg["E"], cfg["K"]
     L, M = args.layers, args.M
-    fmt, gs = cfg["fmt"], cfg["gs"]
+    fmt = cfg["fmt"]
+    steps, repeats = args.steps, max(1, args.repeats)
 
     be = Backend()
     if be.init_devices((local,)) != 1:
         raise RuntimeError("coli_cuda_init failed: the CUDA backend is required (no CPU fallback)")
     be.set_tensor_core(args.tc)
-    layers, handles, host_keep, biases = [], [], [], []
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    if name == "c5_ep":
+        Lep = args.layers if args.layers != 16 else 4
+        Mep = args.M if args.M != 1 else 2048
+        sampler = ClockSampler(local).start() if rank == 0 else None
+        ep = run_ep_block(args, be, world, rank, local, Lep, Mep, n_experts=args.experts or None, steps=args.steps,
+                          balanced=not args.ep_blocks)
+        clocks = sampler.stop() if sampler else None
+        if rank == 0:
+            line = {"metric": "moe_expert_ffn_hbm_gbs", "value": ep["value"], "unit": "GB/s", "n_gpus": world,
+                    "steps": ep["steps"], "warmup": 3, "ms_per_step": ep["ms_per_step"], "higher_is_better": True,
+                    "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                    "config": {"workload": ep["workload"], "l2": "weights touched per step exceed L2 (126 MB)",
+                               **{k: ep[k] for k in ("bytes_per_step", "phase_ms", "a2a_bytes_per_rank_per_layer",
+                                                     "imbalance_max_over_mean_rows", "rows_received_per_step")}},
+                    "e2e": ep["e2e"], "gpu_launches": ep["gpu_launches_per_step"] * ep["steps"] * world,
+                    "clocks": clocks, "roofline": ep["roofline"], "cpu_baseline": None}
+            print(json.dumps(line), flush=True)
+        be.shutdown()
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    layers, handles, biases = [], [], []
     up = lambda t: be.upload(t.w, t.s, t.fmt, t.I, t.O, local, t.gs)
+    xs, lgs, biases = host_inputs(cfg, L, M, rank)
     for li in range(L):
         gate, upw, down = gen_layer_host(torch, cfg, 1000 * (rank + 1) + li, dev)
         hg, hu, hd = [up(t) for t in gate], [up(t) for t in upw], [up(t) for t in down]
         shared = None
-        sh_host = None
         if cfg["shared"]:
             sg, su, sd = gen_layer_host(torch, cfg, 777000 + 1000 * (rank + 1) + li, dev, n_experts=1)
-            sh_host = (sg[0], su[0], sd[0])
-            shared = tuple(up(t) for t in sh_host)
+            shared = tuple(up(t) for t in (sg[0], su[0], sd[0]))
         if not all(hg + hu + hd + list(shared or ())):
             raise RuntimeError("tensor upload failed")
         handles.append((hg, hu, hd, shared))
-        bias = None
-        if cfg["gating"] == 1:
-            bias = (np.random.default_rng(31 + li).standard_normal(E) * 0.01).astype(np.float32)
-        biases.append(bias)
         layers.append(MoeLayer(be, D, I, E, K, hg, hu, hd, cfg["gating"], cfg["norm_topk"], ROUTED_SCALE, 0.0,
-                               router_bias=bias, shared=shared, max_rows=max(M, 8)))
-        if rank == 0 and li < args.cpu_layers and not args.quick:
-            host_keep.append((gate, upw, down, sh_host))
+                               router_bias=biases[li], shared=shared, max_rows=max(M, 8)))
         del gate, upw, down
     torch.cuda.synchronize()
 
-    xs = [W.activations(M, D, 100 + li + 1000 * rank) for li in range(L)]
-    lgs = [W.router_logits(M, E, 200 + li + 1000 * rank) for li in range(L)]
     # distinct experts per layer call for the byte accounting, from the device's own routing
     nus = []
     for li in range(L):
@@ -391,301 +687,181 @@ def run_gpu_arm(args):
 
     def step_dev():
         for li in range(L):
-            ok = be.moe_layer_dev(layers[li].handle, out_dev[li].data_ptr(), x_dev[li].data_ptr(),
-                                  lg_dev[li].data_ptr(), M, None, None, None)
-            if not ok:
+            if not be.moe_layer_dev(layers[li].handle, out_dev[li].data_ptr(), x_dev[li].data_ptr(),
+                                    lg_dev[li].data_ptr(), M, None, None, None):
                 raise RuntimeError("coli_cuda_moe_layer_dev failed")
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    # ---- device-resident value ----------------------------------------------
+    # ---- device-resident value: median of `repeats` blocks of `steps` steps ---------------
     for _ in range(max(args.warmup, 3)):
         step_dev()
     barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for _ in range(args.steps):
-        step_dev()
-    e1.record(stream)
-    barrier()
-    ms = e0.elapsed_time(e1)
-    launches = 0
-    lt_ms, lt_n = C.c_float(), C.c_int()
-    be.set_timing(1)
+    sampler = ClockSampler(local).start() if rank == 0 else None
+    block_ms = []
+    for _ in range(repeats):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            step_dev()
+        e1.record(stream)
+        barrier()
+        block_ms.append(e0.elapsed_time(e1))
+    n0 = be.launch_total(local)
     step_dev()
     torch.cuda.synchronize()
-    be.set_timing(0)
-    be.last_timing(local, C.byref(lt_ms), C.byref(lt_n))
-    launches = lt_n.value * L * args.steps
+    launches_step = int(be.launch_total(local) - n0)
     if be.kernel_status(local) != 0:
         raise RuntimeError("a kernel wait guard expired")
+    clocks = sampler.stop() if sampler else None
 
-    # ---- dominant kernel, event-bracketed -----------------------------------
+    # ---- dominant kernel, event-bracketed (a separate pass: the brackets serialise the launches) ----
     be.set_kernel_events(1)
-    for _ in range(args.steps):
+    for _ in range(min(steps, 20)):
         step_dev()
     k_ms, k_n = C.c_float(), C.c_int()
     be.kernel_events(local, C.byref(k_ms), C.byref(k_n))
     be.set_kernel_events(0)
-    if rank == 0:
-        clocks = sampler.stop()
+    bracket_steps = min(steps, 20)
 
-    # ---- e2e through the host-buffer call -------------------------------------
+    # ---- e2e through the host-buffer call ---------------------------------------------------
     outs_host = [np.empty((M, D), np.float32) for _ in range(L)]
 
     def step_host():
         for li in range(L):
             layers[li].run_into(xs[li], lgs[li], outs_host[li])
-    e2e_s = float("nan")
+    e2e_blocks = [float("nan")]
     if not args.quick:
         for _ in range(max(args.warmup, 3)):
             step_host()
-        barrier()
-        t0 = time.perf_counter()
-        for _ in range(args.steps):
-            step_host()
-        torch.cuda.synchronize()
-        e2e_s = time.perf_counter() - t0
-
-    tmax = torch.tensor([ms, e2e_s * 1e3], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-        tot = torch.tensor([float(step_bytes)], device=dev, dtype=torch.float64)
-        dist.all_reduce(tot, op=dist.ReduceOp.SUM)
-        all_bytes = float(tot.item())
-    else:
-        all_bytes = float(step_bytes)
-    ms_all, e2e_ms_all = float(tmax[0].item()), float(tmax[1].item())
-
-    if rank == 0:
-        peak, which = measured_peaks()
-        value = all_bytes * args.steps / (ms_all * 1e-3) / 1e9
-        e2e = all_bytes * args.steps / (e2e_ms_all * 1e-3) / 1e9
-        ach = (weight_bytes_step * args.steps) / (k_ms.value * 1e-3) / 1e9 if k_ms.value > 0 else None
-        # CPU baseline on a bounded sample (first cpu_layers layers of the step)
-        cpu = None
-        try:
-            if args.quick:
-                raise RuntimeError("skipped (--quick)")
-            from oracle.oracle import Oracle, RefCpu
-            orc = Oracle()
-            ref = RefCpu() if RefCpu.available() else None
-            kind = "reference" if ref else "port"
-            if ref is None:
-                class Port:
-                    def expert_mlp(self, x, g, u, d): return orc.expert_mlp(x, g, u, d)
-                    def threads(self): return orc.threads()
-                ref = Port()
-            ids = list(range(len(host_keep)))
-            cpu_step(ref, orc, cfg, host_keep, xs, lgs, ids, biases)
+        e2e_blocks = []
+        for _ in range(repeats):
+            barrier()
             t0 = time.perf_counter()
-            nb, reps = 0, 0
-            while time.perf_counter() - t0 < args.cpu_seconds:
-                nb += cpu_step(ref, orc, cfg, host_keep, xs, lgs, ids, biases)
-                reps += 1
-            dt = time.perf_counter() - t0
-            cpu = {"value": nb / dt / 1e9, "unit": "GB/s", "cores": ref.threads(), "kind": kind,
-                   "sample": f"{reps} passes over the first {len(ids)} of {L} layers, {dt:.1f} s"}
-        except Exception as ex:   # the baseline is reported, never required
-            cpu = {"value": None, "unit": "GB/s", "cores": 0, "kind": "port", "sample": f"failed: {ex}"}
-        line = {
-            "metric": "moe_expert_ffn_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_all / args.steps,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic",
-            "config": {"workload": f"{args.workload}: MoE layer op (D={D}, I={I}, E={E}"
-                                   f"{'+1 shared' if cfg['shared'] else ''}, top-{K} "
-                                   f"{'softmax' if cfg['gating'] == 0 else 'sigmoid'}), "
-                                   f"{'int4 g32 fp16-valued scales' if fmt == 4 else 'MXFP4'}, M={M} rows, "
-                                   f"{L} distinct layers per step",
-                       "l2": f"{L} distinct layers, {weight_bytes_step / 1e6:.0f} MB of weights touched per step "
-                             f"(> 126 MB L2); no flush needed",
-                       "bytes_per_step": step_bytes, "distinct_experts_per_layer": nus,
-                       # one step = the MoE FFNs of all layers for M tokens: the decode rate this path alone allows
-                       "moe_only_tokens_per_s": M * args.steps / (ms_all * 1e-3),
-                       "vs_8tbs_nominal": value / world / 8000.0},
-            "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": L * (M * D * 4 + M * E * 4),
-                    "d2h_bytes_per_step": L * M * D * 4, "ms_per_step": e2e_ms_all / args.steps},
-            "gpu_launches": launches,
-            "clocks": clocks,
-            "roofline": (tensor_roofline(sum((M * K + (M if cfg["shared"] else 0)) * 6.0 * D * I for _ in range(L)) * args.steps,
-                                         k_ms.value, k_n.value, 3 if fmt == 4 else 2)
-                         if M >= 32 and (args.tc == 2 or (args.tc == 1 and M * K >= TC_MEAN_ROWS * E)) else
-                         {"bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s",
-                          "frac": (ach / peak) if ach else None,
-                          "traffic": NCU_TRAFFIC_BYTES.get((args.workload, M, E)),
-                          "algorithmic_bytes_per_launch": weight_bytes_step / L,
-                          "kernel": "k_moe_decode" if M <= 8 else "k_gemv_stream", "launches": k_n.value,
-                          "avg_launch_us": (k_ms.value / k_n.value * 1e3) if k_n.value else None,
-                          "peak_source": which}),
-            "cpu_baseline": cpu,
-        }
-        print(json.dumps(line), flush=True)
+            for _ in range(steps):
+                step_host()
+            torch.cuda.synchronize()
+            e2e_blocks.append((time.perf_counter() - t0) * 1e3)
+
     for lay in layers:
         lay.free()
     for hg, hu, hd, sh in handles:
         for t in hg + hu + hd + list(sh or ()):
             be.tensor_free(t)
-    be.shutdown()
+    layers, handles = [], []
+
+    # max over ranks block by block, then the median block
+    tb = torch.tensor([block_ms, e2e_blocks if len(e2e_blocks) == repeats else [float("nan")] * repeats],
+                      device=dev, dtype=torch.float64)
+    tot = torch.tensor([float(step_bytes)], device=dev, dtype=torch.float64)
     if world > 1:
-        dist.destroy_process_group()
+        dist.all_reduce(tb, op=dist.ReduceOp.MAX)
+        dist.all_reduce(tot, op=dist.ReduceOp.SUM)
+    all_bytes = float(tot.item())
+    blocks = np.array(tb[0].tolist())
+    e2e_b = np.array(tb[1].tolist())
+    ms_med = float(np.median(blocks))
 
+    # ---- the sharded configuration on the same ranks (every N, 1 included) --------------------
+    ep = None
+    if name == "c2_decode" and not args.quick and not args.no_ep:
+        try:
+            ep = run_ep_block(args, be, world, rank, local, args.ep_layers, 2048, balanced=not args.ep_blocks)
+        except Exception as ex:      # reported, never fatal for the headline line
+            ep = {"failed": f"{type(ex).__name__}: {ex}"} if rank == 0 else None
 
-# ---------------------------------------------------------------------------
-# expert-parallel workload (configuration 5)
-# ---------------------------------------------------------------------------
-def run_ep_arm(args):
-    """Configuration 5: GLM-scale layer (D 6144, I 2048, 256 routed experts + 1 shared,
-    top-8 sigmoid, MXFP4), 4 layers, M = 2048 rows in total, Zipf(1.1)-skewed logits;
-    experts sharded over the ranks, dispatch and combine as NCCL all-to-all. Strong
-    scaling: the total work is fixed. value = algorithmic weight bytes of all ranks
-    (distinct experts actually used + one shared expert per rank) + activations, per
-    step / max-over-ranks time."""
-    import torch
-    import torch.distributed as dist
-    from colibri_b200.backend import Backend
-    from colibri_b200.ep import CudaEpLayer, ep_moe_layer
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
-    cfg = dict(W.CONFIGS["c5"])
-    if args.experts:
-        cfg["E"] = args.experts
-    D, I, E, K = cfg["D"], cfg["I"], cfg["E"], cfg["K"]
-    L = args.layers if args.layers != 16 else 4
-    M = args.M if args.M != 1 else 2048
-    assert E % world == 0 and M % world == 0
-    e_loc, m = E // world, M // world
-    be = Backend()
-    if be.init_devices((local,)) != 1:
-        raise RuntimeError("coli_cuda_init failed: the CUDA backend is required (no CPU fallback)")
-    up = lambda t: be.upload(t.w, t.s, t.fmt, t.I, t.O, local, t.gs)
-    layers = []
-    for li in range(L):
-        hs = [[], [], []]
-        for e in range(rank * e_loc, (rank + 1) * e_loc):
-            for k, (O, Kd) in enumerate(((I, D), (I, D), (D, I))):
-                pk, sc = gen_mxfp4_torch(torch, 1, O, Kd, ((li * 1024 + e) * 4 + k) * 7 + 5, dev)
-                hs[k].append(up(QTensor(pk[0], sc[0], 7, Kd, O, 0)))
-        sh = []
-        for k, (O, Kd) in enumerate(((I, D), (I, D), (D, I))):
-            pk, sc = gen_mxfp4_torch(torch, 1, O, Kd, ((li * 1024 + 1000) * 4 + k) * 7 + 5, dev)
-            sh.append(up(QTensor(pk[0], sc[0], 7, Kd, O, 0)))
-        if not all(hs[0] + hs[1] + hs[2] + sh):
-            raise RuntimeError("tensor upload failed")
-        bias = torch.from_numpy((np.random.default_rng(31 + li).standard_normal(E) * 0.01).astype(np.float32)).to(dev)
-        layers.append(CudaEpLayer(be, local, cfg, hs[0], hs[1], hs[2], tuple(sh), bias, rank * e_loc, ROUTED_SCALE))
-    xs = [torch.from_numpy(W.activations(M, D, 500 + li)[rank * m:(rank + 1) * m].copy()).to(dev) for li in range(L)]
-    lg_all = [W.router_logits(M, E, 600 + li, zipf=1.1) for li in range(L)]
-    lgs = [torch.from_numpy(l[rank * m:(rank + 1) * m].copy()).to(dev) for l in lg_all]
-    # byte accounting from the routing of all rows, done on this rank's GPU
-    eb = expert_bytes_device(cfg)
-    step_bytes = 0
-    for li in range(L):
-        lay = layers[li]
-        lay.logits = torch.from_numpy(lg_all[li]).to(dev)
-        ridx, _, rkeff = lay.route(torch.empty((M, 1), device=dev))
-        live = ridx[torch.arange(K, device=dev).unsqueeze(0) < rkeff.unsqueeze(1)]
-        step_bytes += (int(torch.unique(live).numel()) + world) * eb + 2 * M * D * 4
-    torch.cuda.synchronize()
-
-    def step():
-        outs = []
-        for li in range(L):
-            lay = layers[li]
-            lay.logits = lgs[li]
-            out, _ = ep_moe_layer(xs[li], lay.route, lay.experts, lay.shared_fn, E, combine=lay.combine)
-            outs.append(out)
-        return outs
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-    for _ in range(max(args.warmup, 3)):
-        step()
-    barrier()
-    sampler = ClockSampler(local)
     if rank == 0:
-        sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1)
-    # kernels launched per step, and the grouped-GEMM kernel time, from one more step
-    n0 = be.launch_total(local)
-    be.set_kernel_events(1)
-    step()
-    k_ms, k_n = C.c_float(), C.c_int()
-    be.kernel_events(local, C.byref(k_ms), C.byref(k_n))
-    be.set_kernel_events(0)
-    launches_step = int(be.launch_total(local) - n0)
-    clocks = sampler.stop() if rank == 0 else None
-    # end to end: rows and logits start in pinned host memory, the result is read back
-    x_pin = [x.cpu().pin_memory() for x in xs]
-    lg_pin = [l.cpu().pin_memory() for l in lgs]
-    out_pin = torch.empty((m, D), dtype=torch.float32).pin_memory()
-
-    def step_host():
-        for li in range(L):
-            lay = layers[li]
-            xd = x_pin[li].to(dev, non_blocking=True)
-            lay.logits = lg_pin[li].to(dev, non_blocking=True)
-            out, _ = ep_moe_layer(xd, lay.route, lay.experts, lay.shared_fn, E, combine=lay.combine)
-            out_pin.copy_(out, non_blocking=True)
-        torch.cuda.synchronize()
-    for _ in range(2):
-        step_host()
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        step_host()
-    barrier()
-    e2e_ms = (time.perf_counter() - t0) * 1e3
-    t = torch.tensor([ms, e2e_ms, k_ms.value], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_all, e2e_all, k_ms_all = float(t[0].item()), float(t[1].item()), float(t[2].item())
-    if be.kernel_status(local) != 0:
-        raise RuntimeError("a kernel wait guard expired")
-    if rank == 0:
-        peak, which = measured_peaks()
-        value = step_bytes * args.steps / (ms_all * 1e-3) / 1e9
+        hbm_peak, tc_peak, which = peaks()
+        value = all_bytes * steps / (ms_med * 1e-3) / 1e9
+        e2e_med = float(np.median(e2e_b))
+        e2e = all_bytes * steps / (e2e_med * 1e-3) / 1e9
+        fused = M <= 8
+        uses_tc = M >= 32 and (args.tc == 2 or (args.tc == 1 and M * K >= TC_MEAN_ROWS * E))
+        if fused:
+            # one launch per layer call: the kernel's share of the timed step (launch gaps included)
+            launch_us = ms_med / steps / L * 1e3
+            ach = (weight_bytes_step / L) / (launch_us * 1e-6) / 1e9
+            kernel, kl = "k_moe_decode", L * steps
+        else:
+            launch_us = (k_ms.value / k_n.value * 1e3) if k_n.value else None
+            ach = (weight_bytes_step * bracket_steps) / (k_ms.value * 1e-3) / 1e9 if k_ms.value > 0 else None
+            kernel, kl = ("k_expert_gemm_tc" if uses_tc else "k_gemv_stream"), k_n.value
+        roofline = {"bound": "hbm", "achieved": ach, "peak": hbm_peak, "unit": "GB/s",
+                    "frac": (ach / hbm_peak) if ach else None,
+                    "traffic": NCU_TRAFFIC_BYTES.get((name, M, E)),
+                    "algorithmic_bytes_per_launch": weight_bytes_step / L if fused else None,
+                    "kernel": kernel, "launches": kl, "avg_launch_us": launch_us,
+                    "timing": "timed step / launches (same run as value)" if fused else "event-bracketed launches (separate pass)",
+                    "bracketed_avg_launch_us": (k_ms.value / k_n.value * 1e3) if k_n.value else None,
+                    "peak_source": which}
+        if uses_tc:
+            flop = sum((M * K + (M if cfg["shared"] else 0)) * 6.0 * D * I for _ in range(L)) * bracket_steps
+            terms = 3 if fmt == 4 else 2
+            tf = flop / (k_ms.value * 1e-3) / 1e12 if k_ms.value > 0 else None
+            roofline["tensor"] = {"achieved": tf, "peak": tc_peak, "unit": "TFLOP/s", "frac": tf / tc_peak if tf else None,
+                                  "mma_terms_per_product": terms}
+        # CPU baseline: the same layers with the reference's kernels, all host threads
+        cpu = None
+        try:
+            if args.quick:
+                raise RuntimeError("skipped (--quick)")
+            restore_omp_threads()
+            cpux = CpuExperts()
+            hl = host_layers_for(cpux.oracle, cfg, L, lgs, biases)
+            ids = list(range(L))
+            cpu_step(cpux, cfg, hl, xs, lgs, ids, biases)
+            t0 = time.perf_counter()
+            nb, reps = 0, 0
+            while time.perf_counter() - t0 < args.cpu_seconds:
+                nb += cpu_step(cpux, cfg, hl, xs, lgs, ids, biases)
+                reps += 1
+            dt = time.perf_counter() - t0
+            cpu = {"value": nb / dt / 1e9, "unit": "GB/s", "cores": cpux.threads(), "kind": cpux.kind,
+                   "sample": f"{reps} passes over all {L} layers of the step, {dt:.1f} s; {cpux.build}; exact f32 kernels "
+                             f"(matmul_{'i4_grouped' if fmt == 4 else 'mxfp4'}), the reference's default for this format"}
+            if fmt == 7:
+                t0 = time.perf_counter()
+                nb2, reps2 = 0, 0
+                while time.perf_counter() - t0 < args.cpu_seconds / 2:
+                    nb2 += cpu_step(cpux, cfg, hl, xs, lgs, ids, biases, idot=True)
+                    reps2 += 1
+                dt2 = time.perf_counter() - t0
+                cpu["idot"] = {"value": nb2 / dt2 / 1e9, "unit": "GB/s", "kernel": f"matmul_mxfp4_i8 ({cpux.idot_kernel()})",
+                               "note": "int8-quantised activations: the reference's fastest path, not bit-comparable"}
+            else:
+                cpu["idot"] = {"value": None, "note": "the reference has no integer-dot kernel for grouped int4 (fmt 4): "
+                                                      "matmul_qt_ex sends it to matmul_i4_grouped whatever IDOT says"}
+        except Exception as ex:   # the baseline is reported, never required
+            cpu = {"value": None, "unit": "GB/s", "cores": 0, "kind": "port", "sample": f"failed: {ex}"}
         line = {
             "metric": "moe_expert_ffn_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_all / args.steps,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_med / steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
-            "config": {"workload": f"c5_ep: expert-parallel MoE layer (D={D}, I={I}, E={E}+1 shared, top-{K} sigmoid, "
-                                   f"MXFP4), M={M} rows in total, {L} layers per step, Zipf(1.1) logit bias, "
-                                   f"experts sharded over {world} rank(s), NCCL all-to-all dispatch/combine (f32 rows)",
-                       "l2": "weights touched per step exceed L2 (126 MB)", "bytes_per_step": step_bytes,
-                       "a2a_bytes_per_rank_per_layer": int(2 * (M // world) * K * D * 4 * (world - 1) / max(world, 1))},
-            "e2e": {"value": step_bytes * args.steps / (e2e_all * 1e-3) / 1e9, "unit": "GB/s",
-                    "h2d_bytes_per_step": L * world * (m * D * 4 + m * E * 4), "d2h_bytes_per_step": L * world * m * D * 4,
-                    "ms_per_step": e2e_all / args.steps},
-            "gpu_launches": launches_step * args.steps * world, "clocks": clocks,
-            # per GPU: this rank's share of the rows (an even share is assumed for the FLOP count)
-            "roofline": tensor_roofline((M * K / world + m) * 6.0 * D * I * L, k_ms_all, k_n.value, 2),
-            "cpu_baseline": None,
+            "spread": {"repeats": repeats, "ms_per_step_min": float(blocks.min()) / steps,
+                       "ms_per_step_max": float(blocks.max()) / steps,
+                       "value_min": all_bytes * steps / (float(blocks.max()) * 1e-3) / 1e9,
+                       "value_max": all_bytes * steps / (float(blocks.min()) * 1e-3) / 1e9},
+            "config": {"workload": workload_string(name, cfg, M, L),
+                       "l2": f"{L} distinct layers, {weight_bytes_step / 1e6:.0f} MB of weights touched per step "
+                             f"(> 126 MB L2); no flush needed",
+                       "bytes_per_step": step_bytes, "distinct_experts_per_layer": nus,
+                       # one step = the MoE FFNs of all layers for M tokens: the decode rate this path alone allows
+                       "moe_only_tokens_per_s": M * steps / (ms_med * 1e-3),
+                       "vs_8tbs_nominal": value / world / 8000.0,
+                       "c5_ep": ep},
+            "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": L * (M * D * 4 + M * E * 4),
+                    "d2h_bytes_per_step": L * M * D * 4, "ms_per_step": e2e_med / steps,
+                    "ms_per_step_min": float(np.min(e2e_b)) / steps, "ms_per_step_max": float(np.max(e2e_b)) / steps},
+            "gpu_launches": launches_step * steps * repeats * world,
+            "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
         }
-        print(json.dumps(line), flush=True)
     be.shutdown()
+    if rank == 0:
+        if world == 1 and not args.quick and not args.no_gpu_baseline and M <= 8:
+            try:
+                line["gpu_baseline"] = gpu_baseline_reference_cuda(cfg, L, M, min(steps, 20), xs, lgs, biases, torch, dev)
+            except Exception as ex:
+                line["gpu_baseline"] = {"unavailable": f"{type(ex).__name__}: {ex}"}
+        print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
@@ -738,8 +914,7 @@ def run_stack_arm(args):
     ids = [ids_rng.integers(0, vocab, size=K) for _ in range(args.steps + max(args.warmup, 3))]
     for i in range(max(args.warmup, 3)):
         st.step(ids[i], want_logits=False)
-    sampler = ClockSampler(0)
-    sampler.start()
+    sampler = ClockSampler(0).start()
     n0 = be.launch_total(0)
     t0 = time.perf_counter()
     for i in range(args.steps):
@@ -753,7 +928,7 @@ def run_stack_arm(args):
     nu = E * (1.0 - (1.0 - Kt / E) ** K) + 1
     eb = expert_bytes_device(cfg)
     step_bytes = NL * nu * eb + vocab * D * 4 + 2 * K * D * 4
-    peak, which = measured_peaks()
+    hbm_peak, _, which = peaks()
     value = step_bytes * args.steps / dt / 1e9
     line = {
         "metric": "moe_expert_ffn_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
@@ -766,8 +941,8 @@ def run_stack_arm(args):
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": K * D * 4, "d2h_bytes_per_step": K * 4,
                 "ms_per_step": dt / args.steps * 1e3},
         "gpu_launches": launches, "clocks": clocks,
-        "roofline": {"bound": "hbm", "achieved": value, "peak": peak, "unit": "GB/s", "frac": value / peak,
-                     "traffic": None, "kernel": "whole step (k_moe_decode x4, k_generic_matmul head)", "peak_source": which},
+        "roofline": {"bound": "hbm", "achieved": value, "peak": hbm_peak, "unit": "GB/s", "frac": value / hbm_peak,
+                     "traffic": None, "kernel": "whole step (k_moe_decode x4, k_dense_gemv head)", "peak_source": which},
         "cpu_baseline": None,
     }
     print(json.dumps(line), flush=True)
@@ -783,19 +958,24 @@ def run_stack_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=100, help="steps per timed block")
+    ap.add_argument("--repeats", type=int, default=10, help="timed blocks; the median is reported")
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2_decode", choices=["c2_decode", "c3_decode", "c4_decode", "c5_ep", "c4_stack"],
                     help="layer shape and weight format (configuration 2, 3 or 4 of the benchmark)")
     ap.add_argument("--M", type=int, default=1, help="rows per layer call")
     ap.add_argument("--experts", type=int, default=0, help="override the expert count (profiling subsets)")
-    ap.add_argument("--quick", action="store_true", help="device-resident timing only (no e2e, no CPU baseline)")
+    ap.add_argument("--quick", action="store_true", help="device-resident timing only (no e2e, CPU, baseline or sharded legs)")
     ap.add_argument("--layers", type=int, default=16)
-    ap.add_argument("--cpu-layers", type=int, default=4, help="layers kept on the host for the CPU baseline sample")
-    ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--tc", type=int, default=1, choices=[0, 1, 2],
                     help="tensor-core path: 0 never, 1 when it pays (default), 2 whenever possible")
+    ap.add_argument("--no-ep", action="store_true", help="skip the sharded configuration attached to the default line")
+    ap.add_argument("--ep-layers", type=int, default=4)
+    ap.add_argument("--ep-steps", type=int, default=5)
+    ap.add_argument("--ep-blocks", action="store_true", help="place experts in equal blocks instead of by routing histogram")
+    ap.add_argument("--no-gpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.workload == "c4_stack":
         if args.impl == "reference":
@@ -803,12 +983,9 @@ def main():
                               "weights on the host; the reference CPU arm is timed on the default workload"}))
         else:
             run_stack_arm(args)
-    elif args.workload == "c5_ep":
-        if args.impl == "reference":
-            print(json.dumps({"impl": "reference", "unavailable": "the reference has no expert-parallel path "
-                              "(no collective library); its CPU arm is timed on the default workload"}))
-        else:
-            run_ep_arm(args)
+    elif args.workload == "c5_ep" and args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": "the reference has no expert-parallel path "
+                          "(no collective library); its CPU arm is timed on the default workload"}))
     elif args.impl == "reference":
         run_reference_arm(args)
     else:

@@ -51,6 +51,7 @@ REFERENCE_ABI = [
     ("coli_cuda_fp8_set_lut", C.c_int, [_vp]),
     ("coli_cuda_tensor_upload_g", C.c_int, [C.POINTER(_vp), _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     ("coli_cuda_tensor_upload", C.c_int, [C.POINTER(_vp), _vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int]),
+    ("coli_cuda_tensor_upload_compressed", C.c_int, None),
     ("coli_cuda_tensor_free", None, [_vp]),
     ("coli_cuda_tensor_bytes", C.c_size_t, [_vp]),
     ("coli_cuda_tensor_device", C.c_int, [_vp]),

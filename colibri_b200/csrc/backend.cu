@@ -150,7 +150,7 @@ static int tc_smem_bytes() { return tc_smem_total(MODE); }
 extern "C" void coli_cuda_shutdown(void);
 
 static int decode_smem_bytes(int mode) {
-    return DEC_WARPS * DEC_NST * chunk_bytes_of(mode) + 512 + (int)((sizeof(DecShared) + 127) & ~127) +
+    return DEC_WARPS * DEC_NST * chunk_bytes_of(mode) + 1024 + (int)((sizeof(DecShared) + 127) & ~127) +
            2 * DEC_PART_BYTES + dec_act_bytes(mode);
 }
 
@@ -489,8 +489,8 @@ extern "C" int coli_cuda_tensor_upload_g(ColiCudaTensor **tensor, const void *we
 }
 // The entropy-coded upload of builds with -DCOLI_ANS (c/backend_cuda.h:60-67): this backend
 // holds no decoder for it and refuses, which the engine answers by uploading the plain bytes.
-extern "C" int coli_cuda_tensor_upload_compressed(ColiCudaTensor **, const void *, size_t, const void *, size_t,
-                                                  int, int, int, int) { return 0; }
+extern "C" int coli_cuda_tensor_upload_compressed(ColiCudaTensor **, const void *, const float *, int, int, int,
+                                                  int) { return 0; }
 extern "C" void coli_cuda_tensor_free(ColiCudaTensor *t) {
     if (!t) return;
     DeviceCtx *c = find_ctx(t->device);

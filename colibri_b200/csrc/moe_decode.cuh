@@ -106,7 +106,7 @@ struct DecShared {
 };
 
 #ifdef COLI_DECODE_PROBE
-#define DEC_NPROBE 12
+#define DEC_NPROBE 16
 #define DEC_PROBE(a, slot)                                                             \
     do {                                                                               \
         if ((a).probe && threadIdx.x == 0) {                                           \
@@ -440,23 +440,32 @@ __device__ __forceinline__ void dec_it_next(DecIt &it, const DecPhase &ph1, cons
     it.mat = 0;
     it.u += ph.ng;
     if (it.u < ph.u1) { dec_it_unit<CH>(it, ph, sh); return; }
-    if (it.ph == 1) dec_it_start<CH>(it, 2, ph1, ph2, sh); else it.ph = 3;
+    // the stream runs on into the down phase, except into a local one (its ring geometry differs:
+    // the kernel restarts the stream itself once this warp's gate/up blocks are consumed)
+    if (it.ph == 1 && !ph2.local) dec_it_start<CH>(it, 2, ph1, ph2, sh); else it.ph = 3;
 }
 
-// Ring state of one warp across the phases of the kernel.
+// Ring state of one warp across the phases of the kernel: `nst` slots of `sb` bytes, one
+// mbarrier per slot (six exist per warp). A barrier's phase parity lives in `parbits`, so the
+// slot geometry can change between the phases (3 whole chunks, or 6 half-chunks for the local
+// down phase) without re-initialising anything, as long as nothing is in flight at the switch.
 struct WarpRing {
     uint32_t ring, bars;
-    int issued, consumed;
-    bool ok;          // false once a wait has expired: later waits are skipped
+    int issued, consumed;     // totals (issued - consumed = copies in flight)
+    int pi, ci;               // slot the next copy goes to / the next wait looks at
+    int nst, sb;
+    uint32_t parbits;
+    bool ok;                  // false once a wait has expired: later waits are skipped
 };
+#define DEC_BARS_PER_WARP 6
 
 template <int CH, int NST>
 __device__ __forceinline__ void dec_issue_one(WarpRing &wr, DecIt &it, const DecPhase &ph1, const DecPhase &ph2,
                                               const DecShared *sh, int lane) {
     if (it.ph > 2) return;
-    if (wr.issued - wr.consumed >= NST) return;
+    if (wr.issued - wr.consumed >= wr.nst) return;
     if (lane == 0) {
-        const uint32_t bar = wr.bars + (wr.issued % NST) * 8, dst = wr.ring + (wr.issued % NST) * CH;
+        const uint32_t bar = wr.bars + wr.pi * 8, dst = wr.ring + wr.pi * wr.sb;
         if (it.ph == 2 && ph2.local) {
             // one 16-row half: 1024 bytes of codes, then its half of the scales
             constexpr int SCH = (CH - CODE_BYTES) / 2;
@@ -469,15 +478,22 @@ __device__ __forceinline__ void dec_issue_one(WarpRing &wr, DecIt &it, const Dec
         }
     }
     wr.issued++;
+    if (++wr.pi == wr.nst) wr.pi = 0;
     dec_it_next<CH>(it, ph1, ph2, sh);
 }
 
 // Waits for the oldest outstanding chunk of the ring; returns its shared-memory address.
 template <int CH, int NST>
 __device__ __forceinline__ uint32_t dec_wait_chunk(WarpRing &wr) {
-    const int stage = wr.consumed % NST;
-    if (wr.ok && !mbar_wait_bounded(wr.bars + stage * 8, (wr.consumed / NST) & 1)) wr.ok = false;
-    return wr.ring + stage * CH;
+    const int slot = wr.ci;
+    if (wr.ok && !mbar_wait_bounded(wr.bars + slot * 8, (wr.parbits >> slot) & 1u)) wr.ok = false;
+    return wr.ring + slot * wr.sb;
+}
+// after the chunk has been read: its slot is free again
+__device__ __forceinline__ void dec_release_chunk(WarpRing &wr) {
+    wr.parbits ^= 1u << wr.ci;
+    wr.consumed++;
+    if (++wr.ci == wr.nst) wr.ci = 0;
 }
 
 // This CTA's contiguous share [t0, t1) of n units: sizes differ by at most one.
@@ -500,9 +516,9 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
     constexpr int CH = CODE_BYTES + (MODE == SC_H16 ? 256 : MODE == SC_F32 ? 512 : MODE == SC_MX ? 128 : 0);
     constexpr int NST = DEC_NST;
     extern __shared__ __align__(128) uint8_t smem[];
-    // layout: rings | mbarriers (512 B) | DecShared | partial sums (2 buffers; the routing
+    // layout: rings | mbarriers (1024 B) | DecShared | partial sums (2 buffers; the routing
     // scratch and tables live here first) | activation region
-    DecShared *sh = reinterpret_cast<DecShared *>(smem + DEC_WARPS * NST * CH + 512);
+    DecShared *sh = reinterpret_cast<DecShared *>(smem + DEC_WARPS * NST * CH + 1024);
     uint8_t *part = reinterpret_cast<uint8_t *>(sh) + ((sizeof(DecShared) + 127) & ~127);
     uint8_t *act = part + 2 * DEC_PART_BYTES;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
@@ -512,8 +528,8 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
     const int nkb1 = D / BLOCK_K, nkb2 = I / BLOCK_K, nt1 = I / TILE_ROWS, nt2 = D / TILE_ROWS;
     WarpRing wr;
     wr.ring = smem_u32(smem) + warp * (NST * CH);
-    wr.bars = smem_u32(smem) + DEC_WARPS * NST * CH + warp * NST * 8;
-    wr.issued = 0; wr.consumed = 0; wr.ok = true;
+    wr.bars = smem_u32(smem) + DEC_WARPS * NST * CH + warp * DEC_BARS_PER_WARP * 8;
+    wr.issued = 0; wr.consumed = 0; wr.pi = 0; wr.ci = 0; wr.nst = NST; wr.sb = CH; wr.parbits = 0; wr.ok = true;
     // routing scratch inside the partial-sum buffers (dead before the first partial sum is written)
     float *score = reinterpret_cast<float *>(part);                     // [M*E]  (<= 8 KB)
     float *choice = reinterpret_cast<float *>(part + 8192);             // [M*E]
@@ -581,13 +597,14 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
         }
     }
     if (lane == 0) {
-        for (int s = 0; s < NST; s++) mbar_init(wr.bars + s * 8, 1);
+        for (int s = 0; s < DEC_BARS_PER_WARP; s++) mbar_init(wr.bars + s * 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (tid == 0) { sh->failed = 0; sh->nu = 0; }
     for (int e = tid; e < E; e += blockDim.x) { t_first[e] = 0x7fffffff; t_cnt[e] = 0; }
     wtab[lane] = tab_v;          // this warp's own copy of the table (no CTA-wide wait before the routing)
     __syncwarp();
+    if (tid == 0) DEC_PROBE_T(a, 12);        // first loads have returned
 
     // ---- routing, redundantly in every CTA -------------------------------------------
     // Scores: softmax rows by one warp each (the serial denominator is the long pole),
@@ -620,6 +637,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
                 sc[e2] = p; chc[e2] = p;
                 bad |= !(p > -1e30f);
             }
+            if (tid == 0) DEC_PROBE_T(a, 13);    // scores of row 0 written
         }
     } else {
 #pragma unroll
@@ -651,6 +669,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
     }
     if (tid < E) { ptab[tid] = pre_g; ptab[E + tid] = pre_u; ptab[2 * E + tid] = pre_d; }
     const int any_bad = __syncthreads_or(bad ? 1 : 0);
+    if (tid == 0) DEC_PROBE_T(a, 14);            // scores, x fragments and pointer table complete
     if (any_bad) {
         // a NaN or a value <= -1e30 among the candidates: the general form, which also
         // reproduces the engine's "nothing found -> expert kk" degradation row by row
@@ -864,7 +883,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
                     for (int s = 0; s < 2; s++)
 #pragma unroll
                         for (int i = 0; i < 4; i++) R[s][i] = fmaf(bacc[0][s][i], ixs, R[s][i]);
-                    wr.consumed++;
+                    dec_release_chunk(wr);
                     __syncwarp();
                     if (tid == 0 && wr.consumed == 1) DEC_PROBE_T(a, 3);      // first block of the stream consumed
                     dec_issue_one<CH, NST>(wr, it, ph1, ph2, sh, lane);
@@ -904,6 +923,13 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
                 }
             }
         }
+    }
+    if (a.local2) {
+        // every gate/up block of this warp has landed and been read: the ring becomes six slots of
+        // half a chunk, and the down stream starts now, ahead of the barrier
+        wr.nst = 2 * NST; wr.sb = CH / 2; wr.pi = 0; wr.ci = 0; wr.issued = 0; wr.consumed = 0;
+        dec_it_start<CH>(it, 2, ph1, ph2, sh);
+        for (int s = 0; s < 2 * NST; s++) dec_issue_one<CH, NST>(wr, it, ph1, ph2, sh, lane);
     }
     DEC_PROBE(a, 4);   // gate/up consumed (the ring already holds the first down blocks)
     bool ok = grid_barrier(a.sync, &sh->failed);
@@ -977,7 +1003,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
                     block_mma<MODE, 1, true, 1>(st, lane, g, [&](int grp, int) { return bpre[grp]; }, bacc, ixg);
 #pragma unroll
                     for (int i = 0; i < 4; i++) R[i] += bacc[0][0][i];
-                    wr.consumed++;
+                    dec_release_chunk(wr);
                     __syncwarp();
                     dec_issue_one<CH, NST>(wr, it, ph1, ph2, sh, lane);
                 }
@@ -1043,7 +1069,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
                 for (int s = 0; s < 2; s++)
 #pragma unroll
                     for (int i = 0; i < 4; i++) R[s][i] += bacc[0][s][i];
-                wr.consumed++;
+                dec_release_chunk(wr);
                 __syncwarp();
                 dec_issue_one<CH, NST>(wr, it, ph1, ph2, sh, lane);
             }
@@ -1092,8 +1118,11 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
     if (!ok || sh->failed) {
         if (tid == 0) kstat_set(a.status, sh->failed == 2 ? KSTAT_MBAR_TIMEOUT : KSTAT_GRID_TIMEOUT);
         // drain copies still in flight before the shared memory goes away (bounded)
-        for (int i = wr.consumed; i < wr.issued; i++)
-            if (!mbar_wait_bounded(wr.bars + (i % NST) * 8, (i / NST) & 1)) break;
+        for (int i = wr.consumed; i < wr.issued; i++) {
+            if (!mbar_wait_bounded(wr.bars + wr.ci * 8, (wr.parbits >> wr.ci) & 1u)) break;
+            wr.parbits ^= 1u << wr.ci;
+            if (++wr.ci == wr.nst) wr.ci = 0;
+        }
     }
 }
 

@@ -48,21 +48,28 @@ void coli_cuda_group_stats(uint64_t *calls, uint64_t *experts, uint64_t *rows,
 void coli_cuda_group_stats_device(int device, uint64_t *calls, uint64_t *experts, uint64_t *rows,
                                   double *h2d_ms, double *kernel_ms, double *d2h_ms);
 
-/* Decode tables for formats outside this backend's scope — c/backend_cuda.h:45-50.
- * fmt=6 (E8 lattice) and fmt=8 (FP8 block) tensors are refused, so both return 0. */
+/* Decode tables — c/backend_cuda.h:45-50. fmt=6 (E8 lattice) tensors are outside this
+ * backend's scope and refused, so coli_cuda_e8_set_grid returns 0. coli_cuda_fp8_set_lut
+ * takes the engine's 256-entry FP8 E4M3 table (c/quant.h:468-503) once after init; fmt=8
+ * uploads are refused until it has (c/backend_cuda.cu:1116). */
 int coli_cuda_e8_set_grid(const void *grid);
 int coli_cuda_fp8_set_lut(const float *lut);
 
 /* Resident tensors — c/backend_cuda.h:53-59,142-149.
  * fmt: 0=f32, 1=int8 per-row scale, 2=int4 per-row, 3=int2 per-row, 4=int4 with
  * one f32 scale per `gs` columns (scales[o*ceil(I/gs)+g]), 7=MXFP4 (e2m1
- * nibbles, `scales` points at [O, ceil(I/32)] ue8m0 BYTES). With *tensor
+ * nibbles, `scales` points at [O, ceil(I/32)] ue8m0 BYTES), 8=FP8 E4M3 bytes with
+ * one f32 scale per 128x128 block (scales[(o/128)*ceil(I/128) + i/128]). With *tensor
  * already set the call only checks that (fmt,I,O,device,gs) match and works
  * with NULL host pointers. */
 int coli_cuda_tensor_upload_g(ColiCudaTensor **tensor, const void *weights, const float *scales,
                               int fmt, int I, int O, int device, int gs);
 int coli_cuda_tensor_upload(ColiCudaTensor **tensor, const void *weights, const float *scales,
                             int fmt, int I, int O, int device);
+/* The entropy-coded upload of engines built with -DCOLI_ANS (c/backend_cuda.h:60-67).
+ * This backend holds no decoder for it: always 0, the engine then uploads plain bytes. */
+int coli_cuda_tensor_upload_compressed(ColiCudaTensor **tensor, const void *weights, const float *scales,
+                                       int fmt, int I, int O, int device);
 void coli_cuda_tensor_free(ColiCudaTensor *tensor);
 size_t coli_cuda_tensor_bytes(const ColiCudaTensor *tensor);
 int coli_cuda_tensor_device(const ColiCudaTensor *tensor);
@@ -138,7 +145,9 @@ int coli_cuda_pipe_rmsnorm(int device, float *y_dev, const float *x_dev, const f
                            int S, int D, float eps);
 int coli_cuda_pipe_rmsnorm_s(int device, float *y_dev, const float *x_dev, const float *w_dev,
                              int S, int D, float eps, int xstride, int ystride);
-/* RoPE belongs to the attention path: both return 0. */
+/* Interleaved rotary embedding of rows of the resident pipeline (c/backend_cuda.cu:2049-2063,
+ * 2123-2139): R <= 256 floats at v + row*stride + offset, position pos[row / heads] or
+ * pos_base + row / heads. */
 int coli_cuda_pipe_rope(int device, float *v_dev, const int *pos_dev, int rows, int stride,
                         int offset, int R, int heads, float theta);
 int coli_cuda_pipe_rope_base(int device, float *v_dev, int pos_base, int rows, int stride,
@@ -244,6 +253,37 @@ int coli_cuda_route_topk_dev(int device, const float *logits_dev, const float *b
  * the answer at 0). Lets a device-resident decode loop download S integers instead of
  * S*N logits. Enqueues on the backend's stream. No counterpart in the reference. */
 int coli_cuda_pipe_argmax(int device, int *idx_dev, const float *x_dev, int S, int N);
+
+/* ---- Expert-parallel layer, device side (no counterpart in the reference, which pins whole
+ * experts to devices and moves rows host -> device per call, c/colibri.c:4819-4839,
+ * 8367-8417). One process per GPU; the host issues the all-to-all exchanges (NCCL) between
+ * these calls. All three enqueue on the backend's stream.
+ *
+ * coli_cuda_ep_plan_dev: from this rank's routing (idx [m,K], keff [m]) and the placement
+ * (dest[e] = owning rank, slot[e] = index among that rank's experts; G ranks, at most `slots`
+ * experts per rank) it fills counts [G*slots] (live entries per destination rank and local
+ * expert), entry_of [m*K] (position of every live entry in the send buffer, -1 for dead ones)
+ * and send [n, D]: the rows in (destination rank, local expert, row order) as bf16
+ * (payload_bf16 != 0; *inexact is raised when a value is not exact in bf16, which would change
+ * results) or f32. send must hold m*K rows. K <= 31.
+ *
+ * coli_cuda_ep_expert_group_dev: expert FFN over the rows this rank received. x_dev holds them
+ * in receive order (source rank, local expert, row order), recv_counts (host) [nsrc][nslots]
+ * says how many; results go to y_dev [n, D] f32 in the same order, ready to be sent back.
+ *
+ * coli_cuda_ep_combine_dev: out[s] = sum_{kk < keff[s]} w[s,kk] * y[entry_of[s*K+kk]]
+ * (+ shared[s]), y in send-buffer order: each row's selection order, shared expert last, so
+ * the layer's result does not depend on the number of ranks or the placement. */
+int coli_cuda_ep_plan_dev(int device, const float *x_dev, int m, int D, int K, const int *idx_dev,
+                          const int *keff_dev, const int *dest_dev, const int *slot_dev, int E, int G,
+                          int slots, int payload_bf16, int *counts_dev, int *entry_of_dev, void *send_dev,
+                          int *inexact_dev);
+int coli_cuda_ep_expert_group_dev(ColiCudaTensor *const *gates, ColiCudaTensor *const *ups,
+                                  ColiCudaTensor *const *downs, int nslots, const int *recv_counts,
+                                  int nsrc, float *y_dev, const void *x_dev, int x_bf16);
+int coli_cuda_ep_combine_dev(int device, float *out_dev, const float *y_dev, const int *entry_of_dev,
+                             const float *w_dev, const int *keff_dev, const float *shared_dev, int m,
+                             int K, int D);
 
 /* Weighted combine of an expert-parallel layer on device buffers:
  *   out[s] = sum_{kk < keff[s]} w[s,kk] * y[entry_of[s*K+kk]]   (+ shared[s] when shared_dev != NULL)

@@ -91,7 +91,9 @@ def quant_int4_g32_torch(torch, w, fp16_scales=True):
     O, I = w.shape[-2], w.shape[-1]
     wr = w.reshape(*w.shape[:-1], I // 32, 32)
     amax = wr.abs().amax(dim=-1, keepdim=True)
-    s = torch.clamp(amax / 7.0, min=1e-8)
+    # tensor / tensor: CUDA's tensor / python-scalar multiplies by the reciprocal, one ulp off the
+    # converter's true division
+    s = torch.clamp(torch.div(amax, torch.full_like(amax, 7.0)), min=1e-8)
     if fp16_scales:
         s = s.to(torch.float16).to(torch.float32).clamp(min=6e-8)
     q = torch.clamp(torch.round(wr / s), -8, 7).to(torch.int32) + 8
@@ -105,7 +107,8 @@ def quant_mxfp4_torch(torch, w):
     O, I = w.shape[-2], w.shape[-1]
     wr = w.reshape(*w.shape[:-1], I // 32, 32)
     amax = wr.abs().amax(dim=-1, keepdim=True)
-    e = torch.where(amax > 0, torch.ceil(torch.log2(amax.double() / 6.0)), torch.full_like(amax, -127).double())
+    a64 = amax.double()
+    e = torch.where(amax > 0, torch.ceil(torch.log2(torch.div(a64, torch.full_like(a64, 6.0)))), torch.full_like(a64, -127))
     e = e.clamp(-127, 127)
     scale = torch.pow(torch.tensor(2.0, device=w.device, dtype=torch.float64), e).float()
     norm = (wr / scale).clamp(-6.0, 6.0)

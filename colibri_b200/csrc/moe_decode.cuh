@@ -414,6 +414,9 @@ template <int CH>
 __device__ __forceinline__ void dec_it_start(DecIt &it, int which, const DecPhase &ph1, const DecPhase &ph2,
                                              const DecShared *sh) {
     for (int w = which; w <= 2; w++) {
+        // a stream that starts in the gate/up phase never runs on into a LOCAL down phase: that
+        // phase uses another ring geometry and is started by the kernel itself
+        if (w == 2 && which == 1 && ph2.local) break;
         const DecPhase &ph = w == 1 ? ph1 : ph2;
         if (ph.first_u < ph.u1 && ph.wl < ph.nkb && (!ph.local || ph.gidx < ph.npass)) {
             it.ph = w; it.u = ph.first_u; it.kb = ph.wl; it.mat = 0; it.p = ph.gidx;

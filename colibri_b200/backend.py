@@ -91,6 +91,7 @@ REFERENCE_ABI = [
     ("coli_cuda_expert_group_resident_issue", C.c_int, [C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), _vp, C.c_int, C.c_int, _vp, _vp]),
     ("coli_cuda_expert_group_resident_take", C.c_int, [C.c_int, _i32p, C.c_int, _vp, _vp, C.c_int]),
 ]
+REFERENCE_OPTIONAL = {"coli_cuda_tensor_upload_compressed"}       # c/backend_cuda.h:60-67, only with -DCOLI_ANS
 ADDITIVE_ABI = [
     ("coli_cuda_moe_layer_create", C.c_int, [C.POINTER(_vp), C.POINTER(MoeDesc), C.c_int]),
     ("coli_cuda_moe_layer_free", None, [_vp]),
@@ -138,6 +139,8 @@ class Backend:
         self.lib = C.CDLL(self.path)
         self.additive = (path is None) if additive is None else additive
         for name, res, args in REFERENCE_ABI + (ADDITIVE_ABI if self.additive else []):
+            if name in REFERENCE_OPTIONAL and not hasattr(self.lib, name):
+                continue                   # declared under #ifdef in the reference header: a build may lack it
             fn = getattr(self.lib, name)   # raises AttributeError on a missing export
             fn.restype = res
             if args is not None:

@@ -89,3 +89,21 @@ def test_ep_layer_c5_shape_matches_oracle(be, oracle):
     assert be.kernel_status(0) == 0
     for t in hg + hu + hd + list(hs):
         be.tensor_free(t)
+
+
+def test_ep_layer_over_nccl_is_bit_identical_to_one_rank():
+    """Two (or four) ranks over NCCL: tests/ep_multi_check.py under torchrun. Skipped on a
+    one-GPU box."""
+    import os
+    import subprocess
+    import sys
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs two or more GPUs")
+    world = 4 if n >= 4 else 2
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    run = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+                          "--master-addr", "127.0.0.1", "--master-port", "29641", os.path.join(here, "ep_multi_check.py")],
+                         capture_output=True, text=True, timeout=600, env=env)
+    assert run.returncode == 0 and "EP_MULTI_OK" in run.stdout, run.stdout[-2000:] + run.stderr[-3000:]

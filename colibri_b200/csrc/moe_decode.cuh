@@ -82,12 +82,14 @@ struct DecodeArgs {
     const __half *xq; const float *xs;   // x already split by k_prep_rows (only read when act_smem == 0)
     __half *hq; float *hs;               // SwiGLU activations: [npos][I/128][256] halfs, [npos][I/32] inverse scales
     float *Y;                            // down-projection results per pass row: [npos][D]
-    unsigned int *sync;                  // [0] barrier arrivals, [1] barrier generation, [16 + tile] tickets
+    unsigned int *sync;                  // [0] barrier arrivals (256 per launch), [16 + tile] tickets
     const unsigned long long *exp_tab;   // global copy of the 2^(i/32) table
     int *status;
     int M, act_smem;
     int wpk1, wpk2;                      // warps per unit in the gate/up and the down phase (4, 8 or 16)
     int local2;                          // down phase: 1 = a CTA owns 16 output rows over every pass and combines them itself
+    // divisions by launch constants as multiply-shift (dec_magic): by the grid size, I/32 and D/32
+    unsigned long long mg_grid, mg_nt1, mg_nt2;
 #ifdef COLI_DECODE_PROBE
     unsigned long long *probe;           // optional [gridDim.x][DEC_NPROBE] phase timestamps (ns)
 #endif
@@ -103,6 +105,8 @@ struct DecShared {
     float rowtmp[2 * DEC_MAX_M];
     int rowflag[DEC_MAX_M];
     unsigned long long exp_tab[32];
+    RouteRule rule;                      // copy for the out-of-line general routing (cold path)
+    uint4 zeros[32];                     // what lanes without a token row read as activations and scales
 };
 
 #ifdef COLI_DECODE_PROBE
@@ -129,32 +133,48 @@ struct DecShared {
 #define DEC_PROBE_T(a, slot) do { } while (0)
 #endif
 
+// n / d for 0 <= n, n * d < 2^32, as a multiply and a shift: m = dec_magic(d) = ceil(2^32 / d).
+static inline unsigned long long dec_magic(unsigned int d) { return (0x100000000ULL + d - 1) / d; }
+__device__ __forceinline__ int dec_div(int n, unsigned long long m) {
+    return (int)(((unsigned long long)(unsigned int)n * m) >> 32);
+}
+
+// Asynchronous global -> shared copies of 4 and 16 bytes (the thread waits for its own with
+// cp.async.wait_all); both addresses aligned to the size.
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void *src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
 __device__ __forceinline__ void bar_sync_named(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
-// All threads of the CTA call this. One arrival counter and one generation word: the last
-// CTA to arrive clears the counter and advances the generation, the others poll the
-// generation they read before arriving. Returns false on timeout (about 20 ms).
-__device__ __forceinline__ bool grid_barrier(unsigned int *sync, int *s_failed) {
+// Grid barrier on one counter. Every launch adds exactly 256 to it (CTA 0 adds what the
+// others leave), so between launches it is a multiple of 256, also across the wrap of the
+// 32-bit word. The target is the next multiple above the value thread 0 read at any time
+// before arriving (grid_barrier_target: off the critical path); arriving is a reduction without
+// a return value, and everybody polls the counter itself for the target. All threads of the
+// CTA call grid_barrier; it returns false on timeout (about 20 ms). Needs gridDim.x <= 256.
+__device__ __forceinline__ unsigned int grid_barrier_target(const unsigned int *sync) {
+    unsigned int c0;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(c0) : "l"(sync) : "memory");
+    return (c0 & ~255u) + 256u;
+}
+__device__ __forceinline__ bool grid_barrier(unsigned int *sync, int *s_failed, unsigned int target) {
     __syncthreads();
     if (threadIdx.x == 0) {
-        unsigned int gen0, old;
-        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(gen0) : "l"(sync + 1) : "memory");
-        // acq_rel add: orders this CTA's earlier writes (made visible to thread 0 by the CTA
-        // barrier above) before the arrival, and the arrival before what follows
-        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(sync) : "memory");
-        if (old == gridDim.x - 1) {
-            asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(sync), "r"(0u) : "memory");
-            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(sync + 1), "r"(gen0 + 1u) : "memory");
-        } else {
-            long long t0 = clock64();
-            for (;;) {
-                unsigned int v;
-                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(sync + 1) : "memory");
-                if (v != gen0) break;
-                if (clock64() - t0 > 40000000LL) { *s_failed = 1; break; }   // a barrier takes microseconds
-            }
+        // release: orders this CTA's earlier writes (made visible to thread 0 by the CTA barrier
+        // above) before the arrival
+        const unsigned int add = blockIdx.x == 0 ? 256u - (gridDim.x - 1u) : 1u;
+        asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(sync), "r"(add) : "memory");
+        long long t0 = clock64();
+        for (;;) {
+            unsigned int v;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(sync) : "memory");
+            if (v == target) break;
+            if (clock64() - t0 > 40000000LL) { *s_failed = 1; break; }   // a barrier takes microseconds
         }
     }
     __syncthreads();
@@ -261,7 +281,7 @@ __device__ __forceinline__ void route_row_warp(const float *z, const float *bias
 // CTA-parallel routing of M rows (all threads of the CTA). score/choice: [M*E] floats
 // of scratch; outputs idx/wk [M*K], keff [M] in shared memory. Same arithmetic, element
 // for element, as route_row_warp.
-__device__ __forceinline__ void route_rows_cta(const float *logits, const float *bias, const RouteRule &rule,
+__device__ __noinline__ void route_rows_cta(const float *logits, const float *bias, const RouteRule &rule,
                                                int M, float *score, float *choice, float *rowtmp,
                                                int *rowflag, int *idx, float *wk, int *keff,
                                                const uint64_t *tab) {
@@ -384,14 +404,15 @@ __device__ __forceinline__ void route_rows_cta(const float *logits, const float 
 struct DecPhase {
     int which;        // 1: gate/up, 2: down
     int nt, nkb;      // 32-row tiles of the output, 128-column blocks of the contraction
-    int wpk, ng;
+    int wpk, ng, wsh;  // wsh = log2(wpk)
+    unsigned long long mg_nt;
     int u0, u1, first_u, wl, gidx;
     int local, npass; // local: units are 16-row halves of the output, every group walks passes gidx, gidx + ng, ...
 };
 
-// Position of a warp's copy stream: it runs through phase 1 and on into phase 2.
+// Position of a warp's copy stream inside one phase.
 struct DecIt {
-    int ph, u, kb, mat, p;           // ph 3: nothing left; p: pass (local down phase only)
+    int live, u, kb, mat, p;         // live 0: nothing left; p: pass (local down phase only)
     const uint8_t *base0, *base1;    // block 0 of the current tile: gate / up, or down / unused
                                      // (local down phase: codes / scales of the 16-row half)
 };
@@ -404,48 +425,35 @@ __device__ __forceinline__ void dec_it_unit(DecIt &it, const DecPhase &ph, const
         it.base1 = tile0 + CODE_BYTES + (it.u & 1) * ((CH - CODE_BYTES) / 2);
         return;
     }
-    const int pass = it.u / ph.nt, tile = it.u - pass * ph.nt;
+    const int pass = dec_div(it.u, ph.mg_nt), tile = it.u - pass * ph.nt;
     const DecPass &ps = sh->pass[pass];
     const size_t off = (size_t)tile * ph.nkb * CH;
     if (ph.which == 1) { it.base0 = ps.wg + off; it.base1 = ps.wu + off; }
     else { it.base0 = ps.wd + off; it.base1 = nullptr; }
 }
 template <int CH>
-__device__ __forceinline__ void dec_it_start(DecIt &it, int which, const DecPhase &ph1, const DecPhase &ph2,
-                                             const DecShared *sh) {
-    for (int w = which; w <= 2; w++) {
-        // a stream that starts in the gate/up phase never runs on into a LOCAL down phase: that
-        // phase uses another ring geometry and is started by the kernel itself
-        if (w == 2 && which == 1 && ph2.local) break;
-        const DecPhase &ph = w == 1 ? ph1 : ph2;
-        if (ph.first_u < ph.u1 && ph.wl < ph.nkb && (!ph.local || ph.gidx < ph.npass)) {
-            it.ph = w; it.u = ph.first_u; it.kb = ph.wl; it.mat = 0; it.p = ph.gidx;
-            dec_it_unit<CH>(it, ph, sh);
-            return;
-        }
-    }
-    it.ph = 3;
+__device__ __forceinline__ void dec_it_start(DecIt &it, const DecPhase &ph, const DecShared *sh) {
+    it.live = ph.first_u < ph.u1 && ph.wl < ph.nkb && (!ph.local || ph.gidx < ph.npass);
+    it.u = ph.first_u; it.kb = ph.wl; it.mat = 0; it.p = ph.gidx;
+    it.base0 = nullptr; it.base1 = nullptr;
+    if (it.live) dec_it_unit<CH>(it, ph, sh);
 }
 template <int CH>
-__device__ __forceinline__ void dec_it_next(DecIt &it, const DecPhase &ph1, const DecPhase &ph2,
-                                            const DecShared *sh) {
-    const DecPhase &ph = it.ph == 1 ? ph1 : ph2;
+__device__ __forceinline__ void dec_it_next(DecIt &it, const DecPhase &ph, const DecShared *sh) {
     it.kb += ph.wpk;
     if (it.kb < ph.nkb) return;
     it.kb = ph.wl;
     if (ph.local) {
         it.p += ph.ng;
         if (it.p >= ph.npass) { it.p = ph.gidx; it.u += 1; }
-        if (it.u < ph.u1) dec_it_unit<CH>(it, ph, sh); else it.ph = 3;
+    } else if (ph.which == 1 && it.mat == 0) {
+        it.mat = 1;
         return;
+    } else {
+        it.mat = 0;
+        it.u += ph.ng;
     }
-    if (ph.which == 1 && it.mat == 0) { it.mat = 1; return; }
-    it.mat = 0;
-    it.u += ph.ng;
-    if (it.u < ph.u1) { dec_it_unit<CH>(it, ph, sh); return; }
-    // the stream runs on into the down phase, except into a local one (its ring geometry differs:
-    // the kernel restarts the stream itself once this warp's gate/up blocks are consumed)
-    if (it.ph == 1 && !ph2.local) dec_it_start<CH>(it, 2, ph1, ph2, sh); else it.ph = 3;
+    if (it.u < ph.u1) dec_it_unit<CH>(it, ph, sh); else it.live = 0;
 }
 
 // Ring state of one warp across the phases of the kernel: `nst` slots of `sb` bytes, one
@@ -463,13 +471,13 @@ struct WarpRing {
 #define DEC_BARS_PER_WARP 6
 
 template <int CH, int NST>
-__device__ __forceinline__ void dec_issue_one(WarpRing &wr, DecIt &it, const DecPhase &ph1, const DecPhase &ph2,
-                                              const DecShared *sh, int lane) {
-    if (it.ph > 2) return;
+__device__ __forceinline__ void dec_issue_one(WarpRing &wr, DecIt &it, const DecPhase &ph, const DecShared *sh,
+                                              int lane) {
+    if (!it.live) return;
     if (wr.issued - wr.consumed >= wr.nst) return;
     if (lane == 0) {
         const uint32_t bar = wr.bars + wr.pi * 8, dst = wr.ring + wr.pi * wr.sb;
-        if (it.ph == 2 && ph2.local) {
+        if (ph.local) {
             // one 16-row half: 1024 bytes of codes, then its half of the scales
             constexpr int SCH = (CH - CODE_BYTES) / 2;
             mbar_expect_tx(bar, 1024 + SCH);
@@ -482,7 +490,7 @@ __device__ __forceinline__ void dec_issue_one(WarpRing &wr, DecIt &it, const Dec
     }
     wr.issued++;
     if (++wr.pi == wr.nst) wr.pi = 0;
-    dec_it_next<CH>(it, ph1, ph2, sh);
+    dec_it_next<CH>(it, ph, sh);
 }
 
 // Waits for the oldest outstanding chunk of the ring; returns its shared-memory address.
@@ -500,9 +508,9 @@ __device__ __forceinline__ void dec_release_chunk(WarpRing &wr) {
 }
 
 // This CTA's contiguous share [t0, t1) of n units: sizes differ by at most one.
-__device__ __forceinline__ void dec_cta_range(int n, int &t0, int &t1) {
+__device__ __forceinline__ void dec_cta_range(int n, unsigned long long mg_grid, int &t0, int &t1) {
     const int G = gridDim.x, b = blockIdx.x;
-    const int q = n / G, r = n - q * G;
+    const int q = dec_div(n, mg_grid), r = n - q * G;
     t0 = b * q + (b < r ? b : r);
     t1 = t0 + q + (b < r ? 1 : 0);
 }
@@ -564,48 +572,55 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
     DEC_PROBE(a, 0);
-    // Loads whose addresses do not depend on the routing are issued first and consumed after
-    // it, so their latency hides behind the routing: the exponential table, this thread's
-    // expert's tensor pointers (E <= 256 <= threads) and, when the activations live in shared
-    // memory, this warp's blocks of x (at most 8 per warp: M*D*4 B fit the 64 KB region).
+    // Inputs whose addresses do not depend on the routing are requested first and consumed after
+    // the set-up, so their latency hides behind it: the exponential table, this thread's
+    // expert's tensor pointers (E <= 256 <= threads) and, by asynchronous copies straight into
+    // shared memory, the logits (each by the thread, or the row's warp, that will read it) and,
+    // when the activations live in shared memory, this warp's blocks of x. The loops stay
+    // rolled: this code runs once per launch, and what it costs is the fetch of its instructions.
     const unsigned long long tab_v = a.exp_tab[lane];
-    float zpre[8];            // softmax: this lane's logits of row `warp`; sigmoid: this thread's elements
-    float bpre_r[4];
-#pragma unroll
-    for (int j = 0; j < 8; j++) zpre[j] = 0.f;
+    unsigned int bar_target = 0;
+    if (tid == 0) bar_target = grid_barrier_target(a.sync);
+    __half *xq_s = reinterpret_cast<__half *>(act);
+    float *xs_s = reinterpret_cast<float *>(act + (size_t)M * nkb1 * 512);
     if (r.gating == 0) {
         if (warp < M) {
-#pragma unroll
-            for (int j = 0; j < 8; j++) { const int e = j * 32 + lane; if (e < E) zpre[j] = a.logits[(size_t)warp * E + e]; }
+#pragma unroll 1
+            for (int e = lane; e < E; e += 32)
+                cp_async4(smem_u32(choice + (size_t)warp * E + e), a.logits + (size_t)warp * E + e);
         }
     } else {
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const int i = tid + j * DEC_WARPS * 32;
-            bpre_r[j] = 0.f;
-            if (i < M * E) { zpre[j] = a.logits[i]; if (a.router_bias) bpre_r[j] = a.router_bias[i % E]; }
+#pragma unroll 1
+        for (int i = tid; i < M * E; i += DEC_WARPS * 32) {
+            cp_async4(smem_u32(choice + i), a.logits + i);
+            if (a.router_bias) cp_async4(smem_u32(score + i), a.router_bias + i % E);
         }
+    }
+    if (a.act_smem) {
+        // block `wid` of x (row wid / nkb1, columns 128 * (wid % nkb1) ...) lands, as floats, in
+        // the 512 bytes its fp16 hi/lo fragments will occupy
+#pragma unroll 1
+        for (int wid = warp; wid < M * nkb1; wid += DEC_WARPS)
+            cp_async16(smem_u32(act + (size_t)wid * 512 + lane * 16), a.x + (size_t)wid * BLOCK_K + lane * 4);
     }
     const uint8_t *pre_g = nullptr, *pre_u = nullptr, *pre_d = nullptr;
     if (tid < E) { pre_g = a.tab.gate_pk[tid]; pre_u = a.tab.up_pk[tid]; pre_d = a.tab.down_pk[tid]; }
-    float4 xpre[8];
-    if (a.act_smem) {
-#pragma unroll
-        for (int u = 0; u < 8; u++) {
-            const int wid = warp + u * DEC_WARPS;
-            if (wid < M * nkb1) {
-                const int row = wid / nkb1, kb = wid - row * nkb1;
-                xpre[u] = *reinterpret_cast<const float4 *>(a.x + (size_t)row * D + kb * BLOCK_K + lane * 4);
-            }
-        }
-    }
     if (lane == 0) {
+#pragma unroll 1
         for (int s = 0; s < DEC_BARS_PER_WARP; s++) mbar_init(wr.bars + s * 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (tid == 0) { sh->failed = 0; sh->nu = 0; }
+    if (tid < 32) sh->zeros[tid] = make_uint4(0, 0, 0, 0);
+    if (tid == 0) {
+        sh->failed = 0; sh->nu = 0;
+        // one more barrier, behind the warps' own: the SwiGLU activations arriving for the down phase
+        mbar_init(smem_u32(smem) + DEC_WARPS * NST * CH + DEC_WARPS * DEC_BARS_PER_WARP * 8, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+#pragma unroll 1
     for (int e = tid; e < E; e += blockDim.x) { t_first[e] = 0x7fffffff; t_cnt[e] = 0; }
     wtab[lane] = tab_v;          // this warp's own copy of the table (no CTA-wide wait before the routing)
+    asm volatile("cp.async.wait_all;" ::: "memory");
     __syncwarp();
     if (tid == 0) DEC_PROBE_T(a, 12);        // first loads have returned
 
@@ -617,24 +632,27 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
         if (warp < M) {
             float *sc = score + (size_t)warp * E, *chc = choice + (size_t)warp * E;
             float m = -1e30f;
-#pragma unroll
-            for (int j = 0; j < 8; j++) if (j * 32 + lane < E && zpre[j] > m) m = zpre[j];
+#pragma unroll 1
+            for (int e = lane; e < E; e += 32) { const float v = chc[e]; if (v > m) m = v; }
 #pragma unroll
             for (int off = 16; off; off >>= 1) { float o = __shfl_xor_sync(0xffffffffu, m, off); if (o > m) m = o; }
-#pragma unroll
-            for (int j = 0; j < 8; j++)
-                if (j * 32 + lane < E)
-                    sc[j * 32 + lane] = coli_expf_exact(__fsub_rn(zpre[j], m), reinterpret_cast<const uint64_t *>(wtab));
+#pragma unroll 4
+            for (int e = lane; e < E; e += 32)      // double-precision chains: keep several in flight
+                sc[e] = coli_expf_exact(__fsub_rn(chc[e], m), reinterpret_cast<const uint64_t *>(wtab));
             __syncwarp();
             float tot = 0.f;     // the engine's serial ascending sum, by every lane (broadcast reads)
             int e = 0;
-            if ((E & 3) == 0)
+            if ((E & 3) == 0) {
+#pragma unroll 4
                 for (; e < E; e += 4) {
                     const float4 v = *reinterpret_cast<const float4 *>(sc + e);
                     tot = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(tot, v.x), v.y), v.z), v.w);
                 }
+            }
+#pragma unroll 1
             for (; e < E; e++) tot = __fadd_rn(tot, sc[e]);
             __syncwarp();
+#pragma unroll 4
             for (int e2 = lane; e2 < E; e2 += 32) {
                 const float p = __fdiv_rn(sc[e2], tot);
                 sc[e2] = p; chc[e2] = p;
@@ -643,31 +661,25 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
             if (tid == 0) DEC_PROBE_T(a, 13);    // scores of row 0 written
         }
     } else {
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const int i = tid + j * DEC_WARPS * 32;
-            if (i < M * E) {
-                const float sg = __fdiv_rn(1.f, __fadd_rn(1.f, coli_expf_exact(-zpre[j], reinterpret_cast<const uint64_t *>(wtab))));
-                const float c = a.router_bias ? __fadd_rn(sg, bpre_r[j]) : sg;
-                score[i] = sg; choice[i] = c;
-                bad |= !(c > -1e30f);
-            }
+#pragma unroll 1
+        for (int i = tid; i < M * E; i += DEC_WARPS * 32) {
+            const float sg = __fdiv_rn(1.f, __fadd_rn(1.f, coli_expf_exact(-choice[i], reinterpret_cast<const uint64_t *>(wtab))));
+            const float c = a.router_bias ? __fadd_rn(sg, score[i]) : sg;
+            score[i] = sg; choice[i] = c;
+            bad |= !(c > -1e30f);
         }
     }
-    // x -> fp16 hi/lo fragments in this CTA's activation region (independent of the routing)
-    __half *xq_s = reinterpret_cast<__half *>(act);
-    float *xs_s = reinterpret_cast<float *>(act + (size_t)M * nkb1 * 512);
+    // x -> fp16 hi/lo fragments, in place (independent of the routing)
     if (a.act_smem) {
-#pragma unroll
-        for (int u = 0; u < 8; u++) {
-            const int wid = warp + u * DEC_WARPS;
-            if (wid < M * nkb1) {
-                const int row = wid / nkb1, kb = wid - row * nkb1;
-                const float m = warp_max(fmaxf(fmaxf(fabsf(xpre[u].x), fabsf(xpre[u].y)), fmaxf(fabsf(xpre[u].z), fabsf(xpre[u].w))));
-                const float sc = block_scale_from_max(m);
-                store_split4(xq_s + ((size_t)row * nkb1 + kb) * 256, lane, xpre[u], sc);
-                if (lane == 0) xs_s[(size_t)row * nkb1 + kb] = 1.f / sc;
-            }
+#pragma unroll 1
+        for (int wid = warp; wid < M * nkb1; wid += DEC_WARPS) {
+            const float4 v = *reinterpret_cast<const float4 *>(act + (size_t)wid * 512 + lane * 16);
+            // the reduction below is also the point where every lane has read its floats, before
+            // any lane overwrites the block with fragments
+            const float m = warp_max(fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+            const float sc = block_scale_from_max(m);
+            store_split4(xq_s + (size_t)wid * 256, lane, v, sc);
+            if (lane == 0) xs_s[wid] = 1.f / sc;
         }
     }
     if (tid < E) { ptab[tid] = pre_g; ptab[E + tid] = pre_u; ptab[2 * E + tid] = pre_d; }
@@ -677,57 +689,82 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
         // a NaN or a value <= -1e30 among the candidates: the general form, which also
         // reproduces the engine's "nothing found -> expert kk" degradation row by row
         if (warp == 0) sh->exp_tab[lane] = tab_v;
+        if (tid == 0) sh->rule = r;
         __syncthreads();
-        route_rows_cta(a.logits, a.router_bias, r, M, score, choice, sh->rowtmp, sh->rowflag, sh->idx, sh->w,
+        route_rows_cta(a.logits, a.router_bias, sh->rule, M, score, choice, sh->rowtmp, sh->rowflag, sh->idx, sh->w,
                        sh->keff, reinterpret_cast<const uint64_t *>(sh->exp_tab));
     } else {
-        // Selection by ranking (see route_row_warp): slot kk holds the element of rank kk.
-        for (int i = tid; i < M * E; i += blockDim.x) {
-            const int s = i / E, e = i - s * E;
-            const float c = choice[i];
-            const float *row = choice + (size_t)s * E;
-            int rank = 0, o = 0;
-            if ((E & 3) == 0) {
-#pragma unroll 4
-                for (; o < E; o += 4) {
-                    const float4 v = *reinterpret_cast<const float4 *>(row + o);
-                    rank += (v.x > c) || (v.x == c && o < e);
-                    rank += (v.y > c) || (v.y == c && o + 1 < e);
-                    rank += (v.z > c) || (v.z == c && o + 2 < e);
-                    rank += (v.w > c) || (v.w == c && o + 3 < e);
+        // Selection by ranking (see route_row_warp): slot kk holds the element of rank kk. Four
+        // neighbouring lanes share an element: each counts over a quarter of the candidates.
+        {
+            const int q = tid & 3;
+#pragma unroll 1
+            for (int i0 = 0; i0 < M * E; i0 += (DEC_WARPS * 32) / 4) {
+                const int i = i0 + (tid >> 2);
+                const bool live = i < M * E;
+                const int s = (live && M > 1) ? i / E : 0, e = live ? i - s * E : 0;
+                const float c = live ? choice[i] : 0.f;
+                const float *row = choice + (size_t)s * E;
+                int rank = 0;
+                if (live) {
+                    if ((E & 3) == 0) {      // rows start 16-byte aligned then
+#pragma unroll 2
+                        for (int o = q * 4; o < E; o += 16) {
+                            const float4 v = *reinterpret_cast<const float4 *>(row + o);
+                            rank += (v.x > c) || (v.x == c && o < e);
+                            rank += (v.y > c) || (v.y == c && o + 1 < e);
+                            rank += (v.z > c) || (v.z == c && o + 2 < e);
+                            rank += (v.w > c) || (v.w == c && o + 3 < e);
+                        }
+                    } else {
+#pragma unroll 1
+                        for (int o = q; o < E; o += 4) { const float v = row[o]; rank += (v > c) || (v == c && o < e); }
+                    }
                 }
+                rank += __shfl_xor_sync(0xffffffffu, rank, 1);
+                rank += __shfl_xor_sync(0xffffffffu, rank, 2);
+                if (live && q == 0 && rank < K) { sh->idx[s * K + rank] = e; sh->w[s * K + rank] = score[i]; }
             }
-            for (; o < E; o++) { const float v = row[o]; rank += (v > c) || (v == c && o < e); }
-            if (rank < K) { sh->idx[s * K + rank] = e; sh->w[s * K + rank] = score[i]; }
         }
         __syncthreads();
-        if (tid < M) {      // the engine's tail on the K selected weights, one thread per row
-            sh->rowflag[tid] = 0;
-            int *ix = sh->idx + tid * K;
-            float *w = sh->w + tid * K;
+        if (warp < M) {     // the engine's tail on the K selected weights: one warp per row
+            int *ix = sh->idx + warp * K;
+            float *w = sh->w + warp * K;
             int Ke = K;
             if (r.gating == 1 && r.topp > 0.f && r.topp < 1.f) {
-                for (int p = 1; p < K; p++) {
-                    int ii = ix[p]; float ww = w[p]; int b = p - 1;
-                    while (b >= 0 && w[b] < ww) { w[b + 1] = w[b]; ix[b + 1] = ix[b]; b--; }
-                    w[b + 1] = ww; ix[b + 1] = ii;
+                if (lane == 0) {
+#pragma unroll 1
+                    for (int p = 1; p < K; p++) {
+                        int ii = ix[p]; float ww = w[p]; int b = p - 1;
+                        while (b >= 0 && w[b] < ww) { w[b + 1] = w[b]; ix[b + 1] = ix[b]; b--; }
+                        w[b + 1] = ww; ix[b + 1] = ii;
+                    }
+                    float tot = 1e-20f;
+#pragma unroll 1
+                    for (int kk = 0; kk < K; kk++) tot = __fadd_rn(tot, w[kk]);
+                    float cum = 0.f;
+#pragma unroll 1
+                    for (int kk = 0; kk < K; kk++) {
+                        cum = __fadd_rn(cum, w[kk]);
+                        if (cum >= __fmul_rn(r.topp, tot)) { Ke = kk + 1; break; }
+                    }
                 }
-                float tot = 1e-20f;
-                for (int kk = 0; kk < K; kk++) tot = __fadd_rn(tot, w[kk]);
-                float cum = 0.f;
-                for (int kk = 0; kk < K; kk++) {
-                    cum = __fadd_rn(cum, w[kk]);
-                    if (cum >= __fmul_rn(r.topp, tot)) { Ke = kk + 1; break; }
-                }
+                Ke = __shfl_sync(0xffffffffu, Ke, 0);
+                __syncwarp();
             }
+            // every lane forms the same serial sum; lane kk then scales weight kk (K <= 16 lanes)
+            float mine = lane < Ke ? w[lane] : 0.f;
             if (r.norm_topk) {
                 float sm = 0.f;
+#pragma unroll 1
                 for (int kk = 0; kk < Ke; kk++) sm = __fadd_rn(sm, w[kk]);
                 if (r.gating == 1) sm = __fadd_rn(sm, 1e-20f);
-                for (int kk = 0; kk < Ke; kk++) w[kk] = __fdiv_rn(w[kk], sm);
+                mine = __fdiv_rn(mine, sm);
             }
-            if (r.gating == 1) for (int kk = 0; kk < Ke; kk++) w[kk] = __fmul_rn(w[kk], r.routed_scale);
-            sh->keff[tid] = Ke;
+            if (r.gating == 1) mine = __fmul_rn(mine, r.routed_scale);
+            __syncwarp();       // every lane has read the weights it needs
+            if (lane < Ke) w[lane] = mine;
+            if (lane == 0) { sh->keff[warp] = Ke; sh->rowflag[warp] = 0; }
         }
         __syncthreads();
     }
@@ -754,6 +791,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
         }
         __syncthreads();
     } else {
+#pragma unroll 1
         for (int i = tid; i < M * K; i += blockDim.x) {
             int s = i / K, kk = i - s * K;
             if (kk < sh->keff[s]) { int e = sh->idx[i]; atomicMin(&t_first[e], i); atomicAdd(&t_cnt[e], 1); }
@@ -761,14 +799,17 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
         __syncthreads();
         // union in first-appearance order: entry i opens a new expert iff it is that
         // expert's first entry; its rank is the number of such entries before it
+#pragma unroll 1
         for (int i = tid; i < M * K; i += blockDim.x) {
             int s = i / K, kk = i - s * K;
             sh->pos_of[i] = (kk < sh->keff[s] && t_first[sh->idx[i]] == i) ? 1 : 0;
         }
         __syncthreads();
+#pragma unroll 1
         for (int i = tid; i < M * K; i += blockDim.x) {
             if (sh->pos_of[i]) {
                 int rank = 0;
+#pragma unroll 1
                 for (int q = 0; q < i; q++) rank += sh->pos_of[q];
                 t_uniq[rank] = sh->idx[i];
                 atomicAdd(&sh->nu, 1);
@@ -776,8 +817,10 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
         }
         __syncthreads();
         const int nu = sh->nu;
+#pragma unroll 1
         for (int j = tid; j < nu; j += blockDim.x) {
             int pos = 0, np = 0;
+#pragma unroll 1
             for (int q = 0; q < j; q++) { int c = t_cnt[t_uniq[q]]; pos += c; np += (c + 3) >> 2; }
             int e = t_uniq[j];
             t_base[e] = pos; t_passbase[e] = np;
@@ -786,9 +829,11 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
                 int spos = pos + c, npass = np + ((c + 3) >> 2);
                 sh->shared_pos0 = spos;
                 if (a.tab.sh_gate_pk) {
+#pragma unroll 1
                     for (int p = 0; p < (M + 3) / 4; p++) {
                         DecPass &ps = sh->pass[npass + p];
                         ps.e = -1; ps.pos0 = spos + 4 * p; ps.nrows = min(4, M - 4 * p);
+#pragma unroll 1
                         for (int q = 0; q < ps.nrows; q++) ps.rowid[q] = 4 * p + q;
                     }
                     npass += (M + 3) / 4; spos += M;
@@ -797,12 +842,16 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
             }
         }
         __syncthreads();
+#pragma unroll 1
         for (int i = tid; i < M * K; i += blockDim.x) {
             int s = i / K, kk = i - s * K;
             if (kk < sh->keff[s]) {
                 int e = sh->idx[i], rr = 0;
+#pragma unroll 1
                 for (int s2 = 0; s2 < s; s2++)
+#pragma unroll 1
                     for (int k2 = 0; k2 < sh->keff[s2]; k2++) rr += (sh->idx[s2 * K + k2] == e);
+#pragma unroll 1
                 for (int k2 = 0; k2 < kk; k2++) rr += (sh->idx[s * K + k2] == e);
                 int pos = t_base[e] + rr;
                 sh->pos_of[i] = pos;
@@ -813,6 +862,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
         }
         __syncthreads();
     }
+#pragma unroll 1
     for (int p = tid; p < sh->npass; p += blockDim.x) {
         DecPass &ps = sh->pass[p];
         if (ps.e >= 0) { ps.wg = ptab[ps.e]; ps.wu = ptab[E + ps.e]; ps.wd = ptab[2 * E + ps.e]; }
@@ -820,6 +870,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
     }
     __syncthreads();
     if (blockIdx.x == 0) {
+#pragma unroll 1
         for (int i = tid; i < M * K; i += blockDim.x) {
             if (a.idx_out) a.idx_out[i] = sh->idx[i];
             if (a.w_out) a.w_out[i] = sh->w[i];
@@ -830,20 +881,23 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
     const int npass = sh->npass;
 
     DecPhase ph1, ph2;
-    ph1.which = 1; ph1.nt = nt1; ph1.nkb = nkb1; ph1.wpk = a.wpk1; ph1.ng = DEC_WARPS / a.wpk1;
-    dec_cta_range(npass * nt1, ph1.u0, ph1.u1);
-    ph1.gidx = warp / a.wpk1; ph1.wl = warp - ph1.gidx * a.wpk1; ph1.first_u = ph1.u0 + ph1.gidx;
+    ph1.which = 1; ph1.nt = nt1; ph1.nkb = nkb1; ph1.wpk = a.wpk1; ph1.wsh = 31 - __clz(a.wpk1);
+    ph1.ng = DEC_WARPS >> ph1.wsh; ph1.mg_nt = a.mg_nt1;
+    dec_cta_range(npass * nt1, a.mg_grid, ph1.u0, ph1.u1);
+    ph1.gidx = warp >> ph1.wsh; ph1.wl = warp & (a.wpk1 - 1); ph1.first_u = ph1.u0 + ph1.gidx;
     ph1.local = 0; ph1.npass = npass;
-    ph2.which = 2; ph2.nt = nt2; ph2.nkb = nkb2; ph2.wpk = a.wpk2; ph2.ng = DEC_WARPS / a.wpk2;
+    ph2.which = 2; ph2.nt = nt2; ph2.nkb = nkb2; ph2.wpk = a.wpk2; ph2.wsh = 31 - __clz(a.wpk2);
+    ph2.ng = DEC_WARPS >> ph2.wsh; ph2.mg_nt = a.mg_nt2;
     ph2.local = a.local2; ph2.npass = npass;
-    ph2.gidx = warp / a.wpk2; ph2.wl = warp - ph2.gidx * a.wpk2;
-    if (a.local2) { dec_cta_range(2 * nt2, ph2.u0, ph2.u1); ph2.first_u = ph2.u0; }
-    else { dec_cta_range(npass * nt2, ph2.u0, ph2.u1); ph2.first_u = ph2.u0 + ph2.gidx; }
+    ph2.gidx = warp >> ph2.wsh; ph2.wl = warp & (a.wpk2 - 1);
+    if (a.local2) { dec_cta_range(2 * nt2, a.mg_grid, ph2.u0, ph2.u1); ph2.first_u = ph2.u0; }
+    else { dec_cta_range(npass * nt2, a.mg_grid, ph2.u0, ph2.u1); ph2.first_u = ph2.u0 + ph2.gidx; }
 
     // ---- start this warp's weight stream ------------------------------------------------
     DecIt it;
-    dec_it_start<CH>(it, 1, ph1, ph2, sh);
-    for (int s = 0; s < NST; s++) dec_issue_one<CH, NST>(wr, it, ph1, ph2, sh, lane);
+    dec_it_start<CH>(it, ph1, sh);
+#pragma unroll 1
+    for (int s = 0; s < NST; s++) dec_issue_one<CH, NST>(wr, it, ph1, sh, lane);
     DEC_PROBE(a, 2);
     const float mx_fix = (MODE == SC_MX) ? 16384.f : 1.f;   // fp16 fields carry e2m1 * 2^-14
 
@@ -854,13 +908,16 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
         const int nrot = ph1.wpk >> 2;
         int ucount = 0;
         for (int u = ph1.first_u; u < ph1.u1; u += ph1.ng, ucount++) {
-            const int pass = u / nt1, tile = u - pass * nt1;
+            const int pass = dec_div(u, a.mg_nt1), tile = u - pass * nt1;
             const DecPass &ps = sh->pass[pass];
             const int nrows = ps.nrows;
             const int rb = g >> 1;
             const bool bvalid = rb < nrows, svalid = t < nrows;
-            const __half *bptr = xq + (size_t)(bvalid ? ps.rowid[rb] : 0) * nkb1 * 256 + (g & 1) * 32 + t * 8;
-            const float *sptr = xs + (size_t)(svalid ? ps.rowid[t] : 0) * nkb1;
+            // lanes without a token row read zeros (stride 0), so the loop needs no selects
+            const __half *bptr = (bvalid ? xq + (size_t)ps.rowid[rb] * nkb1 * 256
+                                         : reinterpret_cast<const __half *>(sh->zeros)) + (g & 1) * 32 + t * 8;
+            const float *sptr = svalid ? xs + (size_t)ps.rowid[t] * nkb1 : reinterpret_cast<const float *>(sh->zeros);
+            const int bstr = bvalid ? 256 : 0, sstr = svalid ? 1 : 0;
             // this lane's slot of the partial sums: rows g, g+8, 16+g, 24+g of the tile for token
             // row t, gate in the first float4, up in the second
             float4 *pb = reinterpret_cast<float4 *>(part + (ucount & 1) * DEC_PART_BYTES) + (warp * 32 + lane) * 2;
@@ -871,14 +928,14 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
                 for (int s = 0; s < 2; s++)
 #pragma unroll
                     for (int i = 0; i < 4; i++) R[s][i] = 0.f;
+#pragma unroll 1
                 for (int kb = ph1.wl; kb < nkb1; kb += ph1.wpk) {
-                    const float ixs = svalid ? sptr[kb] : 0.f;
+                    const float ixs = sptr[kb * sstr];
                     // the B fragments do not depend on the chunk: fetch them before waiting for it
                     uint4 bpre[4];
 #pragma unroll
                     for (int grp = 0; grp < 4; grp++)
-                        bpre[grp] = bvalid ? *reinterpret_cast<const uint4 *>(bptr + (size_t)kb * 256 + grp * 64)
-                                           : make_uint4(0, 0, 0, 0);
+                        bpre[grp] = *reinterpret_cast<const uint4 *>(bptr + kb * bstr + grp * 64);
                     const uint32_t st = dec_wait_chunk<CH, NST>(wr);
                     float bacc[1][2][4];
                     block_mma<MODE, 1>(st, lane, g, [&](int grp, int) { return bpre[grp]; }, bacc);
@@ -889,7 +946,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
                     dec_release_chunk(wr);
                     __syncwarp();
                     if (tid == 0 && wr.consumed == 1) DEC_PROBE_T(a, 3);      // first block of the stream consumed
-                    dec_issue_one<CH, NST>(wr, it, ph1, ph2, sh, lane);
+                    dec_issue_one<CH, NST>(wr, it, ph1, sh, lane);
                 }
                 pb[mat] = make_float4((R[0][0] + R[0][1]) * mx_fix, (R[0][2] + R[0][3]) * mx_fix,
                                       (R[1][0] + R[1][1]) * mx_fix, (R[1][2] + R[1][3]) * mx_fix);
@@ -897,7 +954,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
             bar_sync_named(1 + ph1.gidx, ph1.wpk * 32);
             // Four warps of the group (a different four every unit) add the per-warp sums in
             // warp order, apply the SwiGLU and write the 32 activations of one token row each.
-            const int lw = (ph1.wl + 4 * (nrot - ucount % nrot)) % ph1.wpk;
+            const int lw = (ph1.wl + 4 * (nrot - (ucount & (nrot - 1)))) & (ph1.wpk - 1);
             if (lw < 4) {
                 const int mrow = lw;
                 int src, el;
@@ -927,56 +984,61 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
             }
         }
     }
-    if (a.local2) {
-        // every gate/up block of this warp has landed and been read: the ring becomes six slots of
-        // half a chunk, and the down stream starts now, ahead of the barrier
-        wr.nst = 2 * NST; wr.sb = CH / 2; wr.pi = 0; wr.ci = 0; wr.issued = 0; wr.consumed = 0;
-        dec_it_start<CH>(it, 2, ph1, ph2, sh);
-        for (int s = 0; s < 2 * NST; s++) dec_issue_one<CH, NST>(wr, it, ph1, ph2, sh, lane);
-    }
+    // Every gate/up block of this warp has landed and been read, so nothing is in flight: the
+    // down stream starts now, ahead of the barrier (its weights do not depend on the other
+    // CTAs). For the local combine the ring becomes six slots of half a chunk.
+    if (a.local2) { wr.nst = 2 * NST; wr.sb = CH / 2; }
+    wr.pi = 0; wr.ci = 0; wr.issued = 0; wr.consumed = 0;
+    dec_it_start<CH>(it, ph2, sh);
+#pragma unroll 1
+    for (int s = 0; s < wr.nst; s++) dec_issue_one<CH, NST>(wr, it, ph2, sh, lane);
     DEC_PROBE(a, 4);   // gate/up consumed (the ring already holds the first down blocks)
-    bool ok = grid_barrier(a.sync, &sh->failed);
+    bool ok = grid_barrier(a.sync, &sh->failed, bar_target);
     DEC_PROBE(a, 5);
     // ---- the SwiGLU activations of this CTA's one or two passes -> shared memory ---------
-    const int pA = ph2.u1 > ph2.u0 ? ph2.u0 / nt2 : 0;
-    const int pB = ph2.u1 > ph2.u0 ? (ph2.u1 - 1) / nt2 : -1;
+    const int pA = ph2.u1 > ph2.u0 ? dec_div(ph2.u0, a.mg_nt2) : 0;
+    const int pB = ph2.u1 > ph2.u0 ? dec_div(ph2.u1 - 1, a.mg_nt2) : -1;
     const int npos = sh->npos;
     // local combine: one slot per pass row (slot = packed row), then the scales, then Y[pos][16]
     float *hs_s = reinterpret_cast<float *>(act + (a.local2 ? (size_t)npos : (size_t)8) * I * 4);
     float *ybuf = hs_s + (size_t)npos * nkb2 * 4;
-    if (a.local2) {
-        if (ph2.u1 > ph2.u0) {
-            const int row16 = I / 4, per = row16 + nkb2;
-            for (int i = tid; i < npos * per; i += blockDim.x) {
-                const int pos = i / per, j = i - pos * per;
-                if (j < row16)
-                    reinterpret_cast<uint4 *>(act + (size_t)pos * I * 4)[j] =
-                        __ldcg(reinterpret_cast<const uint4 *>(a.hq + (size_t)pos * I * 2) + j);
-                else
-                    reinterpret_cast<float4 *>(hs_s + (size_t)pos * nkb2 * 4)[j - row16] =
-                        __ldcg(reinterpret_cast<const float4 *>(a.hs + (size_t)pos * nkb2 * 4) + (j - row16));
-            }
+    // One bulk copy per packed row and one for its scales, issued side by side by the lanes of
+    // warp 0 and counted on one mbarrier. Local combine: slot = packed row, every row is wanted;
+    // otherwise slot = 4 * (pass - pA) + row of the pass.
+    const int nslot = a.local2 ? (ph2.u1 > ph2.u0 ? npos : 0) : (pB - pA + 1) * 4;
+    const uint32_t hbar = smem_u32(smem) + DEC_WARPS * NST * CH + DEC_WARPS * DEC_BARS_PER_WARP * 8;
+    if (warp == 0 && nslot > 0) {
+        const uint32_t row_bytes = (uint32_t)I * 4u, sc_bytes = (uint32_t)nkb2 * 16u;
+        uint32_t mine = 0;
+#pragma unroll 1
+        for (int slot = lane; slot < nslot; slot += 32) {
+            const bool want = a.local2 || (slot & 3) < sh->pass[pA + (slot >> 2)].nrows;
+            if (want) mine += row_bytes + sc_bytes;
         }
-    } else {
-        const int row16 = I / 4;                    // 16-byte pieces of one row of fragments
-        const int sc16 = nkb2;                      // 16-byte pieces of one row of scales
-        const int per = row16 + sc16;
-        const int nslot = (pB - pA + 1) * 4;
-        for (int i = tid; i < nslot * per; i += blockDim.x) {
-            const int slot = i / per, j = i - slot * per;
-            const DecPass &ps = sh->pass[pA + (slot >> 2)];
-            const int mrow = slot & 3;
-            if (mrow >= ps.nrows) continue;
-            const int pos = ps.pos0 + mrow;
-            if (j < row16)
-                reinterpret_cast<uint4 *>(act + (size_t)slot * I * 4)[j] =
-                    __ldcg(reinterpret_cast<const uint4 *>(a.hq + (size_t)pos * I * 2) + j);
-            else
-                reinterpret_cast<float4 *>(hs_s + (size_t)slot * nkb2 * 4)[j - row16] =
-                    __ldcg(reinterpret_cast<const float4 *>(a.hs + (size_t)pos * nkb2 * 4) + (j - row16));
+#pragma unroll
+        for (int off = 16; off; off >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, off);
+        if (lane == 0) {
+            // the rows were written by other CTAs with ordinary stores: order them, as acquired at
+            // the barrier, before the copies of the asynchronous proxy
+            asm volatile("fence.proxy.async;" ::: "memory");
+            mbar_expect_tx(hbar, mine);
+        }
+        __syncwarp();
+#pragma unroll 1
+        for (int slot = lane; slot < nslot; slot += 32) {
+            int pos = slot;
+            if (!a.local2) {
+                const DecPass &ps = sh->pass[pA + (slot >> 2)];
+                if ((slot & 3) >= ps.nrows) continue;
+                pos = ps.pos0 + (slot & 3);
+            }
+            asm volatile("fence.proxy.async;" ::: "memory");
+            bulk_g2s(smem_u32(act + (size_t)slot * row_bytes), a.hq + (size_t)pos * I * 2, row_bytes, hbar);
+            bulk_g2s(smem_u32(hs_s + (size_t)slot * nkb2 * 4), a.hs + (size_t)pos * nkb2 * 4, sc_bytes, hbar);
         }
     }
-    __syncthreads();
+    // every thread observes the completion itself, which also makes the copied bytes visible to it
+    if (nslot > 0 && !mbar_wait_bounded(hbar, 0)) wr.ok = false;
     DEC_PROBE(a, 6);
     if (a.local2) {
         // ---- down with a local combine: this CTA's 16 output rows over every pass ------------
@@ -989,17 +1051,19 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
                 const int nrows = ps.nrows;
                 const int rb = g >> 1;
                 const bool bvalid = rb < nrows, svalid = t < nrows;
-                const __half *bptr = reinterpret_cast<const __half *>(act + (size_t)(ps.pos0 + (bvalid ? rb : 0)) * I * 4) + (g & 1) * 32 + t * 8;
-                const float *sptr = hs_s + (size_t)(ps.pos0 + (svalid ? t : 0)) * nkb2 * 4;
+                const __half *bptr = (bvalid ? reinterpret_cast<const __half *>(act + (size_t)(ps.pos0 + rb) * I * 4)
+                                             : reinterpret_cast<const __half *>(sh->zeros)) + (g & 1) * 32 + t * 8;
+                const float *sptr = svalid ? hs_s + (size_t)(ps.pos0 + t) * nkb2 * 4 : reinterpret_cast<const float *>(sh->zeros);
+                const int bstr = bvalid ? 256 : 0, sstr = svalid ? 4 : 0;
                 float R[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
                 for (int kb = ph2.wl; kb < nkb2; kb += ph2.wpk) {
-                    const float4 ix4 = svalid ? *reinterpret_cast<const float4 *>(sptr + kb * 4) : make_float4(0, 0, 0, 0);
+                    const float4 ix4 = *reinterpret_cast<const float4 *>(sptr + kb * sstr);
                     const float ixg[4] = {ix4.x, ix4.y, ix4.z, ix4.w};
                     uint4 bpre[4];
 #pragma unroll
                     for (int grp = 0; grp < 4; grp++)
-                        bpre[grp] = bvalid ? *reinterpret_cast<const uint4 *>(bptr + (size_t)kb * 256 + grp * 64)
-                                           : make_uint4(0, 0, 0, 0);
+                        bpre[grp] = *reinterpret_cast<const uint4 *>(bptr + kb * bstr + grp * 64);
                     const uint32_t st = dec_wait_chunk<CH, NST>(wr);
                     if (tid == 0 && p == ph2.gidx && kb == ph2.wl) DEC_PROBE_T(a, 11);   // first down block has landed
                     float bacc[1][2][4];
@@ -1008,13 +1072,13 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
                     for (int i = 0; i < 4; i++) R[i] += bacc[0][0][i];
                     dec_release_chunk(wr);
                     __syncwarp();
-                    dec_issue_one<CH, NST>(wr, it, ph1, ph2, sh, lane);
+                    dec_issue_one<CH, NST>(wr, it, ph2, sh, lane);
                 }
                 // rows g and g+8 of the 16-row half for token row t
                 float4 *pb = reinterpret_cast<float4 *>(part + (pcount & 1) * DEC_PART_BYTES) + (warp * 32 + lane) * 2;
                 pb[0] = make_float4((R[0] + R[1]) * mx_fix, (R[2] + R[3]) * mx_fix, 0.f, 0.f);
                 bar_sync_named(1 + ph2.gidx, ph2.wpk * 32);
-                const int lw = (ph2.wl + 4 * (nrot - pcount % nrot)) % ph2.wpk;
+                const int lw = (ph2.wl + 4 * (nrot - (pcount & (nrot - 1)))) & (ph2.wpk - 1);
                 if (lw < 4 && lane < 16) {
                     const int mrow = lw;
                     const float *pbase = reinterpret_cast<const float *>(part + (pcount & 1) * DEC_PART_BYTES) +
@@ -1045,26 +1109,28 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
         unsigned int *tickets = a.sync + 16;
         int ucount = 0;
         for (int u = ph2.first_u; u < ph2.u1; u += ph2.ng, ucount++) {
-            const int pass = u / nt2, tile = u - pass * nt2;
+            const int pass = dec_div(u, a.mg_nt2), tile = u - pass * nt2;
             const DecPass &ps = sh->pass[pass];
             const int nrows = ps.nrows, si = pass - pA;
             const int rb = g >> 1;
             const bool bvalid = rb < nrows, svalid = t < nrows;
-            const __half *bptr = reinterpret_cast<const __half *>(act + (size_t)(si * 4 + rb) * I * 4) + (g & 1) * 32 + t * 8;
-            const float *sptr = hs_s + (size_t)(si * 4 + t) * nkb2 * 4;
+            const __half *bptr = (bvalid ? reinterpret_cast<const __half *>(act + (size_t)(si * 4 + rb) * I * 4)
+                                         : reinterpret_cast<const __half *>(sh->zeros)) + (g & 1) * 32 + t * 8;
+            const float *sptr = svalid ? hs_s + (size_t)(si * 4 + t) * nkb2 * 4 : reinterpret_cast<const float *>(sh->zeros);
+            const int bstr = bvalid ? 256 : 0, sstr = svalid ? 4 : 0;
             float R[2][4];
 #pragma unroll
             for (int s = 0; s < 2; s++)
 #pragma unroll
                 for (int i = 0; i < 4; i++) R[s][i] = 0.f;
+#pragma unroll 1
             for (int kb = ph2.wl; kb < nkb2; kb += ph2.wpk) {
-                const float4 ix4 = svalid ? *reinterpret_cast<const float4 *>(sptr + kb * 4) : make_float4(0, 0, 0, 0);
+                const float4 ix4 = *reinterpret_cast<const float4 *>(sptr + kb * sstr);
                 const float ixg[4] = {ix4.x, ix4.y, ix4.z, ix4.w};
                 uint4 bpre[4];
 #pragma unroll
                 for (int grp = 0; grp < 4; grp++)
-                    bpre[grp] = bvalid ? *reinterpret_cast<const uint4 *>(bptr + (size_t)kb * 256 + grp * 64)
-                                       : make_uint4(0, 0, 0, 0);
+                    bpre[grp] = *reinterpret_cast<const uint4 *>(bptr + kb * bstr + grp * 64);
                 const uint32_t st = dec_wait_chunk<CH, NST>(wr);
                 float bacc[1][2][4];
                 block_mma<MODE, 1, true>(st, lane, g, [&](int grp, int) { return bpre[grp]; }, bacc, ixg);
@@ -1074,13 +1140,13 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
                     for (int i = 0; i < 4; i++) R[s][i] += bacc[0][s][i];
                 dec_release_chunk(wr);
                 __syncwarp();
-                dec_issue_one<CH, NST>(wr, it, ph1, ph2, sh, lane);
+                dec_issue_one<CH, NST>(wr, it, ph2, sh, lane);
             }
             float4 *pb = reinterpret_cast<float4 *>(part + (ucount & 1) * DEC_PART_BYTES) + (warp * 32 + lane) * 2;
             pb[0] = make_float4((R[0][0] + R[0][1]) * mx_fix, (R[0][2] + R[0][3]) * mx_fix,
                                 (R[1][0] + R[1][1]) * mx_fix, (R[1][2] + R[1][3]) * mx_fix);
             bar_sync_named(1 + ph2.gidx, ph2.wpk * 32);
-            const int lw = (ph2.wl + 4 * (nrot - ucount % nrot)) % ph2.wpk;
+            const int lw = (ph2.wl + 4 * (nrot - (ucount & (nrot - 1)))) & (ph2.wpk - 1);
             if (lw < 4) {
                 const int mrow = lw;
                 int src, el;

@@ -241,7 +241,7 @@ static int layer_run(ColiCudaMoeLayer *L, DeviceCtx *c, float *out_dev, const fl
     }
     if (!route_only && g_fused_decode && M <= DEC_MAX_M && r.E <= DEC_MAX_E && r.K <= DEC_MAX_K &&
         L->mode_gu == L->mode_d && r.I <= DEC_MAX_I && r.D / TILE_ROWS <= DEC_MAX_TILES &&
-        M * r.K + 2 <= DEC_MAX_PASS && c->sms >= DEC_MAX_PASS) {
+        M * r.K + 2 <= DEC_MAX_PASS && c->sms >= DEC_MAX_PASS && c->sms <= 256) {
         // one kernel for the whole layer (moe_decode.cuh)
         const size_t act_cap = (size_t)dec_act_bytes(L->mode_gu);
         const int act_smem = (size_t)M * nkb1 * 516 <= act_cap;
@@ -268,6 +268,8 @@ static int layer_run(ColiCudaMoeLayer *L, DeviceCtx *c, float *out_dev, const fl
         a.sync = c->dec_sync; a.exp_tab = c->exp_tab_dev; a.status = c->status;
         a.M = M; a.act_smem = act_smem;
         a.wpk1 = dec_pick_wpk(nkb1, 1); a.wpk2 = dec_pick_wpk(nkb2, 2); a.local2 = local2;
+        a.mg_grid = dec_magic((unsigned int)c->sms); a.mg_nt1 = dec_magic((unsigned int)(r.I / TILE_ROWS));
+        a.mg_nt2 = dec_magic((unsigned int)(r.D / TILE_ROWS));
 #ifdef COLI_DECODE_PROBE
         a.probe = g_decode_probe;
 #endif

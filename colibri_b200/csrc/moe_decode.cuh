@@ -156,19 +156,24 @@ __device__ __forceinline__ void bar_sync_named(int id, int nthreads) {
 // 32-bit word. The target is the next multiple above the value thread 0 read at any time
 // before arriving (grid_barrier_target: off the critical path); arriving is a reduction without
 // a return value, and everybody polls the counter itself for the target. All threads of the
-// CTA call grid_barrier; it returns false on timeout (about 20 ms). Needs gridDim.x <= 256.
+// CTA call grid_barrier; on timeout (about 20 ms) it sets *s_failed. Needs gridDim.x <= 256.
 __device__ __forceinline__ unsigned int grid_barrier_target(const unsigned int *sync) {
     unsigned int c0;
     asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(c0) : "l"(sync) : "memory");
     return (c0 & ~255u) + 256u;
 }
-__device__ __forceinline__ bool grid_barrier(unsigned int *sync, int *s_failed, unsigned int target) {
+__device__ __forceinline__ void grid_barrier(unsigned int *sync, int *s_failed, unsigned int target) {
     __syncthreads();
-    if (threadIdx.x == 0) {
-        // release: orders this CTA's earlier writes (made visible to thread 0 by the CTA barrier
+    if (threadIdx.x < 32) {
+        // Warp 0 arrives and polls (one request for the 32 lanes) and goes straight on when the
+        // target shows; it does not meet the other warps again here: they wait for what warp 0
+        // does next (the activations' copies), or for nothing.
+        // release: orders this CTA's earlier writes (made visible to warp 0 by the CTA barrier
         // above) before the arrival
-        const unsigned int add = blockIdx.x == 0 ? 256u - (gridDim.x - 1u) : 1u;
-        asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(sync), "r"(add) : "memory");
+        if (threadIdx.x == 0) {
+            const unsigned int add = blockIdx.x == 0 ? 256u - (gridDim.x - 1u) : 1u;
+            asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(sync), "r"(add) : "memory");
+        }
         long long t0 = clock64();
         for (;;) {
             unsigned int v;
@@ -176,9 +181,8 @@ __device__ __forceinline__ bool grid_barrier(unsigned int *sync, int *s_failed, 
             if (v == target) break;
             if (clock64() - t0 > 40000000LL) { *s_failed = 1; break; }   // a barrier takes microseconds
         }
+        __syncwarp();
     }
-    __syncthreads();
-    return *s_failed == 0;
 }
 
 // One row of routing by one warp, outputs in shared memory. `tab` is the 2^(i/32)
@@ -569,6 +573,15 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
         else if (lane == 6) pf = reinterpret_cast<const char *>(a.sync);
         else if (lane == 7) pf = reinterpret_cast<const char *>(a.exp_tab);
         if (pf) asm volatile("prefetch.global.L2 [%0];" ::"l"(pf));
+    } else if (warp == 1 && lane < 3 && a.tab.sh_gate_pk) {
+        // The shared expert's weights do not depend on the routing: every CTA asks for its share of
+        // them to be brought into L2 now (no values are read), while the memory system is idle.
+        const uint8_t *base = lane == 0 ? a.tab.sh_gate_pk : lane == 1 ? a.tab.sh_up_pk : a.tab.sh_down_pk;
+        int c0, c1;
+        dec_cta_range(lane < 2 ? nt1 * nkb1 : nt2 * nkb2, a.mg_grid, c0, c1);
+        if (c1 > c0)
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + (size_t)c0 * CH), "r"((c1 - c0) * CH)
+                         : "memory");
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
     DEC_PROBE(a, 0);
@@ -580,7 +593,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
     // rolled: this code runs once per launch, and what it costs is the fetch of its instructions.
     const unsigned long long tab_v = a.exp_tab[lane];
     unsigned int bar_target = 0;
-    if (tid == 0) bar_target = grid_barrier_target(a.sync);
+    if (warp == 0) bar_target = grid_barrier_target(a.sync);
     __half *xq_s = reinterpret_cast<__half *>(act);
     float *xs_s = reinterpret_cast<float *>(act + (size_t)M * nkb1 * 512);
     if (r.gating == 0) {
@@ -685,6 +698,11 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
     if (tid < E) { ptab[tid] = pre_g; ptab[E + tid] = pre_u; ptab[2 * E + tid] = pre_d; }
     const int any_bad = __syncthreads_or(bad ? 1 : 0);
     if (tid == 0) DEC_PROBE_T(a, 14);            // scores, x fragments and pointer table complete
+    // One row, ordinary scores, no top-p cut: the K selections are K distinct experts, so entry kk
+    // is expert number kk of the union, pass kk, packed row kk. The ranking threads then write the
+    // pass list themselves and the weight stream starts one barrier later; the weights' tail
+    // (normalisation, scale) runs in warp 0 beside it and is first needed by the final combine.
+    const bool fast1 = M == 1 && !any_bad && !(r.gating == 1 && r.topp > 0.f && r.topp < 1.f);
     if (any_bad) {
         // a NaN or a value <= -1e30 among the candidates: the general form, which also
         // reproduces the engine's "nothing found -> expert kk" degradation row by row
@@ -723,8 +741,27 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
                 }
                 rank += __shfl_xor_sync(0xffffffffu, rank, 1);
                 rank += __shfl_xor_sync(0xffffffffu, rank, 2);
-                if (live && q == 0 && rank < K) { sh->idx[s * K + rank] = e; sh->w[s * K + rank] = score[i]; }
+                if (live && q == 0 && rank < K) {
+                    sh->idx[s * K + rank] = e; sh->w[s * K + rank] = score[i];
+                    if (fast1) {
+                        sh->pos_of[rank] = rank;
+                        DecPass &ps = sh->pass[rank];
+                        ps.e = e; ps.rowid[0] = 0; ps.nrows = 1; ps.pos0 = rank;
+                        ps.wg = ptab[e]; ps.wu = ptab[E + e]; ps.wd = ptab[2 * E + e];
+                    }
+                }
             }
+        }
+        if (fast1 && tid == 0) {
+            int npass = K, spos = K;
+            sh->shared_pos0 = spos;
+            if (a.tab.sh_gate_pk) {
+                DecPass &ps = sh->pass[npass];
+                ps.e = -1; ps.pos0 = spos; ps.nrows = 1; ps.rowid[0] = 0;
+                ps.wg = a.tab.sh_gate_pk; ps.wu = a.tab.sh_up_pk; ps.wd = a.tab.sh_down_pk;
+                npass++; spos++;
+            }
+            sh->npass = npass; sh->npos = spos; sh->nu = K;
         }
         __syncthreads();
         if (warp < M) {     // the engine's tail on the K selected weights: one warp per row
@@ -765,12 +802,22 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
             __syncwarp();       // every lane has read the weights it needs
             if (lane < Ke) w[lane] = mine;
             if (lane == 0) { sh->keff[warp] = Ke; sh->rowflag[warp] = 0; }
+            if (fast1 && blockIdx.x == 0) {
+                __syncwarp();
+                if (lane < K) {
+                    if (a.idx_out) a.idx_out[lane] = ix[lane];
+                    if (a.w_out) a.w_out[lane] = w[lane];
+                }
+                if (lane == 0 && a.keff_out) a.keff_out[0] = Ke;
+            }
         }
-        __syncthreads();
+        if (!fast1) __syncthreads();
     }
     DEC_PROBE(a, 10);
     // ---- union, packed row order and pass list -----------------------------------------
-    if (M == 1 && sh->rowflag[0] == 0) {
+    if (fast1) {
+        // written by the ranking threads
+    } else if (M == 1 && sh->rowflag[0] == 0) {
         // one row without NaN candidates: its selections are distinct experts, so entry kk is
         // expert number kk of the union, pass kk, position kk
         const int ke = sh->keff[0];
@@ -862,14 +909,16 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
         }
         __syncthreads();
     }
+    if (!fast1) {
 #pragma unroll 1
-    for (int p = tid; p < sh->npass; p += blockDim.x) {
-        DecPass &ps = sh->pass[p];
-        if (ps.e >= 0) { ps.wg = ptab[ps.e]; ps.wu = ptab[E + ps.e]; ps.wd = ptab[2 * E + ps.e]; }
-        else { ps.wg = a.tab.sh_gate_pk; ps.wu = a.tab.sh_up_pk; ps.wd = a.tab.sh_down_pk; }
+        for (int p = tid; p < sh->npass; p += blockDim.x) {
+            DecPass &ps = sh->pass[p];
+            if (ps.e >= 0) { ps.wg = ptab[ps.e]; ps.wu = ptab[E + ps.e]; ps.wd = ptab[2 * E + ps.e]; }
+            else { ps.wg = a.tab.sh_gate_pk; ps.wu = a.tab.sh_up_pk; ps.wd = a.tab.sh_down_pk; }
+        }
+        __syncthreads();
     }
-    __syncthreads();
-    if (blockIdx.x == 0) {
+    if (blockIdx.x == 0 && !fast1) {
 #pragma unroll 1
         for (int i = tid; i < M * K; i += blockDim.x) {
             if (a.idx_out) a.idx_out[i] = sh->idx[i];
@@ -993,7 +1042,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
 #pragma unroll 1
     for (int s = 0; s < wr.nst; s++) dec_issue_one<CH, NST>(wr, it, ph2, sh, lane);
     DEC_PROBE(a, 4);   // gate/up consumed (the ring already holds the first down blocks)
-    bool ok = grid_barrier(a.sync, &sh->failed, bar_target);
+    grid_barrier(a.sync, &sh->failed, bar_target);
     DEC_PROBE(a, 5);
     // ---- the SwiGLU activations of this CTA's one or two passes -> shared memory ---------
     const int pA = ph2.u1 > ph2.u0 ? dec_div(ph2.u0, a.mg_nt2) : 0;
@@ -1042,11 +1091,14 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
     DEC_PROBE(a, 6);
     if (a.local2) {
         // ---- down with a local combine: this CTA's 16 output rows over every pass ------------
-        const int nrot = ph2.wpk >> 2;
+        // Every warp first runs through all its blocks, leaving its partial sums in shared memory
+        // ([packed row][warp of the group][16 rows]); the sums over the group's warps (in warp
+        // order), the per-row scale and the weighted combine follow once per slice, so the blocks
+        // of a warp's passes run back to back without a barrier between them.
         const bool has_shared = a.tab.sh_gate_pk != nullptr;
-        int pcount = 0;
+        float *pp = reinterpret_cast<float *>(part);
         for (int u = ph2.u0; u < ph2.u1; u++) {
-            for (int p = ph2.gidx; p < npass; p += ph2.ng, pcount++) {
+            for (int p = ph2.gidx; p < npass; p += ph2.ng) {
                 const DecPass &ps = sh->pass[p];
                 const int nrows = ps.nrows;
                 const int rb = g >> 1;
@@ -1075,33 +1127,41 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
                     dec_issue_one<CH, NST>(wr, it, ph2, sh, lane);
                 }
                 // rows g and g+8 of the 16-row half for token row t
-                float4 *pb = reinterpret_cast<float4 *>(part + (pcount & 1) * DEC_PART_BYTES) + (warp * 32 + lane) * 2;
-                pb[0] = make_float4((R[0] + R[1]) * mx_fix, (R[2] + R[3]) * mx_fix, 0.f, 0.f);
-                bar_sync_named(1 + ph2.gidx, ph2.wpk * 32);
-                const int lw = (ph2.wl + 4 * (nrot - (pcount & (nrot - 1)))) & (ph2.wpk - 1);
-                if (lw < 4 && lane < 16) {
-                    const int mrow = lw;
-                    const float *pbase = reinterpret_cast<const float *>(part + (pcount & 1) * DEC_PART_BYTES) +
-                                         ((size_t)(ph2.gidx * ph2.wpk) * 32 + (lane & 7) * 4 + mrow) * 8 + (lane >> 3);
-                    float y = 0.f;
-                    for (int w = 0; w < ph2.wpk; w++) y += pbase[w * 256];
-                    const int o = u * 16 + lane;
-                    if (MODE == SC_ROW) y *= (ps.e >= 0 ? a.tab.down_rs[ps.e] : a.tab.sh_down_rs)[o];
-                    if (mrow < nrows) ybuf[(ps.pos0 + mrow) * 16 + lane] = y;
+                if (svalid) {
+                    float *dst = pp + ((size_t)(ps.pos0 + t) * ph2.wpk + ph2.wl) * 16 + g;
+                    dst[0] = (R[0] + R[1]) * mx_fix;
+                    dst[8] = (R[2] + R[3]) * mx_fix;
                 }
             }
             if (tid == 0) DEC_PROBE_T(a, 7);
-            __syncthreads();      // every pass of this slice is in ybuf
+            __syncthreads();      // every partial sum of this slice is in place
             if (tid == 0) DEC_PROBE_T(a, 8);
+#pragma unroll 1
+            for (int p = warp; p < npass; p += DEC_WARPS) {
+                const DecPass &ps = sh->pass[p];
+#pragma unroll 1
+                for (int i = lane; i < ps.nrows * 16; i += 32) {
+                    const int pos = ps.pos0 + (i >> 4), rr = i & 15;
+                    const float *src = pp + (size_t)pos * ph2.wpk * 16 + rr;
+                    float y = 0.f;
+#pragma unroll 4
+                    for (int w = 0; w < ph2.wpk; w++) y += src[w * 16];
+                    if (MODE == SC_ROW) y *= (ps.e >= 0 ? a.tab.down_rs[ps.e] : a.tab.sh_down_rs)[u * 16 + rr];
+                    ybuf[pos * 16 + rr] = y;
+                }
+            }
+            __syncthreads();
+#pragma unroll 1
             for (int i = tid; i < M * 16; i += blockDim.x) {
                 const int s = i >> 4, rr = i & 15;
                 const int ke = sh->keff[s];
                 float acc = 0.f;
+#pragma unroll 4
                 for (int kk = 0; kk < ke; kk++) acc = fmaf(sh->w[s * K + kk], ybuf[sh->pos_of[s * K + kk] * 16 + rr], acc);
                 if (has_shared) acc += ybuf[(sh->shared_pos0 + s) * 16 + rr];
                 a.out[(size_t)s * D + u * 16 + rr] = acc;
             }
-            __syncthreads();      // ybuf is reused by the next slice
+            if (u + 1 < ph2.u1) __syncthreads();      // the buffers are reused by the next slice
         }
     } else {
     // ---- down -> Y, and the weighted combine by whoever completes a slice -----------------
@@ -1184,7 +1244,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
     DEC_PROBE(a, 9);
     if (!wr.ok) sh->failed = 2;
     __syncthreads();
-    if (!ok || sh->failed) {
+    if (sh->failed) {
         if (tid == 0) kstat_set(a.status, sh->failed == 2 ? KSTAT_MBAR_TIMEOUT : KSTAT_GRID_TIMEOUT);
         // drain copies still in flight before the shared memory goes away (bounded)
         for (int i = wr.consumed; i < wr.issued; i++) {

@@ -249,7 +249,8 @@ static int layer_run(ColiCudaMoeLayer *L, DeviceCtx *c, float *out_dev, const fl
         // pass row's activations fit one CTA's shared memory and D/16 slices spread well over the SMs.
         const long units2 = r.D / 16, waves2 = (units2 + c->sms - 1) / c->sms;
         const int local2 = (size_t)p.npos_cap * ((size_t)r.I * 4 + (size_t)nkb2 * 16 + 64) <= act_cap &&
-                           units2 * 100 >= 85 * waves2 * c->sms;
+                           units2 * 100 >= 85 * waves2 * c->sms &&
+                           (size_t)p.npos_cap * dec_pick_wpk(nkb2, 2) * 64 <= (size_t)2 * DEC_PART_BYTES;
         if (!reserve(c, &L->hq, (size_t)p.npos_cap * r.I * 2 * sizeof(__half)) ||
             !reserve(c, &L->hs, (size_t)p.npos_cap * (r.I / 32) * sizeof(float)) ||
             !reserve(c, &L->pd, (size_t)p.npos_cap * r.D * sizeof(float))) return 0;

@@ -38,3 +38,20 @@ def be():
     assert b.fp8_set_lut(lut.ctypes.data) == 1
     yield b
     b.shutdown()
+
+
+def pytest_sessionfinish(session, exitstatus):
+    """After a GPU session: the parity errors the tests noted (floored and plain figures side by
+    side), as a table under gpurun_out/."""
+    from tests import util
+    if not util.ERRORS:
+        return
+    out = os.path.join(ROOT, "gpurun_out")
+    try:
+        os.makedirs(out, exist_ok=True)
+        with open(os.path.join(out, "parity_errors.txt"), "w") as f:
+            f.write("label | max |err|/(|want|+0.01 rms) | max |err|/|want| | max|err|/max|want|\n")
+            for label, e, elem, norm in util.ERRORS:
+                f.write(f"{label} | {e:.3e} | {elem:.3e} | {norm:.3e}\n")
+    except OSError:
+        pass

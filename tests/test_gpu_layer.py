@@ -8,7 +8,7 @@ import pytest
 
 from colibri_b200 import workloads as W
 from colibri_b200.backend import MoeLayer
-from tests.util import upload_layer, free_layer, host_layer, max_rel_err, upload_qt
+from tests.util import upload_layer, free_layer, host_layer, max_rel_err, record_err, upload_qt
 
 pytestmark = pytest.mark.gpu
 TOL = 1e-3
@@ -26,7 +26,7 @@ def check_layer(be, oracle, cfg, L, handles, M, seed, scale=1.0, topp=0.0, use_r
     assert np.array_equal(keff, ok_)
     for s in range(M):
         assert np.array_equal(idx[s, :keff[s]], oi[s, :ok_[s]]), s
-    err = max_rel_err(out, want)
+    err = record_err(f"layer D={cfg['D']} I={cfg['I']} E={cfg['E']} K={cfg['K']} {cfg['gating']} M={M}", out, want)
     assert err <= TOL, err
     out2, _, _, _ = lay(x, lg)
     assert np.array_equal(out.view(np.uint32), out2.view(np.uint32))      # deterministic

@@ -30,6 +30,30 @@ def max_rel_err(got, want):
     return float(np.max(np.abs(got - want) / den)) if want.size else 0.0
 
 
+ERRORS = []      # (label, floored, plain element-wise, norm-wise): written out at the end of a GPU session
+
+
+def plain_rel_errs(got, want):
+    """The two unfloored figures beside max_rel_err: the largest |err| / |want| over the elements
+    with want != 0 (dominated by outputs that cancel to almost nothing), and max|err| / max|want|."""
+    got = np.asarray(got, np.float64)
+    want = np.asarray(want, np.float64)
+    err = np.abs(got - want)
+    nz = want != 0
+    elem = float(np.max(err[nz] / np.abs(want[nz]))) if nz.any() else 0.0
+    norm = float(err.max() / max(np.abs(want).max(), 1e-300)) if want.size else 0.0
+    return elem, norm
+
+
+def record_err(label, got, want):
+    """max_rel_err, also noted with the plain figures for the session's error table."""
+    e = max_rel_err(got, want)
+    elem, norm = plain_rel_errs(got, want)
+    ERRORS.append((label, e, elem, norm))
+    print(f"[parity] {label}: floored {e:.3e}  plain element-wise {elem:.3e}  max|err|/max|want| {norm:.3e}")
+    return e
+
+
 def upload_qt(be, t, device=0):
     h = be.upload(t.w, t.s, t.fmt, t.I, t.O, device, t.gs)
     assert h, f"upload refused fmt={t.fmt} I={t.I} O={t.O} gs={t.gs}"

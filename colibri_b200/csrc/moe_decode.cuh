@@ -20,31 +20,39 @@
 //    (expert pass, 32 output rows) over the whole intermediate dimension, reduced the
 //    same way into Y[pass row, 32 columns].
 //  * Between the phases the CTAs meet at one grid barrier; the weight stream does not
-//    stop for it, because a warp's ring of bulk copies runs ahead into the down phase's
-//    first blocks (weights do not depend on the activations).
+//    stop for it: as soon as a warp has consumed its last gate/up block it refills its ring
+//    of bulk copies with the down phase's first blocks (weights do not depend on the
+//    activations), so those are in shared memory when the barrier opens.
 //  * The weighted combine needs no barrier: the group that completes the last pass of a
 //    32-column slice of the output (a ticket per slice) adds the slice's terms, for
 //    every token in that token's selection order, shared expert last, and resets the ticket.
 //  * When the call is small enough that every pass row's activations fit one CTA's shared
 //    memory (the OLMoE shape at M=1), the down phase is cut the other way: a CTA owns 16
-//    output rows over ALL passes (half-chunks of the weight stream), so the combine is
-//    local and the results leave the CTA once, as the final output.
+//    output rows over ALL passes (half-chunks of the weight stream). Its warps run through
+//    all their blocks back to back, leaving per-warp sums in shared memory; the sums over
+//    the warps, the combine and the store of the final output follow once per slice.
 //
-// Activations: x is split into fp16 hi/lo fragments by every CTA in its own shared
-// memory while the first weight blocks are in flight (or read from global memory, split
-// by a preceding kernel, when M*D*4 bytes do not fit). After the barrier a CTA copies
-// the activations of the one or two expert passes its down units belong to into the
-// same region.
+// Activations: x reaches every CTA's shared memory by asynchronous copies issued at the
+// top of the kernel and is split in place into fp16 hi/lo fragments while the routing
+// runs (or read from global memory, split by a preceding kernel, when M*D*4 bytes do not
+// fit). After the barrier warp 0 brings the SwiGLU activations the CTA's down units need
+// (one bulk copy per packed row, one mbarrier) into the same region.
 //
 // Sums are formed in an order that depends only on the shapes (which warp owns which
 // block is a function of the block index), so a token's result is bit-identical
 // whatever else is in the batch.
 //
-// Waits: the grid barrier (an arrival counter plus a generation word, so it needs no
-// per-launch value from the host and a launch can be replayed from a CUDA graph) and
-// every mbarrier wait are bounded; on expiry a CTA records a status code, keeps walking
-// its loops without waiting (so that no CTA-level barrier is abandoned), drains its
-// copies and returns. The grid is one CTA per SM, so all CTAs are co-resident.
+// Code that runs once per launch is kept small and rolled: a launch executes each of its
+// instructions a handful of times at most, so what such code costs is the fetch of its
+// instructions, not their issue (the general routing for rows with NaN candidates is out
+// of line; divisions by launch constants are multiply-shifts prepared by the host).
+//
+// Waits: the grid barrier (one counter to which every launch adds exactly 256, polled for
+// the next multiple: no per-launch value from the host, so a launch can be replayed from
+// a CUDA graph) and every mbarrier wait are bounded; on expiry a CTA records a status
+// code, keeps walking its loops without waiting (so that no CTA-level barrier is
+// abandoned), drains its copies and returns. The grid is one CTA per SM, so all CTAs are
+// co-resident.
 #pragma once
 #include "common.cuh"
 #include "gemv_stream.cuh"

@@ -69,9 +69,13 @@ def main():
     dist.all_reduce(flag)
     if rank == 0:
         print("EP_MULTI_OK" if int(flag.item()) == 0 else "EP_MULTI_MISMATCH", f"world={world}", flush=True)
-    be.shutdown()
+    rc = 0 if int(flag.item()) == 0 else 1
+    # release in dependency order: the layers and torch's tensors go before the backend's
+    # contexts, the process group before the interpreter exits
+    del lay, out, xr, lr, bias, flag
+    torch.cuda.synchronize()
     dist.destroy_process_group()
-    sys.exit(0 if int(flag.item()) == 0 else 1)
+    sys.exit(rc)
 
 
 if __name__ == "__main__":

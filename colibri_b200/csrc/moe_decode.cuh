@@ -538,10 +538,12 @@ template <int MODE>
 __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) {
     constexpr int CH = CODE_BYTES + (MODE == SC_H16 ? 256 : MODE == SC_F32 ? 512 : MODE == SC_MX ? 128 : 0);
     constexpr int NST = DEC_NST;
+    constexpr int nst = NST;
+    const uint32_t ring_bytes = (uint32_t)DEC_WARPS * nst * CH;
     extern __shared__ __align__(128) uint8_t smem[];
     // layout: rings | mbarriers (1024 B) | DecShared | partial sums (2 buffers; the routing
     // scratch and tables live here first) | activation region
-    DecShared *sh = reinterpret_cast<DecShared *>(smem + DEC_WARPS * NST * CH + 1024);
+    DecShared *sh = reinterpret_cast<DecShared *>(smem + ring_bytes + 1024);
     uint8_t *part = reinterpret_cast<uint8_t *>(sh) + ((sizeof(DecShared) + 127) & ~127);
     uint8_t *act = part + 2 * DEC_PART_BYTES;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
@@ -550,9 +552,9 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
     const int E = r.E, K = r.K, M = a.M, D = r.D, I = r.I;
     const int nkb1 = D / BLOCK_K, nkb2 = I / BLOCK_K, nt1 = I / TILE_ROWS, nt2 = D / TILE_ROWS;
     WarpRing wr;
-    wr.ring = smem_u32(smem) + warp * (NST * CH);
-    wr.bars = smem_u32(smem) + DEC_WARPS * NST * CH + warp * DEC_BARS_PER_WARP * 8;
-    wr.issued = 0; wr.consumed = 0; wr.pi = 0; wr.ci = 0; wr.nst = NST; wr.sb = CH; wr.parbits = 0; wr.ok = true;
+    wr.ring = smem_u32(smem) + warp * (nst * CH);
+    wr.bars = smem_u32(smem) + ring_bytes + warp * DEC_BARS_PER_WARP * 8;
+    wr.issued = 0; wr.consumed = 0; wr.pi = 0; wr.ci = 0; wr.nst = nst; wr.sb = CH; wr.parbits = 0; wr.ok = true;
     // routing scratch inside the partial-sum buffers (dead before the first partial sum is written)
     float *score = reinterpret_cast<float *>(part);                     // [M*E]  (<= 8 KB)
     float *choice = reinterpret_cast<float *>(part + 8192);             // [M*E]
@@ -635,7 +637,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
     if (tid == 0) {
         sh->failed = 0; sh->nu = 0;
         // one more barrier, behind the warps' own: the SwiGLU activations arriving for the down phase
-        mbar_init(smem_u32(smem) + DEC_WARPS * NST * CH + DEC_WARPS * DEC_BARS_PER_WARP * 8, 1);
+        mbar_init(smem_u32(smem) + ring_bytes + DEC_WARPS * DEC_BARS_PER_WARP * 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
 #pragma unroll 1
@@ -711,6 +713,56 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
     // pass list themselves and the weight stream starts one barrier later; the weights' tail
     // (normalisation, scale) runs in warp 0 beside it and is first needed by the final combine.
     const bool fast1 = M == 1 && !any_bad && !(r.gating == 1 && r.topp > 0.f && r.topp < 1.f);
+    // The engine's tail on the K selected weights (top-p cut, normalisation, scale): one warp per row.
+    auto route_tail = [&]() {
+        if (warp < M) {
+            int *ix = sh->idx + warp * K;
+            float *w = sh->w + warp * K;
+            int Ke = K;
+            if (r.gating == 1 && r.topp > 0.f && r.topp < 1.f) {
+                if (lane == 0) {
+#pragma unroll 1
+                    for (int p = 1; p < K; p++) {
+                        int ii = ix[p]; float ww = w[p]; int b = p - 1;
+                        while (b >= 0 && w[b] < ww) { w[b + 1] = w[b]; ix[b + 1] = ix[b]; b--; }
+                        w[b + 1] = ww; ix[b + 1] = ii;
+                    }
+                    float tot = 1e-20f;
+#pragma unroll 1
+                    for (int kk = 0; kk < K; kk++) tot = __fadd_rn(tot, w[kk]);
+                    float cum = 0.f;
+#pragma unroll 1
+                    for (int kk = 0; kk < K; kk++) {
+                        cum = __fadd_rn(cum, w[kk]);
+                        if (cum >= __fmul_rn(r.topp, tot)) { Ke = kk + 1; break; }
+                    }
+                }
+                Ke = __shfl_sync(0xffffffffu, Ke, 0);
+                __syncwarp();
+            }
+            // every lane forms the same serial sum; lane kk then scales weight kk (K <= 16 lanes)
+            float mine = lane < Ke ? w[lane] : 0.f;
+            if (r.norm_topk) {
+                float sm = 0.f;
+#pragma unroll 1
+                for (int kk = 0; kk < Ke; kk++) sm = __fadd_rn(sm, w[kk]);
+                if (r.gating == 1) sm = __fadd_rn(sm, 1e-20f);
+                mine = __fdiv_rn(mine, sm);
+            }
+            if (r.gating == 1) mine = __fmul_rn(mine, r.routed_scale);
+            __syncwarp();       // every lane has read the weights it needs
+            if (lane < Ke) w[lane] = mine;
+            if (lane == 0) { sh->keff[warp] = Ke; sh->rowflag[warp] = 0; }
+            if (fast1 && blockIdx.x == 0) {
+                __syncwarp();
+                if (lane < K) {
+                    if (a.idx_out) a.idx_out[lane] = ix[lane];
+                    if (a.w_out) a.w_out[lane] = w[lane];
+                }
+                if (lane == 0 && a.keff_out) a.keff_out[0] = Ke;
+            }
+        }
+    };
     if (any_bad) {
         // a NaN or a value <= -1e30 among the candidates: the general form, which also
         // reproduces the engine's "nothing found -> expert kk" degradation row by row
@@ -772,53 +824,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
             sh->npass = npass; sh->npos = spos; sh->nu = K;
         }
         __syncthreads();
-        if (warp < M) {     // the engine's tail on the K selected weights: one warp per row
-            int *ix = sh->idx + warp * K;
-            float *w = sh->w + warp * K;
-            int Ke = K;
-            if (r.gating == 1 && r.topp > 0.f && r.topp < 1.f) {
-                if (lane == 0) {
-#pragma unroll 1
-                    for (int p = 1; p < K; p++) {
-                        int ii = ix[p]; float ww = w[p]; int b = p - 1;
-                        while (b >= 0 && w[b] < ww) { w[b + 1] = w[b]; ix[b + 1] = ix[b]; b--; }
-                        w[b + 1] = ww; ix[b + 1] = ii;
-                    }
-                    float tot = 1e-20f;
-#pragma unroll 1
-                    for (int kk = 0; kk < K; kk++) tot = __fadd_rn(tot, w[kk]);
-                    float cum = 0.f;
-#pragma unroll 1
-                    for (int kk = 0; kk < K; kk++) {
-                        cum = __fadd_rn(cum, w[kk]);
-                        if (cum >= __fmul_rn(r.topp, tot)) { Ke = kk + 1; break; }
-                    }
-                }
-                Ke = __shfl_sync(0xffffffffu, Ke, 0);
-                __syncwarp();
-            }
-            // every lane forms the same serial sum; lane kk then scales weight kk (K <= 16 lanes)
-            float mine = lane < Ke ? w[lane] : 0.f;
-            if (r.norm_topk) {
-                float sm = 0.f;
-#pragma unroll 1
-                for (int kk = 0; kk < Ke; kk++) sm = __fadd_rn(sm, w[kk]);
-                if (r.gating == 1) sm = __fadd_rn(sm, 1e-20f);
-                mine = __fdiv_rn(mine, sm);
-            }
-            if (r.gating == 1) mine = __fmul_rn(mine, r.routed_scale);
-            __syncwarp();       // every lane has read the weights it needs
-            if (lane < Ke) w[lane] = mine;
-            if (lane == 0) { sh->keff[warp] = Ke; sh->rowflag[warp] = 0; }
-            if (fast1 && blockIdx.x == 0) {
-                __syncwarp();
-                if (lane < K) {
-                    if (a.idx_out) a.idx_out[lane] = ix[lane];
-                    if (a.w_out) a.w_out[lane] = w[lane];
-                }
-                if (lane == 0 && a.keff_out) a.keff_out[0] = Ke;
-            }
-        }
+        if (!fast1) route_tail();
         if (!fast1) __syncthreads();
     }
     DEC_PROBE(a, 10);
@@ -951,11 +957,18 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
     else { dec_cta_range(npass * nt2, a.mg_grid, ph2.u0, ph2.u1); ph2.first_u = ph2.u0 + ph2.gidx; }
 
     // ---- start this warp's weight stream ------------------------------------------------
+    // One copy per warp and round, the CTA's warps in step between the rounds: every warp's
+    // first block is then requested before anybody's second, so that all warps have something
+    // to multiply early in the time the memory system takes to deliver the first wave.
     DecIt it;
     dec_it_start<CH>(it, ph1, sh);
 #pragma unroll 1
-    for (int s = 0; s < NST; s++) dec_issue_one<CH, NST>(wr, it, ph1, sh, lane);
+    for (int s = 0; s < nst; s++) {
+        dec_issue_one<CH, NST>(wr, it, ph1, sh, lane);
+        if (s + 1 < nst) __syncthreads();
+    }
     DEC_PROBE(a, 2);
+    if (fast1) route_tail();     // beside the stream; the weights are first needed by the final combine
     const float mx_fix = (MODE == SC_MX) ? 16384.f : 1.f;   // fp16 fields carry e2m1 * 2^-14
 
     // ---- gate / up -> SwiGLU activations ------------------------------------------------
@@ -1044,7 +1057,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
     // Every gate/up block of this warp has landed and been read, so nothing is in flight: the
     // down stream starts now, ahead of the barrier (its weights do not depend on the other
     // CTAs). For the local combine the ring becomes six slots of half a chunk.
-    if (a.local2) { wr.nst = 2 * NST; wr.sb = CH / 2; }
+    if (a.local2) { wr.nst = min(2 * nst, DEC_BARS_PER_WARP); wr.sb = CH / 2; }
     wr.pi = 0; wr.ci = 0; wr.issued = 0; wr.consumed = 0;
     dec_it_start<CH>(it, ph2, sh);
 #pragma unroll 1
@@ -1063,7 +1076,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
     // warp 0 and counted on one mbarrier. Local combine: slot = packed row, every row is wanted;
     // otherwise slot = 4 * (pass - pA) + row of the pass.
     const int nslot = a.local2 ? (ph2.u1 > ph2.u0 ? npos : 0) : (pB - pA + 1) * 4;
-    const uint32_t hbar = smem_u32(smem) + DEC_WARPS * NST * CH + DEC_WARPS * DEC_BARS_PER_WARP * 8;
+    const uint32_t hbar = smem_u32(smem) + ring_bytes + DEC_WARPS * DEC_BARS_PER_WARP * 8;
     if (warp == 0 && nslot > 0) {
         const uint32_t row_bytes = (uint32_t)I * 4u, sc_bytes = (uint32_t)nkb2 * 16u;
         uint32_t mine = 0;

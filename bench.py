@@ -420,7 +420,8 @@ def run_ep_block(args, be, world, rank, local, L, M, n_experts=None, steps=None,
             raise RuntimeError("tensor upload failed")
         handles += hs[0] + hs[1] + hs[2] + sh
         layers.append(CudaEpLayer(be, local, cfg, em, rank, hs[0], hs[1], hs[2], tuple(sh),
-                                  torch.from_numpy(biases[li]).to(dev), ROUTED_SCALE, max_rows=m, payload="bf16"))
+                                  torch.from_numpy(biases[li]).to(dev), ROUTED_SCALE, max_rows=m, payload="bf16",
+                                  exchange="peer" if world > 1 else "nccl"))
     xs = [torch.from_numpy(W.activations(M, D, 500 + li)[rank * m:(rank + 1) * m].copy()).to(dev) for li in range(L)]
     lgs = [torch.from_numpy(l[rank * m:(rank + 1) * m].copy()).to(dev) for l in lg_all]
     torch.cuda.synchronize()
@@ -433,39 +434,57 @@ def run_ep_block(args, be, world, rank, local, L, M, n_experts=None, steps=None,
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
-    for _ in range(3):
+
+    def timed():
+        """-> ms of `steps` steps, then the per-phase split of one more step."""
+        for _ in range(3):
+            step()
+        barrier()
+        for lay in layers:
+            lay.check_exact()
+        return timed_body()
+
+    def timed_body():
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(bstream)
+        for _ in range(steps):
+            step()
+        e1.record(bstream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        # per-phase split of one more step (events on the two streams)
+        n0 = be.launch_total(local)
+        be.set_kernel_events(1)
+        for lay in layers:
+            lay.timing = {}
         step()
-    barrier()
-    for lay in layers:
-        lay.check_exact()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(bstream)
-    for _ in range(steps):
-        step()
-    e1.record(bstream)
-    barrier()
-    ms = e0.elapsed_time(e1)
-    # per-phase split of one more step (events on the two streams)
-    n0 = be.launch_total(local)
-    be.set_kernel_events(1)
-    for lay in layers:
-        lay.timing = {}
-    step()
-    torch.cuda.synchronize()
-    k_ms, k_n = C.c_float(), C.c_int()
-    be.kernel_events(local, C.byref(k_ms), C.byref(k_n))
-    be.set_kernel_events(0)
-    launches_step = int(be.launch_total(local) - n0)
-    pack = a2a = gemm = comb = 0.0
-    rows_recv = 0
-    for lay in layers:
-        mk = lay.timing["layers"][0]
-        pack += mk["t0"].elapsed_time(mk["pack"])
-        a2a += mk["pack"].elapsed_time(mk["recv"]) + mk["gemm"].elapsed_time(mk["back"])
-        gemm += mk["g0"].elapsed_time(mk["gemm"])
-        comb += mk["back"].elapsed_time(mk["t1"])
-        rows_recv += lay.last["n_recv"]
-        lay.timing = None
+        torch.cuda.synchronize()
+        k_ms, k_n = C.c_float(), C.c_int()
+        be.kernel_events(local, C.byref(k_ms), C.byref(k_n))
+        be.set_kernel_events(0)
+        launches_step = int(be.launch_total(local) - n0)
+        pack = a2a = gemm = comb = 0.0
+        rows_recv = 0
+        for lay in layers:
+            mk = lay.timing["layers"][0]
+            pack += mk["t0"].elapsed_time(mk["pack"])
+            a2a += mk["pack"].elapsed_time(mk["recv"]) + mk["gemm"].elapsed_time(mk["back"])
+            gemm += mk["g0"].elapsed_time(mk["gemm"])
+            comb += mk["back"].elapsed_time(mk["t1"])
+            rows_recv += lay.last["n_recv"]
+            lay.timing = None
+        return ms, k_ms.value, launches_step, pack, a2a, gemm, comb, rows_recv
+
+    ms, k_ms_v, launches_step, pack, a2a, gemm, comb, rows_recv = timed()
+    nccl_contrast = None
+    if world > 1:
+        # the same layers with NCCL's all-to-all as the exchange, for contrast
+        for lay in layers:
+            lay.exchange = "nccl"
+        c_ms, _, _, c_pack, c_a2a, c_gemm, c_comb, _ = timed()
+        for lay in layers:
+            lay.exchange = "peer"
+        nccl_contrast = [c_ms, c_pack, c_a2a, c_gemm, c_comb]
     # end to end: rows and logits start in pinned host memory, the result is read back
     x_pin = [x.cpu().pin_memory() for x in xs]
     lg_pin = [l.cpu().pin_memory() for l in lgs]
@@ -487,14 +506,15 @@ def run_ep_block(args, be, world, rank, local, L, M, n_experts=None, steps=None,
         step_host()
     barrier()
     e2e_ms = (time.perf_counter() - t0) * 1e3
-    t = torch.tensor([ms, e2e_ms, k_ms.value, pack, a2a, gemm, comb, float(rows_recv)], device=dev, dtype=torch.float64)
+    t = torch.tensor([ms, e2e_ms, k_ms_v, pack, a2a, gemm, comb, float(rows_recv)] + (nccl_contrast or [0.0] * 5),
+                     device=dev, dtype=torch.float64)
     tmin = t.clone()
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dist.all_reduce(tmin, op=dist.ReduceOp.MIN)
     status = be.kernel_status(local)
     for lay in layers:
-        del lay
+        lay.close()
     for h in handles:
         be.tensor_free(h)
     if status != 0:
@@ -507,8 +527,13 @@ def run_ep_block(args, be, world, rank, local, L, M, n_experts=None, steps=None,
     return {
         "workload": f"c5_ep: expert-parallel MoE layer (D={D}, I={I}, E={E}+1 shared, top-{K} sigmoid, MXFP4), "
                     f"M={M} rows in total, {L} layers per step, Zipf(1.1) logit bias, experts placed on {world} rank(s) "
-                    f"{'by routing histogram' if balanced else 'in equal blocks'}, NCCL all-to-all dispatch (bf16 rows) "
-                    f"and combine (f32 rows)",
+                    f"{'by routing histogram' if balanced else 'in equal blocks'}, dispatch (bf16 rows) and combine "
+                    f"(f32 rows) {'as device-to-device copies over peer memory (NVLink), NCCL for the counts and the barriers' if world > 1 else 'local'}",
+        "exchange": "peer copies" if world > 1 else "none",
+        "nccl_all_to_all_contrast": None if world == 1 else {
+            "ms_per_step": float(t[8]) / steps,
+            "phase_ms": {"route_plan_pack": float(t[9]), "a2a_dispatch_and_combine": float(t[10]),
+                         "expert_gemm": float(t[11]), "combine": float(t[12])}},
         "scaling": "strong", "n_gpus": world, "steps": steps, "ms_per_step": ms_all / steps,
         "value": step_bytes * steps / (ms_all * 1e-3) / 1e9, "unit": "GB/s", "bytes_per_step": step_bytes,
         "e2e": {"value": step_bytes * steps / (e2e_all * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_all / steps,
@@ -644,7 +669,8 @@ def run_gpu_arm(args):
                     "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                     "config": {"workload": ep["workload"], "l2": "weights touched per step exceed L2 (126 MB)",
                                **{k: ep[k] for k in ("bytes_per_step", "phase_ms", "a2a_bytes_per_rank_per_layer",
-                                                     "imbalance_max_over_mean_rows", "rows_received_per_step")}},
+                                                     "imbalance_max_over_mean_rows", "rows_received_per_step",
+                                                     "exchange", "nccl_all_to_all_contrast")}},
                     "e2e": ep["e2e"], "gpu_launches": ep["gpu_launches_per_step"] * ep["steps"] * world,
                     "clocks": clocks, "roofline": ep["roofline"], "cpu_baseline": None}
             print(json.dumps(line), flush=True)

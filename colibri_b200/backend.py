@@ -108,6 +108,10 @@ ADDITIVE_ABI = [
     ("coli_cuda_ep_expert_group_dev", C.c_int, [C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), C.c_int, _i32p, C.c_int,
                                                 _vp, _vp, C.c_int]),
     ("coli_cuda_ep_combine_dev", C.c_int, [C.c_int, _vp, _vp, _vp, _vp, _vp, _vp, C.c_int, C.c_int, C.c_int]),
+    ("coli_cuda_pipe_ipc_export", C.c_int, [C.c_int, _vp, _vp]),
+    ("coli_cuda_pipe_ipc_open", _vp, [C.c_int, _vp]),
+    ("coli_cuda_pipe_ipc_close", C.c_int, [C.c_int, _vp]),
+    ("coli_cuda_pipe_copy_async", C.c_int, [C.c_int, _vp, _vp, C.c_size_t, _vp]),
     ("coli_cuda_physical_bytes", C.c_size_t, [C.c_int]),
     ("coli_cuda_last_timing", C.c_int, [C.c_int, _f32p, _i32p]),
     ("coli_cuda_set_timing", None, [C.c_int]),

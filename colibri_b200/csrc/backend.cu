@@ -1169,6 +1169,43 @@ extern "C" void coli_cuda_pipe_free(int device, void *p) {
     if (!p || !select_ctx(c)) return;
     cudaFree(p);
 }
+// Peer access to pipe_alloc'ed buffers across processes (one process per GPU): the owner
+// exports a 64-byte handle, another process opens it and gets a pointer into the owner's HBM
+// that this process's copies and kernels can use (NVLink / NVSwitch path).
+extern "C" int coli_cuda_pipe_ipc_export(int device, void *dev_ptr, void *handle64) {
+    DeviceCtx *c = find_ctx(device);
+    if (!dev_ptr || !handle64 || !select_ctx(c)) return 0;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    cudaIpcMemHandle_t h;
+    if (!cuda_ok(cudaIpcGetMemHandle(&h, dev_ptr), "ipc export")) return 0;
+    std::memcpy(handle64, &h, sizeof(h));
+    return 1;
+}
+extern "C" void *coli_cuda_pipe_ipc_open(int device, const void *handle64) {
+    DeviceCtx *c = find_ctx(device);
+    if (!handle64 || !select_ctx(c)) return nullptr;
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle64, sizeof(h));
+    void *p = nullptr;
+    if (!cuda_ok(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess), "ipc open")) return nullptr;
+    return p;
+}
+extern "C" int coli_cuda_pipe_ipc_close(int device, void *peer_ptr) {
+    DeviceCtx *c = find_ctx(device);
+    if (!peer_ptr || !select_ctx(c)) return 0;
+    return cuda_ok(cudaIpcCloseMemHandle(peer_ptr), "ipc close");
+}
+// Asynchronous device-to-device copy (either side may be a peer pointer) on `stream`
+// (a cudaStream_t; NULL = the backend's stream). Large copies run on the copy engines, beside
+// whatever kernels are resident.
+extern "C" int coli_cuda_pipe_copy_async(int device, void *dst, const void *src, size_t bytes, void *stream) {
+    DeviceCtx *c = find_ctx(device);
+    if (!select_ctx(c)) return 0;
+    if (bytes == 0) return 1;
+    if (!dst || !src) return 0;
+    return cuda_ok(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice,
+                                   stream ? static_cast<cudaStream_t>(stream) : c->stream), "pipe copy");
+}
 extern "C" int coli_cuda_pipe_upload(int device, void *dst, const void *src, size_t bytes) {
     DeviceCtx *c = find_ctx(device);
     if (!select_ctx(c)) return 0;

@@ -274,6 +274,17 @@ int coli_cuda_pipe_argmax(int device, int *idx_dev, const float *x_dev, int S, i
  * coli_cuda_ep_combine_dev: out[s] = sum_{kk < keff[s]} w[s,kk] * y[entry_of[s*K+kk]]
  * (+ shared[s]), y in send-buffer order: each row's selection order, shared expert last, so
  * the layer's result does not depend on the number of ranks or the placement. */
+/* Peer memory for the exchange (one process per GPU; no counterpart in the reference, whose
+ * devices live in one process): coli_cuda_pipe_ipc_export writes a 64-byte handle of a buffer
+ * obtained from coli_cuda_pipe_alloc; another process's coli_cuda_pipe_ipc_open maps it and
+ * returns a pointer into the owner's memory (NULL on refusal), to be released with
+ * coli_cuda_pipe_ipc_close before the owner frees the buffer. coli_cuda_pipe_copy_async
+ * enqueues a device-to-device copy on `stream` (a cudaStream_t; NULL = the backend's stream);
+ * either side may be such a peer pointer. */
+int coli_cuda_pipe_ipc_export(int device, void *dev_ptr, void *handle64);
+void *coli_cuda_pipe_ipc_open(int device, const void *handle64);
+int coli_cuda_pipe_ipc_close(int device, void *peer_ptr);
+int coli_cuda_pipe_copy_async(int device, void *dst, const void *src, size_t bytes, void *stream);
 int coli_cuda_ep_plan_dev(int device, const float *x_dev, int m, int D, int K, const int *idx_dev,
                           const int *keff_dev, const int *dest_dev, const int *slot_dev, int E, int G,
                           int slots, int payload_bf16, int *counts_dev, int *entry_of_dev, void *send_dev,

@@ -4,8 +4,9 @@ one rank per GPU (tests/test_gpu_ep.py launches it when the box has two or more 
 Every rank builds the same synthetic layer (configuration-5-like shape, reduced), runs its
 share of the rows through the expert-parallel layer over NCCL with a histogram-balanced
 placement, then runs the same rows through a single-rank layer that holds every expert, and
-requires the two results to be bit-identical (the combine adds in each row's selection order,
-so neither the number of ranks nor the placement may change a bit)."""
+requires the results to be bit-identical (the combine adds in each row's selection order,
+so neither the number of ranks, nor the placement, nor the way the rows travel — NCCL's
+all-to-all or copies over peer memory — may change a bit)."""
 import os
 import sys
 
@@ -48,7 +49,7 @@ def main():
     load = np.bincount(np.concatenate([idx[s, :keff[s]] for s in range(M)]), minlength=cfg["E"])
     outs = {}
     for name, emap in (("balanced", ExpertMap.balanced(load, world)), ("blocks", ExpertMap(cfg["E"], world)),
-                       ("single", None)):
+                       ("balanced_peer", ExpertMap.balanced(load, world)), ("single", None)):
         if emap is None:
             em1 = ExpertMap(cfg["E"], 1)
             lay = CudaEpLayer(be, local, cfg, em1, 0, g, u, d, sh, bias, 2.5, max_rows=m, payload="bf16")
@@ -57,14 +58,18 @@ def main():
         else:
             loc = emap.local[rank]
             lay = CudaEpLayer(be, local, cfg, emap, rank, [g[e] for e in loc], [u[e] for e in loc], [d[e] for e in loc],
-                              sh, bias, 2.5, max_rows=m, payload="bf16")
+                              sh, bias, 2.5, max_rows=m, payload="bf16",
+                              exchange="peer" if name.endswith("_peer") else "nccl")
             out = lay(xr, lr)
+            if name.endswith("_peer"):
+                out = lay(xr, lr)       # a second call finds the buffers used: same bits again
         torch.cuda.synchronize()
         lay.check_exact()
         outs[name] = out.cpu().numpy()
+        lay.close()
     assert be.kernel_status(local) == 0
-    same = (np.array_equal(outs["balanced"].view(np.uint32), outs["single"].view(np.uint32)) and
-            np.array_equal(outs["blocks"].view(np.uint32), outs["single"].view(np.uint32)))
+    same = all(np.array_equal(outs[k].view(np.uint32), outs["single"].view(np.uint32))
+               for k in ("balanced", "blocks", "balanced_peer"))
     flag = torch.tensor([0 if same else 1], device=dev)
     dist.all_reduce(flag)
     if rank == 0:

@@ -264,6 +264,8 @@ class CudaEpLayer:
         self.counts_all = torch.zeros((G, G * self.emap.slots), dtype=torch.int32, device=self.dev)
         self.counts_all_pin = torch.zeros((G, G * self.emap.slots), dtype=torch.int32).pin_memory()
         self.e_comb = None
+        # one stream per peer, so that the blocks for different ranks travel side by side
+        self.pstreams = [torch.cuda.Stream(device=self.dev) for _ in range(G)]
         dist.barrier(group=self.group)
 
     def close(self):
@@ -385,9 +387,22 @@ class CudaEpLayer:
         be, C, me = self.be, self.C, self.rank
         bs, cs = self.bstream, self.cstream
         esz = 2 if self.bf16 else 4
-        csh = C.c_void_p(cs.cuda_stream)
-        copy = lambda dst, src, nbytes: self._check(be.pipe_copy_async(self.device, C.c_void_p(dst), C.c_void_p(src),
-                                                                       C.c_size_t(nbytes), csh), "coli_cuda_pipe_copy_async")
+        def copy(peer, dst, src, nbytes):
+            self._check(be.pipe_copy_async(self.device, C.c_void_p(dst), C.c_void_p(src), C.c_size_t(nbytes),
+                                           C.c_void_p(self.pstreams[peer].cuda_stream)), "coli_cuda_pipe_copy_async")
+
+        def fan_out(jobs):
+            """jobs: (peer, dst, src, bytes). Each runs on its peer's stream after what cs holds so
+            far; cs continues when all have finished."""
+            if not jobs:
+                return
+            fork = torch.cuda.Event(); fork.record(cs)
+            for peer, dst, src, nbytes in jobs:
+                ps = self.pstreams[peer]
+                ps.wait_event(fork)
+                copy(peer, dst, src, nbytes)
+                done = torch.cuda.Event(); done.record(ps)
+                cs.wait_event(done)
         # 3. every rank's table of counts, and the one read-back of the layer
         with torch.cuda.stream(cs):
             cs.wait_event(e_pack)
@@ -407,11 +422,9 @@ class CudaEpLayer:
         recv_off = np.concatenate(([0], np.cumsum(mat[:, me])))                # sources' blocks in my receive buffer
         # 4. rows out: block (me -> d) goes behind the blocks of the ranks below me in d's buffer
         with torch.cuda.stream(cs):
-            for d in range(G):
-                n = int(mat[me, d])
-                if n:
-                    at = int(mat[:me, d].sum())
-                    copy(self.peer_recv[d] + at * D * esz, self.send.data_ptr() + int(send_off[d]) * D * esz, n * D * esz)
+            fan_out([(d, self.peer_recv[d] + int(mat[:me, d].sum()) * D * esz,
+                      self.send.data_ptr() + int(send_off[d]) * D * esz, int(mat[me, d]) * D * esz)
+                     for d in range(G) if mat[me, d]])
             dist.all_reduce(self.flag, group=self.group)       # every rank's copies were enqueued before it joined
             e_recv = ev(); e_recv.record(cs)
         # 5. local experts on the received rows, results in receive order
@@ -427,11 +440,9 @@ class CudaEpLayer:
         # 6. results back: block (s -> me) returns to where s keeps its block for me
         with torch.cuda.stream(cs):
             cs.wait_event(e_gemm)
-            for s in range(G):
-                n = int(mat[s, me])
-                if n:
-                    at = int(mat[s, :me].sum())
-                    copy(self.peer_got[s] + at * D * 4, y.data_ptr() + int(recv_off[s]) * D * 4, n * D * 4)
+            fan_out([(s, self.peer_got[s] + int(mat[s, :me].sum()) * D * 4,
+                      y.data_ptr() + int(recv_off[s]) * D * 4, int(mat[s, me]) * D * 4)
+                     for s in range(G) if mat[s, me]])
             dist.all_reduce(self.flag, group=self.group)
             e_back = ev(); e_back.record(cs)
         # 7. combine
@@ -444,6 +455,8 @@ class CudaEpLayer:
         self.e_comb = torch.cuda.Event(); self.e_comb.record(bs)
         for t in (y, x, logits):
             t.record_stream(bs); t.record_stream(cs)
+        for ps in self.pstreams:
+            y.record_stream(ps)
         if self.timing is not None:
             marks["t1"] = ev(); marks["t1"].record(bs)
             marks.update(pack=e_pack, recv=e_recv, gemm=e_gemm, back=e_back)

@@ -5,8 +5,9 @@
 // Why one kernel: at decode sizes a layer moves only tens of MB (28 MB for the OLMoE
 // shape at M=1, about 4 us of HBM time), so every kernel boundary, grid-wide barrier
 // and round trip through global memory costs as much as the work itself. The layer
-// therefore has exactly one grid-wide exchange (the SwiGLU activations, which every
-// output row of the down projection needs) and one last-arriver hand-over at the end:
+// therefore has one grid-wide exchange (the SwiGLU activations, which every output row of
+// the down projection needs), and a second one before the combine only when a CTA cannot
+// hold every pass row's activations:
 //
 //  * Routing is computed redundantly by every CTA (top-8 of a few hundred scores is a
 //    microsecond of work and saves a barrier plus a round trip through global memory).
@@ -23,9 +24,11 @@
 //    stop for it: as soon as a warp has consumed its last gate/up block it refills its ring
 //    of bulk copies with the down phase's first blocks (weights do not depend on the
 //    activations), so those are in shared memory when the barrier opens.
-//  * The weighted combine needs no barrier: the group that completes the last pass of a
-//    32-column slice of the output (a ticket per slice) adds the slice's terms, for
-//    every token in that token's selection order, shared expert last, and resets the ticket.
+//  * In that general form the pass rows Y meet at a second grid barrier, after which all
+//    threads of the grid add each output element's terms in the token's selection order,
+//    shared expert last. (A last-arriver ticket per output slice was measured instead: with
+//    4 to 16 short units per warp group, a fence and an atomic per unit cost more than the
+//    barrier.)
 //  * When the call is small enough that every pass row's activations fit one CTA's shared
 //    memory (the OLMoE shape at M=1), the down phase is cut the other way: a CTA owns 16
 //    output rows over ALL passes (half-chunks of the weight stream). Its warps run through
@@ -47,7 +50,7 @@
 // instructions, not their issue (the general routing for rows with NaN candidates is out
 // of line; divisions by launch constants are multiply-shifts prepared by the host).
 //
-// Waits: the grid barrier (one counter to which every launch adds exactly 256, polled for
+// Waits: the grid barrier (one counter to which every barrier adds exactly 256, polled for
 // the next multiple: no per-launch value from the host, so a launch can be replayed from
 // a CUDA graph) and every mbarrier wait are bounded; on expiry a CTA records a status
 // code, keeps walking its loops without waiting (so that no CTA-level barrier is
@@ -90,7 +93,7 @@ struct DecodeArgs {
     const __half *xq; const float *xs;   // x already split by k_prep_rows (only read when act_smem == 0)
     __half *hq; float *hs;               // SwiGLU activations: [npos][I/128][256] halfs, [npos][I/32] inverse scales
     float *Y;                            // down-projection results per pass row: [npos][D]
-    unsigned int *sync;                  // [0] barrier arrivals (256 per launch), [16 + tile] tickets
+    unsigned int *sync;                  // [0] barrier arrivals (256 per barrier)
     const unsigned long long *exp_tab;   // global copy of the 2^(i/32) table
     int *status;
     int M, act_smem;
@@ -159,10 +162,11 @@ __device__ __forceinline__ void bar_sync_named(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
-// Grid barrier on one counter. Every launch adds exactly 256 to it (CTA 0 adds what the
+// Grid barrier on one counter. Every barrier adds exactly 256 to it (CTA 0 adds what the
 // others leave), so between launches it is a multiple of 256, also across the wrap of the
-// 32-bit word. The target is the next multiple above the value thread 0 read at any time
-// before arriving (grid_barrier_target: off the critical path); arriving is a reduction without
+// 32-bit word. The first barrier's target is the next multiple above the value warp 0 read at
+// any time before arriving (grid_barrier_target: off the critical path), a second barrier's is
+// 256 more; arriving is a reduction without
 // a return value, and everybody polls the counter itself for the target. All threads of the
 // CTA call grid_barrier; on timeout (about 20 ms) it sets *s_failed. Needs gridDim.x <= 256.
 __device__ __forceinline__ unsigned int grid_barrier_target(const unsigned int *sync) {
@@ -1185,9 +1189,8 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
             if (u + 1 < ph2.u1) __syncthreads();      // the buffers are reused by the next slice
         }
     } else {
-    // ---- down -> Y, and the weighted combine by whoever completes a slice -----------------
+    // ---- down -> Y; then one more grid barrier and the weighted combine -------------------
         const int nrot = ph2.wpk >> 2;
-        unsigned int *tickets = a.sync + 16;
         int ucount = 0;
         for (int u = ph2.first_u; u < ph2.u1; u += ph2.ng, ucount++) {
             const int pass = dec_div(u, a.mg_nt2), tile = u - pass * nt2;
@@ -1239,27 +1242,31 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 1) k_moe_decode(DecodeArgs a) 
                 const int o = tile * TILE_ROWS + lane;
                 if (MODE == SC_ROW) y *= (ps.e >= 0 ? a.tab.down_rs[ps.e] : a.tab.sh_down_rs)[o];
                 if (mrow < nrows) a.Y[(size_t)(ps.pos0 + mrow) * D + o] = y;
-                // ticket of this 32-column slice of the output: 4 arrivals per pass
-                __threadfence();
-                __syncwarp();
-                int last = 0;
-                if (lane == 0) last = atomicAdd(&tickets[tile], 1u) == (unsigned int)(4 * npass - 1);
-                last = __shfl_sync(0xffffffffu, last, 0);
-                if (last) {
-                    __threadfence();
-                    const bool has_shared = a.tab.sh_gate_pk != nullptr;
-                    for (int s = 0; s < M; s++) {
-                        const int ke = sh->keff[s];
-                        float acc = 0.f;
-#pragma unroll 4
-                        for (int kk = 0; kk < ke; kk++)
-                            acc = fmaf(sh->w[s * K + kk], __ldcg(a.Y + (size_t)sh->pos_of[s * K + kk] * D + o), acc);
-                        if (has_shared) acc += __ldcg(a.Y + (size_t)(sh->shared_pos0 + s) * D + o);
-                        a.out[(size_t)s * D + o] = acc;
-                    }
-                    if (lane == 0) tickets[tile] = 0u;       // ready for the next launch
-                }
             }
+        }
+        // Every pass row of Y is complete once all CTAs are here (a group runs through 4 to 16 short
+        // units in this form: a fence and a ticket per unit cost more than this one barrier).
+        grid_barrier(a.sync, &sh->failed, bar_target + 256u);
+        __syncthreads();
+        const bool has_shared = a.tab.sh_gate_pk != nullptr;
+        const int dq = D >> 2;
+#pragma unroll 1
+        for (int i = blockIdx.x * blockDim.x + tid; i < M * dq; i += gridDim.x * blockDim.x) {
+            const int s = i / dq, d4 = i - s * dq;
+            const int ke = sh->keff[s];
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
+            for (int kk = 0; kk < ke; kk++) {
+                const float wgt = sh->w[s * K + kk];
+                const float4 y = __ldcg(reinterpret_cast<const float4 *>(a.Y + (size_t)sh->pos_of[s * K + kk] * D) + d4);
+                acc.x = fmaf(wgt, y.x, acc.x); acc.y = fmaf(wgt, y.y, acc.y);
+                acc.z = fmaf(wgt, y.z, acc.z); acc.w = fmaf(wgt, y.w, acc.w);
+            }
+            if (has_shared) {
+                const float4 y = __ldcg(reinterpret_cast<const float4 *>(a.Y + (size_t)(sh->shared_pos0 + s) * D) + d4);
+                acc.x += y.x; acc.y += y.y; acc.z += y.z; acc.w += y.w;
+            }
+            reinterpret_cast<float4 *>(a.out + (size_t)s * D)[d4] = acc;
         }
     }
     DEC_PROBE(a, 9);

@@ -241,7 +241,8 @@ static int layer_run(ColiCudaMoeLayer *L, DeviceCtx *c, float *out_dev, const fl
     }
     if (!route_only && g_fused_decode && M <= DEC_MAX_M && r.E <= DEC_MAX_E && r.K <= DEC_MAX_K &&
         L->mode_gu == L->mode_d && r.I <= DEC_MAX_I && r.D / TILE_ROWS <= DEC_MAX_TILES &&
-        M * r.K + 2 <= DEC_MAX_PASS && c->sms >= DEC_MAX_PASS && c->sms <= 256) {
+        M * r.K + 2 <= DEC_MAX_PASS && c->sms >= DEC_MAX_PASS && c->sms <= 256 &&
+        (reinterpret_cast<uintptr_t>(out_dev) & 15) == 0) {
         // one kernel for the whole layer (moe_decode.cuh)
         const size_t act_cap = (size_t)dec_act_bytes(L->mode_gu);
         const int act_smem = (size_t)M * nkb1 * 516 <= act_cap;

@@ -318,7 +318,8 @@ int coli_cuda_last_timing(int device, float *kernel_ms, int *launches);
 void coli_cuda_set_timing(int enabled);
 
 /* Decode-sized layer calls (M <= 8) normally run as one fused kernel of one CTA per SM
- * with one grid barrier inside:
+ * with one grid barrier inside (two when the call's SwiGLU activations do not fit one CTA's
+ * shared memory, from about three rows at the OLMoE shape):
  *   3 (default)  plain launch with programmatic stream serialisation: the next layer
  *                call's CTAs are scheduled as this call's CTAs exit and wait (before
  *                touching global memory) until it has completed, which hides most of
@@ -328,7 +329,7 @@ void coli_cuda_set_timing(int enabled);
  *   0            the multi-kernel path instead (A/B testing)
  * The grid-barrier wait is bounded; a launch whose CTAs were not co-resident would end
  * with the call returning 0, not with a hang. The barrier keeps its state on the device
- * (arrival count + generation), so a captured launch can be replayed from a CUDA graph. */
+ * (one arrival counter), so a captured launch can be replayed from a CUDA graph. */
 void coli_cuda_set_fused_decode(int enabled);
 
 /* Expert groups and layer calls with many rows per expert run on the tcgen05

@@ -192,6 +192,8 @@ extern "C" int coli_cuda_init(const int *devices, int count) {
         }
         *c->status = 0;
         setup_mode<SC_ROW>(); setup_mode<SC_H16>(); setup_mode<SC_F32>(); setup_mode<SC_MX>();
+        set_smem(k_router_logits, ROUTER_TILE_SMEM);
+        set_smem(k_dense_gemv<0>, DENSE_GEMV_SMEM); set_smem(k_dense_gemv<1>, DENSE_GEMV_SMEM); set_smem(k_dense_gemv<8>, DENSE_GEMV_SMEM);
         set_smem(k_moe_decode<SC_ROW>, decode_smem_bytes(SC_ROW)); set_smem(k_moe_decode<SC_H16>, decode_smem_bytes(SC_H16));
         set_smem(k_moe_decode<SC_F32>, decode_smem_bytes(SC_F32)); set_smem(k_moe_decode<SC_MX>, decode_smem_bytes(SC_MX));
         set_smem(k_expert_gemm_tc<SC_ROW>, tc_smem_bytes<SC_ROW>()); set_smem(k_expert_gemm_tc<SC_H16>, tc_smem_bytes<SC_H16>());
@@ -710,9 +712,9 @@ static int linear_raw(DeviceCtx *c, const ColiCudaTensor *t, float *y_dev, const
     if (dense && (reinterpret_cast<uintptr_t>(x_dev) & 15) == 0 && (reinterpret_cast<uintptr_t>(t->raw_w) & 15) == 0) {
         dim3 grid((unsigned)((t->O + 31) / 32), (unsigned)((S + 7) / 8));
         const float *sc = static_cast<const float *>(t->raw_s);
-        if (t->fmt == 0) k_dense_gemv<0><<<grid, 256, 0, c->stream>>>(y_dev, x_dev, t->raw_w, sc, nullptr, S, t->I, t->O);
-        else if (t->fmt == 1) k_dense_gemv<1><<<grid, 256, 0, c->stream>>>(y_dev, x_dev, t->raw_w, sc, nullptr, S, t->I, t->O);
-        else k_dense_gemv<8><<<grid, 256, 0, c->stream>>>(y_dev, x_dev, t->raw_w, sc, c->e4m3_lut_dev, S, t->I, t->O);
+        if (t->fmt == 0) k_dense_gemv<0><<<grid, 256, DENSE_GEMV_SMEM, c->stream>>>(y_dev, x_dev, t->raw_w, sc, nullptr, S, t->I, t->O);
+        else if (t->fmt == 1) k_dense_gemv<1><<<grid, 256, DENSE_GEMV_SMEM, c->stream>>>(y_dev, x_dev, t->raw_w, sc, nullptr, S, t->I, t->O);
+        else k_dense_gemv<8><<<grid, 256, DENSE_GEMV_SMEM, c->stream>>>(y_dev, x_dev, t->raw_w, sc, c->e4m3_lut_dev, S, t->I, t->O);
         c->last_launches++;
         return cuda_ok(cudaGetLastError(), "matmul launch");
     }
@@ -1305,7 +1307,7 @@ extern "C" int coli_cuda_pipe_router(int device, const float *x_dev, const void 
     float *w = (float *)(idx + Ksel);
     int *keff = (int *)(w + Ksel);
     RouteRule rule{D, 0, E, Ksel, 1, norm_topk, routed_scale, topp};
-    k_router_logits<<<(E + 127) / 128, 128, 0, c->stream>>>(logits, x_dev, (const float *)rw_dev, 1, D, E);
+    k_router_logits<<<(E + 63) / 64, 64, ROUTER_TILE_SMEM, c->stream>>>(logits, x_dev, (const float *)rw_dev, 1, D, E);
     size_t sm = (size_t)(2 * E + 2 * ROUTE_MAX_K) * sizeof(float);
     k_route_topk<<<1, 32, sm, c->stream>>>(logits, (const float *)rb_dev, rule, 1, idx, w, keff);
     if (!cuda_ok(cudaGetLastError(), "pipe router launch")) return 0;

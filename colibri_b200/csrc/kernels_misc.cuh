@@ -306,18 +306,23 @@ __global__ void k_generic_matmul(float *__restrict__ y, const float *__restrict_
 // table in `lut`). Bound by HBM: every weight byte is read once with 128-bit loads.
 //   y[s*O + o] = sum_i x[s,i] * w[o,i]
 // One warp owns 4 output rows and up to 8 rows of x (blockIdx.y selects the group of 8);
-// the CTA stages 1024 columns of those x rows in shared memory per round, a lane takes
-// 16-byte pieces of its 4 weight rows and multiplies them with the staged columns, so x
+// the CTA stages 1024 columns of those x rows in shared memory per round (two buffers, filled
+// by asynchronous copies while the previous round is multiplied: one CTA barrier per round), a
+// lane takes 16-byte pieces of its 4 weight rows, always one piece ahead of the one it
+// multiplies (also across rounds, so weight loads stay in flight while x is staged), so x
 // costs one shared-memory read per 4 output rows. Requires I % 16 == 0 (fmt 0: I % 4 == 0).
+// Dynamic shared memory: DENSE_GEMV_SMEM bytes.
 // ---------------------------------------------------------------------------
+#define DENSE_GEMV_CK 1024
+#define DENSE_GEMV_SMEM (2 * 8 * DENSE_GEMV_CK * 4)
 template <int FMT>
-__global__ void __launch_bounds__(256) k_dense_gemv(float *__restrict__ y, const float *__restrict__ x,
+__global__ void __launch_bounds__(256, FMT == 0 ? 3 : 2) k_dense_gemv(float *__restrict__ y, const float *__restrict__ x,
                                                     const void *__restrict__ w, const float *__restrict__ sc,
                                                     const float *__restrict__ lut, int S, int I, int O) {
     constexpr int VPL = FMT == 0 ? 4 : 16;          // values in one 16-byte piece
-    constexpr int CK = 1024;                        // columns of x staged per round
+    constexpr int CK = DENSE_GEMV_CK;               // columns of x staged per round
     constexpr int PIECES = CK / (32 * VPL);
-    __shared__ __align__(16) float xs[8 * CK];
+    extern __shared__ __align__(16) float xs[];     // [2][8][CK]
     __shared__ float s_lut[256];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int s0 = blockIdx.y * 8, ns = min(8, S - s0);
@@ -331,67 +336,85 @@ __global__ void __launch_bounds__(256) k_dense_gemv(float *__restrict__ y, const
     const size_t rowb = FMT == 0 ? (size_t)I * 4 : (size_t)I;       // bytes per weight row
     const uint8_t *wb = static_cast<const uint8_t *>(w);
     const int nblk = (I + 127) >> 7;
-    for (int c0 = 0; c0 < I; c0 += CK) {
-        __syncthreads();
+    // rows of x this CTA does not have read as zeros, in both buffers, for good
+    for (int idx = tid; idx < 2 * 8 * CK / 4; idx += 256) {
+        const int q = (idx / (CK / 4)) & 7;
+        if (q >= ns) reinterpret_cast<float4 *>(xs)[idx] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    auto stage = [&](int c0, int buf) {
         for (int idx = tid; idx < 8 * CK / 4; idx += 256) {
             const int q = idx / (CK / 4), j = idx - q * (CK / 4), col = c0 + j * 4;
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (q < ns && col < I) v = *reinterpret_cast<const float4 *>(x + (size_t)(s0 + q) * I + col);
-            reinterpret_cast<float4 *>(xs)[idx] = v;
+            if (q < ns && col < I) {
+                const uint32_t dst = (uint32_t)__cvta_generic_to_shared(xs + (size_t)buf * 8 * CK) + idx * 16;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(x + (size_t)(s0 + q) * I + col) : "memory");
+            }
         }
-        __syncthreads();
+    };
+    auto load_piece = [&](int col, uint4 (&raw)[4]) {
+#pragma unroll
+        for (int r = 0; r < 4; r++)
+            raw[r] = (col < I && o0 + r < O)
+                         ? __ldcs(reinterpret_cast<const uint4 *>(wb + (size_t)(o0 + r) * rowb + (size_t)col * (FMT == 0 ? 4 : 1)))
+                         : make_uint4(0, 0, 0, 0);
+    };
+    uint4 cur[4], nxt[4];
+    load_piece(lane * VPL, cur);
+    stage(0, 0);
+    int round = 0;
+    for (int c0 = 0; c0 < I; c0 += CK, round++) {
+        asm volatile("cp.async.wait_all;" ::: "memory");
+        __syncthreads();            // this round's x is in place; nobody reads the other buffer any more
+        if (c0 + CK < I) stage(c0 + CK, (round + 1) & 1);
+        const float *xb = xs + (size_t)(round & 1) * 8 * CK;
 #pragma unroll
         for (int p = 0; p < PIECES; p++) {
             const int col = c0 + (p * 32 + lane) * VPL;
-            if (col >= I) continue;
-            if (FMT == 0) {
-                float4 wv[4];
+            load_piece(col + 32 * VPL, nxt);        // the next piece, possibly the next round's first
+            if (col < I) {
+                if (FMT == 0) {
 #pragma unroll
-                for (int r = 0; r < 4; r++)
-                    wv[r] = o0 + r < O ? __ldcs(reinterpret_cast<const float4 *>(wb + (size_t)(o0 + r) * rowb) + (col >> 2))
-                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int q = 0; q < 8; q++) {
+                        const float4 xv = reinterpret_cast<const float4 *>(xb)[q * (CK / 4) + ((col - c0) >> 2)];
 #pragma unroll
-                for (int q = 0; q < 8; q++) {
-                    const float4 xv = reinterpret_cast<const float4 *>(xs)[q * (CK / 4) + ((col - c0) >> 2)];
-#pragma unroll
-                    for (int r = 0; r < 4; r++)
-                        acc[r][q] = fmaf(wv[r].w, xv.w, fmaf(wv[r].z, xv.z, fmaf(wv[r].y, xv.y, fmaf(wv[r].x, xv.x, acc[r][q]))));
-                }
-            } else {
-                float wd[4][16];
-#pragma unroll
-                for (int r = 0; r < 4; r++) {
-                    uint4 raw = make_uint4(0, 0, 0, 0);
-                    float bs = 0.f;
-                    if (o0 + r < O) {
-                        raw = __ldcs(reinterpret_cast<const uint4 *>(wb + (size_t)(o0 + r) * rowb + col));
-                        bs = FMT == 8 ? sc[(size_t)((o0 + r) >> 7) * nblk + (col >> 7)] : 1.f;
+                        for (int r = 0; r < 4; r++) {
+                            const float4 wv = make_float4(__uint_as_float(cur[r].x), __uint_as_float(cur[r].y),
+                                                          __uint_as_float(cur[r].z), __uint_as_float(cur[r].w));
+                            acc[r][q] = fmaf(wv.w, xv.w, fmaf(wv.z, xv.z, fmaf(wv.y, xv.y, fmaf(wv.x, xv.x, acc[r][q]))));
+                        }
                     }
-                    const uint32_t wds[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-                    for (int b = 0; b < 16; b++) {
-                        const uint32_t byte = (wds[b >> 2] >> (8 * (b & 3))) & 0xFFu;
-                        wd[r][b] = FMT == 8 ? s_lut[byte] * bs : (float)(int)(int8_t)byte;
-                    }
-                }
-#pragma unroll
-                for (int q = 0; q < 8; q++) {
-                    float4 xv[4];
-#pragma unroll
-                    for (int k = 0; k < 4; k++)
-                        xv[k] = reinterpret_cast<const float4 *>(xs)[q * (CK / 4) + ((col - c0) >> 2) + k];
+                } else {
+                    float wd[4][16];
 #pragma unroll
                     for (int r = 0; r < 4; r++) {
-                        float a = acc[r][q];
+                        const float bs = (FMT == 8 && o0 + r < O) ? sc[(size_t)((o0 + r) >> 7) * nblk + (col >> 7)] : 1.f;
+                        const uint32_t wds[4] = {cur[r].x, cur[r].y, cur[r].z, cur[r].w};
 #pragma unroll
-                        for (int k = 0; k < 4; k++) {
-                            a = fmaf(wd[r][4 * k + 0], xv[k].x, a); a = fmaf(wd[r][4 * k + 1], xv[k].y, a);
-                            a = fmaf(wd[r][4 * k + 2], xv[k].z, a); a = fmaf(wd[r][4 * k + 3], xv[k].w, a);
+                        for (int b = 0; b < 16; b++) {
+                            const uint32_t byte = (wds[b >> 2] >> (8 * (b & 3))) & 0xFFu;
+                            wd[r][b] = FMT == 8 ? s_lut[byte] * bs : (float)(int)(int8_t)byte;
                         }
-                        acc[r][q] = a;
+                    }
+#pragma unroll
+                    for (int q = 0; q < 8; q++) {
+                        float4 xv[4];
+#pragma unroll
+                        for (int k = 0; k < 4; k++)
+                            xv[k] = reinterpret_cast<const float4 *>(xb)[q * (CK / 4) + ((col - c0) >> 2) + k];
+#pragma unroll
+                        for (int r = 0; r < 4; r++) {
+                            float a = acc[r][q];
+#pragma unroll
+                            for (int k = 0; k < 4; k++) {
+                                a = fmaf(wd[r][4 * k + 0], xv[k].x, a); a = fmaf(wd[r][4 * k + 1], xv[k].y, a);
+                                a = fmaf(wd[r][4 * k + 2], xv[k].z, a); a = fmaf(wd[r][4 * k + 3], xv[k].w, a);
+                            }
+                            acc[r][q] = a;
+                        }
                     }
                 }
             }
+#pragma unroll
+            for (int r = 0; r < 4; r++) cur[r] = nxt[r];
         }
     }
 #pragma unroll

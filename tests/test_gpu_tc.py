@@ -137,6 +137,43 @@ def test_tc_layer_matches_oracle_and_streaming(be, oracle, name, M):
     free_layer(be, h)
 
 
+def test_tc_layer_after_update_to_unqualified_scales(be, oracle):
+    """coli_cuda_tensor_update can give a tensor scales the tensor-core kernel cannot carry exactly
+    (MXFP4 exponents 40 binades apart). The layer looks at its tensors again on every call: the
+    next prefill-sized call, with the tensor-core path forced, must still match the oracle."""
+    from colibri_b200 import workloads as W
+    from colibri_b200.backend import MoeLayer
+    from tests.util import upload_layer, free_layer, host_layer
+    cfg = W.CONFIGS["c3_small"]
+    M = 200
+    L = W.HostLayerWeights(cfg, 78)
+    h = upload_layer(be, L)
+    g, u, d, sh = h
+    lay = MoeLayer(be, cfg["D"], cfg["I"], cfg["E"], cfg["K"], g, u, d, cfg["gating"], cfg["norm_topk"],
+                   2.5, 0.0, router_bias=L.router_bias, shared=sh, max_rows=M)
+    x = W.activations(M, cfg["D"], 11)
+    lg = W.router_logits(M, cfg["E"], 12, zipf=1.1)
+    try:
+        be.set_tensor_core(2)
+        out0, _, _, _ = lay(x, lg)
+        want0 = oracle.moe_layer(host_layer(cfg, L, 2.5, 0.0, 1, False), x, lg)[0]
+        assert max_rel_err(out0, want0) <= 1e-3
+        t = L.gate[3]
+        t.s = t.s.copy()
+        t.s[0, 0] = 80
+        t.s[1, 0] = 121
+        assert be.tensor_update(g[3], t.w.ctypes.data, t.s.ctypes.data)
+        out1, _, _, _ = lay(x, lg)
+    finally:
+        be.set_tensor_core(1)
+    want1 = oracle.moe_layer(host_layer(cfg, L, 2.5, 0.0, 1, False), x, lg)[0]
+    assert max_rel_err(out1, want1) <= 1e-3
+    assert not np.array_equal(out0, out1)          # the update is visible in the result
+    assert be.kernel_status(0) == 0
+    lay.free()
+    free_layer(be, h)
+
+
 def test_tc_many_tasks_per_cta(be, oracle):
     # more tasks than SMs: every CTA runs several tasks back to back, so the rings, the two
     # accumulator halves and their barriers wrap around

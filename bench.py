@@ -366,9 +366,10 @@ def run_ep_block(args, be, world, rank, local, L, M, n_experts=None, steps=None,
     result dictionary on rank 0 (None elsewhere)."""
     import torch
     import torch.distributed as dist
-    from colibri_b200.ep import CudaEpLayer, ExpertMap
+    from colibri_b200.ep import CudaEpLayer, ExpertMap, PeerExchangeUnavailable
 
     dev = torch.device("cuda", local)
+    exchange, peer_note = ("peer" if world > 1 else "nccl"), None
     cfg = dict(W.CONFIGS["c5"])
     if n_experts:
         cfg["E"] = n_experts
@@ -419,9 +420,14 @@ def run_ep_block(args, be, world, rank, local, L, M, n_experts=None, steps=None,
         if not all(hs[0] + hs[1] + hs[2] + sh):
             raise RuntimeError("tensor upload failed")
         handles += hs[0] + hs[1] + hs[2] + sh
-        layers.append(CudaEpLayer(be, local, cfg, em, rank, hs[0], hs[1], hs[2], tuple(sh),
-                                  torch.from_numpy(biases[li]).to(dev), ROUTED_SCALE, max_rows=m, payload="bf16",
-                                  exchange="peer" if world > 1 else "nccl"))
+        mk = lambda exch: CudaEpLayer(be, local, cfg, em, rank, hs[0], hs[1], hs[2], tuple(sh),
+                                      torch.from_numpy(biases[li]).to(dev), ROUTED_SCALE, max_rows=m, payload="bf16",
+                                      exchange=exch)
+        try:
+            layers.append(mk(exchange))
+        except PeerExchangeUnavailable as ex:       # raised on every rank alike
+            exchange, peer_note = "nccl", str(ex)
+            layers.append(mk("nccl"))
     xs = [torch.from_numpy(W.activations(M, D, 500 + li)[rank * m:(rank + 1) * m].copy()).to(dev) for li in range(L)]
     lgs = [torch.from_numpy(l[rank * m:(rank + 1) * m].copy()).to(dev) for l in lg_all]
     torch.cuda.synchronize()
@@ -477,7 +483,7 @@ def run_ep_block(args, be, world, rank, local, L, M, n_experts=None, steps=None,
 
     ms, k_ms_v, launches_step, pack, a2a, gemm, comb, rows_recv = timed()
     nccl_contrast = None
-    if world > 1:
+    if world > 1 and exchange == "peer":
         # the same layers with NCCL's all-to-all as the exchange, for contrast
         for lay in layers:
             lay.exchange = "nccl"
@@ -528,9 +534,9 @@ def run_ep_block(args, be, world, rank, local, L, M, n_experts=None, steps=None,
         "workload": f"c5_ep: expert-parallel MoE layer (D={D}, I={I}, E={E}+1 shared, top-{K} sigmoid, MXFP4), "
                     f"M={M} rows in total, {L} layers per step, Zipf(1.1) logit bias, experts placed on {world} rank(s) "
                     f"{'by routing histogram' if balanced else 'in equal blocks'}, dispatch (bf16 rows) and combine "
-                    f"(f32 rows) {'as device-to-device copies over peer memory (NVLink), NCCL for the counts and the barriers' if world > 1 else 'local'}",
-        "exchange": "peer copies" if world > 1 else "none",
-        "nccl_all_to_all_contrast": None if world == 1 else {
+                    f"(f32 rows) {'local' if world == 1 else 'as device-to-device copies over peer memory (NVLink), NCCL for the counts and the barriers' if exchange == 'peer' else 'as NCCL all-to-all'}",
+        "exchange": "none" if world == 1 else "peer copies" if exchange == "peer" else f"nccl all-to-all (peer memory unavailable: {peer_note})",
+        "nccl_all_to_all_contrast": None if (world == 1 or exchange != "peer") else {
             "ms_per_step": float(t[8]) / steps,
             "phase_ms": {"route_plan_pack": float(t[9]), "a2a_dispatch_and_combine": float(t[10]),
                          "expert_gemm": float(t[11]), "combine": float(t[12])}},

@@ -1307,7 +1307,7 @@ extern "C" int coli_cuda_pipe_router(int device, const float *x_dev, const void 
     float *w = (float *)(idx + Ksel);
     int *keff = (int *)(w + Ksel);
     RouteRule rule{D, 0, E, Ksel, 1, norm_topk, routed_scale, topp};
-    k_router_logits<<<(E + 63) / 64, 64, ROUTER_TILE_SMEM, c->stream>>>(logits, x_dev, (const float *)rw_dev, 1, D, E);
+    k_router_logits<<<(E + 63) / 64, ROUTER_THREADS, ROUTER_TILE_SMEM, c->stream>>>(logits, x_dev, (const float *)rw_dev, 1, D, E);
     size_t sm = (size_t)(2 * E + 2 * ROUTE_MAX_K) * sizeof(float);
     k_route_topk<<<1, 32, sm, c->stream>>>(logits, (const float *)rb_dev, rule, 1, idx, w, keff);
     if (!cuda_ok(cudaGetLastError(), "pipe router launch")) return 0;

@@ -235,7 +235,7 @@ static int layer_run(ColiCudaMoeLayer *L, DeviceCtx *c, float *out_dev, const fl
     if (!lg) {
         if (!L->router_w) return 0;
         int n = M * r.E;
-        k_router_logits<<<(n + 63) / 64, 64, ROUTER_TILE_SMEM, c->stream>>>((float *)L->logits.p, x_dev, L->router_w, M, r.D, r.E);
+        k_router_logits<<<(n + 63) / 64, ROUTER_THREADS, ROUTER_TILE_SMEM, c->stream>>>((float *)L->logits.p, x_dev, L->router_w, M, r.D, r.E);
         c->last_launches++;
         lg = (const float *)L->logits.p;
     }

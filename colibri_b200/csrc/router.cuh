@@ -33,16 +33,18 @@ __device__ __forceinline__ float expf_host_exact(float x) { return coli_expf_exa
 // the copies run ROUTER_STAGES - 1 tiles ahead of the arithmetic, which hides the memory
 // latency behind the chain (one tile ahead left the kernel waiting for memory: 300 us for
 // 8 x 256 outputs of 7168 terms).
-// Launch: 64 threads, ROUTER_TILE_SMEM bytes of dynamic shared memory.
+// The CTA has ROUTER_THREADS threads: all of them issue copies, the first 64 own the outputs.
+// Launch: ROUTER_THREADS threads, ROUTER_TILE_SMEM bytes of dynamic shared memory.
+#define ROUTER_THREADS 256
 #define ROUTER_TILE 64
 #define ROUTER_LD 68
 #define ROUTER_STAGES 6
 #define ROUTER_TILE_SMEM (ROUTER_STAGES * 2 * 64 * ROUTER_LD * 4)
-__global__ void __launch_bounds__(64) k_router_logits(float *__restrict__ logits, const float *__restrict__ x,
+__global__ void __launch_bounds__(ROUTER_THREADS) k_router_logits(float *__restrict__ logits, const float *__restrict__ x,
                                                       const float *__restrict__ W, int M, int D, int E) {
     extern __shared__ __align__(16) float rt[];         // [stage][w | x][64][68]
     __shared__ const float *s_wrow[64], *s_xrow[64];
-    constexpr int LD = ROUTER_LD, NS = ROUTER_STAGES;
+    constexpr int LD = ROUTER_LD, NS = ROUTER_STAGES, NW = ROUTER_THREADS / 32;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int i0 = blockIdx.x * 64, n = M * E;
     const int nrow = min(64, n - i0);
@@ -64,7 +66,7 @@ __global__ void __launch_bounds__(64) k_router_logits(float *__restrict__ logits
             if (al16) {
                 // half a warp per row: 16 pieces of 16 bytes
                 const int j = (lane & 15) * 4;
-                for (int r = warp * 2 + (lane >> 4); r < nrow; r += 4) {
+                for (int r = warp * 2 + (lane >> 4); r < nrow; r += 2 * NW) {
                     if (j < width) {
                         const uint32_t dw = (uint32_t)__cvta_generic_to_shared(wt + r * LD + j);
                         asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dw), "l"(s_wrow[r] + c0 + j) : "memory");
@@ -75,7 +77,7 @@ __global__ void __launch_bounds__(64) k_router_logits(float *__restrict__ logits
                     }
                 }
             } else {
-                for (int r = warp; r < nrow; r += 2)
+                for (int r = warp; r < nrow; r += NW)
                     for (int j = lane; j < width; j += 32) {
                         const uint32_t dw = (uint32_t)__cvta_generic_to_shared(wt + r * LD + j);
                         asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dw), "l"(s_wrow[r] + c0 + j) : "memory");
@@ -98,8 +100,9 @@ __global__ void __launch_bounds__(64) k_router_logits(float *__restrict__ logits
         const float *wt = rt + (size_t)(t % NS) * 2 * 64 * LD + tid * LD;
         const float *xt = rt + (size_t)(t % NS) * 2 * 64 * LD + 64 * LD + (one_x ? 0 : tid) * LD;
         const int width = min(ROUTER_TILE, D - c0);
+        if (tid >= 64) continue;        // copy-only warps
         if (width == ROUTER_TILE) {
-#pragma unroll 4
+#pragma unroll 8
             for (int j = 0; j < ROUTER_TILE; j += 4) {
                 const float4 xv = *reinterpret_cast<const float4 *>(xt + j), wv = *reinterpret_cast<const float4 *>(wt + j);
                 a = __fadd_rn(a, __fmul_rn(xv.x, wv.x));

@@ -175,6 +175,11 @@ def ep_moe_layer(x: torch.Tensor, route, experts, shared, emap: ExpertMap, group
     return _combine_torch(got, plan.entry_of, w, keff, ys), (idx, w, keff)
 
 
+class PeerExchangeUnavailable(RuntimeError):
+    """Raised on EVERY rank when some rank could not export or map the peer buffers (the ranks
+    agree on it with a collective), so that a caller can build the layer with exchange="nccl"."""
+
+
 class CudaEpLayer:
     """One expert-parallel MoE layer on this rank's GPU through the backend's device-pointer
     entries. `gates/ups/downs` are the handles of this rank's experts in slot order.
@@ -238,28 +243,40 @@ class CudaEpLayer:
         self.got_bytes = max_rows * K * D * 4
         self.recv_buf = be.pipe_alloc(self.device, self.recv_bytes)
         self.got_buf = be.pipe_alloc(self.device, self.got_bytes)
-        if not self.recv_buf or not self.got_buf:
-            raise RuntimeError("expert-parallel peer buffers: allocation refused")
+        why = "" if self.recv_buf and self.got_buf else "peer buffers: allocation refused"
         mine = []
         for ptr in (self.recv_buf, self.got_buf):
             h = (C.c_ubyte * 64)()
-            self._check(be.pipe_ipc_export(self.device, ptr, h), "coli_cuda_pipe_ipc_export")
+            if not why and not be.pipe_ipc_export(self.device, ptr, h):
+                why = "coli_cuda_pipe_ipc_export refused"
             mine.append(bytes(h))
         every = [None] * G
-        dist.all_gather_object(every, mine, group=self.group)
-        self.peer_recv, self.peer_got = [], []
-        for r in range(G):
-            if r == self.rank:
-                self.peer_recv.append(self.recv_buf); self.peer_got.append(self.got_buf)
-                continue
-            ptrs = []
-            for hb in every[r]:
-                h = (C.c_ubyte * 64).from_buffer_copy(hb)
-                q = be.pipe_ipc_open(self.device, h)
-                if not q:
-                    raise RuntimeError(f"rank {self.rank}: cannot map rank {r}'s buffer (coli_cuda_pipe_ipc_open)")
-                ptrs.append(q)
-            self.peer_recv.append(ptrs[0]); self.peer_got.append(ptrs[1])
+        dist.all_gather_object(every, (mine, why), group=self.group)
+        self.peer_recv, self.peer_got = [None] * G, [None] * G
+        self.peer_recv[self.rank], self.peer_got[self.rank] = self.recv_buf, self.got_buf
+        if not any(w for _, w in every):
+            for r in range(G):
+                if r == self.rank:
+                    continue
+                ptrs = [be.pipe_ipc_open(self.device, (C.c_ubyte * 64).from_buffer_copy(hb)) for hb in every[r][0]]
+                if not all(ptrs):
+                    why = f"rank {self.rank} cannot map rank {r}'s buffers (coli_cuda_pipe_ipc_open)"
+                self.peer_recv[r], self.peer_got[r] = ptrs
+        # every rank learns whether all of them succeeded
+        verdicts = [None] * G
+        dist.all_gather_object(verdicts, why, group=self.group)
+        bad = [w for w in verdicts if w] + [w for _, w in every if w]
+        if bad:
+            for r in range(G):
+                if r != self.rank:
+                    for q in (self.peer_recv[r], self.peer_got[r]):
+                        if q:
+                            be.pipe_ipc_close(self.device, q)
+            for q in (self.recv_buf, self.got_buf):
+                if q:
+                    be.pipe_free(self.device, q)
+            self.exchange = "nccl"
+            raise PeerExchangeUnavailable("; ".join(sorted(set(bad))))
         self.flag = torch.zeros((1,), dtype=torch.int32, device=self.dev)
         self.counts_all = torch.zeros((G, G * self.emap.slots), dtype=torch.int32, device=self.dev)
         self.counts_all_pin = torch.zeros((G, G * self.emap.slots), dtype=torch.int32).pin_memory()

@@ -263,9 +263,9 @@ class CudaEpLayer:
                     why = f"rank {self.rank} cannot map rank {r}'s buffers (coli_cuda_pipe_ipc_open)"
                 self.peer_recv[r], self.peer_got[r] = ptrs
         # every rank learns whether all of them succeeded
-        verdicts = [None] * G
-        dist.all_gather_object(verdicts, why, group=self.group)
-        bad = [w for w in verdicts if w] + [w for _, w in every if w]
+        answers = [None] * G
+        dist.all_gather_object(answers, why, group=self.group)
+        bad = [w for w in answers if w] + [w for _, w in every if w]
         if bad:
             for r in range(G):
                 if r != self.rank:

@@ -42,7 +42,7 @@ def be():
 
 def pytest_sessionfinish(session, exitstatus):
     """After a GPU session: the parity errors the tests noted (floored and plain figures side by
-    side), as a table under gpurun_out/."""
+    side), as a table in the run's output folder."""
     from tests import util
     if not util.ERRORS:
         return

@@ -35,7 +35,8 @@ CASES = [  # name, fmt, gs, S, I, O  (shapes of c/tests/test_i4_grouped.c and te
 ]
 
 
-REFERENCE = os.environ.get("COLI_REFERENCE", "/root/reference")
+# the reference checkout: COLI_REFERENCE, or a directory "reference" beside this repository
+REFERENCE = os.environ.get("COLI_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))), "reference")
 
 
 def quantiser_vectors():

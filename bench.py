@@ -59,7 +59,7 @@ TC_MEAN_ROWS = 12     # the backend's rule for prefill-sized layer calls: mean r
 ROUTED_SCALE = 2.5    # sigmoid-gated configurations (GLM / DeepSeek-V3 style)
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the fused decode kernel (one ncu
 # capture of configuration 2 at M=1); other workloads have no capture and report null
-NCU_TRAFFIC_BYTES = {("c2_decode", 1, 64): 28.45e6}
+NCU_TRAFFIC_BYTES = {("c2_decode", 1, 64): 28.40e6}
 
 
 def peaks():

@@ -107,3 +107,27 @@ def test_ep_layer_over_nccl_is_bit_identical_to_one_rank():
                           "--master-addr", "127.0.0.1", "--master-port", "29641", os.path.join(here, "ep_multi_check.py")],
                          capture_output=True, text=True, timeout=600, env=env)
     assert run.returncode == 0 and "EP_MULTI_OK" in run.stdout, run.stdout[-2000:] + run.stderr[-3000:]
+
+
+def test_peer_copy_entry_points_on_one_gpu(be):
+    """The pieces of the peer exchange that one process can exercise: a device-to-device copy on
+    the backend's stream, the export of a buffer's handle, and the refusals."""
+    import ctypes as C
+    n = 1 << 20
+    src = np.arange(n, dtype=np.float32)
+    a, b = be.pipe_alloc(0, src.nbytes), be.pipe_alloc(0, src.nbytes)
+    assert a and b and be.pipe_upload(0, a, src.ctypes.data, src.nbytes)
+    assert be.pipe_copy_async(0, b, a, src.nbytes, None) == 1
+    assert be.pipe_copy_async(0, b, a, 0, None) == 1                 # nothing to do
+    assert be.pipe_copy_async(0, None, a, 16, None) == 0
+    assert be.pipe_copy_async(9999, b, a, 16, None) == 0
+    got = np.zeros_like(src)
+    assert be.pipe_download(0, b, got.ctypes.data, got.nbytes)         # synchronises the stream first
+    assert np.array_equal(got, src)
+    h = (C.c_ubyte * 64)()
+    assert be.pipe_ipc_export(0, a, h) == 1 and any(bytes(h))
+    assert be.pipe_ipc_export(0, None, h) == 0
+    assert not be.pipe_ipc_open(0, None)
+    assert be.pipe_ipc_close(0, None) == 0
+    be.pipe_free(0, a)
+    be.pipe_free(0, b)

@@ -904,6 +904,83 @@ def run_gpu_arm(args):
 # ---------------------------------------------------------------------------
 # batched multi-token decode through a 4-layer stack (configuration 4)
 # ---------------------------------------------------------------------------
+def run_head_arm(args):
+    """The two dense kernels around configuration 4's layers, alone and at a size a profiler can
+    hold: the f32 head GEMV (coli_cuda_pipe_gemm on a row-major [rows, 7168] tensor, rows =
+    --experts x 128, default 32768 = a quarter of the 129280-entry head, 0.94 GB) for K = --M
+    (default 8) rows, and the exact-order router GEMV (coli_cuda_pipe_router, 256 experts) for one
+    row. value = head weight bytes / device time of a head call."""
+    import torch
+    from colibri_b200.backend import Backend
+    D, E = 7168, 256
+    O = (args.experts or 256) * 128
+    S = args.M if args.M > 1 else 8
+    torch.cuda.set_device(0)
+    be = Backend()
+    if be.init_devices((0,)) != 1:
+        raise RuntimeError("coli_cuda_init failed: the CUDA backend is required (no CPU fallback)")
+    rng = np.random.default_rng(3)
+    w = (rng.standard_normal((O, D), dtype=np.float32) * np.float32(0.02)).astype(np.float32)
+    head = be.upload(w, None, 0, D, O, 0, 0)
+    rw = (rng.standard_normal((E, D), dtype=np.float32) * np.float32(0.02)).astype(np.float32)
+    x = rng.standard_normal((S, D), dtype=np.float32)
+    dev_buf = lambda a: (lambda p: (be.pipe_upload(0, p, a.ctypes.data, a.nbytes), p)[1])(be.pipe_alloc(0, a.nbytes))
+    xd, rwd, rbd = dev_buf(x), dev_buf(rw), dev_buf(np.zeros(E, np.float32))
+    yd = be.pipe_alloc(0, S * O * 4)
+    if not (head and xd and rwd and rbd and yd):
+        raise RuntimeError("allocation failed")
+    stream = torch.cuda.ExternalStream(be.stream(0))
+    steps = args.steps
+
+    def timed(fn):
+        for _ in range(max(3, args.warmup)):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    def head_call():
+        if not be.pipe_gemm(head, yd, xd, S):
+            raise RuntimeError("coli_cuda_pipe_gemm failed")
+
+    r_idx, r_w, r_keff = (C.c_int * 8)(), (C.c_float * 8)(), C.c_int()
+
+    def router_call():          # a blocking call: logits, top-8 and the read-back of the picks
+        if not be.pipe_router(0, xd, rwd, rbd, D, E, 8, C.c_float(0.0), 1, C.c_float(ROUTED_SCALE), r_idx, r_w,
+                              C.byref(r_keff)):
+            raise RuntimeError("coli_cuda_pipe_router failed")
+    sampler = ClockSampler(0).start()
+    head_ms = timed(head_call)
+    for _ in range(3):
+        router_call()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        router_call()
+    router_ms = (time.perf_counter() - t0) * 1e3 / steps
+    clocks = sampler.stop()
+    y = np.zeros((S, O), np.float32)
+    be.pipe_download(0, yd, y.ctypes.data, y.nbytes)
+    err = float(np.abs(y[:, :64] - x @ w[:64].T).max())
+    hbm_peak, _, which = peaks()
+    val = O * D * 4 / (head_ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "moe_expert_ffn_hbm_gbs", "value": val, "unit": "GB/s", "n_gpus": 1, "steps": steps, "warmup": max(3, args.warmup),
+        "ms_per_step": head_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"c4_head: f32 head GEMV [{O} x {D}] for {S} rows, and the exact-order router GEMV [{E} x {D}] for one row",
+                   "l2": "the head's weights (0.94 GB at the default size) exceed L2",
+                   "router_us_per_blocking_call": router_ms * 1e3,
+                   "head_max_abs_err_first_64_outputs": err},
+        "e2e": None, "gpu_launches": 2 * steps, "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": val, "peak": hbm_peak, "unit": "GB/s", "frac": val / hbm_peak, "traffic": None,
+                     "kernel": "k_dense_gemv<0>", "peak_source": which}, "cpu_baseline": None}), flush=True)
+    be.shutdown()
+
+
 def run_stack_arm(args):
     """Configuration 4: K candidate tokens per step (K = --M, default 8) through 4 MoE layers of
     the DeepSeek-V3-style shape with int4 g32 experts, residual resident on the device
@@ -997,7 +1074,7 @@ def main():
     ap.add_argument("--repeats", type=int, default=10, help="timed blocks; the median is reported")
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2_decode", choices=["c2_decode", "c3_decode", "c4_decode", "c5_ep", "c4_stack"],
+    ap.add_argument("--workload", default="c2_decode", choices=["c2_decode", "c3_decode", "c4_decode", "c5_ep", "c4_stack", "c4_head"],
                     help="layer shape and weight format (configuration 2, 3 or 4 of the benchmark)")
     ap.add_argument("--M", type=int, default=1, help="rows per layer call")
     ap.add_argument("--experts", type=int, default=0, help="override the expert count (profiling subsets)")
@@ -1012,7 +1089,13 @@ def main():
     ap.add_argument("--ep-blocks", action="store_true", help="place experts in equal blocks instead of by routing histogram")
     ap.add_argument("--no-gpu-baseline", action="store_true")
     args = ap.parse_args()
-    if args.workload == "c4_stack":
+    if args.workload == "c4_head":
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "a profiling subset; the reference CPU arm is timed on "
+                              "the default workload"}))
+        else:
+            run_head_arm(args)
+    elif args.workload == "c4_stack":
         if args.impl == "reference":
             print(json.dumps({"impl": "reference", "unavailable": "the CPU run of this stack needs 25 GB of expert "
                               "weights on the host; the reference CPU arm is timed on the default workload"}))

@@ -102,13 +102,25 @@ __global__ void __launch_bounds__(ROUTER_THREADS) k_router_logits(float *__restr
         const int width = min(ROUTER_TILE, D - c0);
         if (tid >= 64) continue;        // copy-only warps
         if (width == ROUTER_TILE) {
-#pragma unroll 8
-            for (int j = 0; j < ROUTER_TILE; j += 4) {
-                const float4 xv = *reinterpret_cast<const float4 *>(xt + j), wv = *reinterpret_cast<const float4 *>(wt + j);
-                a = __fadd_rn(a, __fmul_rn(xv.x, wv.x));
-                a = __fadd_rn(a, __fmul_rn(xv.y, wv.y));
-                a = __fadd_rn(a, __fmul_rn(xv.z, wv.z));
-                a = __fadd_rn(a, __fmul_rn(xv.w, wv.w));
+            // all of the tile's operands first (independent loads, products off the chain), then
+            // the 64 additions back to back
+            float4 wv[ROUTER_TILE / 4], xv[ROUTER_TILE / 4];
+#pragma unroll
+            for (int q = 0; q < ROUTER_TILE / 4; q++) {
+                wv[q] = reinterpret_cast<const float4 *>(wt)[q];
+                xv[q] = reinterpret_cast<const float4 *>(xt)[q];
+            }
+#pragma unroll
+            for (int q = 0; q < ROUTER_TILE / 4; q++) {
+                wv[q].x = __fmul_rn(xv[q].x, wv[q].x); wv[q].y = __fmul_rn(xv[q].y, wv[q].y);
+                wv[q].z = __fmul_rn(xv[q].z, wv[q].z); wv[q].w = __fmul_rn(xv[q].w, wv[q].w);
+            }
+#pragma unroll
+            for (int q = 0; q < ROUTER_TILE / 4; q++) {
+                a = __fadd_rn(a, wv[q].x);
+                a = __fadd_rn(a, wv[q].y);
+                a = __fadd_rn(a, wv[q].z);
+                a = __fadd_rn(a, wv[q].w);
             }
         } else {
             for (int j = 0; j < width; j++) a = __fadd_rn(a, __fmul_rn(xt[j], wt[j]));

@@ -191,7 +191,7 @@ class CudaEpLayer:
 
     exchange: "nccl" moves the rows with all_to_all_single; "peer" (several ranks on one NVLink
     domain) pushes every block straight into the receiver's buffer with device-to-device copies
-    over peer memory (copy engines, so they need no SM and run beside the GEMMs; about twice
+    over peer memory (copy engines, so they need no SM; about twice
     NCCL's all-to-all rate between two B200s), with a 4-byte all-reduce as the "everybody's rows
     have landed" barrier. Both give the same bits. max_rows must be the same on every rank."""
 
@@ -281,8 +281,7 @@ class CudaEpLayer:
         self.counts_all = torch.zeros((G, G * self.emap.slots), dtype=torch.int32, device=self.dev)
         self.counts_all_pin = torch.zeros((G, G * self.emap.slots), dtype=torch.int32).pin_memory()
         self.e_comb = None
-        # one stream per peer, so that the blocks for different ranks travel side by side
-        self.pstreams = [torch.cuda.Stream(device=self.dev) for _ in range(G)]
+        self.cnt_np = self.counts_all_pin.numpy().reshape(G, G, self.emap.slots)      # [src][dest][slot], pinned
         dist.barrier(group=self.group)
 
     def close(self):
@@ -404,22 +403,15 @@ class CudaEpLayer:
         be, C, me = self.be, self.C, self.rank
         bs, cs = self.bstream, self.cstream
         esz = 2 if self.bf16 else 4
-        def copy(peer, dst, src, nbytes):
-            self._check(be.pipe_copy_async(self.device, C.c_void_p(dst), C.c_void_p(src), C.c_size_t(nbytes),
-                                           C.c_void_p(self.pstreams[peer].cuda_stream)), "coli_cuda_pipe_copy_async")
+        csh = C.c_void_p(cs.cuda_stream)
 
         def fan_out(jobs):
-            """jobs: (peer, dst, src, bytes). Each runs on its peer's stream after what cs holds so
-            far; cs continues when all have finished."""
-            if not jobs:
-                return
-            fork = torch.cuda.Event(); fork.record(cs)
-            for peer, dst, src, nbytes in jobs:
-                ps = self.pstreams[peer]
-                ps.wait_event(fork)
-                copy(peer, dst, src, nbytes)
-                done = torch.cuda.Event(); done.record(ps)
-                cs.wait_event(done)
+            """jobs: (peer, dst, src, bytes), one after the other on the exchange stream: they all
+            leave through this GPU's NVLink ports, which one copy already fills (streams per peer
+            were measured: no faster, and their events cost host time)."""
+            for _, dst, src, nbytes in jobs:
+                self._check(be.pipe_copy_async(self.device, C.c_void_p(dst), C.c_void_p(src), C.c_size_t(nbytes), csh),
+                            "coli_cuda_pipe_copy_async")
         # 3. every rank's table of counts, and the one read-back of the layer
         with torch.cuda.stream(cs):
             cs.wait_event(e_pack)
@@ -429,9 +421,9 @@ class CudaEpLayer:
             self.counts_all_pin.copy_(self.counts_all, non_blocking=True)
             e_cnt = ev(); e_cnt.record(cs)
         e_cnt.synchronize()
-        mat = self.counts_all_pin.numpy().reshape(G, G, slots).sum(axis=2)      # [src][dest] rows
+        mat = self.cnt_np.sum(axis=2)                                           # [src][dest] rows
         send_splits = mat[me].tolist()
-        recv_counts = np.ascontiguousarray(self.counts_all_pin.numpy().reshape(G, G, slots)[:, me, :])   # [src][slot]
+        recv_counts = np.ascontiguousarray(self.cnt_np[:, me, :])               # [src][slot]
         recv_splits = mat[:, me].tolist()
         n_send, n_recv = int(sum(send_splits)), int(sum(recv_splits))
         assert n_recv * D * esz <= self.recv_bytes and n_send * D * 4 <= self.got_bytes
@@ -472,8 +464,6 @@ class CudaEpLayer:
         self.e_comb = torch.cuda.Event(); self.e_comb.record(bs)
         for t in (y, x, logits):
             t.record_stream(bs); t.record_stream(cs)
-        for ps in self.pstreams:
-            y.record_stream(ps)
         if self.timing is not None:
             marks["t1"] = ev(); marks["t1"].record(bs)
             marks.update(pack=e_pack, recv=e_recv, gemm=e_gemm, back=e_back)

@@ -46,7 +46,7 @@ struct DeviceCtx {
     size_t host_x_cap = 0, host_y_cap = 0;
     int group_pending = 0;
     int *status = nullptr;                    // pinned host int the kernels store into (kstat_set): sticky kernel status
-    unsigned int *dec_sync = nullptr;         // fused decode kernel: barrier arrivals, generation, output-slice tickets
+    unsigned int *dec_sync = nullptr;         // fused decode kernel: the grid barriers' arrival counter
     unsigned long long *exp_tab_dev = nullptr; // global-memory copy of the 2^(i/32) table
     const float *e4m3_lut_dev = nullptr;       // device address of the fmt 8 decode table
     int sticky_status = 0;                    // last non-zero kernel status seen by the host
@@ -733,7 +733,7 @@ static int check_status(DeviceCtx *c) {
     const int v = *reinterpret_cast<volatile int *>(c->status);
     if (v) {
         std::fprintf(stderr, "[CUDA] kernel wait guard expired (status %d)\n", v);
-        // the grid barrier's arrival count and the tickets may be mid-way: start over
+        // the grid barrier's arrival count may be mid-way: start over
         cudaMemsetAsync(c->dec_sync, 0, DEC_SYNC_WORDS * sizeof(unsigned int), c->stream);
         *reinterpret_cast<volatile int *>(c->status) = 0;
         c->sticky_status = v;

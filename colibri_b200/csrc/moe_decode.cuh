@@ -74,8 +74,7 @@
 __host__ __device__ constexpr int dec_act_bytes(int mode) { return mode == SC_F32 ? 65536 + 2048 : 78 * 1024; }
 #define DEC_PART_BYTES 16384     // one buffer of per-warp partial sums: 16 warps x 32 lanes x 2 float4
 #define DEC_MAX_I 2048           // two passes x 4 rows x I x 4 bytes must fit the activation region
-#define DEC_MAX_TILES 1024       // tickets: D / 32
-#define DEC_SYNC_WORDS (16 + DEC_MAX_TILES)
+#define DEC_SYNC_WORDS 16
 
 struct DecPass {
     int e;            // expert id, or -1 for the shared expert

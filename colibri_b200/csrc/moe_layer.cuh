@@ -240,7 +240,7 @@ static int layer_run(ColiCudaMoeLayer *L, DeviceCtx *c, float *out_dev, const fl
         lg = (const float *)L->logits.p;
     }
     if (!route_only && g_fused_decode && M <= DEC_MAX_M && r.E <= DEC_MAX_E && r.K <= DEC_MAX_K &&
-        L->mode_gu == L->mode_d && r.I <= DEC_MAX_I && r.D / TILE_ROWS <= DEC_MAX_TILES &&
+        L->mode_gu == L->mode_d && r.I <= DEC_MAX_I &&
         M * r.K + 2 <= DEC_MAX_PASS && c->sms >= DEC_MAX_PASS && c->sms <= 256 &&
         (reinterpret_cast<uintptr_t>(out_dev) & 15) == 0) {
         // one kernel for the whole layer (moe_decode.cuh)

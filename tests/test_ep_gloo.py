@@ -93,6 +93,16 @@ def test_two_ranks_equal_one_rank_and_the_oracle(oracle):
     np.testing.assert_allclose(one, want, rtol=1e-4, atol=1e-6)
 
 
+def test_four_ranks_equal_one_rank():
+    """World 4, blocks and balanced placement: the same bits as one rank."""
+    M = 24
+    one = run_world(1, M, 29621)
+    four = run_world(4, M, 29622)
+    assert np.array_equal(one.view(np.uint32), four.view(np.uint32))
+    bal = run_world(4, M, 29623, balanced=True)
+    assert np.array_equal(one.view(np.uint32), bal.view(np.uint32))
+
+
 def test_dispatch_plan_orders_by_rank_expert_row():
     idx = torch.tensor([[5, 1, 6], [1, 7, 0], [6, 5, 2]])
     keff = torch.tensor([3, 2, 3])

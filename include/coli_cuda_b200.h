@@ -235,10 +235,10 @@ int coli_cuda_expert_group_dev(ColiCudaTensor *const *gates, ColiCudaTensor *con
  * scratch in a fixed 8 MiB device array that each GPU holds from library load to
  * process exit. Limits: S <= 32 and 20 KiB + S*I*4 + slices*S*O*4 bytes <= 8 MiB
  * (slices <= I/256); a call beyond them prints the reason and returns 0. All
- * calls on a device share the array, so calls that overlap on the GPU race. The
- * first call on a device resolves the array's address and should be made before
- * any stream capture. Runs on the backend's stream for the device; returns
- * after enqueueing. */
+ * calls on a device share the array, so calls that overlap on the GPU race. Not
+ * capturable into a CUDA graph: every call stages two small descriptors from
+ * pageable host memory (and the first call on a device resolves the array's
+ * address). Runs on the backend's stream for the device; returns after enqueueing. */
 int coli_cuda_pipe_gemm_noalloc(ColiCudaTensor *t, float *y_dev, const float *x_dev, int S);
 
 /* Routing without a layer handle (an expert-parallel rank owns only some of the
